@@ -1,0 +1,979 @@
+// Flash attention for sm_100a on tcgen05 / TMEM: forward (O, LSE), and a two-kernel backward
+// (dK,dV per key block; dQ per query block) that recomputes the scores.  Causal or full, GQA,
+// head dim 64 or 128, arbitrary (s, b, head) strides so that Q/K/V are read straight out of the
+// packed QKV projection and O is written in [tokens, heads*hd] layout for the output projection.
+//
+// Every score-like product runs as  tcgen05.mma (SS, both operands K-major, TMA-loaded),
+// accumulators live in TMEM, each softmax thread owns one accumulator row (tcgen05.ld 32x32b),
+// probabilities go back to shared memory as the bf16 K-major A operand of the second product,
+// whose B operand is the same TMA tile of V / dO / Q / K read through an MN-major descriptor.
+//
+// Replaces flash_attn_varlen_func / _flash_attn_forward / _flash_attn_backward as called from
+// galvatron/core/runtime/transformer/attention_impl.py:55-111,587-616,696-727.
+#include "sm100_common.cuh"
+
+namespace hg {
+namespace attn {
+
+constexpr int kThreads = 192;  // warp 0: TMA, warp 1: UMMA, warps 2-5: softmax / epilogue
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Head -> slot mapping inside the (possibly packed) tensor:  slot = (h / qpg) * gs + (h % qpg) * hs + off
+struct SlotMap {
+  int gs, hs, off;
+  __device__ __forceinline__ int slot(int h, int qpg) const { return (h / qpg) * gs + (h % qpg) * hs + off; }
+};
+
+struct FwdParams {
+  int Sq, Skv, B, nheads, qpg;  // qpg = query heads per kv head
+  int causal;
+  int q_pos0, k_pos0;           // global positions of row 0 / key 0 (ring / context-parallel steps)
+  float scale;                  // softmax scale (1/sqrt(hd))
+  SlotMap qmap, kmap, vmap;
+  __nv_bfloat16* O;             // element (s, b, h, d) at O + s*o_ss + b*o_sb + h*hd + d
+  int64_t o_ss, o_sb;
+  float* LSE;                   // [B, nheads, Sq]
+  int* status;
+};
+
+// K-major operand: `rows` x (64*slabs) bf16 stored as slabs of [rows x 128 B]; descriptor for k-step kk.
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t base, int rows, int kk) {
+  return make_smem_desc(base + (kk >> 2) * rows * 128 + (kk & 3) * 32, 16, 1024);
+}
+// The same buffer viewed as an MN-major operand (MN = the 64*slabs columns, K = rows); k-step kk = rows 16kk..
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t base, int rows, int kk) {
+  return make_smem_desc(base + kk * 2048, rows * 128, 1024);
+}
+
+// =================================================================================================
+// Forward
+// =================================================================================================
+template <int HD>
+struct FwdSmem {
+  static constexpr int kQ = 128 * HD * 2;
+  static constexpr int kKV = 128 * HD * 2;
+  static constexpr int kP = 128 * 128 * 2;
+  static constexpr int kTotal = kQ + 4 * kKV + kP + 1024 + 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;
+  uint8_t* sK = sQ + FwdSmem<HD>::kQ;              // 2 stages
+  uint8_t* sV = sK + 2 * FwdSmem<HD>::kKV;         // 2 stages
+  uint8_t* sP = sV + 2 * FwdSmem<HD>::kKV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + FwdSmem<HD>::kP);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* k_empty = bars + 3;     // 2
+  uint64_t* v_full = bars + 5;      // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // 2
+  uint64_t* s_empty = bars + 11;    // 2
+  uint64_t* p_full = bars + 13;     // 1
+  uint64_t* o_done = bars + 14;     // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int qb = gridDim.x - 1 - blockIdx.x;  // heavy (late) query blocks first under a causal mask
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb * 128;
+
+  // key blocks this query block attends to
+  int kv_len = p.Skv;
+  if (p.causal) {
+    const int last = p.q_pos0 + q0 + 127 - p.k_pos0;  // last visible key index for the last row
+    kv_len = min(p.Skv, last + 1);
+  }
+  const int n_kv = kv_len > 0 ? (kv_len + 127) / 128 : 0;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(p_full, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS[2] = {tmem, tmem + 128};
+  const uint32_t tO = tmem + 256;
+
+  const int qslot = p.qmap.slot(h, p.qpg), kslot = p.kmap.slot(h, p.qpg), vslot = p.vmap.slot(h, p.qpg);
+
+  if (warp == 0) {
+    if (lane_id() == 0 && n_kv > 0) {
+      mbar_expect_tx(q_full, FwdSmem<HD>::kQ);
+#pragma unroll
+      for (int j = 0; j < HD / 64; ++j) tma_load_4d(sQ + j * 128 * 128, &tmQ, q_full, j * 64, qslot, q0, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (*abort_flag || !mbar_wait(&k_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        mbar_expect_tx(&k_full[st], FwdSmem<HD>::kKV);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sK + st * FwdSmem<HD>::kKV + c * 128 * 128, &tmK, &k_full[st], c * 64, kslot, j * 128, b);
+        if (*abort_flag || !mbar_wait(&v_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        mbar_expect_tx(&v_full[st], FwdSmem<HD>::kKV);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          tma_load_4d(sV + st * FwdSmem<HD>::kKV + c * 128 * 128, &tmV, &v_full[st], c * 64, vslot, j * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane_id() == 0 && n_kv > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, HD, false, true);
+      const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
+      bool ok = mbar_wait(q_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      auto issue_s = [&](int j) -> bool {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (*abort_flag || !mbar_wait(&k_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait(&s_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * FwdSmem<HD>::kKV);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_f16_ss(tS[st], kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 128, kk), idesc_s, kk != 0);
+        umma_commit(&s_full[st]);
+        umma_commit(&k_empty[st]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        if (j + 1 < n_kv) { ok = issue_s(j + 1); if (!ok) break; }
+        const int st = j & 1;
+        if (*abort_flag || !mbar_wait(p_full, j & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(&v_full[st], (j >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aV = smem_u32(sV + st * FwdSmem<HD>::kKV);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16_ss(tO, kmajor_desc(aP, 128, kk), mnmajor_desc(aV, 128, kk), idesc_o, (j | kk) != 0);
+        umma_commit(&v_empty[st]);
+        umma_commit(o_done);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    // ---- softmax: thread == query row ----
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane_id();
+    const uint32_t lane_off = uint32_t(wq * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    const int q_pos = p.q_pos0 + q0 + row;
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kv; ++j) {
+      const int st = j & 1;
+      if (*abort_flag || !mbar_wait_warp(&s_full[st], (j >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      float s[128];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tS[st] + lane_off + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
+      }
+      tc_fence_before();
+      mbar_arrive(&s_empty[st]);
+      // masking (only blocks that cross the diagonal or the ragged end need it)
+      const int k_base = p.k_pos0 + j * 128;
+      const bool need_mask = (p.causal && (k_base + 127 > p.q_pos0 + q0)) || (j * 128 + 128 > p.Skv);
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const bool dead = (j * 128 + i >= p.Skv) || (p.causal && (k_base + i > q_pos));
+          if (dead) s[i] = -INFINITY;
+        }
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      mx *= sl2;
+      // lazy rescale: keep the running reference max unless the new max exceeds it by more than 2^8
+      float alpha = 1.f;
+      bool rescale = false;
+      if (mx > m_used + 8.f) {
+        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
+        m_used = mx;
+        rescale = (j > 0);
+      }
+      const float mref = (m_used == -INFINITY) ? 0.f : m_used;
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 128; ++i) {
+        s[i] = exp2f(s[i] * sl2 - mref);
+        sum += s[i];
+      }
+      l = l * alpha + sum;
+      if (j > 0) {
+        if (!mbar_wait_warp(o_done, (j - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+      }
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tO + lane_off + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(tO + lane_off + c * 32, r);
+        }
+        tmem_st_wait();
+      }
+      // P -> shared memory, bf16, 128B-swizzled K-major (two 64-column slabs)
+#pragma unroll
+      for (int cc = 0; cc < 16; ++cc) {
+        uint4 u;
+        u.x = pack_bf16(s[cc * 8 + 0], s[cc * 8 + 1]);
+        u.y = pack_bf16(s[cc * 8 + 2], s[cc * 8 + 3]);
+        u.z = pack_bf16(s[cc * 8 + 4], s[cc * 8 + 5]);
+        u.w = pack_bf16(s[cc * 8 + 6], s[cc * 8 + 7]);
+        *reinterpret_cast<uint4*>(sP + (cc >> 3) * 128 * 128 + sw128_offset(row, cc & 7)) = u;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_full);
+    }
+    // ---- epilogue: O / l -> global, LSE ----
+    const int srow = q0 + row;
+    if (n_kv == 0) {
+      if (srow < p.Sq) {
+        __nv_bfloat16* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(0, 0, 0, 0);
+        p.LSE[(size_t(b) * p.nheads + h) * p.Sq + srow] = -INFINITY;
+      }
+    } else if (ok && !*abort_flag && mbar_wait_warp(o_done, (n_kv - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tO + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (srow < p.Sq) {
+          __nv_bfloat16* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD + c * 32;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(r[q * 8 + 0]) * inv, __uint_as_float(r[q * 8 + 1]) * inv);
+            u.y = pack_bf16(__uint_as_float(r[q * 8 + 2]) * inv, __uint_as_float(r[q * 8 + 3]) * inv);
+            u.z = pack_bf16(__uint_as_float(r[q * 8 + 4]) * inv, __uint_as_float(r[q * 8 + 5]) * inv);
+            u.w = pack_bf16(__uint_as_float(r[q * 8 + 6]) * inv, __uint_as_float(r[q * 8 + 7]) * inv);
+            reinterpret_cast<uint4*>(o)[q] = u;
+          }
+        }
+      }
+      if (srow < p.Sq)
+        p.LSE[(size_t(b) * p.nheads + h) * p.Sq + srow] = (l > 0.f) ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+    } else {
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =================================================================================================
+// Backward, part 0:  D[b,h,s] = sum_d dO * O
+// =================================================================================================
+__global__ void attn_bwd_dot_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+                                    int64_t ss, int64_t sb, int64_t dss, int64_t dsb, int S, int B, int nheads, int hd,
+                                    float* __restrict__ D) {
+  // one warp per (s, b, h)
+  const int64_t total = int64_t(S) * B * nheads;
+  const int64_t gw = (blockIdx.x * int64_t(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (gw >= total) return;
+  const int h = int(gw % nheads);
+  const int b = int((gw / nheads) % B);
+  const int s = int(gw / (int64_t(nheads) * B));
+  const __nv_bfloat16* o = O + s * ss + b * sb + h * hd;
+  const __nv_bfloat16* d = dO + s * dss + b * dsb + h * hd;
+  float acc = 0.f;
+  for (int i = lane * 2; i < hd; i += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
+    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
+    acc += a.x * c.x + a.y * c.y;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) D[(size_t(b) * nheads + h) * S + s] = acc;
+}
+
+// =================================================================================================
+// Backward parameters (shared by the dK/dV and the dQ kernels)
+// =================================================================================================
+struct BwdParams {
+  int Sq, Skv, B, nheads, qpg;
+  int causal;
+  int q_pos0, k_pos0;
+  float scale;
+  SlotMap qmap, kmap, vmap, domap;  // dO uses slot = h (gs = qpg, hs = 1, off = 0)
+  const float* LSE;                 // [B, nheads, Sq]
+  const float* D;                   // [B, nheads, Sq]
+  // outputs: element (s, b, slot, d) at base + s*ss + b*sb + slot*hd + d
+  __nv_bfloat16* dQ; int64_t dq_ss, dq_sb; SlotMap dqmap;
+  __nv_bfloat16* dK; int64_t dk_ss, dk_sb; SlotMap dkmap;
+  __nv_bfloat16* dV; int64_t dv_ss, dv_sb; SlotMap dvmap;
+  int* status;
+};
+
+// =================================================================================================
+// Backward, part 1: one CTA per (key block of 128, kv head, batch); loops over the query heads of the
+// group and over 64-row query steps.  Thread == key row.
+//   S^T = K Q^T, dP^T = V dO^T  (M = 128 keys, N = 64 queries)
+//   P^T = exp2(S^T*c - lse), dS^T = P^T * (dP^T - D)
+//   dV += P^T dO, dK += dS^T Q   (A from shared memory written by the threads; B = the dO / Q tile, MN-major)
+// =================================================================================================
+template <int HD>
+struct DkvSmem {
+  static constexpr int kKV = 128 * HD * 2;     // resident K or V
+  static constexpr int kQD = 64 * HD * 2;      // one stage of Q or dO
+  static constexpr int kPT = 128 * 64 * 2;     // P^T or dS^T
+  static constexpr int kStats = 2 * 2 * 64 * 4;  // lse2/D, double buffered
+  static constexpr int kTotal = 2 * kKV + 4 * kQD + 2 * kPT + kStats + 1024 + 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                     const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sK = base;
+  uint8_t* sV = sK + DkvSmem<HD>::kKV;
+  uint8_t* sQ = sV + DkvSmem<HD>::kKV;            // 2 stages
+  uint8_t* sDO = sQ + 2 * DkvSmem<HD>::kQD;       // 2 stages
+  uint8_t* sPT = sDO + 2 * DkvSmem<HD>::kQD;
+  uint8_t* sDST = sPT + DkvSmem<HD>::kPT;
+  float* sStats = reinterpret_cast<float*>(sDST + DkvSmem<HD>::kPT);  // [2][2][64]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStats) + DkvSmem<HD>::kStats);
+  uint64_t* kv_full = bars;        // 1
+  uint64_t* qd_full = bars + 1;    // 2
+  uint64_t* qd_empty = bars + 3;   // 2
+  uint64_t* st_full = bars + 5;    // 2
+  uint64_t* st_empty = bars + 7;   // 2
+  uint64_t* pds_full = bars + 9;   // 1
+  uint64_t* pds_empty = bars + 10; // 1
+  uint64_t* stats_full = bars + 11; // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int kb = blockIdx.x, g = blockIdx.y, b = blockIdx.z;  // g = kv head
+  const int k0 = kb * 128;
+  // first query row that can see this key block
+  int q_first = 0;
+  if (p.causal) q_first = max(0, p.k_pos0 + k0 - p.q_pos0);
+  const int qs0 = (q_first / 64);                       // first 64-row query step
+  const int n_qs = (p.Sq + 63) / 64;
+  const int steps_per_head = max(0, n_qs - qs0);
+  const int n_it = steps_per_head * p.qpg;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&qd_full[i], 1);
+      mbar_init(&qd_empty[i], 1);
+      mbar_init(&st_full[i], 1);
+      mbar_init(&st_empty[i], 128);
+    }
+    mbar_init(pds_full, 128);
+    mbar_init(pds_empty, 1);
+    mbar_init(&stats_full[0], 128);
+    mbar_init(&stats_full[1], 128);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  // columns: S^T[0] 0..63, dP^T[0] 64..127, S^T[1] 128..191, dP^T[1] 192..255, dV 256.., dK 384..
+  const uint32_t tST[2] = {tmem, tmem + 128};
+  const uint32_t tDPT[2] = {tmem + 64, tmem + 192};
+  const uint32_t tDV = tmem + 256, tDK = tmem + 384;
+
+  const int h0 = g * p.qpg;  // first query head of the group
+  const int kslot = p.kmap.slot(h0, p.qpg), vslot = p.vmap.slot(h0, p.qpg);
+
+  if (warp == 0) {
+    if (lane_id() == 0 && n_it > 0) {
+      mbar_expect_tx(kv_full, 2 * DkvSmem<HD>::kKV);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_4d(sK + c * 128 * 128, &tmK, kv_full, c * 64, kslot, k0, b);
+        tma_load_4d(sV + c * 128 * 128, &tmV, kv_full, c * 64, vslot, k0, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        const int h = h0 + it / steps_per_head;
+        const int qrow = (qs0 + it % steps_per_head) * 64;
+        if (*abort_flag || !mbar_wait(&qd_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        mbar_expect_tx(&qd_full[st], 2 * DkvSmem<HD>::kQD);
+        const int qslot = p.qmap.slot(h, p.qpg), doslot = p.domap.slot(h, p.qpg);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_4d(sQ + st * DkvSmem<HD>::kQD + c * 64 * 128, &tmQ, &qd_full[st], c * 64, qslot, qrow, b);
+          tma_load_4d(sDO + st * DkvSmem<HD>::kQD + c * 64 * 128, &tmDO, &qd_full[st], c * 64, doslot, qrow, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane_id() == 0 && n_it > 0) {
+      constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, HD, false, true);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), aDST = smem_u32(sDST);
+      bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      auto issue_st = [&](int it) -> bool {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (*abort_flag || !mbar_wait(&qd_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait(&st_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + st * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + st * DkvSmem<HD>::kQD);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_f16_ss(tST[st], kmajor_desc(aK, 128, kk), kmajor_desc(aQ, 64, kk), idesc_st, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_f16_ss(tDPT[st], kmajor_desc(aV, 128, kk), kmajor_desc(aDO, 64, kk), idesc_st, kk != 0);
+        umma_commit(&st_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_st(0);
+      for (int it = 0; ok && it < n_it; ++it) {
+        if (it + 1 < n_it) { ok = issue_st(it + 1); if (!ok) break; }
+        const int st = it & 1;
+        if (*abort_flag || !mbar_wait(pds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + st * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + st * DkvSmem<HD>::kQD);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16_ss(tDV, kmajor_desc(aPT, 128, kk), mnmajor_desc(aDO, 64, kk), idesc_acc, (it | kk) != 0);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16_ss(tDK, kmajor_desc(aDST, 128, kk), mnmajor_desc(aQ, 64, kk), idesc_acc, (it | kk) != 0);
+        umma_commit(&qd_empty[st]);
+        umma_commit(pds_empty);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane_id();  // key row inside the block
+    const int tid = threadIdx.x - 64;     // 0..127 among the softmax threads
+    const uint32_t lane_off = uint32_t(wq * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    const int k_pos = p.k_pos0 + k0 + row;
+    const bool k_valid = (k0 + row) < p.Skv;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it & 1;
+      const int h = h0 + it / steps_per_head;
+      const int qrow = (qs0 + it % steps_per_head) * 64;
+      // per-query statistics of this step -> shared memory
+      {
+        float* dst = sStats + st * 128;
+        const int q = qrow + (tid & 63);
+        const size_t idx = (size_t(b) * p.nheads + h) * p.Sq + q;
+        float v = 0.f;
+        if (q < p.Sq) v = (tid < 64) ? p.LSE[idx] * kLog2e : p.D[idx];
+        else v = (tid < 64) ? INFINITY : 0.f;   // rows past the end: exp2(-inf) = 0
+        dst[tid] = v;
+      }
+      mbar_arrive(&stats_full[st]);
+      if (*abort_flag || !mbar_wait_warp(&stats_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      if (*abort_flag || !mbar_wait_warp(&st_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      float pt[64], ds[64];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tST[st] + lane_off + c * 32, r0);
+        tmem_ld32(tDPT[st] + lane_off + c * 32, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { pt[c * 32 + i] = __uint_as_float(r0[i]); ds[c * 32 + i] = __uint_as_float(r1[i]); }
+      }
+      tc_fence_before();
+      mbar_arrive(&st_empty[st]);
+      const float* lse2 = sStats + st * 128;
+      const float* dd = lse2 + 64;
+      const bool need_mask = p.causal && (p.q_pos0 + qrow < p.k_pos0 + k0 + 127);
+#pragma unroll
+      for (int i = 0; i < 64; ++i) {
+        float pv = exp2f(pt[i] * sl2 - lse2[i]);
+        if (!k_valid || (need_mask && (k_pos > p.q_pos0 + qrow + i))) pv = 0.f;
+        pt[i] = pv;
+        ds[i] = pv * (ds[i] - dd[i]);
+      }
+      if (it > 0) {
+        if (!mbar_wait_warp(pds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        uint4 u, w;
+        u.x = pack_bf16(pt[cc * 8 + 0], pt[cc * 8 + 1]); u.y = pack_bf16(pt[cc * 8 + 2], pt[cc * 8 + 3]);
+        u.z = pack_bf16(pt[cc * 8 + 4], pt[cc * 8 + 5]); u.w = pack_bf16(pt[cc * 8 + 6], pt[cc * 8 + 7]);
+        w.x = pack_bf16(ds[cc * 8 + 0], ds[cc * 8 + 1]); w.y = pack_bf16(ds[cc * 8 + 2], ds[cc * 8 + 3]);
+        w.z = pack_bf16(ds[cc * 8 + 4], ds[cc * 8 + 5]); w.w = pack_bf16(ds[cc * 8 + 6], ds[cc * 8 + 7]);
+        *reinterpret_cast<uint4*>(sPT + sw128_offset(row, cc)) = u;
+        *reinterpret_cast<uint4*>(sDST + sw128_offset(row, cc)) = w;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+    }
+    // ---- epilogue ----
+    const int krow = k0 + row;
+    const int dkslot = p.dkmap.slot(h0, p.qpg), dvslot = p.dvmap.slot(h0, p.qpg);
+    __nv_bfloat16* dk = p.dK + int64_t(krow) * p.dk_ss + int64_t(b) * p.dk_sb + int64_t(dkslot) * HD;
+    __nv_bfloat16* dv = p.dV + int64_t(krow) * p.dv_ss + int64_t(b) * p.dv_sb + int64_t(dvslot) * HD;
+    if (n_it == 0) {
+      if (krow < p.Skv) {
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+          reinterpret_cast<uint4*>(dk)[i] = make_uint4(0, 0, 0, 0);
+          reinterpret_cast<uint4*>(dv)[i] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else if (ok && !*abort_flag && mbar_wait_warp(pds_empty, (n_it - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tDV + lane_off + c * 32, r0);
+        tmem_ld32(tDK + lane_off + c * 32, r1);
+        tmem_ld_wait();
+        if (krow < p.Skv) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u, w;
+            u.x = pack_bf16(__uint_as_float(r0[q * 8 + 0]), __uint_as_float(r0[q * 8 + 1]));
+            u.y = pack_bf16(__uint_as_float(r0[q * 8 + 2]), __uint_as_float(r0[q * 8 + 3]));
+            u.z = pack_bf16(__uint_as_float(r0[q * 8 + 4]), __uint_as_float(r0[q * 8 + 5]));
+            u.w = pack_bf16(__uint_as_float(r0[q * 8 + 6]), __uint_as_float(r0[q * 8 + 7]));
+            w.x = pack_bf16(__uint_as_float(r1[q * 8 + 0]) * p.scale, __uint_as_float(r1[q * 8 + 1]) * p.scale);
+            w.y = pack_bf16(__uint_as_float(r1[q * 8 + 2]) * p.scale, __uint_as_float(r1[q * 8 + 3]) * p.scale);
+            w.z = pack_bf16(__uint_as_float(r1[q * 8 + 4]) * p.scale, __uint_as_float(r1[q * 8 + 5]) * p.scale);
+            w.w = pack_bf16(__uint_as_float(r1[q * 8 + 6]) * p.scale, __uint_as_float(r1[q * 8 + 7]) * p.scale);
+            reinterpret_cast<uint4*>(dv + c * 32)[q] = u;
+            reinterpret_cast<uint4*>(dk + c * 32)[q] = w;
+          }
+        }
+      }
+    } else {
+      *abort_flag = 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =================================================================================================
+// Backward, part 2: one CTA per (query block of 128, head, batch); loops over 64-row key steps.
+// Thread == query row.   S = Q K^T, dP = dO V^T (N = 64);  dS = P * (dP - D);  dQ += dS K
+// =================================================================================================
+template <int HD>
+struct DqSmem {
+  static constexpr int kQ = 128 * HD * 2;     // resident Q or dO
+  static constexpr int kKV = 64 * HD * 2;     // one stage of K or V
+  static constexpr int kDS = 128 * 64 * 2;
+  static constexpr int kTotal = 2 * kQ + 4 * kKV + kDS + 1024 + 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kThreads, 1)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                    const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;
+  uint8_t* sDO = sQ + DqSmem<HD>::kQ;
+  uint8_t* sK = sDO + DqSmem<HD>::kQ;            // 2 stages
+  uint8_t* sV = sK + 2 * DqSmem<HD>::kKV;        // 2 stages
+  uint8_t* sDS = sV + 2 * DqSmem<HD>::kKV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + DqSmem<HD>::kDS);
+  uint64_t* qdo_full = bars;       // 1
+  uint64_t* kv_full = bars + 1;    // 2
+  uint64_t* kv_empty = bars + 3;   // 2
+  uint64_t* s_full = bars + 5;     // 2
+  uint64_t* s_empty = bars + 7;    // 2
+  uint64_t* ds_full = bars + 9;    // 1
+  uint64_t* ds_empty = bars + 10;  // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int qb = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb * 128;
+  int kv_len = p.Skv;
+  if (p.causal) kv_len = min(p.Skv, p.q_pos0 + q0 + 127 - p.k_pos0 + 1);
+  const int n_it = kv_len > 0 ? (kv_len + 63) / 64 : 0;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+    mbar_init(qdo_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+    }
+    mbar_init(ds_full, 128);
+    mbar_init(ds_empty, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS[2] = {tmem, tmem + 128};
+  const uint32_t tDP[2] = {tmem + 64, tmem + 192};
+  const uint32_t tDQ = tmem + 256;
+
+  const int qslot = p.qmap.slot(h, p.qpg), kslot = p.kmap.slot(h, p.qpg), vslot = p.vmap.slot(h, p.qpg),
+            doslot = p.domap.slot(h, p.qpg);
+
+  if (warp == 0) {
+    if (lane_id() == 0 && n_it > 0) {
+      mbar_expect_tx(qdo_full, 2 * DqSmem<HD>::kQ);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_4d(sQ + c * 128 * 128, &tmQ, qdo_full, c * 64, qslot, q0, b);
+        tma_load_4d(sDO + c * 128 * 128, &tmDO, qdo_full, c * 64, doslot, q0, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        if (*abort_flag || !mbar_wait(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        mbar_expect_tx(&kv_full[st], 2 * DqSmem<HD>::kKV);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_4d(sK + st * DqSmem<HD>::kKV + c * 64 * 128, &tmK, &kv_full[st], c * 64, kslot, it * 64, b);
+          tma_load_4d(sV + st * DqSmem<HD>::kKV + c * 64 * 128, &tmV, &kv_full[st], c * 64, vslot, it * 64, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane_id() == 0 && n_it > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
+      bool ok = mbar_wait(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      auto issue_s = [&](int it) -> bool {
+        const int st = it & 1;
+        const uint32_t ph = (it >> 1) & 1;
+        if (*abort_flag || !mbar_wait(&kv_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait(&s_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * DqSmem<HD>::kKV), aV = smem_u32(sV + st * DqSmem<HD>::kKV);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_f16_ss(tS[st], kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 64, kk), idesc_s, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_f16_ss(tDP[st], kmajor_desc(aDO, 128, kk), kmajor_desc(aV, 64, kk), idesc_s, kk != 0);
+        umma_commit(&s_full[st]);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int it = 0; ok && it < n_it; ++it) {
+        if (it + 1 < n_it) { ok = issue_s(it + 1); if (!ok) break; }
+        const int st = it & 1;
+        if (*abort_flag || !mbar_wait(ds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * DqSmem<HD>::kKV);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)
+          umma_f16_ss(tDQ, kmajor_desc(aDS, 128, kk), mnmajor_desc(aK, 64, kk), idesc_dq, (it | kk) != 0);
+        umma_commit(&kv_empty[st]);
+        umma_commit(ds_empty);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane_id();
+    const uint32_t lane_off = uint32_t(wq * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    const int srow = q0 + row;
+    const int q_pos = p.q_pos0 + srow;
+    float lse2 = INFINITY, dsum = 0.f;
+    if (srow < p.Sq) {
+      const size_t idx = (size_t(b) * p.nheads + h) * p.Sq + srow;
+      lse2 = p.LSE[idx] * kLog2e;
+      dsum = p.D[idx];
+    }
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it & 1;
+      if (*abort_flag || !mbar_wait_warp(&s_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      float ds[64];
+      {
+        float sv[64];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tS[st] + lane_off + c * 32, r0);
+          tmem_ld32(tDP[st] + lane_off + c * 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { sv[c * 32 + i] = __uint_as_float(r0[i]); ds[c * 32 + i] = __uint_as_float(r1[i]); }
+        }
+        tc_fence_before();
+        mbar_arrive(&s_empty[st]);
+        const int kbase = it * 64;
+        const bool need_mask = (p.causal && (p.k_pos0 + kbase + 63 > p.q_pos0 + q0)) || (kbase + 64 > p.Skv);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          float pv = exp2f(sv[i] * sl2 - lse2);
+          if (need_mask && ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos)))) pv = 0.f;
+          ds[i] = pv * (ds[i] - dsum);
+        }
+      }
+      if (it > 0) {
+        if (!mbar_wait_warp(ds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        uint4 w;
+        w.x = pack_bf16(ds[cc * 8 + 0], ds[cc * 8 + 1]); w.y = pack_bf16(ds[cc * 8 + 2], ds[cc * 8 + 3]);
+        w.z = pack_bf16(ds[cc * 8 + 4], ds[cc * 8 + 5]); w.w = pack_bf16(ds[cc * 8 + 6], ds[cc * 8 + 7]);
+        *reinterpret_cast<uint4*>(sDS + sw128_offset(row, cc)) = w;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    const int dqslot = p.dqmap.slot(h, p.qpg);
+    __nv_bfloat16* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
+    if (n_it == 0) {
+      if (srow < p.Sq) {
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4*>(dq)[i] = make_uint4(0, 0, 0, 0);
+      }
+    } else if (ok && !*abort_flag && mbar_wait_warp(ds_empty, (n_it - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tDQ + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (srow < p.Sq) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(r[q * 8 + 0]) * p.scale, __uint_as_float(r[q * 8 + 1]) * p.scale);
+            u.y = pack_bf16(__uint_as_float(r[q * 8 + 2]) * p.scale, __uint_as_float(r[q * 8 + 3]) * p.scale);
+            u.z = pack_bf16(__uint_as_float(r[q * 8 + 4]) * p.scale, __uint_as_float(r[q * 8 + 5]) * p.scale);
+            u.w = pack_bf16(__uint_as_float(r[q * 8 + 6]) * p.scale, __uint_as_float(r[q * 8 + 7]) * p.scale);
+            reinterpret_cast<uint4*>(dq + c * 32)[q] = u;
+          }
+        }
+      }
+    } else {
+      *abort_flag = 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace attn
+}  // namespace hg
+
+// ------------------------------------------------------------------------------------------------
+// Host launchers
+// ------------------------------------------------------------------------------------------------
+using namespace hg::attn;
+
+namespace {
+
+// 4-D tensor map over (d, slot, s, b) of a bf16 tensor whose element (s, b, slot, d) sits at
+// base + s*ss + b*sb + slot*hd + d.  Box = (64, 1, box_rows, 1).
+int make_map(CUtensorMap* out, const void* base, int hd, int slots, int S, int B, int64_t ss, int64_t sb,
+             int box_rows) {
+  auto enc = hg_host::get_encode_fn();
+  if (enc == nullptr) return -2;
+  cuuint64_t dims[4] = {cuuint64_t(hd), cuuint64_t(slots), cuuint64_t(S), cuuint64_t(B)};
+  cuuint64_t strides[3] = {cuuint64_t(hd) * 2, cuuint64_t(ss) * 2, cuuint64_t(sb) * 2};
+  cuuint32_t box[4] = {64, 1, cuuint32_t(box_rows), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (B == 1) strides[2] = strides[1] * cuuint64_t(S);  // any legal value; the coordinate is always 0
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -3;
+}
+
+template <typename K>
+int set_smem(K kernel, int bytes) {
+  return int(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+}
+
+}  // namespace
+
+extern "C" {
+
+// Tensor descriptor passed from Python: base pointer, strides (elements) over s and b, number of head
+// slots in a token row, and the head->slot map (gs, hs, off).
+struct HgAttnTensor {
+  void* ptr;
+  long long ss, sb;
+  int slots;
+  int gs, hs, off;
+};
+
+int hg_flash_fwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTensor* v, const HgAttnTensor* o,
+                 void* lse, int Sq, int Skv, int B, int nheads, int nkv, int hd, int causal, int q_pos0, int k_pos0,
+                 float scale, void* stream) {
+  if (hd != 64 && hd != 128) return -1;
+  if (Sq <= 0 || Skv <= 0 || B <= 0) return 0;
+  CUtensorMap tq, tk, tv;
+  int rc;
+  if ((rc = make_map(&tq, q->ptr, hd, q->slots, Sq, B, q->ss, q->sb, 128))) return rc;
+  if ((rc = make_map(&tk, k->ptr, hd, k->slots, Skv, B, k->ss, k->sb, 128))) return rc;
+  if ((rc = make_map(&tv, v->ptr, hd, v->slots, Skv, B, v->ss, v->sb, 128))) return rc;
+  FwdParams p{};
+  p.Sq = Sq; p.Skv = Skv; p.B = B; p.nheads = nheads; p.qpg = nheads / nkv; p.causal = causal;
+  p.q_pos0 = q_pos0; p.k_pos0 = k_pos0; p.scale = scale;
+  p.qmap = {q->gs, q->hs, q->off}; p.kmap = {k->gs, k->hs, k->off}; p.vmap = {v->gs, v->hs, v->off};
+  p.O = reinterpret_cast<__nv_bfloat16*>(o->ptr); p.o_ss = o->ss; p.o_sb = o->sb;
+  p.LSE = reinterpret_cast<float*>(lse);
+  p.status = hg_host::status_ptr();
+  dim3 grid((Sq + 127) / 128, nheads, B);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (hd == 128) {
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(flash_fwd_kernel<128>, FwdSmem<128>::kTotal))) return rc; cfg = true; }
+    flash_fwd_kernel<128><<<grid, kThreads, FwdSmem<128>::kTotal, st>>>(tq, tk, tv, p);
+  } else {
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(flash_fwd_kernel<64>, FwdSmem<64>::kTotal))) return rc; cfg = true; }
+    flash_fwd_kernel<64><<<grid, kThreads, FwdSmem<64>::kTotal, st>>>(tq, tk, tv, p);
+  }
+  return int(cudaGetLastError());
+}
+
+// dsum: scratch [B, nheads, Sq] fp32 (filled here with rowsum(dO*O)).
+int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTensor* v, const HgAttnTensor* o,
+                 const HgAttnTensor* d_o, const void* lse, void* dsum, const HgAttnTensor* dq, const HgAttnTensor* dk,
+                 const HgAttnTensor* dv, int Sq, int Skv, int B, int nheads, int nkv, int hd, int causal, int q_pos0,
+                 int k_pos0, float scale, void* stream) {
+  if (hd != 64 && hd != 128) return -1;
+  if (Sq <= 0 || Skv <= 0 || B <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  int rc;
+  {
+    const int64_t warps = int64_t(Sq) * B * nheads;
+    const int blocks = int((warps * 32 + 255) / 256);
+    attn_bwd_dot_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o->ptr, (const __nv_bfloat16*)d_o->ptr, o->ss,
+                                                o->sb, d_o->ss, d_o->sb, Sq, B, nheads, hd, (float*)dsum);
+  }
+  BwdParams p{};
+  p.Sq = Sq; p.Skv = Skv; p.B = B; p.nheads = nheads; p.qpg = nheads / nkv; p.causal = causal;
+  p.q_pos0 = q_pos0; p.k_pos0 = k_pos0; p.scale = scale;
+  p.qmap = {q->gs, q->hs, q->off}; p.kmap = {k->gs, k->hs, k->off}; p.vmap = {v->gs, v->hs, v->off};
+  p.domap = {d_o->gs, d_o->hs, d_o->off};
+  p.LSE = (const float*)lse; p.D = (const float*)dsum;
+  p.dQ = (__nv_bfloat16*)dq->ptr; p.dq_ss = dq->ss; p.dq_sb = dq->sb; p.dqmap = {dq->gs, dq->hs, dq->off};
+  p.dK = (__nv_bfloat16*)dk->ptr; p.dk_ss = dk->ss; p.dk_sb = dk->sb; p.dkmap = {dk->gs, dk->hs, dk->off};
+  p.dV = (__nv_bfloat16*)dv->ptr; p.dv_ss = dv->ss; p.dv_sb = dv->sb; p.dvmap = {dv->gs, dv->hs, dv->off};
+  p.status = hg_host::status_ptr();
+  {
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_map(&tq, q->ptr, hd, q->slots, Sq, B, q->ss, q->sb, 64))) return rc;
+    if ((rc = make_map(&tk, k->ptr, hd, k->slots, Skv, B, k->ss, k->sb, 128))) return rc;
+    if ((rc = make_map(&tv, v->ptr, hd, v->slots, Skv, B, v->ss, v->sb, 128))) return rc;
+    if ((rc = make_map(&tdo, d_o->ptr, hd, d_o->slots, Sq, B, d_o->ss, d_o->sb, 64))) return rc;
+    dim3 grid((Skv + 127) / 128, nkv, B);
+    if (hd == 128) {
+      static bool cfg = false;
+      if (!cfg) { if ((rc = set_smem(flash_bwd_dkv_kernel<128>, DkvSmem<128>::kTotal))) return rc; cfg = true; }
+      flash_bwd_dkv_kernel<128><<<grid, kThreads, DkvSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    } else {
+      static bool cfg = false;
+      if (!cfg) { if ((rc = set_smem(flash_bwd_dkv_kernel<64>, DkvSmem<64>::kTotal))) return rc; cfg = true; }
+      flash_bwd_dkv_kernel<64><<<grid, kThreads, DkvSmem<64>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    }
+  }
+  {
+    CUtensorMap tq, tk, tv, tdo;
+    if ((rc = make_map(&tq, q->ptr, hd, q->slots, Sq, B, q->ss, q->sb, 128))) return rc;
+    if ((rc = make_map(&tk, k->ptr, hd, k->slots, Skv, B, k->ss, k->sb, 64))) return rc;
+    if ((rc = make_map(&tv, v->ptr, hd, v->slots, Skv, B, v->ss, v->sb, 64))) return rc;
+    if ((rc = make_map(&tdo, d_o->ptr, hd, d_o->slots, Sq, B, d_o->ss, d_o->sb, 128))) return rc;
+    dim3 grid((Sq + 127) / 128, nheads, B);
+    if (hd == 128) {
+      static bool cfg = false;
+      if (!cfg) { if ((rc = set_smem(flash_bwd_dq_kernel<128>, DqSmem<128>::kTotal))) return rc; cfg = true; }
+      flash_bwd_dq_kernel<128><<<grid, kThreads, DqSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    } else {
+      static bool cfg = false;
+      if (!cfg) { if ((rc = set_smem(flash_bwd_dq_kernel<64>, DqSmem<64>::kTotal))) return rc; cfg = true; }
+      flash_bwd_dq_kernel<64><<<grid, kThreads, DqSmem<64>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    }
+  }
+  return int(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -1,0 +1,350 @@
+"""Autograd wrappers of the memory-bound sm_100a kernels: RMSNorm / LayerNorm (residual add fused),
+RoPE on the packed QKV projection, SwiGLU / GeGLU / GELU, vocab-parallel embedding and cross-entropy.
+
+Each op takes the CUDA kernel when its input lives on a GPU and the plain-PyTorch restatement of the
+same math (the numerical oracle of the tests, and the CPU/gloo plumbing path) otherwise.
+"""
+from __future__ import annotations
+
+import math
+from functools import lru_cache
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+
+_NORM_PARTS = 296  # CTAs (and partial rows) of the norm backward
+
+
+# --------------------------------------------------------------------------------------------
+# Norms
+# --------------------------------------------------------------------------------------------
+def _norm_ref(h, w, b, eps, rms):
+    hf = h.float()
+    if rms:
+        y = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    else:
+        y = torch.nn.functional.layer_norm(hf, (h.shape[-1],), w.float(), None if b is None else b.float(), eps)
+    return y.to(h.dtype)
+
+
+class _Norm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, residual, w, b, eps, rms):
+        lib = _lib.load()
+        rows, H = x.shape
+        y = torch.empty_like(x)
+        h = torch.empty_like(x) if residual is not None else x
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        mean = None if rms else torch.empty(rows, dtype=torch.float32, device=x.device)
+        rc = lib.hg_norm_fwd(x.data_ptr(), _lib.ptr(residual), w.data_ptr(), _lib.ptr(b), y.data_ptr(),
+                             h.data_ptr() if residual is not None else 0, rstd.data_ptr(), _lib.ptr(mean), rows, H,
+                             float(eps), int(rms), _lib.stream())
+        _lib.check(rc, "hg_norm_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(h, w, rstd, mean if mean is not None else rstd)
+        ctx.rms, ctx.has_res, ctx.has_bias = rms, residual is not None, b is not None
+        if residual is None:
+            return y
+        return y, h
+
+    @staticmethod
+    def backward(ctx, dy, dh=None):
+        h, w, rstd, mean = ctx.saved_tensors
+        lib = _lib.load()
+        rows, H = h.shape
+        dy = dy.contiguous()
+        dres = dh.contiguous() if dh is not None else None
+        dx = torch.empty_like(h)
+        parts = _NORM_PARTS
+        partial = torch.empty((2 if not ctx.rms else 1) * parts * H, dtype=torch.float32, device=h.device)
+        mgw = getattr(w, "main_grad", None)
+        dw = mgw if mgw is not None else torch.empty(H, dtype=torch.float32, device=h.device)
+        db = None
+        if ctx.has_bias:
+            db = torch.empty(H, dtype=torch.float32, device=h.device)
+        rc = lib.hg_norm_bwd(dy.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(),
+                             0 if ctx.rms else mean.data_ptr(), _lib.ptr(dres), dx.data_ptr(), dw.data_ptr(),
+                             _lib.ptr(db), partial.data_ptr(), parts, rows, H, int(ctx.rms),
+                             1 if mgw is not None else 0, _lib.stream())
+        _lib.check(rc, "hg_norm_bwd")
+        _lib.count_launch(2 if ctx.rms else 3)
+        gw = None if mgw is not None else dw.to(w.dtype)
+        gb = db.to(w.dtype) if db is not None else None
+        # dx carries the gradient of both x and the residual input (they are summed in the forward)
+        return dx, (dx if ctx.has_res else None), gw, gb, None, None
+
+
+def norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None, eps: float = 1e-5, rms: bool = True,
+         residual: torch.Tensor | None = None):
+    """Returns ``(normalised, h)`` with ``h = x + residual`` (``h is x`` without a residual).
+
+    Fusing the residual add means the block computes ``h = x + attn_out`` and ``norm(h)`` in one pass
+    over memory.  Note for LayerNorm with bias: the bias gradient is returned through the normal
+    autograd path (fp32 -> parameter dtype)."""
+    shp = x.shape
+    if not x.is_cuda:
+        h = x if residual is None else x + residual
+        return _norm_ref(h, w, b, eps, rms), h
+    x2 = x.reshape(-1, shp[-1]).contiguous()
+    r2 = residual.reshape(-1, shp[-1]).contiguous() if residual is not None else None
+    if r2 is None:
+        return _Norm.apply(x2, None, w, b, eps, rms).view(shp), x
+    y, h = _Norm.apply(x2, r2, w, b, eps, rms)
+    return y.view(shp), h.view(shp)
+
+
+# --------------------------------------------------------------------------------------------
+# RoPE
+# --------------------------------------------------------------------------------------------
+@lru_cache(maxsize=16)
+def rope_tables(max_pos: int, rot_dim: int, base: float, device: str, interp: float = 1.0):
+    """fp32 ``cos``/``sin`` tables ``[max_pos, rot_dim/2]`` (inv_freq = base^(-2i/dim), positions / interp)."""
+    inv = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim))
+    pos = torch.arange(max_pos, dtype=torch.float32) / interp
+    f = torch.outer(pos, inv)
+    return f.cos().to(device).contiguous(), f.sin().to(device).contiguous()
+
+
+def _rope_ref(t, cos, sin, pos, sign=1.0):
+    # t: [tokens, heads, hd]; rotate-half on the first 2*half channels
+    half = cos.shape[1]
+    c = cos[pos][:, None, :]
+    s = sin[pos][:, None, :] * sign
+    a, b = t[..., :half].float(), t[..., half:2 * half].float()
+    out = t.clone()
+    out[..., :half] = (a * c - b * s).to(t.dtype)
+    out[..., half:2 * half] = (b * c + a * s).to(t.dtype)
+    return out
+
+
+class _RopeInplace(torch.autograd.Function):
+    """Rotates the listed head slots of a ``[tokens, slots*hd]`` buffer in place."""
+
+    @staticmethod
+    def forward(ctx, buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim):
+        ctx.args = (head_off, cos, sin, batch, pos, pos_offset, rot_dim)
+        _rope_launch(buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim, False)
+        ctx.mark_dirty(buf)
+        return buf
+
+    @staticmethod
+    def backward(ctx, g):
+        head_off, cos, sin, batch, pos, pos_offset, rot_dim = ctx.args
+        # the incoming gradient buffer is produced by the attention backward for this op alone, so it is
+        # rotated back in place
+        if not g.is_contiguous():
+            g = g.contiguous()
+        _rope_launch(g, head_off, cos, sin, batch, pos, pos_offset, rot_dim, True)
+        return g, None, None, None, None, None, None, None
+
+
+def _rope_launch(buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim, backward):
+    lib = _lib.load()
+    tokens, pitch = buf.shape
+    rc = lib.hg_rope(buf.data_ptr(), head_off.data_ptr(), head_off.numel(), pitch, tokens, batch, _lib.ptr(pos),
+                     pos_offset, cos.data_ptr(), sin.data_ptr(), rot_dim, int(backward), _lib.stream())
+    _lib.check(rc, "hg_rope")
+    _lib.count_launch()
+
+
+def rope_packed(qkv: torch.Tensor, head_slots: torch.Tensor, hd: int, cos: torch.Tensor, sin: torch.Tensor,
+                batch: int, pos: torch.Tensor | None = None, pos_offset: int = 0) -> torch.Tensor:
+    """Apply rotate-half RoPE to the head slots ``head_slots`` (int32 slot indices) of ``qkv``
+    ``[tokens, slots*hd]`` (token t = s*batch + b has position ``pos[t]`` or ``s + pos_offset``)."""
+    rot_dim = 2 * cos.shape[1]
+    if not qkv.is_cuda:
+        tokens = qkv.shape[0]
+        t3 = qkv.view(tokens, -1, hd)
+        if pos is None:
+            p = torch.arange(tokens, device=qkv.device) // batch + pos_offset
+        else:
+            p = pos.long()
+        out = t3.clone()
+        idx = head_slots.long()
+        out[:, idx] = _rope_ref(t3[:, idx], cos, sin, p)
+        return out.view_as(qkv)
+    head_off = (head_slots.to(torch.int32) * hd).contiguous()
+    if pos is not None:
+        pos = pos.to(torch.int32).contiguous()
+    return _RopeInplace.apply(qkv, head_off, cos, sin, batch, pos, pos_offset, rot_dim)
+
+
+# --------------------------------------------------------------------------------------------
+# Gated activations
+# --------------------------------------------------------------------------------------------
+_KIND = {"swiglu": 0, "geglu": 1, "gelu": 2}
+
+
+def _act_ref(y, kind):
+    if kind == "gelu":
+        return torch.nn.functional.gelu(y.float(), approximate="tanh").to(y.dtype)
+    a, b = y.float().chunk(2, dim=-1)
+    act = torch.nn.functional.silu(a) if kind == "swiglu" else torch.nn.functional.gelu(a, approximate="tanh")
+    return (act * b).to(y.dtype)
+
+
+class _Glu(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, kind):
+        lib = _lib.load()
+        rows = y.shape[0]
+        F = y.shape[1] if kind == 2 else y.shape[1] // 2
+        out = torch.empty((rows, F), dtype=y.dtype, device=y.device)
+        _lib.check(lib.hg_glu_fwd(y.data_ptr(), out.data_ptr(), rows, F, kind, _lib.stream()), "hg_glu_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(y)
+        ctx.kind = kind
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (y,) = ctx.saved_tensors
+        lib = _lib.load()
+        g = g.contiguous()
+        dy = torch.empty_like(y)
+        F = g.shape[1]
+        _lib.check(lib.hg_glu_bwd(g.data_ptr(), y.data_ptr(), dy.data_ptr(), y.shape[0], F, ctx.kind, _lib.stream()),
+                   "hg_glu_bwd")
+        _lib.count_launch()
+        return dy, None
+
+
+def activation(y: torch.Tensor, kind: str = "swiglu") -> torch.Tensor:
+    """``swiglu`` / ``geglu``: ``act(y[..., :F]) * y[..., F:]``;  ``gelu``: tanh-approximated GELU."""
+    if not y.is_cuda:
+        return _act_ref(y, kind)
+    shp = y.shape
+    out = _Glu.apply(y.reshape(-1, shp[-1]).contiguous(), _KIND[kind])
+    return out.view(*shp[:-1], out.shape[-1])
+
+
+# --------------------------------------------------------------------------------------------
+# Embedding (vocab-parallel aware)
+# --------------------------------------------------------------------------------------------
+class _Embedding(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, ids, W, pos_emb, v0, batch, pos_offset):
+        lib = _lib.load()
+        tokens = ids.numel()
+        H = W.shape[1]
+        out = torch.empty((tokens, H), dtype=W.dtype, device=W.device)
+        _lib.check(lib.hg_embedding_fwd(ids.data_ptr(), W.data_ptr(), _lib.ptr(pos_emb), out.data_ptr(), tokens, H,
+                                        v0, v0 + W.shape[0], batch, pos_offset, _lib.stream()), "hg_embedding_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(ids)
+        ctx.W, ctx.pos_emb, ctx.args = W, pos_emb, (v0, batch, pos_offset)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        (ids,) = ctx.saved_tensors
+        W, pos_emb = ctx.W, ctx.pos_emb
+        v0, batch, pos_offset = ctx.args
+        lib = _lib.load()
+        g = g.contiguous()
+        mg = getattr(W, "main_grad", None)
+        dW = mg if mg is not None else torch.zeros(W.shape, dtype=torch.float32, device=W.device)
+        dpos = None
+        if pos_emb is not None:
+            mgp = getattr(pos_emb, "main_grad", None)
+            dpos = mgp if mgp is not None else torch.zeros(pos_emb.shape, dtype=torch.float32, device=W.device)
+        _lib.check(lib.hg_embedding_bwd(ids.data_ptr(), g.data_ptr(), dW.data_ptr(), _lib.ptr(dpos), ids.numel(),
+                                        W.shape[1], v0, v0 + W.shape[0], batch, pos_offset, _lib.stream()),
+                   "hg_embedding_bwd")
+        _lib.count_launch()
+        gW = None if mg is not None else dW.to(W.dtype)
+        gP = None
+        if pos_emb is not None and getattr(pos_emb, "main_grad", None) is None:
+            gP = dpos.to(pos_emb.dtype)
+        return None, gW, gP, None, None, None
+
+
+def embedding(ids: torch.Tensor, W: torch.Tensor, v0: int = 0, pos_emb: torch.Tensor | None = None, batch: int = 1,
+              pos_offset: int = 0) -> torch.Tensor:
+    """Masked lookup ``W[id - v0]`` (zero rows for ids outside this shard) for flat ``ids`` ``[tokens]``;
+    optionally adds learned absolute positions ``pos_emb[s + pos_offset]`` (token t = s*batch + b)."""
+    ids = ids.reshape(-1)
+    if not W.is_cuda:
+        local = ids - v0
+        mask = (local < 0) | (local >= W.shape[0])
+        out = torch.nn.functional.embedding(local.clamp(0, W.shape[0] - 1), W)
+        out = out.masked_fill(mask[:, None], 0)
+        if pos_emb is not None:
+            p = torch.arange(ids.numel(), device=ids.device) // batch + pos_offset
+            out = out + pos_emb[p]
+        return out
+    return _Embedding.apply(ids.contiguous().long(), W, pos_emb, v0, batch, pos_offset)
+
+
+# --------------------------------------------------------------------------------------------
+# Vocab-parallel cross entropy
+# --------------------------------------------------------------------------------------------
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, targets, v0, group):
+        lib = _lib.load()
+        rows, V = logits.shape
+        dev = logits.device
+        stats = torch.empty((3, rows), dtype=torch.float32, device=dev)
+        _lib.check(lib.hg_xent_stats(logits.data_ptr(), logits.stride(0), targets.data_ptr(), v0, V,
+                                     stats[0].data_ptr(), stats[1].data_ptr(), stats[2].data_ptr(), rows,
+                                     _lib.stream()), "hg_xent_stats")
+        _lib.count_launch()
+        lmax, lsum, pred = stats[0], stats[1], stats[2]
+        if group is not None and dist.get_world_size(group) > 1:
+            gmax = lmax.clone()
+            dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+            packed = torch.stack([lsum * torch.exp(lmax - gmax), pred])
+            dist.all_reduce(packed, group=group)
+            gsum, pred = packed[0], packed[1]
+        else:
+            gmax, gsum = lmax, lsum
+        loss = torch.log(gsum) + gmax - pred
+        ctx.save_for_backward(logits, targets, gmax, gsum)
+        ctx.v0 = v0
+        return loss
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, targets, gmax, gsum = ctx.saved_tensors
+        lib = _lib.load()
+        rows, V = logits.shape
+        g = g.float().contiguous()
+        # the logits buffer is dead after the loss: overwrite it with its own gradient
+        _lib.check(lib.hg_xent_bwd(logits.data_ptr(), logits.stride(0), targets.data_ptr(), ctx.v0, V,
+                                   gmax.data_ptr(), gsum.data_ptr(), g.data_ptr(), rows, _lib.stream()),
+                   "hg_xent_bwd")
+        _lib.count_launch()
+        return logits, None, None, None
+
+
+def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, v0: int = 0, group=None) -> torch.Tensor:
+    """Per-token loss ``[rows]`` (fp32) of ``logits [rows, V_local]`` against global ``targets``; with a
+    vocab-parallel ``group`` the shard statistics are combined by one MAX and one SUM all-reduce.
+    The backward overwrites ``logits`` in place (the tensor must not be used afterwards)."""
+    targets = targets.reshape(-1)
+    if not logits.is_cuda:
+        lf = logits.float()
+        lmax = lf.max(-1).values
+        if group is not None and dist.get_world_size(group) > 1:
+            gmax = lmax.clone()
+            dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
+        else:
+            gmax = lmax
+        ex = torch.exp(lf - gmax[:, None])
+        local = targets - v0
+        inside = (local >= 0) & (local < logits.shape[1])
+        pred = torch.where(inside, lf.gather(1, local.clamp(0, logits.shape[1] - 1)[:, None])[:, 0],
+                           torch.zeros_like(gmax))
+        ssum = ex.sum(-1)
+        if group is not None and dist.get_world_size(group) > 1:
+            from ..parallel.mappings import all_reduce_sum
+
+            packed = all_reduce_sum(torch.stack([ssum, pred]), group)
+            ssum, pred = packed[0], packed[1]
+        return torch.log(ssum) + gmax.detach() - pred
+    if logits.stride(1) != 1:
+        logits = logits.contiguous()
+    return _CrossEntropy.apply(logits, targets.contiguous().long(), v0, group)

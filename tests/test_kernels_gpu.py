@@ -1,0 +1,276 @@
+"""Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
+import math
+
+import pytest
+import torch
+
+from hetu_galvatron_b200 import ops
+from hetu_galvatron_b200.ops import _lib
+from hetu_galvatron_b200.ops.gemm import OUT_BF16_ACC, OUT_F32, OUT_F32_ACC
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def rel_err(a, b):
+    a, b = a.float(), b.float()
+    return ((a - b).norm() / (b.norm() + 1e-12)).item()
+
+
+@pytest.fixture(autouse=True)
+def _healthy():
+    yield
+    _lib.assert_healthy()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (4096, 4096, 4096), (1000, 776, 520),
+                                   (77, 130, 72), (8192, 1024, 2048)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_variants(M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    if (M % 8 or N % 8) and (a_mn or b_mn):
+        pytest.skip("transposed operands need a pitch that is a multiple of 8")
+    c = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn)
+    A = a.float().t() if a_mn else a.float()
+    B = b.float() if b_mn else b.float().t()
+    ref = A @ B
+    assert rel_err(c, ref) < 1e-2
+
+
+def test_gemm_output_modes_and_bias():
+    torch.manual_seed(1)
+    M, N, K = 512, 768, 320
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    bias = torch.randn(N, device=DEV, dtype=torch.bfloat16)
+    ref = a.float() @ b.float().t()
+    assert rel_err(ops.gemm(a, b, bias=bias), ref + bias.float()) < 1e-2
+    c32 = ops.gemm(a, b, out_mode=OUT_F32)
+    assert c32.dtype == torch.float32 and rel_err(c32, ref) < 1e-3
+    acc = torch.ones(M, N, device=DEV, dtype=torch.float32)
+    ops.gemm(a, b, out=acc, out_mode=OUT_F32_ACC)
+    ops.gemm(a, b, out=acc, out_mode=OUT_F32_ACC)
+    assert rel_err(acc, 2 * ref + 1) < 1e-3
+    acc16 = torch.ones(M, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm(a, b, out=acc16, out_mode=OUT_BF16_ACC)
+    assert rel_err(acc16, ref + 1) < 1e-2
+
+
+def test_linear_autograd():
+    torch.manual_seed(2)
+    T, K, N = 384, 256, 512
+    x = torch.randn(T, K, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.randn(N, K, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(T, N, device=DEV, dtype=torch.bfloat16)
+    y = ops.linear(x, w)
+    y.backward(g)
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    (xr @ wr.t()).backward(g.float())
+    assert rel_err(y, xr @ wr.t()) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 1e-2
+    assert rel_err(w.grad, wr.grad) < 1e-2
+    # fp32 main_grad accumulation
+    w2 = w.detach().clone().requires_grad_()
+    w2.main_grad = torch.zeros(N, K, device=DEV, dtype=torch.float32)
+    for _ in range(2):
+        ops.linear(x.detach(), w2).backward(g)
+    assert w2.grad is None and rel_err(w2.main_grad, 2 * wr.grad) < 1e-3
+
+
+def test_grouped_gemm_and_wgrad():
+    torch.manual_seed(3)
+    G, N, K = 4, 384, 256
+    seg = [128, 0, 256, 192]
+    rs = torch.tensor([0] + list(torch.tensor(seg).cumsum(0)), device=DEV, dtype=torch.int32)
+    rows = int(rs[-1])
+    a = torch.randn(rows, K, device=DEV, dtype=torch.bfloat16)
+    for b_mn in (False, True):
+        b = torch.randn((G, K, N) if b_mn else (G, N, K), device=DEV, dtype=torch.bfloat16)
+        out = ops.grouped_gemm(a, b, rs, b_mn=b_mn)
+        ref = torch.zeros(rows, N, device=DEV)
+        for g in range(G):
+            Bm = b[g].float() if b_mn else b[g].float().t()
+            ref[rs[g]:rs[g + 1]] = a[rs[g]:rs[g + 1]].float() @ Bm
+        assert rel_err(out, ref) < 1e-2
+    dy = torch.randn(rows, N, device=DEV, dtype=torch.bfloat16)
+    dw = torch.full((G, N, K), 1.0, device=DEV, dtype=torch.float32)
+    ops.grouped_wgrad(dy, a, rs, dw, accumulate=True)
+    ref = torch.stack([dy[rs[g]:rs[g + 1]].float().t() @ a[rs[g]:rs[g + 1]].float() for g in range(G)]) + 1
+    assert rel_err(dw, ref) < 1e-3
+
+
+@pytest.mark.parametrize("rms", [True, False])
+@pytest.mark.parametrize("H", [256, 4096, 5120])
+def test_norm(rms, H):
+    torch.manual_seed(4)
+    T = 300
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    r = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = (1 + 0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    b = None if rms else (0.1 * torch.randn(H, device=DEV)).to(torch.bfloat16).requires_grad_()
+    y, h = ops.norm(x, w, b, 1e-5, rms, residual=r)
+    gy = torch.randn_like(y)
+    gh = torch.randn_like(h)
+    torch.autograd.backward([y, h], [gy, gh])
+    xr, rr = x.detach().float().requires_grad_(), r.detach().float().requires_grad_()
+    wr = w.detach().float().requires_grad_()
+    br = None if rms else b.detach().float().requires_grad_()
+    hr = (xr + rr).to(torch.bfloat16).float() + ((xr + rr) - (xr + rr).detach())  # bf16-rounded value, fp32 grad
+    if rms:
+        yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    else:
+        yr = torch.nn.functional.layer_norm(hr, (H,), wr, br, 1e-5)
+    torch.autograd.backward([yr, hr], [gy.float(), gh.float()])
+    assert rel_err(y, yr) < 1e-2 and rel_err(h, hr) < 1e-2
+    assert rel_err(x.grad, xr.grad) < 1e-2 and rel_err(r.grad, rr.grad) < 1e-2
+    assert rel_err(w.grad, wr.grad) < 2e-2
+    if not rms:
+        assert rel_err(b.grad, br.grad) < 2e-2
+
+
+def test_rope_packed():
+    torch.manual_seed(5)
+    S, B, nh, ng, hd = 96, 2, 8, 2, 128
+    slots = nh + 2 * ng
+    qkv = torch.randn(S * B, slots * hd, device=DEV, dtype=torch.bfloat16)
+    cos, sin = ops.rope_tables(256, hd, 10000.0, DEV)
+    qpg = nh // ng
+    rot = torch.tensor([g * (qpg + 2) + j for g in range(ng) for j in range(qpg + 1)], dtype=torch.int32, device=DEV)
+    ref_in = qkv.clone().cpu()
+    ref = ops.rope_packed(ref_in, rot.cpu(), hd, cos.cpu(), sin.cpu(), B)
+    x = qkv.clone().requires_grad_()
+    out = ops.rope_packed(x * 1.0, rot, hd, cos, sin, B)
+    assert rel_err(out.cpu(), ref) < 1e-2
+    g = torch.randn_like(out)
+    out.backward(g.clone())
+    xr = ref_in.float().requires_grad_()
+    ops.rope_packed(xr, rot.cpu(), hd, cos.cpu(), sin.cpu(), B).backward(g.cpu().float())
+    assert rel_err(x.grad.cpu(), xr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("kind", ["swiglu", "geglu", "gelu"])
+def test_activation(kind):
+    torch.manual_seed(6)
+    T, F = 257, 1376
+    y = torch.randn(T, F if kind == "gelu" else 2 * F, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = ops.activation(y, kind)
+    g = torch.randn_like(out)
+    out.backward(g)
+    yr = y.detach().float().cpu().requires_grad_()
+    ref = ops.activation(yr, kind)
+    ref.backward(g.float().cpu())
+    assert rel_err(out.cpu(), ref) < 1e-2 and rel_err(y.grad.cpu(), yr.grad) < 1e-2
+
+
+def test_embedding():
+    torch.manual_seed(7)
+    V, H, T = 1000, 256, 512
+    W = torch.randn(V // 2, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    ids = torch.randint(0, V, (T,), device=DEV)
+    out = ops.embedding(ids, W, v0=V // 2)
+    g = torch.randn_like(out)
+    out.backward(g)
+    Wr = W.detach().float().cpu().requires_grad_()
+    ref = ops.embedding(ids.cpu(), Wr, v0=V // 2)
+    ref.backward(g.float().cpu())
+    assert torch.equal(out.float().cpu(), ref.detach())
+    assert rel_err(W.grad.cpu(), Wr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("V", [1000, 32000, 50257 + 7])
+def test_cross_entropy(V):
+    torch.manual_seed(8)
+    T = 200
+    V = V - V % 8
+    logits = (3 * torch.randn(T, V, device=DEV)).to(torch.bfloat16)
+    tgt = torch.randint(0, V, (T,), device=DEV)
+    x = logits.clone().requires_grad_()
+    xin = x * 1.0
+    loss = ops.cross_entropy(xin, tgt)
+    w = torch.rand(T, device=DEV)
+    (loss * w).sum().backward()
+    xr = logits.float().requires_grad_()
+    lr = torch.nn.functional.cross_entropy(xr, tgt, reduction="none")
+    (lr * w).sum().backward()
+    assert torch.allclose(loss, lr, rtol=1e-3, atol=1e-3)
+    assert rel_err(x.grad, xr.grad) < 2e-2
+
+
+@pytest.mark.parametrize("hd", [128, 64])
+@pytest.mark.parametrize("S,B,nh,ng,causal", [(128, 1, 2, 2, True), (512, 2, 4, 2, True), (384, 1, 4, 1, False),
+                                              (200, 1, 2, 2, True), (1024, 1, 8, 8, True)])
+def test_flash_attention(hd, S, B, nh, ng, causal):
+    torch.manual_seed(9)
+    q = torch.randn(S, B, nh, hd, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k = torch.randn(S, B, ng, hd, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(S, B, ng, hd, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out, lse = ops.flash_attention(q, k, v, causal=causal, return_lse=True)
+    g = torch.randn_like(out)
+    out.backward(g)
+    qr, kr, vr = (t.detach().float().requires_grad_() for t in (q, k, v))
+    ref, lse_ref = ops.attention_reference(qr, kr, vr, causal)
+    ref.backward(g.float())
+    assert rel_err(out, ref) < 2e-2
+    assert torch.allclose(lse, lse_ref, rtol=1e-3, atol=2e-3)
+    assert rel_err(q.grad, qr.grad) < 3e-2
+    assert rel_err(k.grad, kr.grad) < 3e-2
+    assert rel_err(v.grad, vr.grad) < 3e-2
+
+
+def test_flash_attention_packed():
+    torch.manual_seed(10)
+    S, B, nh, ng, hd = 256, 2, 8, 2, 128
+    qkv = torch.randn(S * B, (nh + 2 * ng) * hd, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = ops.flash_attention_packed(qkv, S, B, nh, ng, hd)
+    g = torch.randn_like(out)
+    out.backward(g)
+    xr = qkv.detach().float().cpu().requires_grad_()
+    ref = ops.flash_attention_packed(xr, S, B, nh, ng, hd)
+    ref.backward(g.float().cpu())
+    assert rel_err(out.cpu(), ref) < 2e-2
+    assert rel_err(qkv.grad.cpu(), xr.grad) < 3e-2
+
+
+def test_adamw_and_clip():
+    torch.manual_seed(11)
+    n = 1_000_003
+    p = torch.randn(n, device=DEV)
+    g = torch.randn(n, device=DEV)
+    ref_p = torch.nn.Parameter(p.clone())
+    opt = torch.optim.AdamW([ref_p], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    m, v = torch.zeros_like(p), torch.zeros_like(p)
+    lp = torch.empty(n, device=DEV, dtype=torch.bfloat16)
+    for step in (1, 2, 3):
+        ref_p.grad = g.clone()
+        opt.step()
+        ops.adamw_step(p, g, m, v, lp, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=step)
+    assert torch.allclose(p, ref_p.data, rtol=1e-5, atol=1e-6)
+    assert torch.equal(lp, p.to(torch.bfloat16))
+    tot = torch.zeros(1, device=DEV)
+    ops.sumsq(g, tot, accumulate=False)
+    ops.sumsq(g.to(torch.bfloat16), tot, accumulate=True)
+    ref = g.pow(2).sum() + g.to(torch.bfloat16).float().pow(2).sum()
+    assert abs(tot.item() - ref.item()) / ref.item() < 1e-4
+    coef, nrm = torch.zeros(1, device=DEV), torch.zeros(1, device=DEV)
+    ops.clip_coefficient(tot, 1.0, coef, nrm)
+    assert abs(nrm.item() - math.sqrt(ref.item())) / nrm.item() < 1e-4
+    assert abs(coef.item() - 1.0 / (nrm.item() + 1e-6)) < 1e-6
+    g2 = g.clone()
+    ops.scale_(g2, coef)
+    assert torch.allclose(g2, g * coef, rtol=1e-6)
+
+
+def test_bounded_wait_reports_status():
+    """A gate that nothing opens: the GEMM producer's bounded wait must give up, record a status code and
+    leave the context usable."""
+    lib = _lib.load()
+    if not hasattr(lib, "hg_gemm_gated_selftest"):
+        pytest.skip("self-test entry not built")
+    rc = lib.hg_gemm_gated_selftest(_lib.stream())
+    assert rc == 0
+    code = _lib.read_status(clear=True)
+    assert code == 5
+    x = torch.ones(4, device=DEV)
+    assert (x + 1).sum().item() == 8
