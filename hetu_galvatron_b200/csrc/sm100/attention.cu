@@ -862,7 +862,7 @@ int make_map(CUtensorMap* out, const void* base, int hd, int slots, int S, int B
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
+  return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
 }
 
 template <typename K>

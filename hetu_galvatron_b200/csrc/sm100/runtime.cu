@@ -23,7 +23,19 @@ int* status_ptr() {
   return g_status[dev];
 }
 
+// cuTensorMapEncodeTiled is a driver call and needs a current context on the calling thread; threads
+// that have only been handed work by another thread (autograd's backward workers) may not have bound
+// the primary context yet, so bind it once per thread through the runtime.
+static void ensure_context_on_this_thread() {
+  static thread_local bool bound = false;
+  if (!bound) {
+    cudaFree(nullptr);
+    bound = true;
+  }
+}
+
 EncodeTiledFn get_encode_fn() {
+  ensure_context_on_this_thread();
   std::lock_guard<std::mutex> lk(g_mu);
   if (g_encode == nullptr) {
     void* fn = nullptr;
@@ -46,7 +58,7 @@ int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
+  return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
 }
 
 int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1,
@@ -60,7 +72,7 @@ int make_tmap_3d_bf16(CUtensorMap* out, const void* base, uint64_t d0, uint64_t 
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? 0 : -3;
+  return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
 }
 
 }  // namespace hg_host

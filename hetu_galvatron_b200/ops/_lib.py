@@ -46,9 +46,9 @@ _SIGNATURES = {
     "hg_sumsq": [c_void_p, c_ll, c_int, c_void_p, c_void_p, c_int, c_float, c_void_p],
     "hg_clip_coef": [c_void_p, c_float, c_void_p, c_void_p, c_void_p],
     "hg_scale": [c_void_p, c_ll, c_int, c_void_p, c_float, c_void_p],
-    "hg_flash_fwd": [ctypes.POINTER(AttnTensor)] * 4 + [c_void_p] + [c_int] * 10 + [c_float, c_void_p],
+    "hg_flash_fwd": [ctypes.POINTER(AttnTensor)] * 4 + [c_void_p] + [c_int] * 9 + [c_float, c_void_p],
     "hg_flash_bwd": [ctypes.POINTER(AttnTensor)] * 5 + [c_void_p, c_void_p] + [ctypes.POINTER(AttnTensor)] * 3 +
-                    [c_int] * 10 + [c_float, c_void_p],
+                    [c_int] * 9 + [c_float, c_void_p],
     "hg_read_status": [c_int],
     "hg_gemm_gated_selftest": [c_void_p],
     "hg_library_version": [],

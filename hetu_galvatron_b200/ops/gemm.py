@@ -73,7 +73,11 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     lib = _lib.load()
     rc = lib.hg_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K, a.stride(0),
                           b.stride(0), out.stride(0), int(a_mn), int(b_mn), out_mode, max_ctas, _lib.stream())
-    _lib.check(rc, "hg_gemm_bf16")
+    if rc != 0:
+        raise _lib.KernelError(
+            "hg_gemm_bf16 failed with code %d (M=%d N=%d K=%d a_mn=%d b_mn=%d a=%s/%s b=%s/%s out=%s/%s mode=%d)" %
+            (rc, M, N, K, a_mn, b_mn, tuple(a.shape), a.stride(), tuple(b.shape), b.stride(), tuple(out.shape),
+             out.stride(), out_mode))
     _lib.count_launch()
     return out
 

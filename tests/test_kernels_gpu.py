@@ -117,7 +117,7 @@ def test_norm(rms, H):
     xr, rr = x.detach().float().requires_grad_(), r.detach().float().requires_grad_()
     wr = w.detach().float().requires_grad_()
     br = None if rms else b.detach().float().requires_grad_()
-    hr = (xr + rr).to(torch.bfloat16).float() + ((xr + rr) - (xr + rr).detach())  # bf16-rounded value, fp32 grad
+    hr = (xr + rr).detach().to(torch.bfloat16).float() + ((xr + rr) - (xr + rr).detach())  # bf16-rounded value, fp32 grad
     if rms:
         yr = hr * torch.rsqrt(hr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
     else:
