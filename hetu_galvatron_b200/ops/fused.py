@@ -67,7 +67,9 @@ class _Norm(torch.autograd.Function):
         rc = lib.hg_norm_bwd(dy.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(),
                              0 if ctx.rms else mean.data_ptr(), _lib.ptr(dres), dx.data_ptr(), dw.data_ptr(),
                              _lib.ptr(db), partial.data_ptr(), parts, rows, H, int(ctx.rms),
-                             1 if mgw is not None else 0, _lib.stream())
+                             1 if (mgw is not None and not getattr(w, "mg_fresh", False)) else 0, _lib.stream())
+        if mgw is not None:
+            w.mg_fresh = False
         _lib.check(rc, "hg_norm_bwd")
         _lib.count_launch(2 if ctx.rms else 3)
         gw = None if mgw is not None else dw.to(w.dtype)
@@ -245,10 +247,16 @@ class _Embedding(torch.autograd.Function):
         lib = _lib.load()
         g = g.contiguous()
         mg = getattr(W, "main_grad", None)
+        if mg is not None and getattr(W, "mg_fresh", False):
+            mg.zero_()
+            W.mg_fresh = False
         dW = mg if mg is not None else torch.zeros(W.shape, dtype=torch.float32, device=W.device)
         dpos = None
         if pos_emb is not None:
             mgp = getattr(pos_emb, "main_grad", None)
+            if mgp is not None and getattr(pos_emb, "mg_fresh", False):
+                mgp.zero_()
+                pos_emb.mg_fresh = False
             dpos = mgp if mgp is not None else torch.zeros(pos_emb.shape, dtype=torch.float32, device=W.device)
         _lib.check(lib.hg_embedding_bwd(ids.data_ptr(), g.data_ptr(), dW.data_ptr(), _lib.ptr(dpos), ids.numel(),
                                         W.shape[1], v0, v0 + W.shape[0], batch, pos_offset, _lib.stream()),

@@ -99,8 +99,9 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             mg = getattr(w, "main_grad", None)
             if mg is not None:
-                gemm(dy, x, a_mn=True, b_mn=True, out=mg, out_mode=OUT_F32_ACC)
-                w.grad_added_to_main_grad = True
+                fresh = getattr(w, "mg_fresh", False)
+                gemm(dy, x, a_mn=True, b_mn=True, out=mg, out_mode=OUT_F32 if fresh else OUT_F32_ACC)
+                w.mg_fresh = False
                 dw = None
             else:
                 dw = gemm(dy, x, a_mn=True, b_mn=True)

@@ -1,0 +1,166 @@
+"""``GalvatronModel``: the assembled hybrid-parallel model and its training step.
+
+    model = build_model(args)                      # groups, stage modules, ZeRO units, pipeline engine
+    loss  = model.forward_backward(batch, iter, profiler, loss_func, labels=..., loss_mask=...)
+    optimizer.step()
+
+``batch`` is this rank's share of the global batch (``[B_local, S]`` token ids, split over the vocab
+layers' data-parallel group by the data loader); the engine slices the sequence for context parallelism,
+cuts micro-batches, runs the schedule (no-PP accumulation / GPipe / 1F1B-flush) and returns the mean loss
+of the step (a 0-dim device tensor; the caller decides when to read it).
+
+Capability parity: galvatron/core/runtime/hybrid_parallel_model.py:51-97 (``forward_backward``, loss
+reduction), :99-301 (assembly), models/builder.py:158-187 (``build_model``).
+"""
+from __future__ import annotations
+
+import os
+from typing import Callable, Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config.model_config import resolve_model_config
+from ..models.builder import ModelGroups, StageModel, build_stage
+from ..models.modules import zigzag_positions
+from ..models.spec import ModelSpec, spec_from_args
+from ..parallel.groups import GroupFactory
+from ..parallel.pipeline import PipelineEngine, chunk_batch
+from .plan import HybridPlan, build_plan
+
+
+def slice_for_cp(t: Optional[torch.Tensor], cp: int, cp_rank: int) -> Optional[torch.Tensor]:
+    """Zig-zag context-parallel slice of ``[B, S, ...]`` along the sequence: chunks ``r`` and ``2c-1-r``."""
+    if t is None or cp == 1:
+        return t
+    S = t.shape[1]
+    idx = zigzag_positions(S, cp, cp_rank, t.device)
+    return t.index_select(1, idx)
+
+
+def default_loss_func(loss_mask: Optional[torch.Tensor], cp: int = 1) -> Callable:
+    """``sum(loss * mask) / sum(mask)`` over this rank's tokens, pre-divided by the context-parallel
+    degree because gradients are summed (not averaged) over the cp ranks."""
+
+    def fn(per_token_loss: torch.Tensor) -> torch.Tensor:
+        if loss_mask is None:
+            return per_token_loss.float().mean() / cp
+        m = loss_mask.to(per_token_loss.dtype)
+        return (per_token_loss * m).sum() / m.sum().clamp(min=1) / cp
+
+    return fn
+
+
+class GalvatronModel:
+    def __init__(self, args, spec: ModelSpec, plan: HybridPlan, groups: ModelGroups, stage: StageModel, device):
+        self.args, self.spec, self.plan, self.groups, self.model, self.device = args, spec, plan, groups, stage, device
+        self.engine = PipelineEngine(stage, groups, plan, spec, device)
+        self.vocab_ctx = groups.ctx(plan.layers[0], spec.seq_len)
+        self.iter = 0
+
+    # ---- introspection ------------------------------------------------------------------------------------
+    @property
+    def sharded_units(self):
+        return self.model.sharded
+
+    def parameters(self):
+        return self.model.parameters()
+
+    def named_units(self):
+        return [(lp.name, u) for lp, u in zip(self.model.plans, self.model.units)]
+
+    @property
+    def is_first_stage(self):
+        return self.engine.first
+
+    @property
+    def is_last_stage(self):
+        return self.engine.last
+
+    def local_batch_size(self) -> int:
+        lp = self.plan.layers[0]
+        return self.plan.global_batch_size // self.plan.dp_size(lp)
+
+    # ---- training step ------------------------------------------------------------------------------------
+    def forward_backward(self, batch, iter: int = 0, profiler=None, loss_func: Optional[Callable] = None,
+                         labels: Optional[torch.Tensor] = None, loss_mask: Optional[torch.Tensor] = None,
+                         forward_only: bool = False, **kwargs):
+        tokens = batch[0] if isinstance(batch, (list, tuple)) else batch
+        c = self.vocab_ctx
+        if labels is None:
+            labels = kwargs.get("labels")
+        chunks = max(1, min(self.plan.chunks, tokens.shape[0]))
+        tok = slice_for_cp(tokens, c.cp_size, c.cp_rank)
+        lab = slice_for_cp(labels, c.cp_size, c.cp_rank)
+        msk = slice_for_cp(loss_mask, c.cp_size, c.cp_rank)
+        toks, labs, msks = chunk_batch(tok, chunks), chunk_batch(lab, chunks), chunk_batch(msk, chunks)
+        chunks = len(toks)
+        d_vocab = self.plan.dp_size(self.plan.layers[0])
+        mb_sizes = [t.shape[0] * d_vocab for t in toks]
+        if loss_func is None:
+            fns = [default_loss_func(m, c.cp_size) for m in msks]
+        else:
+            fns = [loss_func] * chunks
+        if profiler is not None:
+            profiler.profile_memory(iter, "Before Forward")
+        losses = self.engine.run(toks, labs, fns, mb_sizes, forward_only=forward_only)
+        if profiler is not None:
+            profiler.profile_memory(iter, "After Backward")
+        self.iter = iter
+        return self._reduce_loss(losses)
+
+    def _reduce_loss(self, losses: List[torch.Tensor]):
+        """Step loss for logging: sum of the (already 1/chunks-scaled) micro-batch losses, summed over cp,
+        averaged over the vocab layers' dp group; valid on the last pipeline stage (``None`` elsewhere)."""
+        if not losses:
+            return None
+        total = torch.stack([l.float() for l in losses]).sum()
+        c = self.vocab_ctx
+        if c.cp_size > 1:
+            dist.all_reduce(total, group=c.cp.group)
+        if c.dp is not None and c.dp.size > 1 and c.dp.group is not None:
+            dist.all_reduce(total, group=c.dp.group)
+            total = total / c.dp.size
+        return total
+
+    # ---- tied embeddings across pipeline stages ---------------------------------------------------------
+    def sync_tied_embedding_grads(self):
+        """First and last stage hold a copy of the tied embedding / LM-head weight: sum their gradients."""
+        if not self.spec.tied or self.plan.pp_deg == 1:
+            return
+        g = self.groups.embedding
+        if g.size < 2 or g.group is None:
+            return
+        for lp, u in zip(self.model.plans, self.model.units):
+            if lp.kind in ("embedding", "lm_head"):
+                w = u.inner.embed_tokens.weight if lp.kind == "embedding" else u.inner.lm_head.weight
+                dist.all_reduce(w.main_grad, group=g.group)
+
+
+def build_model(args, device=None, full_init: bool = False, fused_comm: Optional[bool] = None) -> GalvatronModel:
+    """Resolve the configuration, create the process groups and instantiate this rank's stage."""
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    resolve_model_config(args, vocab_tp=None)
+    plan = build_plan(args, world)
+    # pad the vocabulary for the vocab tensor-parallel degree
+    from ..config.model_config import finalize_model_args
+
+    finalize_model_args(args.model, vocab_tp=plan.vocab_tp if not plan.vocab_sp else 1)
+    spec = spec_from_args(args)
+    if device is None:
+        if torch.cuda.is_available():
+            device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", args.local_rank)))
+        else:
+            device = torch.device("cpu")
+    backend = None
+    factory = GroupFactory(rank, world, backend)
+    groups = ModelGroups(factory, plan, rank)
+    if fused_comm is None:
+        fused_comm = bool(int(os.environ.get("HG_FUSED_COMM", "0"))) and device.type == "cuda"
+    stage = build_stage(spec, plan, groups, device, seed=args.train.seed or 1234, full_init=full_init,
+                        fused_comm=fused_comm, reduce_in_fp32=args.parallel.reduce_in_fp32 or True)
+    if rank == 0 and os.environ.get("HG_QUIET", "0") != "1":
+        print("================ hybrid-parallel plan (%s) ================" % plan.source)
+        print(plan.describe())
+    return GalvatronModel(args, spec, plan, groups, stage, device)
