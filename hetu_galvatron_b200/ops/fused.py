@@ -335,7 +335,7 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, v0: int = 0, grou
     targets = targets.reshape(-1)
     if not logits.is_cuda:
         lf = logits.float()
-        lmax = lf.max(-1).values
+        lmax = lf.max(-1).values.detach()  # the shift cancels analytically: it must not carry a gradient
         if group is not None and dist.get_world_size(group) > 1:
             gmax = lmax.clone()
             dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
@@ -352,7 +352,7 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, v0: int = 0, grou
 
             packed = all_reduce_sum(torch.stack([ssum, pred]), group)
             ssum, pred = packed[0], packed[1]
-        return torch.log(ssum) + gmax.detach() - pred
+        return torch.log(ssum) + gmax - pred
     if logits.stride(1) != 1:
         logits = logits.contiguous()
     return _CrossEntropy.apply(logits, targets.contiguous().long(), v0, group)

@@ -1,0 +1,138 @@
+"""Single-kernel micro-benchmarks (CUDA-event timed, L2 flushed between iterations).
+
+    python -m hetu_galvatron_b200.profiler.kernel_bench gemm --m 8192 --n 4096 --k 4096 [--variant fwd|dgrad|wgrad]
+    python -m hetu_galvatron_b200.profiler.kernel_bench attn --s 4096 --b 1 --heads 32 --kv-heads 32 --hd 128 [--bwd]
+    python -m hetu_galvatron_b200.profiler.kernel_bench norm|glu|xent|adam --rows 8192 --cols 4096
+
+Prints one JSON line with the achieved rate and its fraction of the measured peaks (``MEASURED_PEAKS.json``
+at the repository root when present, else 6650 GB/s and 1590 TFLOP/s, marked "of fallback").  The same
+command line is what the committed ncu summaries under ``profiles/`` were captured from (small ``--iters``).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def peaks():
+    here = os.path.dirname(os.path.abspath(__file__))
+    path = os.path.join(here, "..", "..", "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return p["hbm_gbs"], p["bf16_tflops"], "of measured"
+    return 6650.0, 1590.0, "of fallback"
+
+
+def timed(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+def main(argv=None):
+    from hetu_galvatron_b200 import ops
+    from hetu_galvatron_b200.ops import _lib
+    from hetu_galvatron_b200.ops.gemm import OUT_F32_ACC
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("kernel", choices=["gemm", "attn", "norm", "glu", "xent", "adam"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--variant", default="fwd", choices=["fwd", "dgrad", "wgrad"])
+    ap.add_argument("--s", type=int, default=4096)
+    ap.add_argument("--b", type=int, default=1)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=32)
+    ap.add_argument("--hd", type=int, default=128)
+    ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--rows", type=int, default=8192)
+    ap.add_argument("--cols", type=int, default=4096)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args(argv)
+    dev = "cuda"
+    hbm, tf, tag = peaks()
+    flush = None if a.no_flush else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    bf = torch.bfloat16
+    out = {"kernel": a.kernel}
+    if a.kernel == "gemm":
+        M, N, K = a.m, a.n, a.k
+        x = torch.randn(M, K, device=dev, dtype=bf)
+        w = torch.randn(N, K, device=dev, dtype=bf)
+        dy = torch.randn(M, N, device=dev, dtype=bf)
+        mg = torch.zeros(N, K, device=dev, dtype=torch.float32)
+        fn = {"fwd": lambda: ops.gemm(x, w), "dgrad": lambda: ops.gemm(dy, w, b_mn=True),
+              "wgrad": lambda: ops.gemm(dy, x, a_mn=True, b_mn=True, out=mg, out_mode=OUT_F32_ACC)}[a.variant]
+        ms = timed(fn, a.iters, a.warmup, flush)
+        rate = 2.0 * M * N * K / ms / 1e9
+        out.update(shape=[M, N, K], variant=a.variant, ms=ms, tflops=rate, frac=rate / tf, frac_of=tag)
+    elif a.kernel == "attn":
+        S, B, nh, ng, hd = a.s, a.b, a.heads, a.kv_heads, a.hd
+        q = torch.randn(S, B, nh, hd, device=dev, dtype=bf, requires_grad=True)
+        k = torch.randn(S, B, ng, hd, device=dev, dtype=bf, requires_grad=True)
+        v = torch.randn(S, B, ng, hd, device=dev, dtype=bf, requires_grad=True)
+        fl = 4.0 * S * S * B * nh * hd / 2
+        if a.bwd:
+            o, lse = ops.flash_attention(q, k, v, return_lse=True)
+            g = torch.randn_like(o)
+            fn = lambda: ops.flash_backward(q.detach(), k.detach(), v.detach(), o.detach(), g, lse, True,
+                                            1.0 / hd ** 0.5)
+            fl *= 2.5
+        else:
+            fn = lambda: ops.flash_attention(q.detach(), k.detach(), v.detach())
+        ms = timed(fn, a.iters, a.warmup, flush)
+        rate = fl / ms / 1e9
+        out.update(shape=[S, B, nh, ng, hd], bwd=a.bwd, ms=ms, tflops=rate, frac=rate / tf, frac_of=tag)
+    else:
+        R, C = a.rows, a.cols
+        if a.kernel == "norm":
+            x = torch.randn(R, C, device=dev, dtype=bf)
+            r = torch.randn_like(x)
+            w = torch.ones(C, device=dev, dtype=bf)
+            fn = lambda: ops.norm(x, w, None, 1e-5, True, residual=r)
+            nbytes = 4 * R * C * 2
+        elif a.kernel == "glu":
+            y = torch.randn(R, 2 * C, device=dev, dtype=bf)
+            fn = lambda: ops.activation(y, "swiglu")
+            nbytes = 3 * R * C * 2
+        elif a.kernel == "xent":
+            lg = torch.randn(R, C, device=dev, dtype=bf)
+            tg = torch.randint(0, C, (R,), device=dev)
+            fn = lambda: ops.cross_entropy(lg, tg)
+            nbytes = R * C * 2
+        else:
+            n = R * C
+            p = torch.randn(n, device=dev)
+            g = torch.randn(n, device=dev)
+            m, v = torch.zeros_like(p), torch.zeros_like(p)
+            lp = torch.empty(n, device=dev, dtype=bf)
+            fn = lambda: ops.adamw_step(p, g, m, v, lp, lr=1e-3, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1,
+                                        step=1)
+            nbytes = n * 30
+        ms = timed(fn, a.iters, a.warmup, flush)
+        rate = nbytes / ms / 1e6
+        out.update(shape=[R, C], ms=ms, gbs=rate, frac=rate / hbm, frac_of=tag)
+    out["status"] = _lib.read_status()
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
