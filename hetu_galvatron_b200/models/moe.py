@@ -1,0 +1,391 @@
+"""Mixture-of-experts decoder layer: attention block, top-k router, token dispatch, expert MLPs.
+
+Units / parameter names (checkpoint contract, reference models/moe_modules.py:19-155):
+
+    GalvatronMoEAttention   attn.* (as the dense attention block) + pre_router_norm.weight
+    GalvatronMoERouter      router.weight [E, H] fp32 (+ router.expert_bias)
+    GalvatronMoEMLP         experts.linear_fc1.weight [E_loc, 2F/etp, H], experts.linear_fc2.weight [E_loc, H, F/etp]
+                            (exported per expert as experts.local_experts.{j}.linear_fc{1,2}.weight)
+
+Routing (reference moe/router.py:98-438, moe/moe_utils.py:430-544): fp32 gate, softmax-then-top-k or
+top-k-then-softmax, sigmoid scores with optional selection bias, group-limited top-k, capacity dropping
+(``probs`` / ``position`` policy), switch-style auxiliary load-balancing loss, z-loss.
+
+Dispatch: tokens are sorted by expert (expert-major, token-minor -- moe_utils.py:219-353), exchanged with
+an all-to-all-v over the expert-parallel group (``alltoall``) or all-gathered (``allgather``), re-sorted
+``[source][local expert] -> [local expert][source]`` into 128-row-aligned, zero-padded segments, run
+through the grouped tcgen05 GEMM (fc1 -> SwiGLU -> fc2), and returned by the mirror path where the
+routing weights are applied in fp32 (token_dispatcher.py:116-284, :287-740; moe/mlp.py:26-211).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..parallel import mappings as mp
+from ..parallel.zero import ShardedUnit, UnitWrapper
+from .modules import GalvatronAttention, Norm, _param, init_normal_sharded_, ops_add
+from .spec import LayerCtx, ModelSpec
+
+SEG_ALIGN = 128  # rows; expert segments start on tile boundaries and are zero padded
+
+
+# --------------------------------------------------------------------------------------------
+# aux-loss plumbing
+# --------------------------------------------------------------------------------------------
+class _AuxLossScaler(torch.autograd.Function):
+    """Attaches an auxiliary loss to an activation: identity forward, injects d(aux)=scale in the backward."""
+
+    scale = 1.0
+
+    @staticmethod
+    def forward(ctx, x, aux):
+        ctx.save_for_backward(aux)
+        return x
+
+    @staticmethod
+    def backward(ctx, g):
+        (aux,) = ctx.saved_tensors
+        return g, torch.ones_like(aux) * _AuxLossScaler.scale
+
+
+def set_aux_loss_scale(scale: float):
+    _AuxLossScaler.scale = float(scale)
+
+
+# --------------------------------------------------------------------------------------------
+# router
+# --------------------------------------------------------------------------------------------
+def topk_routing(logits: torch.Tensor, spec: ModelSpec, expert_bias: Optional[torch.Tensor] = None):
+    """logits [T, E] (fp32) -> (probs [T, k], idx [T, k]); differentiable in probs."""
+    k, E = spec.topk, logits.shape[1]
+
+    def limited_topk(scores):
+        if spec.router_groups and spec.router_group_topk:
+            T = scores.shape[0]
+            g = spec.router_groups
+            grouped = scores.view(T, g, E // g)
+            gscore = grouped.topk(max(1, k // spec.router_group_topk), dim=-1).values.sum(-1)
+            keep = gscore.topk(spec.router_group_topk, dim=-1).indices
+            mask = torch.zeros(T, g, dtype=torch.bool, device=scores.device).scatter_(1, keep, True)
+            scores = scores.masked_fill(~mask.unsqueeze(-1).expand(T, g, E // g).reshape(T, E), float("-inf"))
+        return scores.topk(k, dim=-1)
+
+    if spec.router_score == "softmax":
+        if spec.router_pre_softmax:
+            scores = torch.softmax(logits, dim=-1)
+            probs, idx = limited_topk(scores)
+        else:
+            vals, idx = limited_topk(logits)
+            probs = torch.softmax(vals, dim=-1)
+    else:
+        scores = torch.sigmoid(logits)
+        sel = scores + expert_bias if expert_bias is not None else scores
+        _, idx = limited_topk(sel)
+        probs = scores.gather(1, idx)
+        if k > 1:
+            probs = probs / (probs.sum(-1, keepdim=True) + 1e-20)
+    if spec.router_scaling:
+        probs = probs * spec.router_scaling
+    return probs, idx
+
+
+def apply_capacity(probs, idx, E: int, capacity: int, policy: str):
+    """Drop assignments beyond ``capacity`` per expert; dropped slots get probability 0 and index -1."""
+    T, k = idx.shape
+    flat_e = idx.reshape(-1)
+    if policy == "probs":
+        order = torch.argsort(probs.reshape(-1), descending=True, stable=True)
+    else:
+        order = torch.arange(T * k, device=idx.device)
+    e_sorted = flat_e[order]
+    onehot = torch.nn.functional.one_hot(e_sorted, E)
+    rank_in_e = (onehot.cumsum(0) - 1).gather(1, e_sorted[:, None])[:, 0]
+    keep_sorted = rank_in_e < capacity
+    keep = torch.zeros(T * k, dtype=torch.bool, device=idx.device)
+    keep[order] = keep_sorted
+    keep = keep.view(T, k)
+    return probs * keep, torch.where(keep, idx, torch.full_like(idx, -1))
+
+
+def switch_aux_loss(logits, idx, E, k, coeff, group=None):
+    """``sum_e mean_prob_e * fraction_e * E * coeff`` with counts summed over the sequence-partition group."""
+    T = logits.shape[0]
+    scores = torch.softmax(logits, dim=-1)
+    counts = torch.zeros(E, dtype=torch.float32, device=logits.device)
+    valid = idx.reshape(-1)
+    valid = valid[valid >= 0]
+    counts.index_add_(0, valid, torch.ones_like(valid, dtype=torch.float32))
+    total_T = T
+    if group is not None and group.size > 1 and group.group is not None:
+        dist.all_reduce(counts, group=group.group)
+        total_T = T * group.size
+    agg = scores.sum(0)
+    return (agg * counts).sum() * (E * coeff / (k * total_T * T))
+
+
+def z_loss(logits, coeff):
+    return torch.logsumexp(logits, dim=-1).pow(2).mean() * coeff
+
+
+class GalvatronMoERouter(nn.Module):
+    def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str):
+        super().__init__()
+        self.spec, self.ctx, self.name = spec, ctx, name
+        self.router = nn.Module()
+        self.router.weight = _param((spec.experts, spec.hidden), torch.float32, device)
+        self.router.weight.tp_replicated = True
+        if spec.router_expert_bias:
+            self.router.register_buffer("expert_bias", torch.zeros(spec.experts, device=device))
+            self.router.register_buffer("local_tokens_per_expert", torch.zeros(spec.experts, device=device))
+
+    def reset_parameters(self, seed=1234, full_init=False):
+        init_normal_sharded_(self.router.weight, self.spec.init_std, (self.spec.experts, self.spec.hidden), None, 0, 1,
+                             seed, self.name + ".router.weight", full_init)
+
+    def forward(self, x2d: torch.Tensor):
+        """x2d [T, H] -> (probs [T, k] fp32, idx [T, k] int64 with -1 for dropped, x2d possibly carrying aux losses)."""
+        s = self.spec
+        xin = x2d
+        if s.jitter_eps and self.training:
+            noise = torch.empty_like(xin).uniform_(1.0 - s.jitter_eps, 1.0 + s.jitter_eps)
+            xin = xin * noise
+        dt = torch.float64 if s.router_dtype == "fp64" else torch.float32
+        logits = torch.nn.functional.linear(xin.to(dt), self.router.weight.to(dt)).float()
+        if s.z_loss_coeff and self.training:
+            logits = _AuxLossScaler.apply(logits, z_loss(logits, s.z_loss_coeff))
+        bias = getattr(self.router, "expert_bias", None)
+        probs, idx = topk_routing(logits, s, bias)
+        if s.capacity_factor is not None:
+            cap = math.ceil(x2d.shape[0] * s.topk / s.experts * s.capacity_factor)
+            probs, idx = apply_capacity(probs, idx, s.experts, cap, s.drop_policy)
+        if s.aux_loss_coeff and s.load_balancing in ("aux_loss", "seq_aux_loss") and self.training:
+            grp = self.ctx.tp if self.ctx.tp_size > 1 else (self.ctx.sp if self.ctx.sp_size > 1 else None)
+            probs = _AuxLossScaler.apply(probs, switch_aux_loss(logits, idx, s.experts, s.topk, s.aux_loss_coeff, grp))
+        if bias is not None:
+            with torch.no_grad():
+                v = idx.reshape(-1)
+                self.router.local_tokens_per_expert.index_add_(0, v[v >= 0], torch.ones_like(v[v >= 0], dtype=torch.float32))
+        return probs, idx
+
+
+# --------------------------------------------------------------------------------------------
+# experts
+# --------------------------------------------------------------------------------------------
+class _GroupedLinear(torch.autograd.Function):
+    """Per-segment ``y = x @ w[g].T`` on the grouped tcgen05 GEMM; weight gradients go to ``main_grad``."""
+
+    @staticmethod
+    def forward(ctx, x, w, row_start):
+        ctx.save_for_backward(x, w, row_start)
+        return ops.grouped_gemm(x, w, row_start)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w, row_start = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = ops.grouped_gemm(dy, w, row_start, b_mn=True)
+        mg = getattr(w, "main_grad", None)
+        if mg is not None:
+            fresh = getattr(w, "mg_fresh", False)
+            ops.grouped_wgrad(dy, x, row_start, mg, accumulate=not fresh)
+            w.mg_fresh = False
+            return dx, None, None
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        ops.grouped_wgrad(dy, x, row_start, dw, accumulate=False)
+        return dx, dw.to(w.dtype), None
+
+
+def grouped_linear(x, w, row_start):
+    if not x.is_cuda:
+        rs = row_start.tolist()
+        outs = [torch.nn.functional.linear(x[rs[g]:rs[g + 1]], w[g]) for g in range(w.shape[0])]
+        pad = x.new_zeros((x.shape[0] - rs[-1], w.shape[1]))
+        return torch.cat(outs + [pad], dim=0)
+    return _GroupedLinear.apply(x, w, row_start)
+
+
+class ExpertMLP(nn.Module):
+    def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str):
+        super().__init__()
+        self.spec, self.ctx, self.name = spec, ctx, name
+        if spec.experts % ctx.ep_size:
+            raise ValueError("experts (%d) must be divisible by ep=%d" % (spec.experts, ctx.ep_size))
+        self.E_loc = spec.experts // ctx.ep_size
+        t = ctx.etp_size
+        self.Fl = spec.moe_ffn // t
+        mult = 2 if spec.gated else 1
+        self.linear_fc1 = nn.Module()
+        self.linear_fc1.weight = _param((self.E_loc, mult * self.Fl, spec.hidden), spec.dtype, device)
+        self.linear_fc2 = nn.Module()
+        self.linear_fc2.weight = _param((self.E_loc, spec.hidden, self.Fl), spec.dtype, device)
+
+    def reset_parameters(self, seed, full_init):
+        s, c = self.spec, self.ctx
+        for j in range(self.E_loc):
+            e = c.ep_rank * self.E_loc + j
+            base = "%s.local_experts.%d" % (self.name, e)
+            w1 = self.linear_fc1.weight[j]
+            if s.gated:
+                init_normal_sharded_(w1[: self.Fl], s.init_std, (s.moe_ffn, s.hidden), 0, c.etp_rank, c.etp_size, seed,
+                                     base + ".gate", full_init)
+                init_normal_sharded_(w1[self.Fl:], s.init_std, (s.moe_ffn, s.hidden), 0, c.etp_rank, c.etp_size, seed,
+                                     base + ".up", full_init)
+            else:
+                init_normal_sharded_(w1, s.init_std, (s.moe_ffn, s.hidden), 0, c.etp_rank, c.etp_size, seed,
+                                     base + ".fc1", full_init)
+            init_normal_sharded_(self.linear_fc2.weight[j], s.init_std, (s.hidden, s.moe_ffn), 1, c.etp_rank, c.etp_size,
+                                 seed, base + ".fc2", full_init)
+
+    def forward(self, x: torch.Tensor, row_start: torch.Tensor) -> torch.Tensor:
+        y = grouped_linear(x, self.linear_fc1.weight, row_start)
+        a = ops.activation(y, self.spec.activation)
+        return grouped_linear(a, self.linear_fc2.weight, row_start)
+
+
+# --------------------------------------------------------------------------------------------
+# dispatch
+# --------------------------------------------------------------------------------------------
+def _aligned_starts(counts: torch.Tensor) -> Tuple[torch.Tensor, int]:
+    """Segment starts (int32 [G+1]) with every start a multiple of SEG_ALIGN; needs the host total."""
+    padded = (counts + SEG_ALIGN - 1) // SEG_ALIGN * SEG_ALIGN
+    starts = torch.zeros(counts.numel() + 1, dtype=torch.int64, device=counts.device)
+    starts[1:] = padded.cumsum(0)
+    return starts, int(starts[-1].item())
+
+
+class GalvatronMoEMLP(nn.Module):
+    """Token dispatch + experts + combine."""
+
+    def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str):
+        super().__init__()
+        self.spec, self.ctx = spec, ctx
+        self.experts = ExpertMLP(spec, ctx, device, name + ".experts")
+
+    def reset_parameters(self, seed=1234, full_init=False):
+        self.experts.reset_parameters(seed, full_init)
+
+    def forward(self, x2d: torch.Tensor, probs: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        s, c = self.spec, self.ctx
+        T, H = x2d.shape
+        k, E, ep, E_loc = s.topk, s.experts, c.ep_size, self.experts.E_loc
+        flat_e = idx.reshape(-1)
+        valid = flat_e >= 0
+        sort_key = torch.where(valid, flat_e, torch.full_like(flat_e, E))
+        order = torch.argsort(sort_key, stable=True)               # expert-major, token-minor
+        n_valid = int(valid.sum().item()) if s.capacity_factor is not None else T * k
+        order = order[:n_valid]
+        tok_of = order // k
+        e_sorted = flat_e[order]
+        counts = torch.bincount(e_sorted, minlength=E)              # tokens per (global) expert from this rank
+        send = x2d.index_select(0, tok_of)                           # [n_valid, H]
+        if ep > 1:
+            all_counts = mp.all_gather_first(counts, c.ep).view(ep, E)
+            mine = all_counts[:, c.ep_rank * E_loc:(c.ep_rank + 1) * E_loc]          # [src, local expert]
+            in_splits = counts.view(ep, E_loc).sum(1).tolist()
+            out_splits = mine.sum(1).tolist()
+            recv = mp.all_to_all(send, c.ep, out_splits, in_splits)                  # [src][local expert] order
+        else:
+            mine = counts.view(1, E_loc)
+            recv = send
+        # [src][local expert] -> [local expert][src], into aligned zero-padded segments
+        per_expert = mine.sum(0)
+        starts, total = _aligned_starts(per_expert)
+        seg = mine.t().contiguous()                                   # [local expert, src]
+        within = torch.cumsum(seg, dim=1) - seg                       # offset of each src block inside its expert
+        src_block_start = (torch.cumsum(mine.reshape(-1), 0) - mine.reshape(-1)).view(mine.shape)  # in recv order
+        n_src = mine.shape[0]
+        rows = torch.arange(recv.shape[0], device=recv.device)
+        blk_ends = torch.cumsum(mine.reshape(-1), 0)
+        blk = torch.bucketize(rows, blk_ends, right=True)             # which (src, expert) block a row is in
+        b_src, b_exp = blk // E_loc, blk % E_loc
+        dest = starts[b_exp] + within[b_exp, b_src] + (rows - src_block_start.reshape(-1)[blk])
+        buf = recv.new_zeros((max(total, SEG_ALIGN), H)).index_copy(0, dest, recv)
+        row_start = starts.to(torch.int32)
+        if c.etp_size > 1:
+            raise NotImplementedError("expert tensor parallelism > 1 is planned; use etp = 1")
+        out_buf = self.experts(buf, row_start)
+        back = out_buf.index_select(0, dest)
+        if ep > 1:
+            back = mp.all_to_all(back, c.ep, in_splits, out_splits)
+        w = probs.reshape(-1)[order].to(torch.float32)
+        out = torch.zeros((T, H), dtype=torch.float32, device=x2d.device)
+        out = out.index_add(0, tok_of, back.float() * w[:, None])
+        return out.to(x2d.dtype)
+
+
+# --------------------------------------------------------------------------------------------
+# layer + wrapping
+# --------------------------------------------------------------------------------------------
+class GalvatronMoEAttention(nn.Module):
+    def __init__(self, spec, ctx, device, name):
+        super().__init__()
+        self.attn = GalvatronAttention(spec, ctx, device, name + ".attn")
+        self.pre_router_norm = Norm(spec, device)
+
+    def reset_parameters(self, seed=1234, full_init=False):
+        self.attn.reset_parameters(seed, full_init)
+        self.pre_router_norm.reset_parameters()
+
+    def forward(self, x):
+        a = self.attn(x)
+        n, h = self.pre_router_norm(a, residual=x)
+        return n, h
+
+
+class GalvatronMoEDecoderLayer(nn.Module):
+    def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str):
+        super().__init__()
+        self.spec, self.ctx = spec, ctx
+        self.attention = GalvatronMoEAttention(spec, ctx, device, name)
+        self.router = GalvatronMoERouter(spec, ctx, device, name)
+        self.mlp = GalvatronMoEMLP(spec, ctx, device, name + ".mlp")
+
+    def reset_parameters(self, seed=1234, full_init=False):
+        self.attention.reset_parameters(seed, full_init)
+        self.router.reset_parameters(seed, full_init)
+        self.mlp.reset_parameters(seed, full_init)
+
+
+class MoELayerRunner(nn.Module):
+    """Runs the three units of an MoE layer in order (each between its own ZeRO hooks)."""
+
+    def __init__(self, attention: UnitWrapper, router: UnitWrapper, mlp: UnitWrapper, units: List[ShardedUnit]):
+        super().__init__()
+        self.attention, self.router, self.mlp = attention, router, mlp
+        self.sharded_units = units
+        self.wrappers = [attention, router, mlp]
+
+    @property
+    def inner(self):
+        return self
+
+    def finish_backward(self):
+        for w in self.wrappers:
+            w.finish_backward()
+
+    def forward(self, x):
+        n, h = self.attention(x)
+        S, B, H = n.shape
+        n2 = n.reshape(S * B, H)
+        probs, idx = self.router(n2)
+        y = self.mlp(n2, probs, idx)
+        return ops_add(h, y.view(S, B, H))
+
+
+def wrap_moe_units(layer: GalvatronMoEDecoderLayer, lp, ctx: LayerCtx, plan, reduce_in_fp32: bool):
+    dp_size = plan.dp_size(lp)
+    defer = plan.async_grad_reduce
+    u_attn = ShardedUnit(layer.attention, lp.name + "_attention", ctx.sdp, dp_size, lp.dp_type, reduce_in_fp32, tp=ctx.tp,
+                         defer_sync=defer)
+    u_router = ShardedUnit(layer.router, lp.name + "_router", ctx.sdp, dp_size, "ddp", reduce_in_fp32, tp=ctx.tp,
+                           defer_sync=defer)
+    u_mlp = ShardedUnit(layer.mlp, lp.name + "_mlp", ctx.dp_of_ep, dp_size, lp.dp_type, reduce_in_fp32, tp=None,
+                        defer_sync=defer)
+    return MoELayerRunner(UnitWrapper(layer.attention, u_attn, lp.checkpoint), UnitWrapper(layer.router, u_router),
+                          UnitWrapper(layer.mlp, u_mlp, lp.checkpoint), [u_attn, u_router, u_mlp])

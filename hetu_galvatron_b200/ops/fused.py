@@ -63,7 +63,8 @@ class _Norm(torch.autograd.Function):
         dw = mgw if mgw is not None else torch.empty(H, dtype=torch.float32, device=h.device)
         db = None
         if ctx.has_bias:
-            db = torch.empty(H, dtype=torch.float32, device=h.device)
+            # zero-filled: the kernel's accumulate switch is shared with dw (which may add into main_grad)
+            db = torch.zeros(H, dtype=torch.float32, device=h.device)
         rc = lib.hg_norm_bwd(dy.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(),
                              0 if ctx.rms else mean.data_ptr(), _lib.ptr(dres), dx.data_ptr(), dw.data_ptr(),
                              _lib.ptr(db), partial.data_ptr(), parts, rows, H, int(ctx.rms),

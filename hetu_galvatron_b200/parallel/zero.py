@@ -357,7 +357,15 @@ class UnitWrapper(nn.Module):
             e.gather()
         grad_mode = torch.is_grad_enabled()
         if grad_mode:
-            args = tuple(_Boundary.apply(a, self._post_backward) if torch.is_tensor(a) and a.requires_grad else a
+            # the unit's backward is over once the gradient has left through *every* differentiable input
+            pending = [sum(1 for a in args if torch.is_tensor(a) and a.requires_grad)]
+
+            def _one_input_done():
+                pending[0] -= 1
+                if pending[0] <= 0:
+                    self._post_backward()
+
+            args = tuple(_Boundary.apply(a, _one_input_done) if torch.is_tensor(a) and a.requires_grad else a
                          for a in args)
         if self.checkpoint and grad_mode:
             out = _torch_checkpoint(self.inner, *args, use_reentrant=False, **kwargs)
