@@ -73,7 +73,7 @@ GalvatronParallelArgs = _build("GalvatronParallelArgs", {
     "sdp": (Literal[0, 1], 0),
     "default_dp_type": (Literal["ddp", "zero2", "zero3"], "ddp"),
     "pipeline_type": (Literal["gpipe", "pipedream_flush"], "gpipe"),
-    "galvatron_config_path": (O[str], None),
+    "galvatron_config_path": (Any, None),  # path of a strategy JSON, or the parsed dict
     "vocab_sdp": (Literal[0, 1], 0),
     "vocab_tp": (int, 1, dict(ge=1)),
     "vocab_cp": (int, 1, dict(ge=1)),

@@ -124,7 +124,9 @@ def build_stage(spec: ModelSpec, plan: HybridPlan, groups: ModelGroups, device, 
                 stage.has_embedding = True
             if lp.kind == "lm_head":
                 stage.has_head = True
-            dp_size = plan.dp_size(lp)
+            # every gradient is a sum over samples weighted by 1/(samples per *loss* replica): one divisor for
+            # all units, the data-parallel degree of the vocab (loss) layers
+            dp_size = plan.dp_size(plan.layers[0])
             if lp.kind == "moe_decoder":
                 from .moe import wrap_moe_units
 
@@ -132,6 +134,8 @@ def build_stage(spec: ModelSpec, plan: HybridPlan, groups: ModelGroups, device, 
             else:
                 su = ShardedUnit(mod, lp.name, ctx.sdp, dp_size, lp.dp_type, reduce_in_fp32, tp=ctx.tp,
                                  defer_sync=plan.async_grad_reduce)
+                if lp.kind == "lm_head" and spec.tied and plan.pp_deg > 1:
+                    su.count_in_norm = False  # the first stage's copy of the tied weight carries the norm
                 stage.sharded.append(su)
                 unit = UnitWrapper(mod, su, checkpoint=lp.checkpoint)
                 if tied is not None:

@@ -379,7 +379,7 @@ class MoELayerRunner(nn.Module):
 
 
 def wrap_moe_units(layer: GalvatronMoEDecoderLayer, lp, ctx: LayerCtx, plan, reduce_in_fp32: bool):
-    dp_size = plan.dp_size(lp)
+    dp_size = plan.dp_size(plan.layers[0])
     defer = plan.async_grad_reduce
     u_attn = ShardedUnit(layer.attention, lp.name + "_attention", ctx.sdp, dp_size, lp.dp_type, reduce_in_fp32, tp=ctx.tp,
                          defer_sync=defer)

@@ -302,7 +302,7 @@ class _CrossEntropy(torch.autograd.Function):
                                      _lib.stream()), "hg_xent_stats")
         _lib.count_launch()
         lmax, lsum, pred = stats[0], stats[1], stats[2]
-        if group is not None and dist.get_world_size(group) > 1:
+        if group is not None:
             gmax = lmax.clone()
             dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
             packed = torch.stack([lsum * torch.exp(lmax - gmax), pred])
@@ -334,10 +334,13 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, v0: int = 0, grou
     vocab-parallel ``group`` the shard statistics are combined by one MAX and one SUM all-reduce.
     The backward overwrites ``logits`` in place (the tensor must not be used afterwards)."""
     targets = targets.reshape(-1)
+    from ..parallel.mappings import _pg
+
+    group, n_ranks, _ = _pg(group)  # CommGroup / ProcessGroup / None -> ProcessGroup or None (single rank)
     if not logits.is_cuda:
         lf = logits.float()
         lmax = lf.max(-1).values.detach()  # the shift cancels analytically: it must not carry a gradient
-        if group is not None and dist.get_world_size(group) > 1:
+        if group is not None:
             gmax = lmax.clone()
             dist.all_reduce(gmax, op=dist.ReduceOp.MAX, group=group)
         else:
@@ -348,7 +351,7 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, v0: int = 0, grou
         pred = torch.where(inside, lf.gather(1, local.clamp(0, logits.shape[1] - 1)[:, None])[:, 0],
                            torch.zeros_like(gmax))
         ssum = ex.sum(-1)
-        if group is not None and dist.get_world_size(group) > 1:
+        if group is not None:
             from ..parallel.mappings import all_reduce_sum
 
             packed = all_reduce_sum(torch.stack([ssum, pred]), group)

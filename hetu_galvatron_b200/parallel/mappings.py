@@ -84,13 +84,26 @@ def all_to_all_first(t: torch.Tensor, group, out_splits: Optional[List[int]] = N
     else:
         out = torch.empty((sum(out_splits),) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
     if t.device.type == "cpu":
+        # gloo has no all-to-all: pairwise isend / irecv between the members of the group
         ins = list(t.split(in_splits, 0)) if in_splits is not None else list(t.chunk(n, 0))
         outs = list(out.split(out_splits, 0)) if out_splits is not None else list(out.chunk(n, 0))
-        ins = [x.contiguous() for x in ins]
-        outs_c = [torch.empty_like(x) for x in outs]
-        dist.all_to_all(outs_c, ins, group=pg)
-        for dst, src in zip(outs, outs_c):
-            dst.copy_(src)
+        me = dist.get_rank(pg)
+        outs[me].copy_(ins[me])
+        reqs, keep = [], []
+        for peer in range(n):
+            if peer == me:
+                continue
+            g_peer = dist.get_global_rank(pg, peer)
+            if outs[peer].numel():
+                buf = torch.empty_like(outs[peer])
+                keep.append((outs[peer], buf))
+                reqs.append(dist.irecv(buf, src=g_peer))
+            if ins[peer].numel():
+                reqs.append(dist.isend(ins[peer].contiguous(), dst=g_peer))
+        for r in reqs:
+            r.wait()
+        for dst, buf in keep:
+            dst.copy_(buf)
     else:
         dist.all_to_all_single(out, t, output_split_sizes=out_splits, input_split_sizes=in_splits, group=pg)
     return out

@@ -87,6 +87,7 @@ class ShardedUnit:
         self.step_count = 0
         self._reduced = False
         self._bwd_pending = False
+        self.count_in_norm = True  # False for the second copy of a weight tied across pipeline stages
         if params:
             self._materialise()
 
@@ -187,13 +188,18 @@ class ShardedUnit:
                     p.main_grad.add_(p.grad)
                 p.grad = None
 
-    def _reduce_now(self) -> torch.Tensor:
-        """Sum the current ``main_grad`` over the sdp group; returns the buffer holding this rank's part."""
+    def prepare_grads(self):
+        """Make ``main_grad`` complete for the micro-batches seen so far: fold autograd ``.grad`` tensors in
+        and zero the parameters that received nothing."""
         self._finish_accumulation()
         for p in self.params:
             if getattr(p, "mg_fresh", False):  # received nothing since the last reset
                 p.main_grad.zero_()
                 p.mg_fresh = False
+
+    def _reduce_now(self) -> torch.Tensor:
+        """Sum the current ``main_grad`` over the sdp group; returns the buffer holding this rank's part."""
+        self.prepare_grads()
         if self.tp_n > 1 and self.replicated_numel > 0:
             # norm weights / replicated biases saw only this rank's S/t tokens: sum over the tp group
             dist.all_reduce(self.main_grad[: self.replicated_numel], group=self.tp_pg)
@@ -245,6 +251,8 @@ class ShardedUnit:
     def grad_sumsq(self, out: torch.Tensor):
         """Add this rank's share of the squared gradient norm to ``out[0]`` so that a SUM over all ranks
         counts every parameter element exactly once."""
+        if not self.count_in_norm:
+            return
         g = self.grad_shard
         inv = 1.0 / (self.dp_size * self.dp_size)  # gradients are still dp-sums here
         rep = self.n if self.dp_type == "ddp" else 1  # identical copies held by the sdp group

@@ -134,6 +134,7 @@ class GalvatronModel:
         for lp, u in zip(self.model.plans, self.model.units):
             if lp.kind in ("embedding", "lm_head"):
                 w = u.inner.embed_tokens.weight if lp.kind == "embedding" else u.inner.lm_head.weight
+                w._hg_unit.prepare_grads()
                 dist.all_reduce(w.main_grad, group=g.group)
 
 

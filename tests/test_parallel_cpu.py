@@ -1,0 +1,137 @@
+"""Every parallelism path on CPU ranks (gloo, fp32): loss parity against the single-process model.
+
+DP / ZeRO-2 / ZeRO-3 (deferred and immediate reduction), Megatron TP+SP, vocab TP, Ulysses SP (incl. fewer kv
+heads than ranks), zig-zag context parallelism, GPipe and 1F1B-flush pipelines, layer-wise heterogeneous
+strategies with resharding, tied embeddings across pipeline stages, activation checkpointing, MoE with
+expert parallelism."""
+import json
+import os
+import sys
+
+import pytest
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from tests.dist_utils import run_distributed, worker_main  # noqa: E402
+
+STEPS = 3
+GBSZ, SEQ, VOCAB = 8, 128, 1024
+
+
+def make_args(cfg):
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+
+    model = dict(model_size="llama-test", hidden_size=256, num_layers=4, num_attention_heads=4, ffn_hidden_size=688,
+                 vocab_size=VOCAB, normalization="RMSNorm", activation_func="torch.nn.functional.silu",
+                 gated_linear_unit=True, make_vocab_size_divisible_by=8)
+    model.update(cfg.get("model", {}))
+    parallel = dict(mixed_precision="fp32")
+    parallel.update(cfg.get("parallel", {}))
+    train = dict(seq_length=SEQ, global_batch_size=GBSZ, chunks=cfg.get("chunks", 1), lr=1e-3, seed=1234)
+    return GalvatronRuntimeArgs(parallel=parallel, model=model, train=train)
+
+
+def train(cfg):
+    import torch
+    import torch.distributed as dist
+
+    from hetu_galvatron_b200.runtime.engine import build_model
+    from hetu_galvatron_b200.runtime.optimizer import ShardedAdamW
+
+    torch.manual_seed(0)
+    args = make_args(cfg)
+    model = build_model(args, device=torch.device("cpu"), full_init=True)
+    opt = ShardedAdamW(model.sharded_units, lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01, clip_grad=1.0)
+    g = torch.Generator().manual_seed(7)
+    tok = torch.randint(0, VOCAB, (GBSZ, SEQ + 1), generator=g)
+    B = model.local_batch_size()
+    d = model.vocab_ctx.dp.rank if model.vocab_ctx.dp is not None else 0
+    mine = tok[d * B:(d + 1) * B]
+    out = []
+    for it in range(STEPS):
+        opt.zero_grad()
+        loss = model.forward_backward(mine[:, :-1], it, labels=mine[:, 1:])
+        model.sync_tied_embedding_grads()
+        opt.step()
+        val = float(loss) if loss is not None else None
+        out.append([val, opt.grad_norm()])
+    return out
+
+
+REGISTRY = {"train": train}
+
+_baselines = {}
+
+
+def baseline(key, cfg):
+    if key not in _baselines:
+        _baselines[key] = run_distributed(__file__, "train", 1, cfg)[0]
+    return _baselines[key]
+
+
+def check(world, cfg, base_cfg=None, key="dense", rtol=2e-4, norm_rtol=2e-3):
+    ref = baseline(key, base_cfg or {"chunks": 1})
+    res = run_distributed(__file__, "train", world, cfg)
+    seen = False
+    for r in res:
+        for (l, n), (l0, n0) in zip(r, ref):
+            if l is not None:
+                seen = True
+                assert abs(l - l0) / abs(l0) < rtol, (cfg, res, ref)
+            assert abs(n - n0) / abs(n0) < norm_rtol, (cfg, res, ref)
+    assert seen
+
+
+@pytest.mark.parametrize("dp_type,async_reduce,chunks", [("ddp", True, 1), ("zero2", True, 2), ("zero3", True, 2),
+                                                         ("zero3", False, 2), ("zero2", False, 1)])
+def test_data_parallel_and_zero(dp_type, async_reduce, chunks):
+    check(2, {"chunks": chunks, "parallel": {"default_dp_type": dp_type, "sdp": 1 if dp_type == "zero3" else 0,
+                                             "async_grad_reduce": async_reduce}})
+
+
+def test_tensor_parallel_with_sequence_parallel_and_vocab_tp():
+    check(2, {"parallel": {"global_tp_deg": 2, "vocab_tp": 2}})
+
+
+def test_tp2_dp2_zero3_checkpoint():
+    check(4, {"chunks": 2, "parallel": {"global_tp_deg": 2, "vocab_tp": 1, "sdp": 1, "global_checkpoint": 1}})
+
+
+@pytest.mark.parametrize("kv", [None, 1])
+def test_ulysses(kv):
+    model = {"num_query_groups": kv} if kv else {}
+    base = {"chunks": 1, "model": model}
+    check(2, {"parallel": {"global_tp_deg": 2, "use_ulysses": True, "vocab_tp": 2}, "model": model}, base,
+          key="kv%s" % kv)
+
+
+def test_context_parallel_zigzag():
+    check(2, {"parallel": {"global_cp_deg": 2, "vocab_cp": 2}})
+
+
+@pytest.mark.parametrize("ptype,chunks", [("gpipe", 2), ("pipedream_flush", 4)])
+def test_pipeline(ptype, chunks):
+    check(2, {"chunks": chunks, "parallel": {"pp_deg": 2, "pipeline_type": ptype}})
+
+
+def test_pipeline_tied_embeddings_tp():
+    model = {"untie_embeddings_and_output_weights": False}
+    check(4, {"chunks": 2, "parallel": {"pp_deg": 2, "pipeline_type": "pipedream_flush", "global_tp_deg": 2,
+                                        "vocab_tp": 2}, "model": model}, {"chunks": 1, "model": model}, key="tied")
+
+
+def test_layerwise_heterogeneous_strategy():
+    strategy = {"pp_deg": 1, "tp_sizes_enc": "1,2,4,2", "tp_consecutive_flags": "1,1,1,1", "dp_types_enc": "0,1,0,1",
+                "use_sp": "0,0,0,1", "checkpoint": "0,1,0,0", "global_bsz": GBSZ, "chunks": 2, "pp_division": "4",
+                "pipeline_type": "gpipe", "default_dp_type": "zero2", "vtp": 2, "vsp": 0, "embed_sdp": 1}
+    check(4, {"parallel": {"galvatron_config_path": strategy}})
+
+
+def test_moe_expert_parallel():
+    model = {"num_moe_experts": 4, "moe_ffn_hidden_size": 256, "moe_router_topk": 2, "is_moe_model": True,
+             "moe_token_dispatcher_type": "alltoall", "moe_aux_loss_coeff": 1e-2}
+    base = {"chunks": 1, "model": model}
+    check(2, {"parallel": {"global_ep_deg": 2}, "model": model}, base, key="moe", rtol=1e-3, norm_rtol=2e-2)
+
+
+if __name__ == "__main__":
+    worker_main(REGISTRY)
