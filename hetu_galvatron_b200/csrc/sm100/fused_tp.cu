@@ -1,0 +1,411 @@
+// Fused tensor-parallel kernels over NVLink peer memory (one launch each, tcgen05 tiles + P2P traffic in the
+// same kernel):
+//
+//   all-gather -> column GEMM   : every rank's activation slab sits in its symmetric staging buffer; the
+//                                 communication warps of the persistent GEMM CTAs pull the peers' slabs
+//                                 (plain 16-byte peer loads over NVSwitch) into this GPU's own gathered buffer,
+//                                 block by block, and publish a flag per 128-row block; the TMA producer waits
+//                                 for the flag of the block a tile needs.  Tiles of the local slab run first,
+//                                 so the transfer hides behind the math.  TMA only ever reads local memory.
+//   row GEMM -> reduce-scatter  : each output tile is a partial sum that belongs to the rank owning its row
+//                                 slab; the epilogue stores it (plain peer stores) into the owner's staging
+//                                 area and raises the tile's flag; after its last tile every CTA turns to the
+//                                 tiles of its own slab, waits for the t partials and reduces them in fp32.
+//                                 Remote slabs are computed first, the own slab last.
+//
+// Cross-rank hazards are covered by epochs (one per call) and two staging parities; every wait is bounded and
+// reports through the status word.  No cluster-multicast load is used anywhere.
+//
+// Replaces the NCCL all-gather / reduce-scatter + cuBLAS sequences of
+// galvatron/core/runtime/tensor_parallel/layers.py:289-303 (N1), :320-376 (N2, N3), :925-980 and
+// mappings.py:174-214 (N5).
+#include "gemm_core.cuh"
+
+namespace hg {
+namespace fused {
+
+using namespace hg::gemm;
+
+constexpr int kMaxRanks = 8;
+constexpr int kThreads = 256;  // 6 GEMM warps + 2 communication warps
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void comm_bar() { asm volatile("bar.sync 1, 64;" ::: "memory"); }
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+// Bounded poll of a flag (system scope).  Returns false on time-out / abort.
+__device__ __forceinline__ bool wait_flag_sys(const int* flag, int target, int* status, volatile int* abort) {
+  const uint64_t t0 = globaltimer_ns();
+  while (ld_acquire_sys(flag) < target) {
+    if ((abort != nullptr && *abort) || globaltimer_ns() - t0 > kWaitLimitNs) {
+      set_status(status, kTimeoutPeerFlag);
+      return false;
+    }
+    __nanosleep(100);
+  }
+  return true;
+}
+
+// ------------------------------------------------------------------------------------------------
+// all-gather -> GEMM
+// ------------------------------------------------------------------------------------------------
+struct AgParams {
+  const uint4* src[kMaxRanks];   // every rank's staging slab (src[me] is local)
+  int* signal[kMaxRanks];        // signal[p]: rank p's "data ready" slots (int[kMaxRanks]); we write slot `me`
+  int* my_signal;                // our own slots: my_signal[p] >= epoch once rank p's slab may be read
+  uint4* gathered;               // local [t * slab_rows, K] buffer the GEMM reads
+  int* block_ready;              // local flags, one per 128-row block of `gathered`
+  int t, me, epoch;
+  int slab_rows;                 // rows per rank (multiple of 128)
+  int row_vec;                   // uint4 per row (K * 2 / 16)
+};
+
+template <bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p,
+               const AgParams ag) {
+  extern __shared__ uint8_t smem_raw[];
+  SmemLayout s = carve(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    init_barriers(s);
+  }
+  if (warp == 1) {
+    tmem_alloc(s.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s.tmem_base;
+
+  if (warp == 0) {
+    if (lane_id() == 0) producer_loop<false, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);
+  } else if (warp == 1) {
+    if (lane_id() == 0) mma_loop<false, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
+  } else if (warp < 6) {
+    epilogue_loop(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
+  } else {
+    // ---- communication warps: 64 threads --------------------------------------------------------
+    const int tid = threadIdx.x - 6 * 32;
+    if (blockIdx.x == 0 && tid == 0) {
+      // our slab was written by earlier work of this stream: publish it to every peer
+      __threadfence_system();
+      for (int q = 0; q < ag.t; ++q)
+        if (q != ag.me) st_release_sys(ag.signal[q] + ag.me, ag.epoch);
+    }
+    const int blocks_per_slab = ag.slab_rows / BM;
+    const int total_blocks = blocks_per_slab * ag.t;
+    const size_t block_vec = size_t(BM) * ag.row_vec;
+    volatile int* comm_go = s.abort + 1;  // written by comm thread 0 between barriers: a uniform verdict
+    for (int i = blockIdx.x; i < total_blocks; i += gridDim.x) {
+      const int hop = i / blocks_per_slab;              // 0 = our own slab, then the ring of peers
+      const int q = (ag.me + hop) % ag.t;
+      const int j = i - hop * blocks_per_slab;
+      if (tid == 0) {
+        bool ok = !*s.abort;
+        if (ok && q != ag.me) ok = wait_flag_sys(ag.my_signal + q, ag.epoch, p.status, s.abort);
+        if (!ok) *s.abort = 1;
+        *comm_go = ok ? 1 : 0;
+      }
+      comm_bar();
+      if (!*comm_go) break;
+      const uint4* src = ag.src[q] + size_t(j) * block_vec;
+      uint4* dst = ag.gathered + (size_t(q) * blocks_per_slab + j) * block_vec;
+      for (size_t v = tid; v < block_vec; v += 64 * 4) {
+        uint4 a0 = src[v], a1, a2, a3;
+        const bool h1 = v + 64 < block_vec, h2 = v + 128 < block_vec, h3 = v + 192 < block_vec;
+        if (h1) a1 = src[v + 64];
+        if (h2) a2 = src[v + 128];
+        if (h3) a3 = src[v + 192];
+        dst[v] = a0;
+        if (h1) dst[v + 64] = a1;
+        if (h2) dst[v + 128] = a2;
+        if (h3) dst[v + 192] = a3;
+      }
+      __threadfence();
+      comm_bar();
+      if (tid == 0) st_release_gpu(ag.block_ready + q * blocks_per_slab + j, ag.epoch);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// GEMM -> reduce-scatter
+// ------------------------------------------------------------------------------------------------
+struct RsParams {
+  __nv_bfloat16* stage[kMaxRanks];  // stage[d]: rank d's staging area [t][slab_rows][N]; we write block `me`
+  int* flags[kMaxRanks];            // flags[d]: rank d's tile flags [t][tiles_per_slab]; we write row `me`
+  const __nv_bfloat16* my_stage;
+  int* my_flags;
+  __nv_bfloat16* out;               // [slab_rows, N] reduced result (local)
+  int ldo;
+  int t, me, epoch;
+  int slab_rows;
+  int tiles_per_slab;               // (slab_rows / 128) * tiles_n
+};
+
+__device__ __forceinline__ void rs_epilogue_loop(const Params& p, const RsParams& rs, const SmemLayout& s,
+                                                 uint32_t tmem_base, int first_tile, int tile_step, int num_tiles) {
+  const int wq = (threadIdx.x >> 5) & 3;
+  const uint32_t lane_off = uint32_t(wq * 32) << 16;
+  const int etid = threadIdx.x - 64;  // 0..127
+  uint32_t acc = 0, acc_phase = 0;
+  volatile int* epi_go = s.abort + 2;  // written by epilogue thread 0 between barriers: a uniform verdict
+  bool alive = true;
+  for (int tile = first_tile; tile < num_tiles; tile += tile_step) {
+    const TileInfo ti = tile_info(p, tile);
+    const int d = ti.m0 / rs.slab_rows;              // owner of this tile's rows
+    const int mblk = (ti.m0 - d * rs.slab_rows) / BM;
+    if (alive && (*s.abort || !mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort))) {
+      *s.abort = 1;
+      alive = false;
+    }
+    if (alive) {
+      tc_fence_after();
+      Params q = p;
+      q.C = rs.stage[d] + size_t(rs.me) * rs.slab_rows * p.N;
+      q.ldc = p.N;
+      q.M = rs.slab_rows;
+      const int row = mblk * BM + wq * 32 + lane_id();
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; c += 2) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tmem_base + lane_off + acc * BN + c * 32, r0);
+        tmem_ld32(tmem_base + lane_off + acc * BN + (c + 1) * 32, r1);
+        tmem_ld_wait();
+        if (ti.n0 + c * 32 < p.N) store_row_chunk(q, row, ti.n0 + c * 32, r0);
+        if (ti.n0 + (c + 1) * 32 < p.N) store_row_chunk(q, row, ti.n0 + (c + 1) * 32, r1);
+      }
+      tc_fence_before();
+      mbar_arrive(&s.tmem_empty[acc]);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      __threadfence_system();
+    }
+    // the four epilogue warps agree on going on before the tile is published to its owner
+    epi_bar();
+    if (etid == 0) *epi_go = *s.abort ? 0 : 1;
+    epi_bar();
+    if (!*epi_go) break;
+    if (etid == 0) st_release_sys(rs.flags[d] + rs.me * rs.tiles_per_slab + mblk * p.tiles_n + ti.n0 / BN, rs.epoch);
+  }
+}
+
+// Reduce the t partials of the tiles of our own slab (fp32 accumulation, bf16 result).
+__device__ __forceinline__ void rs_reduce_phase(const Params& p, const RsParams& rs, const SmemLayout& s) {
+  const int etid = threadIdx.x - 64;
+  volatile int* epi_go = s.abort + 2;
+  const size_t slab_elems = size_t(rs.slab_rows) * p.N;
+  for (int tile = blockIdx.x; tile < rs.tiles_per_slab; tile += gridDim.x) {
+    const int mblk = tile / p.tiles_n, tn = tile - mblk * p.tiles_n;
+    if (etid < rs.t && !wait_flag_sys(rs.my_flags + etid * rs.tiles_per_slab + tile, rs.epoch, p.status, s.abort))
+      *s.abort = 1;
+    epi_bar();
+    if (etid == 0) *epi_go = *s.abort ? 0 : 1;
+    epi_bar();
+    if (!*epi_go) return;
+    const int n0 = tn * BN;
+    const int cols = min(BN, p.N - n0);
+    const int vec_per_row = cols >> 3;               // 8 bf16 per 16 bytes (N is a multiple of 8)
+    for (int v = etid; v < BM * vec_per_row; v += 128) {
+      const int r = v / vec_per_row, c8 = v - r * vec_per_row;
+      const size_t off = size_t(mblk * BM + r) * p.N + n0 + c8 * 8;
+      float accv[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) accv[i] = 0.f;
+      for (int src = 0; src < rs.t; ++src) {
+        const uint4 u = *reinterpret_cast<const uint4*>(rs.my_stage + size_t(src) * slab_elems + off);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __bfloat1622float2(h[i]);
+          accv[2 * i] += f.x;
+          accv[2 * i + 1] += f.y;
+        }
+      }
+      uint4 o;
+      o.x = pack_bf16(accv[0], accv[1]);
+      o.y = pack_bf16(accv[2], accv[3]);
+      o.z = pack_bf16(accv[4], accv[5]);
+      o.w = pack_bf16(accv[6], accv[7]);
+      *reinterpret_cast<uint4*>(rs.out + size_t(mblk * BM + r) * rs.ldo + n0 + c8 * 8) = o;
+    }
+  }
+}
+
+template <bool B_MN>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p,
+               const RsParams rs) {
+  extern __shared__ uint8_t smem_raw[];
+  SmemLayout s = carve(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    init_barriers(s);
+  }
+  if (warp == 1) {
+    tmem_alloc(s.tmem_base, TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *s.tmem_base;
+
+  if (warp == 0) {
+    if (lane_id() == 0) producer_loop<false, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);
+  } else if (warp == 1) {
+    if (lane_id() == 0) mma_loop<false, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
+  } else if (warp < 6) {
+    rs_epilogue_loop(p, rs, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
+    if (!*s.abort) rs_reduce_phase(p, rs, s);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace fused
+}  // namespace hg
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+using namespace hg::gemm;
+using namespace hg::fused;
+
+namespace {
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+  }
+  return n;
+}
+template <typename K>
+int ensure_smem(K k, bool& done) {
+  if (!done) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    if (e != cudaSuccess) return int(e);
+    done = true;
+  }
+  return 0;
+}
+}  // namespace
+
+extern "C" {
+
+// C[t*slab_rows, N] = gather(x)[t*slab_rows, K] x op(B).
+//   src_ptrs[t]    : device addresses of every rank's staging slab [slab_rows, K] (peer-mapped)
+//   signal_ptrs[t] : device addresses of every rank's int[8] "data ready" slots
+//   gathered       : local [t*slab_rows, K]; block_ready: local int[t*slab_rows/128] (zero-initialised once)
+//   epoch          : call counter (>= 1, strictly increasing per workspace parity)
+int hg_ag_gemm_bf16(const void* const* src_ptrs, void* const* signal_ptrs, void* gathered, void* block_ready,
+                    const void* B, void* C, const void* bias, int t, int me, int epoch, int slab_rows, int N, int K,
+                    int ldb, int ldc, int b_mn, int out_mode, void* stream) {
+  if (t < 1 || t > kMaxRanks || slab_rows % BM || (K & 7) || (ldb & 7)) return -1;
+  const int M = t * slab_rows;
+  CUtensorMap ta, tb;
+  int rc = hg_host::make_tmap_2d_bf16(&ta, gathered, M, K, K, BM, 64);
+  if (rc) return rc;
+  rc = b_mn ? hg_host::make_tmap_2d_bf16(&tb, B, K, N, ldb, 64, 64) : hg_host::make_tmap_2d_bf16(&tb, B, N, K, ldb, BN, 64);
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.out_mode = out_mode; p.tiles_m = M / BM; p.tiles_n = (N + BN - 1) / BN; p.group_m = 8;
+  p.status = hg_host::status_ptr();
+  p.ready = reinterpret_cast<const int*>(block_ready); p.rows_per_flag = BM; p.ready_target = epoch;
+  p.m_tile_shift = me * (slab_rows / BM);
+  p.k_ranges = nullptr; p.groups = 1; p.c_group_stride = 0;
+  AgParams ag{};
+  for (int i = 0; i < t; ++i) {
+    ag.src[i] = reinterpret_cast<const uint4*>(src_ptrs[i]);
+    ag.signal[i] = reinterpret_cast<int*>(signal_ptrs[i]);
+  }
+  ag.my_signal = ag.signal[me];
+  ag.gathered = reinterpret_cast<uint4*>(gathered);
+  ag.block_ready = reinterpret_cast<int*>(block_ready);
+  ag.t = t; ag.me = me; ag.epoch = epoch; ag.slab_rows = slab_rows; ag.row_vec = K * 2 / 16;
+  int grid = p.tiles_m * p.tiles_n;
+  if (grid > sm_count()) grid = sm_count();
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  static bool cfg[2] = {false, false};
+  if (b_mn) {
+    if ((rc = ensure_smem(ag_gemm_kernel<true>, cfg[1]))) return rc;
+    ag_gemm_kernel<true><<<grid, kThreads, SMEM_BYTES, st>>>(ta, tb, p, ag);
+  } else {
+    if ((rc = ensure_smem(ag_gemm_kernel<false>, cfg[0]))) return rc;
+    ag_gemm_kernel<false><<<grid, kThreads, SMEM_BYTES, st>>>(ta, tb, p, ag);
+  }
+  return int(cudaGetLastError());
+}
+
+// out[slab_rows, N] = reduce_scatter( A[t*slab_rows, K] x op(B) ) over the t ranks.
+//   stage_ptrs[t] : every rank's staging area [t][slab_rows][N] bf16;  flag_ptrs[t]: every rank's int[t][tiles_per_slab]
+int hg_gemm_rs_bf16(const void* A, const void* B, void* out, void* const* stage_ptrs, void* const* flag_ptrs, int t,
+                    int me, int epoch, int slab_rows, int N, int K, int lda, int ldb, int ldo, int b_mn, void* stream) {
+  if (t < 1 || t > kMaxRanks || slab_rows % BM || (lda & 7) || (ldb & 7) || (N & 7)) return -1;
+  const int M = t * slab_rows;
+  CUtensorMap ta, tb;
+  int rc = hg_host::make_tmap_2d_bf16(&ta, A, M, K, lda, BM, 64);
+  if (rc) return rc;
+  rc = b_mn ? hg_host::make_tmap_2d_bf16(&tb, B, K, N, ldb, 64, 64) : hg_host::make_tmap_2d_bf16(&tb, B, N, K, ldb, BN, 64);
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = N; p.C = nullptr; p.bias = nullptr; p.out_mode = kOutBf16;
+  p.tiles_m = M / BM; p.tiles_n = (N + BN - 1) / BN; p.group_m = 8; p.status = hg_host::status_ptr();
+  p.ready = nullptr; p.rows_per_flag = 1; p.ready_target = 0;
+  p.m_tile_shift = ((me + 1) % t) * (slab_rows / BM);   // peers' slabs first, our own last
+  p.k_ranges = nullptr; p.groups = 1; p.c_group_stride = 0;
+  RsParams rs{};
+  for (int i = 0; i < t; ++i) {
+    rs.stage[i] = reinterpret_cast<__nv_bfloat16*>(stage_ptrs[i]);
+    rs.flags[i] = reinterpret_cast<int*>(flag_ptrs[i]);
+  }
+  rs.my_stage = rs.stage[me]; rs.my_flags = rs.flags[me];
+  rs.out = reinterpret_cast<__nv_bfloat16*>(out); rs.ldo = ldo;
+  rs.t = t; rs.me = me; rs.epoch = epoch; rs.slab_rows = slab_rows;
+  rs.tiles_per_slab = (slab_rows / BM) * p.tiles_n;
+  int grid = p.tiles_m * p.tiles_n;
+  if (grid > sm_count()) grid = sm_count();
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  static bool cfg[2] = {false, false};
+  if (b_mn) {
+    if ((rc = ensure_smem(gemm_rs_kernel<true>, cfg[1]))) return rc;
+    gemm_rs_kernel<true><<<grid, kThreads, SMEM_BYTES, st>>>(ta, tb, p, rs);
+  } else {
+    if ((rc = ensure_smem(gemm_rs_kernel<false>, cfg[0]))) return rc;
+    gemm_rs_kernel<false><<<grid, kThreads, SMEM_BYTES, st>>>(ta, tb, p, rs);
+  }
+  return int(cudaGetLastError());
+}
+
+}  // extern "C"

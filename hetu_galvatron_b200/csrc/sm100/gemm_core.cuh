@@ -167,6 +167,8 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tmA, const CUte
         }
       }
       if (!ok) break;
+      // the rows were written with ordinary stores (generic proxy); TMA reads through the async proxy
+      asm volatile("fence.proxy.async.global;" ::: "memory");
     }
     for (int kb = 0; kb < num_kb; ++kb) {
       if (*s.abort || !mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }

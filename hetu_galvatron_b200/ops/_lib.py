@@ -49,6 +49,8 @@ _SIGNATURES = {
     "hg_flash_fwd": [ctypes.POINTER(AttnTensor)] * 4 + [c_void_p] + [c_int] * 9 + [c_float, c_void_p],
     "hg_flash_bwd": [ctypes.POINTER(AttnTensor)] * 5 + [c_void_p, c_void_p] + [ctypes.POINTER(AttnTensor)] * 3 +
                     [c_int] * 9 + [c_float, c_void_p],
+    "hg_ag_gemm_bf16": [c_void_p] * 7 + [c_int] * 10 + [c_void_p],
+    "hg_gemm_rs_bf16": [c_void_p] * 5 + [c_int] * 10 + [c_void_p],
     "hg_read_status": [c_int],
     "hg_gemm_gated_selftest": [c_void_p],
     "hg_library_version": [],
