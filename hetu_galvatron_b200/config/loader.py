@@ -173,6 +173,10 @@ def load_config(path: str, overrides: Optional[List[str]] = None, mode: str = "t
 load_with_hydra = load_config
 
 _LEGACY_SECTIONS = ("parallel", "model", "profile", "train", "data", "ckpt", "logging")
+# flags of the argparse era whose field was renamed in the YAML schema
+_LEGACY_ALIASES = {"global_train_batch_size": "global_batch_size", "epochs": "train_iters", "adam_weight_decay": "weight_decay",
+                   "dropout_prob": "hidden_dropout", "set_model_config_manually": "set_model_config_manually",
+                   "galvatron_config_path": "galvatron_config_path", "default_dp_type": "default_dp_type"}
 
 
 def legacy_cli_to_overrides(argv: List[str], section_of: Optional[Dict[str, str]] = None) -> List[str]:
@@ -205,6 +209,7 @@ def legacy_cli_to_overrides(argv: List[str], section_of: Optional[Dict[str, str]
             val = vals[0] if len(vals) == 1 else "[" + ",".join(vals) + "]"
         else:
             val = "true"
+        name = _LEGACY_ALIASES.get(name, name)
         sec = section_of.get(name)
         prefix = "runtime.%s." % sec if sec else "runtime."
         out.append("++%s%s=%s" % (prefix, name, val))

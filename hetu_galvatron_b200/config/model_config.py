@@ -135,6 +135,9 @@ def resolve_model_config(args, vocab_tp: Optional[int] = None):
     train = train_args_of(args)
     inline = set(m.model_fields_set)
     yaml_data: Dict[str, Any] = {}
+    if (m.model_config_path is None and m.hf_model_name_or_path is None and m.hidden_size is None and m.model_size
+            and os.path.exists(os.path.join(ZOO_DIR, "%s.yaml" % m.model_size))):
+        m.model_config_path = m.model_size  # a bare ``model_size`` that names a bundled configuration
     if m.model_config_path is not None:
         with open(find_model_yaml(m.model_config_path)) as f:
             yaml_data = {k: v for k, v in (yaml.safe_load(f) or {}).items() if v is not None}

@@ -28,6 +28,8 @@ using namespace hg::gemm;
 
 constexpr int kMaxRanks = 8;
 constexpr int kThreads = 256;  // 6 GEMM warps + 2 communication warps
+constexpr int kSubRows = 8;    // rows per all-gather sub-block
+constexpr int kInFlight = 16;  // independent 16-byte loads per communication thread
 
 __device__ __forceinline__ void st_release_sys(int* p, int v) {
   asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -107,14 +109,17 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       for (int q = 0; q < ag.t; ++q)
         if (q != ag.me) st_release_sys(ag.signal[q] + ag.me, ag.epoch);
     }
-    const int blocks_per_slab = ag.slab_rows / BM;
-    const int total_blocks = blocks_per_slab * ag.t;
-    const size_t block_vec = size_t(BM) * ag.row_vec;
+    // The gathered buffer is filled in sub-blocks of kSubRows rows spread over every CTA, with 16 independent
+    // 16-byte loads in flight per thread: NVLink needs ~2 MB in flight chip-wide to run at link speed.  A
+    // 128-row block is ready once all of its sub-blocks have arrived (arrival counter, zeroed per call).
+    const int subs_per_slab = ag.slab_rows / kSubRows;
+    const int total_subs = subs_per_slab * ag.t;
+    const size_t sub_vec = size_t(kSubRows) * ag.row_vec;
     volatile int* comm_go = s.abort + 1;  // written by comm thread 0 between barriers: a uniform verdict
-    for (int i = blockIdx.x; i < total_blocks; i += gridDim.x) {
-      const int hop = i / blocks_per_slab;              // 0 = our own slab, then the ring of peers
+    for (int i = blockIdx.x; i < total_subs; i += gridDim.x) {
+      const int hop = i / subs_per_slab;                // 0 = our own slab, then the ring of peers
       const int q = (ag.me + hop) % ag.t;
-      const int j = i - hop * blocks_per_slab;
+      const int j = i - hop * subs_per_slab;
       if (tid == 0) {
         bool ok = !*s.abort;
         if (ok && q != ag.me) ok = wait_flag_sys(ag.my_signal + q, ag.epoch, p.status, s.abort);
@@ -123,22 +128,23 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       comm_bar();
       if (!*comm_go) break;
-      const uint4* src = ag.src[q] + size_t(j) * block_vec;
-      uint4* dst = ag.gathered + (size_t(q) * blocks_per_slab + j) * block_vec;
-      for (size_t v = tid; v < block_vec; v += 64 * 4) {
-        uint4 a0 = src[v], a1, a2, a3;
-        const bool h1 = v + 64 < block_vec, h2 = v + 128 < block_vec, h3 = v + 192 < block_vec;
-        if (h1) a1 = src[v + 64];
-        if (h2) a2 = src[v + 128];
-        if (h3) a3 = src[v + 192];
-        dst[v] = a0;
-        if (h1) dst[v + 64] = a1;
-        if (h2) dst[v + 128] = a2;
-        if (h3) dst[v + 192] = a3;
+      const uint4* src = ag.src[q] + size_t(j) * sub_vec;
+      uint4* dst = ag.gathered + (size_t(q) * subs_per_slab + j) * sub_vec;
+      for (size_t v0 = tid; v0 < sub_vec; v0 += 64 * kInFlight) {
+        uint4 buf[kInFlight];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u)
+          if (v0 + size_t(u) * 64 < sub_vec) buf[u] = src[v0 + size_t(u) * 64];
+#pragma unroll
+        for (int u = 0; u < kInFlight; ++u)
+          if (v0 + size_t(u) * 64 < sub_vec) dst[v0 + size_t(u) * 64] = buf[u];
       }
       __threadfence();
       comm_bar();
-      if (tid == 0) st_release_gpu(ag.block_ready + q * blocks_per_slab + j, ag.epoch);
+      if (tid == 0) {
+        int* ctr = ag.block_ready + (q * ag.slab_rows + j * kSubRows) / BM;
+        asm volatile("red.release.gpu.global.add.s32 [%0], 1;" ::"l"(ctr) : "memory");
+      }
     }
   }
 
@@ -154,7 +160,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // GEMM -> reduce-scatter
 // ------------------------------------------------------------------------------------------------
 struct RsParams {
-  __nv_bfloat16* stage[kMaxRanks];  // stage[d]: rank d's staging area [t][slab_rows][N]; we write block `me`
+  __nv_bfloat16* stage[kMaxRanks];  // stage[d]: rank d's staging area [t][tiles_per_slab][64 KB tile]; we write block `me`
   int* flags[kMaxRanks];            // flags[d]: rank d's tile flags [t][tiles_per_slab]; we write row `me`
   const __nv_bfloat16* my_stage;
   int* my_flags;
@@ -183,19 +189,33 @@ __device__ __forceinline__ void rs_epilogue_loop(const Params& p, const RsParams
     }
     if (alive) {
       tc_fence_after();
-      Params q = p;
-      q.C = rs.stage[d] + size_t(rs.me) * rs.slab_rows * p.N;
-      q.ldc = p.N;
-      q.M = rs.slab_rows;
-      const int row = mblk * BM + wq * 32 + lane_id();
+      // Staging is private to this kernel, so a tile is laid out for the wire, not for a reader of rows:
+      // [32-column chunk][8-column group][row] x 16 bytes, i.e. the 32 lanes of a warp (32 consecutive rows)
+      // write 512 contiguous bytes per store instruction instead of 32 scattered 16-byte packets.
+      const int tile_in_slab = mblk * p.tiles_n + ti.n0 / BN;
+      uint4* tile_base = reinterpret_cast<uint4*>(rs.stage[d]) +
+                         (size_t(rs.me) * rs.tiles_per_slab + tile_in_slab) * (BM * BN / 8);
+      const int row_in_tile = wq * 32 + lane_id();
 #pragma unroll 1
       for (int c = 0; c < BN / 32; c += 2) {
         uint32_t r0[32], r1[32];
         tmem_ld32(tmem_base + lane_off + acc * BN + c * 32, r0);
         tmem_ld32(tmem_base + lane_off + acc * BN + (c + 1) * 32, r1);
         tmem_ld_wait();
-        if (ti.n0 + c * 32 < p.N) store_row_chunk(q, row, ti.n0 + c * 32, r0);
-        if (ti.n0 + (c + 1) * 32 < p.N) store_row_chunk(q, row, ti.n0 + (c + 1) * 32, r1);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 u, w;
+          u.x = pack_bf16(__uint_as_float(r0[g * 8 + 0]), __uint_as_float(r0[g * 8 + 1]));
+          u.y = pack_bf16(__uint_as_float(r0[g * 8 + 2]), __uint_as_float(r0[g * 8 + 3]));
+          u.z = pack_bf16(__uint_as_float(r0[g * 8 + 4]), __uint_as_float(r0[g * 8 + 5]));
+          u.w = pack_bf16(__uint_as_float(r0[g * 8 + 6]), __uint_as_float(r0[g * 8 + 7]));
+          w.x = pack_bf16(__uint_as_float(r1[g * 8 + 0]), __uint_as_float(r1[g * 8 + 1]));
+          w.y = pack_bf16(__uint_as_float(r1[g * 8 + 2]), __uint_as_float(r1[g * 8 + 3]));
+          w.z = pack_bf16(__uint_as_float(r1[g * 8 + 4]), __uint_as_float(r1[g * 8 + 5]));
+          w.w = pack_bf16(__uint_as_float(r1[g * 8 + 6]), __uint_as_float(r1[g * 8 + 7]));
+          tile_base[(c * 4 + g) * BM + row_in_tile] = u;
+          tile_base[((c + 1) * 4 + g) * BM + row_in_tile] = w;
+        }
       }
       tc_fence_before();
       mbar_arrive(&s.tmem_empty[acc]);
@@ -215,7 +235,6 @@ __device__ __forceinline__ void rs_epilogue_loop(const Params& p, const RsParams
 __device__ __forceinline__ void rs_reduce_phase(const Params& p, const RsParams& rs, const SmemLayout& s) {
   const int etid = threadIdx.x - 64;
   volatile int* epi_go = s.abort + 2;
-  const size_t slab_elems = size_t(rs.slab_rows) * p.N;
   for (int tile = blockIdx.x; tile < rs.tiles_per_slab; tile += gridDim.x) {
     const int mblk = tile / p.tiles_n, tn = tile - mblk * p.tiles_n;
     if (etid < rs.t && !wait_flag_sys(rs.my_flags + etid * rs.tiles_per_slab + tile, rs.epoch, p.status, s.abort))
@@ -225,30 +244,46 @@ __device__ __forceinline__ void rs_reduce_phase(const Params& p, const RsParams&
     epi_bar();
     if (!*epi_go) return;
     const int n0 = tn * BN;
-    const int cols = min(BN, p.N - n0);
-    const int vec_per_row = cols >> 3;               // 8 bf16 per 16 bytes (N is a multiple of 8)
-    for (int v = etid; v < BM * vec_per_row; v += 128) {
-      const int r = v / vec_per_row, c8 = v - r * vec_per_row;
-      const size_t off = size_t(mblk * BM + r) * p.N + n0 + c8 * 8;
-      float accv[8];
+    const int groups = min(BN, p.N - n0) >> 3;          // valid 8-column groups of this tile
+    constexpr int kV = 4;                               // vectors per thread per step: t * kV loads in flight
+    const size_t tile_vecs = BM * BN / 8;
+    const uint4* my = reinterpret_cast<const uint4*>(rs.my_stage);
+    for (int v0 = etid; v0 < groups * BM; v0 += 128 * kV) {
+      uint4 part[kMaxRanks][kV];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) accv[i] = 0.f;
-      for (int src = 0; src < rs.t; ++src) {
-        const uint4 u = *reinterpret_cast<const uint4*>(rs.my_stage + size_t(src) * slab_elems + off);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+      for (int src = 0; src < kMaxRanks; ++src)
+        if (src < rs.t) {
+          const uint4* base = my + (size_t(src) * rs.tiles_per_slab + tile) * tile_vecs;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float2 f = __bfloat1622float2(h[i]);
-          accv[2 * i] += f.x;
-          accv[2 * i + 1] += f.y;
+          for (int u = 0; u < kV; ++u)
+            if (v0 + u * 128 < groups * BM) part[src][u] = base[v0 + u * 128];
         }
+#pragma unroll
+      for (int u = 0; u < kV; ++u) {
+        const int v = v0 + u * 128;
+        if (v >= groups * BM) continue;
+        float accv[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) accv[i] = 0.f;
+#pragma unroll
+        for (int src = 0; src < kMaxRanks; ++src)
+          if (src < rs.t) {
+            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[src][u]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(h[i]);
+              accv[2 * i] += f.x;
+              accv[2 * i + 1] += f.y;
+            }
+          }
+        uint4 o;
+        o.x = pack_bf16(accv[0], accv[1]);
+        o.y = pack_bf16(accv[2], accv[3]);
+        o.z = pack_bf16(accv[4], accv[5]);
+        o.w = pack_bf16(accv[6], accv[7]);
+        const int grp = v / BM, r = v - grp * BM;       // staging index = group * 128 + row
+        *reinterpret_cast<uint4*>(rs.out + size_t(mblk * BM + r) * rs.ldo + n0 + grp * 8) = o;
       }
-      uint4 o;
-      o.x = pack_bf16(accv[0], accv[1]);
-      o.y = pack_bf16(accv[2], accv[3]);
-      o.z = pack_bf16(accv[4], accv[5]);
-      o.w = pack_bf16(accv[6], accv[7]);
-      *reinterpret_cast<uint4*>(rs.out + size_t(mblk * BM + r) * rs.ldo + n0 + c8 * 8) = o;
     }
   }
 }
@@ -342,7 +377,7 @@ int hg_ag_gemm_bf16(const void* const* src_ptrs, void* const* signal_ptrs, void*
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
   p.out_mode = out_mode; p.tiles_m = M / BM; p.tiles_n = (N + BN - 1) / BN; p.group_m = 8;
   p.status = hg_host::status_ptr();
-  p.ready = reinterpret_cast<const int*>(block_ready); p.rows_per_flag = BM; p.ready_target = epoch;
+  p.ready = reinterpret_cast<const int*>(block_ready); p.rows_per_flag = BM; p.ready_target = BM / kSubRows;
   p.m_tile_shift = me * (slab_rows / BM);
   p.k_ranges = nullptr; p.groups = 1; p.c_group_stride = 0;
   AgParams ag{};
@@ -369,7 +404,7 @@ int hg_ag_gemm_bf16(const void* const* src_ptrs, void* const* signal_ptrs, void*
 }
 
 // out[slab_rows, N] = reduce_scatter( A[t*slab_rows, K] x op(B) ) over the t ranks.
-//   stage_ptrs[t] : every rank's staging area [t][slab_rows][N] bf16;  flag_ptrs[t]: every rank's int[t][tiles_per_slab]
+//   stage_ptrs[t] : every rank's staging area [t][tiles_per_slab][128*256] bf16;  flag_ptrs[t]: every rank's int[t][tiles_per_slab]
 int hg_gemm_rs_bf16(const void* A, const void* B, void* out, void* const* stage_ptrs, void* const* flag_ptrs, int t,
                     int me, int epoch, int slab_rows, int N, int K, int lda, int ldb, int ldo, int b_mn, void* stream) {
   if (t < 1 || t > kMaxRanks || slab_rows % BM || (lda & 7) || (ldb & 7) || (N & 7)) return -1;

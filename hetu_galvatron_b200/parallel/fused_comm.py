@@ -43,7 +43,7 @@ class TPWorkspace:
         t = self.t
         self.flag_bytes = _round_up(t * self.max_tiles * 4, 256)
         self.ag_bytes = _round_up(slab_rows * cols * 2, 256)
-        self.rs_bytes = _round_up(t * slab_rows * cols * 2, 256)
+        self.rs_bytes = t * self.max_tiles * 128 * 256 * 2   # whole 128x256 tiles, wire layout
         self.off_flags = [_SIGNAL_BYTES + i * self.flag_bytes for i in range(2)]
         base = _SIGNAL_BYTES + 2 * self.flag_bytes
         self.off_ag = [base + i * self.ag_bytes for i in range(2)]

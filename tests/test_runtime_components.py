@@ -1,0 +1,343 @@
+"""Host-side runtime pieces on CPU: schedules, micro-batch calculators, the re-run state machine with host-side
+fault injection, data iterators, indexed / GPT / blended datasets against plain numpy oracles, the runtime
+profiler's files, and configuration loading."""
+import json
+import math
+import os
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from hetu_galvatron_b200.runtime import rerun as rr  # noqa: E402
+from hetu_galvatron_b200.runtime import scheduler as sch  # noqa: E402
+
+
+class _Opt:
+    def __init__(self):
+        self.param_groups = [{"lr": 0.0, "weight_decay": 0.0}]
+        self.lr, self.weight_decay = 0.0, 0.0
+
+
+def _sched(style="cosine", **kw):
+    args = dict(init_lr=0.0, max_lr=1e-3, min_lr=1e-4, lr_warmup_steps=100, lr_decay_steps=1000, lr_decay_style=style,
+                start_wd=0.0, end_wd=0.1, wd_incr_steps=1000, wd_incr_style="linear")
+    args.update(kw)
+    return sch.OptimizerParamScheduler(_Opt(), **args)
+
+
+def test_lr_schedules():
+    s = _sched("cosine")
+    s.step(50)
+    assert s.get_lr() == pytest.approx(0.5e-3)
+    s.step(50)
+    assert s.get_lr() == pytest.approx(1e-3)
+    s.step(450)  # half-way through the decay
+    assert s.get_lr() == pytest.approx(1e-4 + 0.5 * 9e-4)
+    s.step(10000)
+    assert s.get_lr() == pytest.approx(1e-4)
+    lin = _sched("linear")
+    lin.step(550)
+    assert lin.get_lr() == pytest.approx(1e-4 + 0.5 * 9e-4)
+    const = _sched("constant")
+    const.step(700)
+    assert const.get_lr() == pytest.approx(1e-3)
+    isq = _sched("inverse-square-root")
+    isq.step(400)
+    assert isq.get_lr() == pytest.approx(1e-3 * math.sqrt(100) / math.sqrt(400))
+    wsd = _sched("WSD", wsd_decay_steps=200, lr_wsd_decay_style="linear")
+    wsd.step(700)
+    assert wsd.get_lr() == pytest.approx(1e-3)
+    wsd.step(200)  # half of the tail
+    assert wsd.get_lr() == pytest.approx(1e-4 + 0.5 * 9e-4)
+
+
+def test_wd_schedule_and_state_roundtrip():
+    s = _sched("cosine")
+    s.step(250)
+    assert s.get_wd() == pytest.approx(0.025)
+    sd = json.loads(json.dumps(s.state_dict()))
+    t = _sched("cosine")
+    t.load_state_dict(sd)
+    assert t.num_steps == 250 and t.get_lr() == pytest.approx(s.get_lr())
+    assert s.optimizer.param_groups[0]["lr"] == pytest.approx(s.get_lr())
+
+
+def test_scheduler_rejects_bad_arguments():
+    with pytest.raises(AssertionError):
+        _sched(lr_warmup_steps=2000)
+    with pytest.raises(AssertionError):
+        _sched(min_lr=1.0)
+    with pytest.raises(AssertionError):
+        _sched("WSD")
+
+
+def test_microbatch_calculators():
+    c = sch.build_num_microbatches_calculator(64, 2, 4)
+    assert c.get() == 8 and c.get_current_global_batch_size() == 64
+    r = sch.build_num_microbatches_calculator(64, 2, 4, [16, 16, 300])
+    assert r.get_current_global_batch_size() == 16 and r.get() == 2
+    r.update(150, True)
+    assert r.get_current_global_batch_size() in (32, 48)
+    r.update(1000, True)
+    assert r.get_current_global_batch_size() == 64 and r.get() == 8
+    with pytest.raises(AssertionError):
+        sch.build_num_microbatches_calculator(60, 8, 4)
+
+
+# ---- re-run state machine -------------------------------------------------------------------------------------
+def _step(m, it, value_of):
+    """One training step under the machine; returns how many times forward-backward ran."""
+    runs = 0
+    while m.should_run_forward_backward(it):
+        batch = next(it)
+        runs += 1
+        m.validate_result(value_of(batch, runs), m.is_unexpectedly_large(10.0), "loss", tolerance=0.0)
+    return runs
+
+
+def test_rerun_disabled_and_clean_steps():
+    m = rr.RerunStateMachine(rr.RerunMode.DISABLED)
+    it = rr.RerunDataIterator(range(100))
+    assert _step(m, it, lambda b, r: 1.0) == 1 and _step(m, it, lambda b, r: 1.0) == 1
+    m = rr.RerunStateMachine(rr.RerunMode.VALIDATE_RESULTS)
+    assert _step(m, it, lambda b, r: 1.0) == 1
+    assert m.should_checkpoint_and_exit() == (False, False, 0)
+
+
+def test_rerun_transient_fault_replays_the_same_batch():
+    m = rr.RerunStateMachine(rr.RerunMode.VALIDATE_RESULTS)
+    it = rr.RerunDataIterator(range(100))
+    seen = []
+
+    def value(b, run):
+        seen.append(b)
+        return float("nan") if run == 1 else 2.0
+
+    assert _step(m, it, value) == 2
+    assert seen == [0, 0]                                      # the re-run saw the same data
+    assert m.log[-1][1] == rr.RerunDiagnostic.TRANSIENT_ERROR.value
+    assert m.should_checkpoint_and_exit() == (False, False, 0)
+    assert _step(m, it, lambda b, r: 1.0) == 1 and next(it) == 2
+
+
+def test_rerun_reproducible_fault_asks_for_checkpoint_then_resolves(tmp_path):
+    tracker = str(tmp_path / "rejected.json")
+    m = rr.RerunStateMachine(rr.RerunMode.VALIDATE_RESULTS, result_rejected_tracker_filename=tracker)
+    it = rr.RerunDataIterator(range(100))
+    assert _step(m, it, lambda b, r: float("inf")) == 2      # same bad value twice
+    save, leave, code = m.should_checkpoint_and_exit()
+    assert (save, leave, code) == (True, True, rr.EXIT_CODE_RESUME_TO_DISAMBIGUATE)
+    sd = json.loads(json.dumps(m.state_dict(it)))
+
+    # "another device": restore, pretend the device id changed, the value differs -> persistent error on the first
+    m2 = rr.RerunStateMachine(rr.RerunMode.VALIDATE_RESULTS, result_rejected_tracker_filename=tracker)
+    it2 = rr.RerunDataIterator(range(100))
+    m2.load_state_dict(sd, it2)
+    m2._device = staticmethod(lambda: 7)
+    assert _step(m2, it2, lambda b, r: 1.5) == 1
+    assert m2.log[-1][1] == rr.RerunDiagnostic.PERSISTENT_ERROR.value
+    assert m2.should_checkpoint_and_exit() == (False, True, rr.EXIT_CODE_FAILED_ON_RESULT_VALIDATION)
+
+    # same value elsewhere -> the value is real; iteration recorded for skipping
+    m3 = rr.RerunStateMachine(rr.RerunMode.VALIDATE_RESULTS, result_rejected_tracker_filename=tracker)
+    it3 = rr.RerunDataIterator(range(100))
+    m3.load_state_dict(sd, it3)
+    m3._device = staticmethod(lambda: 7)
+    assert _step(m3, it3, lambda b, r: float("inf")) == 1
+    assert m3.log[-1][1] == rr.RerunDiagnostic.CORRECT_RESULT.value
+    assert rr.get_skipped_iterations_from_tracker_file(tracker) == [0]
+
+
+def test_rerun_injector_reaches_each_diagnosis():
+    inj = rr.RerunErrorInjector(error_injection_rate=10 ** 6, error_injection_type=rr.RerunDiagnostic.TRANSIENT_ERROR)
+    m = rr.RerunStateMachine(rr.RerunMode.VALIDATE_RESULTS, error_injector=inj)
+    it = rr.RerunDataIterator(range(10))
+    assert _step(m, it, lambda b, r: 1.0) == 2
+    assert m.log[-1][1] == rr.RerunDiagnostic.TRANSIENT_ERROR.value
+    inj = rr.RerunErrorInjector(error_injection_rate=10 ** 6, error_injection_type=rr.RerunDiagnostic.PERSISTENT_ERROR)
+    m = rr.RerunStateMachine(rr.RerunMode.VALIDATE_RESULTS, error_injector=inj)
+    assert _step(m, it, lambda b, r: 1.0) == 2
+    assert m.should_checkpoint_and_exit()[2] == rr.EXIT_CODE_RESUME_TO_DISAMBIGUATE
+
+
+def test_rerun_determinism_stats():
+    m = rr.RerunStateMachine(rr.RerunMode.REPORT_DETERMINISM_STATS)
+    it = rr.RerunDataIterator(range(10))
+    assert _step(m, it, lambda b, r: 1.0 + 1e-3 * (r - 1)) == 2
+    st = m.stats["loss"]
+    assert "max" in st.print_stats()
+
+
+# ---- datasets -------------------------------------------------------------------------------------------------
+def _write_corpus(prefix, docs, dtype=np.uint16):
+    from hetu_galvatron_b200.runtime.datasets.indexed import IndexedDatasetBuilder, bin_path, idx_path
+
+    b = IndexedDatasetBuilder(bin_path(prefix), dtype=dtype)
+    for d in docs:
+        b.add_item(d)
+        b.end_document()
+    b.finalize(idx_path(prefix))
+
+
+def _docs(n=60, seed=0, vocab=500):
+    rng = np.random.RandomState(seed)
+    return [rng.randint(1, vocab, size=rng.randint(5, 90)) for _ in range(n)]
+
+
+def test_indexed_dataset_roundtrip(tmp_path):
+    from hetu_galvatron_b200.runtime.datasets.indexed import IndexedDataset
+
+    docs = _docs()
+    prefix = str(tmp_path / "corpus")
+    _write_corpus(prefix, docs)
+    for mmap in (True, False):
+        ds = IndexedDataset(prefix, mmap=mmap)
+        assert len(ds) == len(docs) and ds.dtype == np.uint16
+        assert list(ds.document_indices) == list(range(len(docs) + 1))
+        for i in (0, 7, len(docs) - 1):
+            assert np.array_equal(ds[i], docs[i])
+        assert np.array_equal(ds.get(3, 2, 3), docs[3][2:5])
+
+
+def test_sample_index_matches_python_oracle():
+    from hetu_galvatron_b200.runtime.datasets.gpt import build_sample_idx, build_sample_idx_reference
+
+    rng = np.random.RandomState(3)
+    sizes = rng.randint(3, 70, size=200).astype(np.int32)
+    for epochs, seq, drop in ((1, 32, True), (3, 17, True), (2, 64, False)):
+        doc_idx = np.tile(np.arange(200, dtype=np.int32), epochs)
+        rng.shuffle(doc_idx)
+        tpe = int(sizes.sum())
+        got = build_sample_idx(sizes, doc_idx, seq, epochs, tpe, drop, 1)
+        want = build_sample_idx_reference(sizes, doc_idx, seq, epochs, tpe, drop, 1)
+        assert got.shape == want.shape and np.array_equal(np.asarray(got, dtype=np.int64), want)
+
+
+def test_gpt_dataset_samples_are_contiguous_token_windows(tmp_path):
+    from hetu_galvatron_b200.runtime.datasets.gpt import GPTDataset, GPTDatasetConfig
+    from hetu_galvatron_b200.runtime.datasets.indexed import IndexedDataset
+
+    docs = _docs(80, seed=5)
+    prefix = str(tmp_path / "c")
+    _write_corpus(prefix, docs)
+    cfg = GPTDatasetConfig(sequence_length=32, random_seed=11, path_to_cache=str(tmp_path / "cache"))
+    ds = GPTDataset(IndexedDataset(prefix), prefix, np.arange(80, dtype=np.int32), 150, "train", cfg)
+    assert len(ds) >= 150
+    # the un-shuffled sample stream is the concatenation of the shuffled documents, windows overlap by one token
+    stream = np.concatenate([docs[d] for d in ds.doc_index])
+    inv = np.argsort(np.asarray(ds.shuffle_index))
+    for k in (0, 1, 17, 149):
+        s = ds[int(inv[k])]
+        assert np.array_equal(s["tokens"].numpy(), stream[k * 32:(k + 1) * 32])
+        assert np.array_equal(s["labels"].numpy(), stream[k * 32 + 1:(k + 1) * 32 + 1])
+        assert s["loss_mask"].shape == (32,) and s["position_ids"][5] == 5
+    # second construction hits the cache and gives the same samples
+    ds2 = GPTDataset(IndexedDataset(prefix), prefix, np.arange(80, dtype=np.int32), 150, "train", cfg)
+    assert torch.equal(ds2[3]["tokens"], ds[3]["tokens"])
+    assert len(os.listdir(str(tmp_path / "cache"))) == 3
+
+
+def test_blended_dataset_follows_weights():
+    from hetu_galvatron_b200.runtime.datasets.blended import BlendedDataset
+
+    class D(torch.utils.data.Dataset):
+        def __init__(self, tag, n):
+            self.tag, self.n = tag, n
+
+        def __len__(self):
+            return self.n
+
+        def __getitem__(self, i):
+            return {"tokens": torch.tensor([self.tag, i])}
+
+    b = BlendedDataset([D(0, 1000), D(1, 1000), D(2, 1000)], [0.5, 0.3, 0.2], 1000)
+    counts = np.bincount(b.dataset_index, minlength=3)
+    assert list(counts) == [500, 300, 200]
+    for prefix in (10, 100, 333):  # greedy: every prefix tracks the weights within one sample
+        c = np.bincount(b.dataset_index[:prefix], minlength=3)
+        assert np.all(np.abs(c - np.array([0.5, 0.3, 0.2]) * prefix) <= 1.0 + 1e-9)
+    item = b[10]
+    assert item["dataset_id"] == int(b.dataset_index[10]) and item["tokens"][1] == int(b.dataset_sample_index[10])
+    ex = BlendedDataset([D(0, 5), D(1, 10)], None, None)
+    assert len(ex) == 15 and list(np.bincount(ex.dataset_index)) == [5, 10]
+
+
+def test_builder_splits_and_collate(tmp_path):
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+    from hetu_galvatron_b200.runtime.datasets import builder
+
+    assert builder.parse_weighted_paths(["0.3", "a", "0.7", "b"]) == (["a", "b"], [0.3, 0.7])
+    assert builder.parse_weighted_paths(["a"]) == (["a"], None)
+    sp = builder.parse_split("90,10,0")
+    assert sp[0] == (0.0, 0.9) and sp[1] == pytest.approx((0.9, 1.0)) and sp[2] is None
+    prefix = str(tmp_path / "c")
+    _write_corpus(prefix, _docs(100, seed=9))
+    args = GalvatronRuntimeArgs(model=dict(model_size="llama-test", hidden_size=64, num_layers=1, num_attention_heads=2, vocab_size=512),
+                                train=dict(seq_length=16, global_batch_size=4, train_iters=10, eval_iters=2, eval_interval=5),
+                                data=dict(data_path=[prefix], split="90,10,0", data_cache_path=str(tmp_path / "cache")))
+    tr, va, te = builder.build_train_valid_test_datasets(args)
+    assert len(tr) >= 40 and va is not None and te is None
+    tokens, kw, _ = builder.gpt_collate_fn([tr[0], tr[1]])
+    assert tokens.shape == (2, 16) and kw["labels"].shape == (2, 16) and kw["loss_mask"].shape == (2, 16)
+
+
+def test_samplers_partition_the_batch():
+    from hetu_galvatron_b200.runtime.data import PretrainingRandomSampler, PretrainingSampler
+
+    per_rank = [list(PretrainingSampler(64, 8, 2, r, 4)) for r in range(4)]
+    first = sorted(sum((pr[0] for pr in per_rank), []))
+    assert first == list(range(8, 16)) and len(per_rank[0]) == 7
+    rnd = [list(PretrainingRandomSampler(64, 64, 0, 2, r, 4, data_sharding=True, seed=1)) for r in range(4)]
+    seen = sorted(sum((sum(pr, []) for pr in rnd), []))
+    assert seen == list(range(64))
+
+
+# ---- runtime profiler ----------------------------------------------------------------------------------------
+def test_runtime_profiler_files(tmp_path):
+    from hetu_galvatron_b200.profiler import runtime as prof
+
+    assert prof.memory_strategy_key(1, 2, 8, False, True, 2).startswith("1_2_4")
+    p = str(tmp_path / "mem.json")
+    prof.save_profiled_memory(p, 1, 2, 8, [1], 8, 0, 100.0, 50.0, 75.0, 0, True, 2, 4096)
+    prof.save_profiled_memory(p, 1, 2, 8, [1], 8, 7, 90.0, 40.0, 70.0, 0, True, 2, 4096)
+    cfg = json.load(open(p))
+    (key, val), = cfg.items()
+    assert "layernum1_bsz8_seq4096_rank0_ms" in val and "layernum1_bsz8_seq4096_rank7_act_peak" in val
+    t = str(tmp_path / "time.json")
+    prof.save_profiled_time(t, 12.5, 8, [2], 4096)
+    assert json.load(open(t)) == {"layernum2_bsz8_seq4096": 12.5}
+
+
+def test_runtime_profiler_time_filter():
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+    from hetu_galvatron_b200.profiler.runtime import RuntimeProfiler
+
+    args = GalvatronRuntimeArgs(model=dict(model_size="llama-test", hidden_size=64, num_layers=1, num_attention_heads=2, vocab_size=512),
+                                train=dict(seq_length=16, global_batch_size=4))
+    p = RuntimeProfiler(args)
+    p.set_time_profiler(0, 100)
+    p.time_list = [10.0] * 20 + [200.0]
+    f = p.filtered_time_samples()
+    assert 200.0 not in f and p.average_time() == pytest.approx(10.0)
+
+
+# ---- configuration ----------------------------------------------------------------------------------------------
+def test_config_loader_overrides_and_zoo(tmp_path):
+    from hetu_galvatron_b200.config import loader
+    from hetu_galvatron_b200.config.model_config import model_name, resolve_model_config
+
+    y = tmp_path / "train.yaml"
+    y.write_text("runtime:\n  model:\n    model_size: llama2-7b\n  train:\n    seq_length: 2048\n    global_batch_size: 16\n"
+                 "  parallel:\n    pp_deg: 2\n    global_tp_deg: ${runtime.parallel.pp_deg}\n")
+    args = loader.load_config(str(y), ["runtime.train.seq_length=4096", "runtime.parallel.sdp=1"], mode="train_dist")
+    assert args.train.seq_length == 4096 and args.parallel.pp_deg == 2 and args.parallel.global_tp_deg == 2
+    assert args.parallel.sdp == 1
+    resolve_model_config(args)
+    assert args.model.hidden_size == 4096 and args.model.num_layers == 32
+    assert "llama" in model_name(args)
+    ov = loader.legacy_cli_to_overrides(["--pp_deg", "4", "--global_train_batch_size", "32", "--use-flash-attn"])
+    assert "++runtime.parallel.pp_deg=4" in ov and "++runtime.train.global_batch_size=32" in ov
