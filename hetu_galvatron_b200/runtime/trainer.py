@@ -1,0 +1,104 @@
+"""The training loop shared by the dense and MoE entry points.
+
+Per iteration: next batch (pinned host memory -> device, asynchronous), forward-backward through the engine,
+gradient reduction + exact global-norm clipping + fused AdamW (:class:`ShardedAdamW.step`), schedule step, profiler
+hooks, periodic checkpoint, re-run validation of the loss when the state machine is enabled.  The loss is read on
+the host once per iteration (for logging and validation), which is the only forced synchronisation.
+
+Capability parity: galvatron/models/gpt/train_dist.py:21-73, models/moe/train_dist.py:36-111 (adds the
+load-balancing loss report), core/runtime/optimizer/utils.py:43-71 (optimizer + scheduler construction).
+"""
+from __future__ import annotations
+
+import os
+import sys
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..config.model_config import model_layer_configs, model_name, resolve_model_config
+from ..profiler.runtime import RuntimeProfiler
+from . import checkpoint as ckpt
+from .data import get_batch, get_train_valid_test_data_iterators
+from .engine import build_model
+from .optimizer import ShardedAdamW
+from .rerun import RerunDataIterator, get_rerun_state_machine
+from .scheduler import get_optimizer_param_scheduler
+
+
+def get_optimizer_and_param_scheduler(model, args):
+    t = args.train
+    opt = ShardedAdamW(model.sharded_units, lr=t.lr, betas=(t.adam_beta1, t.adam_beta2), eps=t.adam_eps,
+                       weight_decay=t.weight_decay, clip_grad=t.clip_grad or 0.0, device=model.device)
+    sched = None
+    if t.train_iters or t.train_samples:
+        sched = get_optimizer_param_scheduler(opt, args)
+    return opt, sched
+
+
+def get_runtime_profiler(args, model, start_iter: int = 10, end_iter: int = 20) -> RuntimeProfiler:
+    prof = RuntimeProfiler(args)
+    prof.set_profiler_dist(path=None, model_layer_configs=model_layer_configs(args), model_name=model_name(args),
+                           start_iter=start_iter, end_iter=end_iter)
+    return prof
+
+
+def train(args, max_iters: Optional[int] = None, profile_window=(10, 20)):
+    """Runs ``args.train.train_iters`` iterations (or ``max_iters``); returns the list of per-iteration losses seen
+    on this rank (``None`` entries on ranks that do not hold the last pipeline stage)."""
+    resolve_model_config(args)
+    model = build_model(args)
+    rank = dist.get_rank() if dist.is_initialized() else 0
+    optimizer, scheduler = get_optimizer_and_param_scheduler(model, args)
+    start = 0
+    c = args.ckpt
+    if c.load is not None:
+        if c.distributed_checkpoint:
+            it = c.load_iteration or 0
+            ckpt.load_distributed_checkpoint(model, optimizer, scheduler, c.load, it)
+            start = it
+        else:
+            ckpt.load_hf_split(model, c.load)
+    args.train.iteration = start
+    train_it, valid_it, _ = get_train_valid_test_data_iterators(args, model)
+    machine = get_rerun_state_machine()
+    train_it = RerunDataIterator(train_it)
+    profiler = get_runtime_profiler(args, model, start_iter=profile_window[0], end_iter=profile_window[1])
+    profiler.profile_memory(0, "After creating model")
+    total = max_iters if max_iters is not None else (args.train.train_iters or 0)
+    gbsz = args.train.global_batch_size
+    losses = []
+    for it in range(start, total):
+        profiler.profile_time_start(it)
+        profiler.profile_memory(it, "Before Forward")
+        loss = None
+        while machine.should_run_forward_backward(train_it):
+            tokens, kw, loss_fn = get_batch(train_it, model.device)
+            optimizer.zero_grad()
+            loss = model.forward_backward([tokens], it, None, loss_fn, labels=kw.get("labels"),
+                                          loss_mask=kw.get("loss_mask"))
+            if loss is not None and machine.get_mode().value != "disabled":
+                machine.validate_result(loss, machine.is_unexpectedly_large(1e4), "loss", tolerance=0.0, fatal=True)
+        profiler.profile_memory(it, "After Backward")
+        model.sync_tied_embedding_grads()
+        optimizer.step()
+        if scheduler is not None:
+            scheduler.step(increment=gbsz)
+        profiler.profile_memory(it, "After optimizer_step")
+        lr = optimizer.param_groups[0]["lr"]
+        loss_val = float(loss) if loss is not None else None
+        losses.append(loss_val)
+        profiler.post_profile_memory(it)
+        profiler.profile_time_end(it, loss_val, lr, optimizer.grad_norm() if optimizer.clip_grad > 0 else None)
+        save, leave, code = machine.should_checkpoint_and_exit()
+        if c.save is not None and (save or (c.save_interval and (it + 1) % c.save_interval == 0)):
+            ckpt.save_distributed_checkpoint(model, optimizer, scheduler, it + 1, c.save,
+                                             extra={"rerun": machine.state_dict(train_it)})
+        if leave:
+            if dist.is_initialized():
+                dist.barrier()
+            sys.exit(code)
+        if dist.is_initialized():
+            dist.barrier()
+    return losses
