@@ -268,3 +268,67 @@ int hg_norm_bwd(const void* dy, const void* h, const void* w, const void* rstd, 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------
+// Allocation-free variant of the norm backward (declared and documented in norm_noalloc.h)
+// ---------------------------------------------------------------------------------------------------
+#include "norm_noalloc.h"
+
+#include <mutex>
+
+namespace {
+
+constexpr int kNoAllocMaxDevices = 64;
+constexpr size_t kNoAllocFloats = size_t(2) * HG_NORM_NOALLOC_PARTS * HG_NORM_NOALLOC_MAX_H;
+
+// Per-CTA partial sums: rows [0, PARTS) for the weight gradient, rows [PARTS, 2*PARTS) for LayerNorm's bias
+// gradient, each row H floats wide (H <= MAX_H).  One copy per device, shared by every call on that device.
+static __device__ __align__(256) float g_norm_bwd_scratch[kNoAllocFloats];
+
+float* g_scratch_addr[kNoAllocMaxDevices] = {};
+std::mutex g_scratch_mu;
+
+// Device address of the array on the current device.  In host code the array's name is only a handle for the
+// runtime, not a device pointer, so the address is asked for once per device and cached.
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return -(1000 + int(e));
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return -1;
+  std::lock_guard<std::mutex> lock(g_scratch_mu);
+  if (g_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_norm_bwd_scratch);
+    if (e != cudaSuccess || p == nullptr) return -(1000 + int(e));
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+
+}  // namespace
+
+extern "C" int hg_norm_bwd_noalloc(const void* dy, const void* h, const void* w, const void* rstd, const void* mean,
+                                   const void* dres, void* dx, void* dw, void* db, int rows, int H, int rms,
+                                   int accumulate, void* stream) {
+  if (rows <= 0) return 0;
+  if ((H & 7) || H <= 0) return -1;
+  if (H > HG_NORM_NOALLOC_MAX_H) return HG_NORM_NOALLOC_TOO_WIDE;
+  float* P = nullptr;
+  if (int rc = noalloc_scratch(&P)) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int parts = HG_NORM_NOALLOC_PARTS;
+  const int grid = rows < parts ? rows : parts;
+  float* PB = P + size_t(parts) * HG_NORM_NOALLOC_MAX_H;
+#define HG_BWD_NA(R_, V_)                                                                                           \
+  norm_bwd_kernel<R_, V_><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,             \
+                                                     (const __nv_bfloat16*)w, (const float*)rstd,                    \
+                                                     (const float*)mean, (const __nv_bfloat16*)dres,                 \
+                                                     (__nv_bfloat16*)dx, P, (R_) ? nullptr : PB, rows, H)
+  if (rms) { if (H <= 4096) HG_BWD_NA(true, 2); else HG_BWD_NA(true, 4); }
+  else     { if (H <= 4096) HG_BWD_NA(false, 2); else HG_BWD_NA(false, 4); }
+#undef HG_BWD_NA
+  reduce_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(P, (float*)dw, grid, H, accumulate);
+  if (!rms && db) reduce_partials_kernel<<<(H + 255) / 256, 256, 0, st>>>(PB, (float*)db, grid, H, accumulate);
+  return int(cudaGetLastError());
+}
