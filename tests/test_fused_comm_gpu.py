@@ -78,67 +78,11 @@ def fused_vs_reference(cfg):
 
 
 def fused_vs_nccl_timing(cfg):
-    """Device-timed (CUDA events, max over ranks) fused kernels vs NCCL collective + the same GEMM."""
-    import torch.distributed as dist
-
-    from hetu_galvatron_b200 import ops
-    from hetu_galvatron_b200.ops import _lib
-    from hetu_galvatron_b200.parallel import fused_comm as fc
+    """Device-timed fused kernels vs NCCL collective + the same GEMM (see profiler/fused_tp_bench.py)."""
+    from hetu_galvatron_b200.profiler.fused_tp_bench import fused_vs_nccl
 
     rank, t, grp = _init()
-    dev = torch.device("cuda", rank)
-    slab, K, N = cfg["slab"], cfg["K"], cfg["N"]
-    x = torch.randn(slab, K, device=dev, dtype=torch.bfloat16)
-    w = torch.randn(N, K, device=dev, dtype=torch.bfloat16) * 0.05
-    x2 = torch.randn(t * slab, K, device=dev, dtype=torch.bfloat16)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
-
-    def timed(fn, iters=10):
-        for _ in range(3):
-            fn()
-        ts = []
-        for _ in range(iters):
-            flush.zero_()
-            dist.barrier()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            fn()
-            b.record()
-            torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b))
-        ts.sort()
-        v = torch.tensor([ts[len(ts) // 2]], device=dev)
-        dist.all_reduce(v, op=dist.ReduceOp.MAX)
-        return float(v)
-
-    def nccl_ag():
-        xg = torch.empty(t * slab, K, device=dev, dtype=torch.bfloat16)
-        dist.all_gather_into_tensor(xg, x)
-        return ops.gemm(xg, w)
-
-    def nccl_rs():
-        y = ops.gemm(x2, w)
-        o = torch.empty(slab, N, device=dev, dtype=torch.bfloat16)
-        dist.reduce_scatter_tensor(o, y)
-        return o
-
-    res = {"ag_fused_ms": timed(lambda: fc.ag_gemm(x, w, grp)), "ag_nccl_ms": timed(nccl_ag),
-           "rs_fused_ms": timed(lambda: fc.gemm_rs(x2, w, grp)), "rs_nccl_ms": timed(nccl_rs),
-           "gemm_only_ms": timed(lambda: ops.gemm(x2, w))}
-    flops = 2.0 * t * slab * K * N
-    res["ag_fused_tflops"] = flops / res["ag_fused_ms"] / 1e9
-    res["rs_fused_tflops"] = flops / res["rs_fused_ms"] / 1e9
-    # roofline: slower of compute at the measured GEMM peak and bytes over NVLink at 770 GB/s per direction
-    peak = 1606.9
-    ag_bytes = (t - 1) * slab * K * 2
-    rs_bytes = (t - 1) * slab * N * 2
-    res["ag_roofline_ms"] = max(flops / peak / 1e9, ag_bytes / 770e9 * 1e3)
-    res["rs_roofline_ms"] = max(flops / peak / 1e9, rs_bytes / 770e9 * 1e3)
-    res["ag_frac_of_roofline"] = res["ag_roofline_ms"] / res["ag_fused_ms"]
-    res["rs_frac_of_roofline"] = res["rs_roofline_ms"] / res["rs_fused_ms"]
-    res["status"] = _lib.read_status()
-    return res
+    return fused_vs_nccl(grp, cfg["slab"], cfg["K"], cfg["N"])
 
 
 REGISTRY = {"fused_vs_reference": fused_vs_reference, "fused_vs_nccl_timing": fused_vs_nccl_timing}
