@@ -21,7 +21,7 @@ def main(argv=None, run_overlap: bool = True):
         raise SystemExit(__doc__)
     args = load_config(argv[0], argv[1:], mode="profiler_hardware")
     prof = HardwareProfiler(args)
-    prof.set_path(os.environ.get("HG_PROFILE_DIR") or os.path.dirname(os.path.dirname(os.path.abspath(argv[0]))))
+    prof.set_path(os.environ.get("HG_PROFILE_DIR") or os.getcwd())
     prof.profile_bandwidth()
     prof.profile_sp_bandwidth()
     if run_overlap and os.environ.get("HG_SKIP_OVERLAP", "0") != "1":

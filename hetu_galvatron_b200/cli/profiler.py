@@ -24,7 +24,7 @@ def main(argv=None):
     args = load_config(argv[0], argv[1:], mode="model_profiler")
     resolve_model_config(args)
     prof = ModelProfiler(args)
-    work_dir = os.environ.get("HG_PROFILE_DIR") or os.path.dirname(os.path.dirname(os.path.abspath(argv[0])))
+    work_dir = os.environ.get("HG_PROFILE_DIR") or os.getcwd()
     prof.set_profiler_launcher(work_dir, model_name(args))
     prof.launch_profiling_scripts()
     prof.process_profiled_data()

@@ -59,6 +59,7 @@ class PipelineEngine:
         self.stage, self.n = groups.stage, plan.pp_deg
         self.p2p = P2P(groups.pp, self.stage, self.n) if self.n > 1 else None
         self.first, self.last = self.stage == 0, self.stage == self.n - 1
+        self.after_forward = None  # optional hook (memory profiling): after the first forward / after all GPipe forwards
 
     # ---- shapes ---------------------------------------------------------------------------------------
     def _boundary_shape(self, lp, mb_global: int):
@@ -111,6 +112,8 @@ class PipelineEngine:
         for i in range(len(tokens)):
             with torch.set_grad_enabled(not forward_only):
                 loss = self._forward(tokens[i], labels[i], loss_fns[i], scale)
+            if i == 0 and self.after_forward is not None:
+                self.after_forward()
             if not forward_only:
                 loss.backward()
                 self._finish_backward()
@@ -137,6 +140,8 @@ class PipelineEngine:
                 losses.append(out.detach())
             inputs.append(x)
             outputs.append(out)
+        if self.after_forward is not None:
+            self.after_forward()
         if forward_only:
             self.p2p.drain()
             return losses

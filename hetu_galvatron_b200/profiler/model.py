@@ -128,7 +128,7 @@ class ModelProfiler(BaseProfiler):
 
     @staticmethod
     def dict_to_str(d: Dict, sep: str = "=") -> str:
-        return "".join("%s%s%s " % (k, sep, v) for k, v in d.items())
+        return "".join("%s%s%s " % (k, sep, "null" if v is None else v) for k, v in d.items())
 
     # ---- command lists ----------------------------------------------------------------------------------------
     def _command(self, overrides: Dict[str, Any], log_dir: str, log_name: str) -> str:

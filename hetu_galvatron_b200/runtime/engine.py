@@ -103,8 +103,10 @@ class GalvatronModel:
             fns = [loss_func] * chunks
         if profiler is not None:
             profiler.profile_memory(iter, "Before Forward")
+            self.engine.after_forward = lambda: profiler.profile_memory(iter, "After Forward")
         losses = self.engine.run(toks, labs, fns, mb_sizes, forward_only=forward_only)
         if profiler is not None:
+            self.engine.after_forward = None
             profiler.profile_memory(iter, "After Backward")
         self.iter = iter
         return self._reduce_loss(losses)

@@ -39,7 +39,8 @@ def get_optimizer_and_param_scheduler(model, args):
 
 def get_runtime_profiler(args, model, start_iter: int = 10, end_iter: int = 20) -> RuntimeProfiler:
     prof = RuntimeProfiler(args)
-    prof.set_profiler_dist(path=None, model_layer_configs=model_layer_configs(args), model_name=model_name(args),
+    # raw measurements land in <dir>/configs/, where the model profiler looks for them
+    prof.set_profiler_dist(path=os.environ.get("HG_PROFILE_DIR") or os.getcwd(), model_layer_configs=model_layer_configs(args), model_name=model_name(args),
                            start_iter=start_iter, end_iter=end_iter)
     return prof
 
@@ -71,26 +72,26 @@ def train(args, max_iters: Optional[int] = None, profile_window=(10, 20)):
     losses = []
     for it in range(start, total):
         profiler.profile_time_start(it)
-        profiler.profile_memory(it, "Before Forward")
+        forward_only = bool(args.profile.profile_forward)
         loss = None
         while machine.should_run_forward_backward(train_it):
             tokens, kw, loss_fn = get_batch(train_it, model.device)
             optimizer.zero_grad()
-            loss = model.forward_backward([tokens], it, None, loss_fn, labels=kw.get("labels"),
-                                          loss_mask=kw.get("loss_mask"))
+            loss = model.forward_backward([tokens], it, profiler, loss_fn, labels=kw.get("labels"),
+                                          loss_mask=kw.get("loss_mask"), forward_only=forward_only)
             if loss is not None and machine.get_mode().value != "disabled":
                 machine.validate_result(loss, machine.is_unexpectedly_large(1e4), "loss", tolerance=0.0, fatal=True)
-        profiler.profile_memory(it, "After Backward")
-        model.sync_tied_embedding_grads()
-        optimizer.step()
-        if scheduler is not None:
-            scheduler.step(increment=gbsz)
+        if not forward_only:
+            model.sync_tied_embedding_grads()
+            optimizer.step()
+            if scheduler is not None:
+                scheduler.step(increment=gbsz)
         profiler.profile_memory(it, "After optimizer_step")
         lr = optimizer.param_groups[0]["lr"]
         loss_val = float(loss) if loss is not None else None
         losses.append(loss_val)
         profiler.post_profile_memory(it)
-        profiler.profile_time_end(it, loss_val, lr, optimizer.grad_norm() if optimizer.clip_grad > 0 else None)
+        profiler.profile_time_end(it, loss_val, lr, optimizer.grad_norm() if (optimizer.clip_grad > 0 and not forward_only) else None)
         save, leave, code = machine.should_checkpoint_and_exit()
         if c.save is not None and (save or (c.save_interval and (it + 1) % c.save_interval == 0)):
             ckpt.save_distributed_checkpoint(model, optimizer, scheduler, it + 1, c.save,

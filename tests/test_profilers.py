@@ -171,5 +171,48 @@ def test_profile_entry_points(tmp_path, monkeypatch):
     assert (tmp_path / "scripts" / "profile_allreduce.sh").exists()
 
 
+RUNTIME_YAML = """
+runtime:
+  parallel: {mixed_precision: fp32}
+  model: {model_size: llama-test, hidden_size: 64, num_layers: 2, num_attention_heads: 4, ffn_hidden_size: 128,
+          vocab_size: 512, normalization: RMSNorm, gated_linear_unit: true, activation_func: torch.nn.functional.silu}
+  profile: {profile: 1}
+  train: {train_iters: 25, lr: 1.0e-3, global_batch_size: 2, chunks: 1, seq_length: 32}
+  data: {use_random_dataset: true}
+"""
+PROFILE_YAML = """
+model_profiler:
+  profile_type: computation
+  profile_mode: static
+  profile_mixed_precision: fp32
+  profile_fixed_batch_size: 2
+  profile_fixed_seq_length_list: [32]
+  profile_layernum_min: 1
+  profile_layernum_max: 3
+  runtime_yaml_template_path: %s
+  model_info: {model_size: llama-test, hidden_size: 64, num_attention_heads: 4, vocab_size: 512}
+"""
+
+
+def test_computation_profiling_end_to_end_on_cpu(tmp_path):
+    """The whole flow: the model profiler launches two forward-only training runs (1 and 3 layers) through the
+    training entry point, each writes its raw time, and post-processing derives the per-layer numbers."""
+    import subprocess
+
+    rt = tmp_path / "runtime.yaml"
+    rt.write_text(RUNTIME_YAML)
+    pf = tmp_path / "profile.yaml"
+    pf.write_text(PROFILE_YAML % rt)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, HG_QUIET="1", HG_PROFILE_DIR=str(tmp_path), PYTHONPATH=root, OMP_NUM_THREADS="2",
+               RUNTIME_LAUNCHER="%s -m hetu_galvatron_b200.cli.train_dist" % sys.executable)
+    r = subprocess.run([sys.executable, "-m", "hetu_galvatron_b200.cli.profiler", str(pf)], env=env, cwd=str(tmp_path),
+                       capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    out = json.load(open(tmp_path / "configs" / "computation_profiling_fp32_llama-test_all.json"))
+    assert out["layernum1_bsz2_seq32"] > 0 and out["layernum3_bsz2_seq32"] > out["layernum1_bsz2_seq32"]
+    assert out["layertype_0_bsz2_seq32"] > 0 and out["layertype_other_bsz2_seq32"] >= 0
+
+
 if __name__ == "__main__":
     worker_main(REGISTRY)
