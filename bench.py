@@ -232,7 +232,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq", type=int, default=SEQ)
-    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("HG_BENCH_MBS", "1")))
+    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("HG_BENCH_MBS", "2")))
     ap.add_argument("--dp-type", default=os.environ.get("HG_BENCH_DP", "zero2"))
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result is not a headline number)")
     ap.add_argument("--checkpoint", type=int, default=0)

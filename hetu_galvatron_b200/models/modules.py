@@ -252,8 +252,27 @@ class GalvatronMLP(nn.Module):
         self.mlp.reset_parameters(seed, full_init)
 
     def forward(self, attn_out, residual):
-        n, h = self.post_attention_layernorm(attn_out, residual=residual)  # h = residual + attn_out
-        return ops_add(h, self.mlp(n))
+        p = self.mlp.spec.hidden_dropout
+        n, h = self.post_attention_layernorm(hidden_dropout(attn_out, p, self.mlp.ctx, self.training),
+                                             residual=residual)  # h = residual + attn_out
+        return ops_add(h, hidden_dropout(self.mlp(n), p, self.mlp.ctx, self.training))
+
+
+def hidden_dropout(x, p: float, ctx, training: bool):
+    """Dropout on a block output.  Under tensor/sequence parallelism every rank of the group holds a different
+    slice of the sequence, so the mask comes from the group's own random stream (``parallel/random.py``)."""
+    if p <= 0.0 or not training:
+        return x
+    shard = max(ctx.tp_size, getattr(ctx, "sp_size", 1))
+    if shard > 1:
+        from ..parallel.random import get_rng_tracker, tensor_parallel_rng_name
+
+        tracker = get_rng_tracker()
+        name = tensor_parallel_rng_name(shard)
+        if not tracker.check(name):
+            with tracker.fork(name):
+                return torch.nn.functional.dropout(x, p, True)
+    return torch.nn.functional.dropout(x, p, True)
 
 
 class _Add(torch.autograd.Function):

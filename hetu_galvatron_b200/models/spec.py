@@ -36,6 +36,7 @@ class ModelSpec:
     qkv_bias: bool = False
     tied: bool = False               # embedding and LM head share one weight
     init_std: float = 0.02
+    hidden_dropout: float = 0.0      # applied to the attention and MLP block outputs before the residual add
     dtype: torch.dtype = torch.bfloat16
     # MoE
     experts: int = 0
@@ -124,6 +125,7 @@ def spec_from_args(args) -> ModelSpec:
         rope_interp=float(m.rotary_seq_len_interpolation_factor or 1.0), bias=m.add_bias_linear,
         qkv_bias=m.add_qkv_bias or m.add_bias_linear, tied=not m.untie_embeddings_and_output_weights,
         init_std=(tr.init_method_std if tr is not None else 0.02), dtype=dtype,
+        hidden_dropout=float(getattr(m, "hidden_dropout", 0.0) or 0.0),
         experts=m.num_moe_experts or 0, moe_ffn=m.moe_ffn_hidden_size or m.ffn_hidden_size or 0,
         topk=m.moe_router_topk, router_score=m.moe_router_score_function, router_pre_softmax=m.moe_router_pre_softmax,
         router_scaling=m.moe_router_topk_scaling_factor, router_groups=m.moe_router_num_groups,

@@ -159,6 +159,13 @@ def build_model(args, device=None, full_init: bool = False, fused_comm: Optional
     backend = None
     factory = GroupFactory(rank, world, backend)
     groups = ModelGroups(factory, plan, rank)
+    # named random streams: one per distinct tensor/sequence-parallel group size (dropout on sharded activations)
+    from ..parallel.random import set_seed_with_group
+
+    ctxs = [groups.ctx(lp, spec.seq_len) for lp in plan.layers]
+    shard_groups = [(c.tp if c.tp_size >= c.sp_size else c.sp) for c in ctxs]
+    set_seed_with_group([g for g in shard_groups if g is not None and g.size > 1], None, args.train.seed or 1234,
+                        cuda=device.type == "cuda")
     if fused_comm is None:
         fused_comm = bool(int(os.environ.get("HG_FUSED_COMM", "0"))) and device.type == "cuda"
     stage = build_stage(spec, plan, groups, device, seed=args.train.seed or 1234, full_init=full_init,

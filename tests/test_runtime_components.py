@@ -341,3 +341,35 @@ def test_config_loader_overrides_and_zoo(tmp_path):
     assert "llama" in model_name(args)
     ov = loader.legacy_cli_to_overrides(["--pp_deg", "4", "--global_train_batch_size", "32", "--use-flash-attn"])
     assert "++runtime.parallel.pp_deg=4" in ov and "++runtime.train.global_batch_size=32" in ov
+
+
+# ---- random streams ---------------------------------------------------------------------------------------------
+def test_rng_tracker_streams():
+    from hetu_galvatron_b200.parallel import random as rnd
+
+    class G:
+        def __init__(self, size, rank):
+            self.size, self.rank = size, rank
+
+    t = rnd.set_seed_with_group([G(2, 1), G(2, 1), G(4, 3)], [G(8, 5)], seed=1234, cuda=False)
+    assert sorted(t.states_) == ["data-parallel-rng", "expert-parallel-rng-8", "model-parallel-rng-2", "model-parallel-rng-4"]
+    before = torch.get_rng_state()
+    with t.fork("model-parallel-rng-2"):
+        a = torch.rand(4)
+    assert torch.equal(torch.get_rng_state(), before)            # the default stream is untouched by the region
+    with t.fork("model-parallel-rng-2"):
+        b = torch.rand(4)
+    assert not torch.equal(a, b)                                 # the named stream advances
+    t2 = rnd.set_seed_with_group([G(2, 1)], None, 1234, cuda=False)
+    with t2.fork("model-parallel-rng-2"):
+        c = torch.rand(4)
+    assert torch.equal(a, c)                                     # same seed, same rank -> same stream
+    t3 = rnd.set_seed_with_group([G(2, 0)], None, 1234, cuda=False)
+    with t3.fork("model-parallel-rng-2"):
+        d = torch.rand(4)
+    assert not torch.equal(a, d)                                 # another rank of the group differs
+    with pytest.raises(ValueError):
+        t3.add("again", 1234)
+    with pytest.raises(KeyError):
+        with t3.fork("missing"):
+            pass
