@@ -1,0 +1,188 @@
+// ZeRO data-parallel hot path over NVLink peer memory: two kernels that replace
+// "NCCL reduce-scatter -> AdamW -> NCCL all-gather" on the flat gradient / parameter buffers of a wrap unit.
+//
+//   zero_reduce_scatter_kernel   out[i] = sum_r grad_r[me*S + i]          every rank's fp32 gradient buffer is read
+//                                                                          through its peer mapping (16-byte loads,
+//                                                                          all ranks' loads of an element group in
+//                                                                          flight together)
+//   zero_adamw_allgather_kernel  AdamW on this rank's shard (fp32 master weights and moments), then the updated
+//                                bf16 values are stored straight into every rank's parameter buffer at this
+//                                shard's offset (16-byte peer stores) -- the all-gather happens in the epilogue
+//
+// Neither kernel waits on another GPU: the callers order them against the peers' work with stream-ordered
+// collectives (a one-element all-reduce before the first kernel and after the second), so there is no spin-wait
+// and nothing here can hang.  Buffers that peers touch must come from one symmetric allocation per rank.
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace {
+
+constexpr int kMaxPeers = 8;
+constexpr int kThreads = 256;
+
+struct PeerPtrs {
+  void* p[kMaxPeers];
+};
+
+struct AdamHyper {
+  float lr, beta1, beta2, eps, weight_decay, bias1, bias2;
+};
+
+inline int grid_for(long long groups) {
+  long long g = (groups + kThreads - 1) / kThreads;
+  const long long cap = 148LL * 8;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return int(g);
+}
+
+// n4 = number of float4 groups of the shard.  T is the rank count (compile-time so that all T loads of a group are
+// issued before the first add).
+template <int T>
+__global__ void __launch_bounds__(kThreads)
+zero_reduce_scatter_kernel(PeerPtrs grads, int me, long long shard_floats, long long n4, float4* __restrict__ out) {
+  const float4* src[T];
+#pragma unroll
+  for (int r = 0; r < T; ++r) {
+    src[r] = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(grads.p[r]) + me * shard_floats);
+  }
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  for (; i + stride < n4; i += 2 * stride) {
+    float4 a[T], b[T];
+#pragma unroll
+    for (int r = 0; r < T; ++r) a[r] = __ldcs(src[r] + i);
+#pragma unroll
+    for (int r = 0; r < T; ++r) b[r] = __ldcs(src[r] + i + stride);
+    // fixed summation order (rank 0, 1, ...): deterministic
+    float4 sa = make_float4(0.f, 0.f, 0.f, 0.f), sb = sa;
+#pragma unroll
+    for (int r = 0; r < T; ++r) {
+      sa.x += a[r].x; sa.y += a[r].y; sa.z += a[r].z; sa.w += a[r].w;
+      sb.x += b[r].x; sb.y += b[r].y; sb.z += b[r].z; sb.w += b[r].w;
+    }
+    out[i] = sa;
+    out[i + stride] = sb;
+  }
+  for (; i < n4; i += stride) {
+    float4 a[T];
+#pragma unroll
+    for (int r = 0; r < T; ++r) a[r] = __ldcs(src[r] + i);
+    float4 sa = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < T; ++r) {
+      sa.x += a[r].x; sa.y += a[r].y; sa.z += a[r].z; sa.w += a[r].w;
+    }
+    out[i] = sa;
+  }
+}
+
+__device__ __forceinline__ float adam_one(float& p, float g, float& m, float& v, const AdamHyper& a, float step,
+                                          float inv_b2) {
+  m = a.beta1 * m + (1.f - a.beta1) * g;
+  v = a.beta2 * v + (1.f - a.beta2) * g * g;
+  p -= a.lr * a.weight_decay * p;
+  p -= step * m / (sqrtf(v) * inv_b2 + a.eps);
+  return p;
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// n8 = number of 8-element groups of the shard.  `params.p[r]` is rank r's bf16 parameter buffer; the shard's
+// values land at element offset `dst_off` in each of the `t_out` buffers.
+__global__ void __launch_bounds__(kThreads)
+zero_adamw_allgather_kernel(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ m,
+                            float* __restrict__ v, PeerPtrs params, int t_out, long long dst_off, long long n8,
+                            AdamHyper a, const float* __restrict__ gscale, const int* __restrict__ skip) {
+  if (skip != nullptr && *skip != 0) return;
+  const float gs = gscale ? *gscale : 1.f;
+  const float step = a.lr / a.bias1;
+  const float inv_b2 = rsqrtf(a.bias2);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += stride) {
+    float4 pv[2], gv[2], mv[2], vv[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      pv[h] = reinterpret_cast<const float4*>(p)[2 * i + h];
+      gv[h] = __ldcs(reinterpret_cast<const float4*>(g) + 2 * i + h);
+      mv[h] = reinterpret_cast<const float4*>(m)[2 * i + h];
+      vv[h] = reinterpret_cast<const float4*>(v)[2 * i + h];
+    }
+    uint4 packed;
+    uint32_t w[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const float x0 = adam_one(pv[h].x, gv[h].x * gs, mv[h].x, vv[h].x, a, step, inv_b2);
+      const float x1 = adam_one(pv[h].y, gv[h].y * gs, mv[h].y, vv[h].y, a, step, inv_b2);
+      const float x2 = adam_one(pv[h].z, gv[h].z * gs, mv[h].z, vv[h].z, a, step, inv_b2);
+      const float x3 = adam_one(pv[h].w, gv[h].w * gs, mv[h].w, vv[h].w, a, step, inv_b2);
+      w[2 * h] = pack2(x0, x1);
+      w[2 * h + 1] = pack2(x2, x3);
+      reinterpret_cast<float4*>(p)[2 * i + h] = pv[h];
+      reinterpret_cast<float4*>(m)[2 * i + h] = mv[h];
+      reinterpret_cast<float4*>(v)[2 * i + h] = vv[h];
+    }
+    packed = make_uint4(w[0], w[1], w[2], w[3]);
+    for (int r = 0; r < t_out; ++r) {
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + dst_off) + i;
+      *dst = packed;
+    }
+  }
+  // peer stores must be visible system-wide before the kernel is reported complete to the ordering collective
+  __threadfence_system();
+}
+
+}  // namespace
+
+extern "C" {
+
+// grads[r]: rank r's fp32 gradient buffer (t * shard_floats elements, peer-mapped).  out: this rank's reduced shard.
+// shard_floats must be a multiple of 4 and every buffer 16-byte aligned.
+int hg_zero_reduce_scatter(void* const* grads, int t, int me, long long shard_floats, void* out, void* stream) {
+  if (t < 1 || t > kMaxPeers || me < 0 || me >= t || shard_floats <= 0 || (shard_floats & 3)) return -1;
+  PeerPtrs pp{};
+  for (int r = 0; r < t; ++r) pp.p[r] = grads[r];
+  const long long n4 = shard_floats / 4;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int grid = grid_for((n4 + 1) / 2);
+#define HG_RS(T_) zero_reduce_scatter_kernel<T_><<<grid, kThreads, 0, st>>>(pp, me, shard_floats, n4, (float4*)out)
+  switch (t) {
+    case 1: HG_RS(1); break;
+    case 2: HG_RS(2); break;
+    case 3: HG_RS(3); break;
+    case 4: HG_RS(4); break;
+    case 5: HG_RS(5); break;
+    case 6: HG_RS(6); break;
+    case 7: HG_RS(7); break;
+    default: HG_RS(8); break;
+  }
+#undef HG_RS
+  return int(cudaGetLastError());
+}
+
+// AdamW on n elements (multiple of 8) of fp32 state; bf16 results stored at element offset dst_off of each of the
+// t_out buffers in params (peer-mapped parameter buffers, or just the local one).
+int hg_zero_adamw_allgather(void* p, const void* g, void* m, void* v, void* const* params, int t_out,
+                            long long dst_off, long long n, float lr, float beta1, float beta2, float eps,
+                            float weight_decay, int step, const void* gscale, const void* skip, void* stream) {
+  if (n <= 0) return 0;
+  if (t_out < 1 || t_out > kMaxPeers || (n & 7) || (dst_off & 7)) return -1;
+  PeerPtrs pp{};
+  for (int r = 0; r < t_out; ++r) pp.p[r] = params[r];
+  AdamHyper a;
+  a.lr = lr; a.beta1 = beta1; a.beta2 = beta2; a.eps = eps; a.weight_decay = weight_decay;
+  a.bias1 = 1.f - powf(beta1, float(step));
+  a.bias2 = 1.f - powf(beta2, float(step));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  zero_adamw_allgather_kernel<<<grid_for(n / 8), kThreads, 0, st>>>((float*)p, (const float*)g, (float*)m, (float*)v, pp,
+                                                                    t_out, dst_off, n / 8, a, (const float*)gscale,
+                                                                    (const int*)skip);
+  return int(cudaGetLastError());
+}
+
+}  // extern "C"

@@ -100,7 +100,8 @@ def _make_module(lp: LayerPlan, spec: ModelSpec, ctx: LayerCtx, device, tied_wei
 
 
 def build_stage(spec: ModelSpec, plan: HybridPlan, groups: ModelGroups, device, seed: int = 1234,
-                full_init: bool = False, fused_comm: bool = False, reduce_in_fp32: bool = True) -> StageModel:
+                full_init: bool = False, fused_comm: bool = False, reduce_in_fp32: bool = True,
+                fused_zero: bool = False) -> StageModel:
     """Instantiate, initialise and wrap the units of this rank's stage."""
     stage = StageModel()
     mine = plan.stage_layers(groups.stage)
@@ -130,10 +131,10 @@ def build_stage(spec: ModelSpec, plan: HybridPlan, groups: ModelGroups, device, 
             if lp.kind == "moe_decoder":
                 from .moe import wrap_moe_units
 
-                unit = wrap_moe_units(mod, lp, ctx, plan, reduce_in_fp32)
+                unit = wrap_moe_units(mod, lp, ctx, plan, reduce_in_fp32, fused_zero)
             else:
                 su = ShardedUnit(mod, lp.name, ctx.sdp, dp_size, lp.dp_type, reduce_in_fp32, tp=ctx.tp,
-                                 defer_sync=plan.async_grad_reduce)
+                                 defer_sync=plan.async_grad_reduce, fused_zero=fused_zero)
                 if lp.kind == "lm_head" and spec.tied and plan.pp_deg > 1:
                     su.count_in_norm = False  # the first stage's copy of the tied weight carries the norm
                 stage.sharded.append(su)

@@ -378,14 +378,15 @@ class MoELayerRunner(nn.Module):
         return ops_add(h, y.view(S, B, H))
 
 
-def wrap_moe_units(layer: GalvatronMoEDecoderLayer, lp, ctx: LayerCtx, plan, reduce_in_fp32: bool):
+def wrap_moe_units(layer: GalvatronMoEDecoderLayer, lp, ctx: LayerCtx, plan, reduce_in_fp32: bool,
+                   fused_zero: bool = False):
     dp_size = plan.dp_size(plan.layers[0])
     defer = plan.async_grad_reduce
     u_attn = ShardedUnit(layer.attention, lp.name + "_attention", ctx.sdp, dp_size, lp.dp_type, reduce_in_fp32, tp=ctx.tp,
-                         defer_sync=defer)
+                         defer_sync=defer, fused_zero=fused_zero)
     u_router = ShardedUnit(layer.router, lp.name + "_router", ctx.sdp, dp_size, "ddp", reduce_in_fp32, tp=ctx.tp,
                            defer_sync=defer)
     u_mlp = ShardedUnit(layer.mlp, lp.name + "_mlp", ctx.dp_of_ep, dp_size, lp.dp_type, reduce_in_fp32, tp=None,
-                        defer_sync=defer)
+                        defer_sync=defer, fused_zero=fused_zero)
     return MoELayerRunner(UnitWrapper(layer.attention, u_attn, lp.checkpoint), UnitWrapper(layer.router, u_router),
                           UnitWrapper(layer.mlp, u_mlp, lp.checkpoint), [u_attn, u_router, u_mlp])

@@ -1,0 +1,89 @@
+"""ZeRO gradient reduce-scatter and "AdamW + parameter all-gather" as our own kernels over NVLink peer memory
+(``csrc/sm100/fused_zero.cu``).
+
+A wrap unit that uses this path keeps its flat fp32 gradient buffer and its flat bf16 parameter buffer in symmetric
+memory (same size on every rank of the sharding group, mapped into every peer).  Per optimizer step:
+
+1. ``peer_barrier``          one-element all-reduce: every rank's backward has finished writing its gradients;
+2. ``reduce_scatter_peer``   this rank's shard = sum over ranks of their gradient buffers' slice (peer loads);
+3. (global gradient norm -- a scalar all-reduce over all ranks, which also orders step 2 on every rank before 4)
+4. ``adamw_allgather_peer``  AdamW on the shard; bf16 results stored into every rank's parameter buffer;
+5. ``peer_barrier``          every rank's stores have landed before anyone's next forward.
+
+The kernels never wait on another GPU; the ordering comes from the stream-ordered collectives of steps 1, 3, 5.
+This replaces FSDP's reduce-scatter / all-gather around the optimizer in the reference
+(galvatron/core/runtime/parallel.py:119-152, pipeline/grad_reduce.py:48-65, optimizer/utils.py:43-52).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, List, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..ops import _lib
+
+MAX_PEERS = 8
+
+
+class SymmetricBuffer:
+    """A tensor allocated identically on every rank of ``pg`` and mapped into all of them."""
+
+    def __init__(self, numel: int, dtype, device, pg):
+        import torch.distributed._symmetric_memory as symm
+
+        self.tensor = symm.empty(numel, dtype=dtype, device=device)
+        self.tensor.zero_()
+        self.handle = symm.rendezvous(self.tensor, pg)
+        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        self.t = len(self.ptrs)
+
+    def ptr_array(self, byte_offset: int = 0):
+        return (ctypes.c_void_p * self.t)(*[p + byte_offset for p in self.ptrs])
+
+
+def available(device, n: int) -> bool:
+    if device.type != "cuda" or n < 2 or n > MAX_PEERS:
+        return False
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+    except Exception:
+        return False
+    return True
+
+
+_TICKS: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def peer_barrier(pg, device):
+    """Stream-ordered rendezvous of the group: when it completes on this rank's stream, everything queued before
+    it on every rank's stream has completed."""
+    key = (id(pg), device.index if device.index is not None else 0)
+    t = _TICKS.get(key)
+    if t is None:
+        t = _TICKS[key] = torch.zeros(1, dtype=torch.float32, device=device)
+    dist.all_reduce(t, group=pg)
+
+
+def reduce_scatter_peer(grads: SymmetricBuffer, me: int, shard_numel: int, out: torch.Tensor):
+    lib = _lib.load()
+    rc = lib.hg_zero_reduce_scatter(grads.ptr_array(), grads.t, me, shard_numel, out.data_ptr(), _lib.stream())
+    _lib.check(rc, "hg_zero_reduce_scatter")
+    _lib.count_launch()
+    return out
+
+
+def adamw_allgather_peer(master, grad, exp_avg, exp_avg_sq, targets, dst_off: int, *, lr, beta1, beta2, eps,
+                         weight_decay, step, gscale=None, skip=None):
+    """``targets``: a ``SymmetricBuffer`` of bf16 parameters (stores go to every rank) or a local bf16 tensor."""
+    lib = _lib.load()
+    if isinstance(targets, SymmetricBuffer):
+        arr, t_out = targets.ptr_array(), targets.t
+    else:
+        arr, t_out = (ctypes.c_void_p * 1)(targets.data_ptr()), 1
+    rc = lib.hg_zero_adamw_allgather(master.data_ptr(), grad.data_ptr(), exp_avg.data_ptr(), exp_avg_sq.data_ptr(), arr,
+                                     t_out, dst_off, master.numel(), float(lr), float(beta1), float(beta2), float(eps),
+                                     float(weight_decay), int(step), _lib.ptr(gscale), _lib.ptr(skip), _lib.stream())
+    _lib.check(rc, "hg_zero_adamw_allgather")
+    _lib.count_launch()

@@ -37,6 +37,23 @@ def ulysses_attention(q, k, v, ctx, S_full: int):
     nh, ng = q.shape[2], k.shape[2]
     if nh % p:
         raise ValueError("query heads (%d) must be divisible by the Ulysses degree %d" % (nh, p))
+    if getattr(ctx, "fused_comm", False) and (ng % p == 0 or p % ng == 0):
+        from . import fused_a2a as fa
+
+        if fa.usable(q, ctx.sp):
+            # peer-memory path: the exchange and the layout change are one pull kernel per tensor; kv heads that
+            # would be replicated are pulled from their single owner instead
+            rep = p // ng if ng < p else 1
+            qg = fa.seq_to_heads(q, ctx.sp, p)
+            kg = fa.seq_to_heads(k, ctx.sp, p, rep)
+            vg = fa.seq_to_heads(v, ctx.sp, p, rep)
+            if ctx.cp_size > 1:
+                from .ring_attention import ring_attention
+
+                og = ring_attention(qg, kg, vg, ctx.cp, S_full)
+            else:
+                og = ops.flash_attention(qg, kg, vg, causal=True)
+            return fa.heads_to_seq(og, ctx.sp, p)
     if ng < p:
         rep = p // ng
         k = k.repeat_interleave(rep, dim=2)

@@ -51,7 +51,8 @@ def _group_info(g):
 
 class ShardedUnit:
     def __init__(self, module: nn.Module, name: str, sdp, dp_size: int, dp_type: str = "ddp",
-                 reduce_in_fp32: bool = True, tp=None, defer_sync: bool = True, grad_sum_group=None):
+                 reduce_in_fp32: bool = True, tp=None, defer_sync: bool = True, grad_sum_group=None,
+                 fused_zero: bool = False):
         self.module, self.name = module, name
         self.pg, self.n, self.rank = _group_info(sdp)
         self.dp_size = max(1, dp_size)
@@ -88,17 +89,32 @@ class ShardedUnit:
         self._reduced = False
         self._bwd_pending = False
         self.count_in_norm = True  # False for the second copy of a weight tied across pipeline stages
+        # own reduce-scatter / AdamW+all-gather kernels over peer memory instead of NCCL (parallel/fused_zero.py)
+        self.fused = False
+        if fused_zero and params and self.dp_type in ("zero2", "zero3"):
+            from . import fused_zero as fz
+
+            self.fused = fz.available(self.device, self.n)
         if params:
             self._materialise()
 
     # ---- construction ----------------------------------------------------------------------------
     def _materialise(self):
         dev = self.device
-        self.flat = torch.zeros(self.numel, dtype=self.dtype, device=dev)
+        self._sym_grad = self._sym_flat = None
+        if self.fused:
+            from . import fused_zero as fz
+
+            # peers read the gradient buffer and (ZeRO-2) write the parameter buffer: both symmetric
+            self._sym_grad = fz.SymmetricBuffer(self.numel, torch.float32, dev, self.pg)
+            if self.dp_type == "zero2" and self.dtype == torch.bfloat16:
+                self._sym_flat = fz.SymmetricBuffer(self.numel, self.dtype, dev, self.pg)
+        self.flat = self._sym_flat.tensor if self._sym_flat is not None else torch.zeros(self.numel, dtype=self.dtype, device=dev)
         for p, o in zip(self.params, self.offsets):
             self.flat[o:o + p.numel()].copy_(p.data.reshape(-1))
         self._bind_params()
-        self.main_grad = torch.zeros(self.numel, dtype=torch.float32, device=dev)
+        self.main_grad = self._sym_grad.tensor if self._sym_grad is not None else \
+            torch.zeros(self.numel, dtype=torch.float32, device=dev)
         for p, o in zip(self.params, self.offsets):
             p.main_grad = self.main_grad[o:o + p.numel()].view(p.shape)
             p.mg_fresh = True
@@ -197,7 +213,14 @@ class ShardedUnit:
                 p.main_grad.zero_()
                 p.mg_fresh = False
 
-    def _reduce_now(self) -> torch.Tensor:
+    def sync_peers(self):
+        """Stream-ordered rendezvous of the sharding group (fused path only)."""
+        if self.fused:
+            from . import fused_zero as fz
+
+            fz.peer_barrier(self.pg, self.device)
+
+    def _reduce_now(self, presynced: bool = False) -> torch.Tensor:
         """Sum the current ``main_grad`` over the sdp group; returns the buffer holding this rank's part."""
         self.prepare_grads()
         if self.tp_n > 1 and self.replicated_numel > 0:
@@ -210,6 +233,15 @@ class ShardedUnit:
             return self.main_grad
         if getattr(self, "_rs_out", None) is None:
             self._rs_out = torch.empty(self.shard_numel, dtype=torch.float32, device=self.device)
+        if self.fused:
+            from . import fused_zero as fz
+
+            if not presynced:
+                self.sync_peers()        # every rank's gradients are complete
+            fz.reduce_scatter_peer(self._sym_grad, self.rank, self.shard_numel, self._rs_out)
+            if not self.defer_sync:
+                self.sync_peers()        # main_grad is reused by the next micro-batch right away
+            return self._rs_out
         if self.main_grad.device.type == "cpu":
             tmp = self.main_grad.clone()
             dist.all_reduce(tmp, group=self.pg)
@@ -218,7 +250,7 @@ class ShardedUnit:
             dist.reduce_scatter_tensor(self._rs_out, self.main_grad, group=self.pg)
         return self._rs_out
 
-    def reduce_grads(self, final: bool = True):
+    def reduce_grads(self, final: bool = True, presynced: bool = False):
         """Gradient synchronisation.  Deferred mode: one reduction at the end of the step.  Immediate mode:
         every micro-batch's gradient is reduced right after the unit's backward and added to the running
         shard, and ``main_grad`` starts fresh for the next micro-batch."""
@@ -226,7 +258,7 @@ class ShardedUnit:
             return
         if self.defer_sync:
             if final:
-                self.grad_shard = self._reduce_now()
+                self.grad_shard = self._reduce_now(presynced)
                 self._reduced = True
             return
         if not final:
@@ -271,6 +303,17 @@ class ShardedUnit:
         g = self.grad_shard
         # fold the 1/dp average into the device-side gradient scale
         self._ensure_scale(clip_coef)
+        if self.fused and self.dtype == torch.bfloat16:
+            from . import fused_zero as fz
+
+            # ZeRO-2: the updated bf16 values go straight into every rank's parameter buffer (no all-gather);
+            # ZeRO-3: into the local bf16 shard.  The caller rendezvouses the group afterwards (sync_peers).
+            target = self._sym_flat if self.dp_type == "zero2" else self.shard_lp
+            off = self.rank * self.shard_numel if self.dp_type == "zero2" else 0
+            fz.adamw_allgather_peer(self.master, g, self.exp_avg, self.exp_avg_sq, target, off, lr=lr, beta1=beta1,
+                                    beta2=beta2, eps=eps, weight_decay=weight_decay, step=self.step_count,
+                                    gscale=self._scale)
+            return
         lp = self.shard_lp if self.dtype != torch.float32 else None
         ops.adamw_step(self.master, g, self.exp_avg, self.exp_avg_sq, lp, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
                        weight_decay=weight_decay, step=self.step_count, gscale=self._scale)

@@ -140,7 +140,8 @@ class GalvatronModel:
                 dist.all_reduce(w.main_grad, group=g.group)
 
 
-def build_model(args, device=None, full_init: bool = False, fused_comm: Optional[bool] = None) -> GalvatronModel:
+def build_model(args, device=None, full_init: bool = False, fused_comm: Optional[bool] = None,
+                fused_zero: Optional[bool] = None) -> GalvatronModel:
     """Resolve the configuration, create the process groups and instantiate this rank's stage."""
     world = dist.get_world_size() if dist.is_initialized() else 1
     rank = dist.get_rank() if dist.is_initialized() else 0
@@ -168,8 +169,11 @@ def build_model(args, device=None, full_init: bool = False, fused_comm: Optional
                         cuda=device.type == "cuda")
     if fused_comm is None:
         fused_comm = bool(int(os.environ.get("HG_FUSED_COMM", "0"))) and device.type == "cuda"
+    if fused_zero is None:
+        fused_zero = bool(int(os.environ.get("HG_FUSED_ZERO", "0"))) and device.type == "cuda"
     stage = build_stage(spec, plan, groups, device, seed=args.train.seed or 1234, full_init=full_init,
-                        fused_comm=fused_comm, reduce_in_fp32=args.parallel.reduce_in_fp32 or True)
+                        fused_comm=fused_comm, reduce_in_fp32=args.parallel.reduce_in_fp32 or True,
+                        fused_zero=fused_zero)
     if rank == 0 and os.environ.get("HG_QUIET", "0") != "1":
         print("================ hybrid-parallel plan (%s) ================" % plan.source)
         print(plan.describe())

@@ -38,9 +38,18 @@ class ShardedAdamW:
         for u in self.units:
             u.zero_grad()
 
-    def reduce_gradients(self):
+    def _sync_fused_groups(self):
+        """One rendezvous per distinct sharding group among the units that use the peer-memory kernels."""
+        seen = set()
         for u in self.units:
-            u.reduce_grads(final=True)
+            if getattr(u, "fused", False) and id(u.pg) not in seen:
+                seen.add(id(u.pg))
+                u.sync_peers()
+
+    def reduce_gradients(self):
+        self._sync_fused_groups()          # every rank's backward has written its gradients
+        for u in self.units:
+            u.reduce_grads(final=True, presynced=True)
 
     def compute_grad_norm(self):
         self._sumsq.zero_()
@@ -61,6 +70,7 @@ class ShardedAdamW:
         coef = self._coef if self.clip_grad > 0 else None
         for u in self.units:
             u.optimizer_step(g["lr"], g["betas"][0], g["betas"][1], g["eps"], g["weight_decay"], coef)
+        self._sync_fused_groups()          # peers' parameter stores have landed before the next forward
 
     def state_dict(self) -> Dict:
         return {"param_groups": self.param_groups, "state": {u.name: u.optimizer_state() for u in self.units}}
