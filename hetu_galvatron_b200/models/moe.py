@@ -274,6 +274,18 @@ class GalvatronMoEMLP(nn.Module):
         s, c = self.spec, self.ctx
         T, H = x2d.shape
         k, E, ep, E_loc = s.topk, s.experts, c.ep_size, self.experts.E_loc
+        if ep > 1 and getattr(c, "fused_comm", False) and c.etp_size == 1:
+            from ..parallel import fused_a2a as fa
+
+            if fa.usable(x2d, c.ep):
+                # peer-memory path: tokens are pulled from their source ranks straight into the aligned expert
+                # segments (all-to-all + permute in one kernel) and the outputs are pulled back home the same way
+                plan = fa.MoERouting(idx.to(torch.int32), c.ep, E, SEG_ALIGN)
+                buf = fa.moe_dispatch(x2d, plan)
+                out_buf = self.experts(buf, plan.row_start)
+                back = fa.moe_combine(out_buf, plan).view(T, k, H)
+                w = torch.where(idx >= 0, probs, torch.zeros_like(probs)).to(torch.float32)
+                return (back.float() * w[..., None]).sum(1).to(x2d.dtype)
         flat_e = idx.reshape(-1)
         valid = flat_e >= 0
         sort_key = torch.where(valid, flat_e, torch.full_like(flat_e, E))

@@ -144,3 +144,113 @@ def gather_rows(slot: SymmetricBuffer, peer: torch.Tensor, row: torch.Tensor, n_
     _lib.check(rc, "hg_peer_gather_rows_bf16")
     _lib.count_launch()
     return out
+
+
+class MoERouting:
+    """Placement of every routed (rank, token, slot) of an expert-parallel group, computed identically on every rank
+    from the all-gathered top-k expert indices.
+
+    Destination rank ``D`` lays its local experts out as aligned, zero-padded segments; within an expert the rows
+    are ordered by (source rank, token, slot).  From that one table follow
+
+    * ``peer_d / tok_d / slot_d`` ``[total_D]``: for each row of this rank's expert buffer, where it comes from
+      (``-1`` for padding rows);
+    * ``peer_s / row_s`` ``[T*k]``: for each of this rank's (token, slot) pairs, where its expert output lives
+      (``-1`` for dropped pairs);
+    * ``row_start`` ``[E_loc + 1]`` int32 segment starts for the grouped GEMM; ``totals`` rows per rank (host list).
+    """
+
+    def __init__(self, idx: torch.Tensor, group, num_experts: int, align: int):
+        import torch.distributed as dist
+
+        ep, me = group.size, group.rank
+        T, k = idx.shape
+        E, E_loc = num_experts, num_experts // ep
+        dev = idx.device
+        idx_all = torch.empty((ep, T, k), dtype=idx.dtype, device=dev)
+        dist.all_gather_into_tensor(idx_all, idx.contiguous(), group=group.group)
+        flat = idx_all.reshape(-1).long()
+        valid = flat >= 0
+        key = torch.where(valid, flat, torch.full_like(flat, E))
+        order = torch.argsort(key, stable=True)
+        key_sorted = key[order]
+        counts = torch.bincount(key, minlength=E + 1)[:E]
+        ustart = torch.cumsum(counts, 0) - counts
+        padded = (counts + align - 1) // align * align
+        per_rank = padded.view(ep, E_loc)
+        astart = (torch.cumsum(per_rank, 1) - per_rank).reshape(-1)            # start of each expert on its rank
+        totals_t = per_rank.sum(1).clamp(min=align)
+        n_valid_sorted = key_sorted < E
+        ks = key_sorted.clamp(max=E - 1)
+        pos = torch.arange(flat.numel(), device=dev) - ustart[ks]
+        dest_row_sorted = torch.where(n_valid_sorted, astart[ks] + pos, torch.full_like(pos, -1))
+        dest_row = torch.empty_like(dest_row_sorted)
+        dest_row[order] = dest_row_sorted
+        dest_rank = torch.where(valid, flat // E_loc, torch.full_like(flat, -1))
+        self.totals = [int(x) for x in totals_t.tolist()]                      # one host read per layer call
+        self.total, self.max_total = self.totals[me], max(self.totals)
+        self.T, self.k, self.ep, self.me = T, k, ep, me
+        n = T * k
+        self.peer_s = dest_rank[me * n:(me + 1) * n].to(torch.int32).contiguous()
+        self.row_s = dest_row[me * n:(me + 1) * n].clamp(min=0).to(torch.int32).contiguous()
+        mine = dest_rank == me
+        src_flat = torch.nonzero(mine, as_tuple=False).squeeze(1)              # index into (r, t, slot)
+        rows = dest_row[src_flat]
+        self.peer_d = torch.full((self.total,), -1, dtype=torch.int32, device=dev)
+        self.tok_d = torch.zeros((self.total,), dtype=torch.int32, device=dev)
+        self.slot_d = torch.zeros((self.total,), dtype=torch.int32, device=dev)
+        r_of, rem = src_flat // n, src_flat % n
+        self.peer_d[rows] = r_of.to(torch.int32)
+        self.tok_d[rows] = (rem // k).to(torch.int32)
+        self.slot_d[rows] = rem.to(torch.int32)
+        local_astart = astart.view(ep, E_loc)[me]
+        self.row_start = torch.cat([local_astart, per_rank[me].sum().reshape(1)]).to(torch.int32)
+        self.group = group
+
+
+def _publish_sized(group, x: torch.Tensor, rows_bound: int) -> SymmetricBuffer:
+    """Publish ``x [rows, width]``; the staging is sized by ``rows_bound`` (the same number on every rank)."""
+    st = staging_for(group, rows_bound * x.shape[1] * 2, x.device)
+    return st.publish(x.contiguous())
+
+
+class _MoEDispatch(torch.autograd.Function):
+    """``x [T, H]`` on every rank -> this rank's expert buffer ``[total, H]`` (aligned, zero-padded segments)."""
+
+    @staticmethod
+    def forward(ctx, x, plan: MoERouting):
+        ctx.plan = plan
+        slot = _publish_sized(plan.group, x, plan.T)
+        return gather_rows(slot, plan.peer_d, plan.tok_d, plan.total, x.shape[1], x.shape[1])
+
+    @staticmethod
+    def backward(ctx, g):
+        p = ctx.plan
+        slot = _publish_sized(p.group, g, p.max_total)
+        # every token sums the gradients of its k copies, wherever they were processed
+        return gather_rows(slot, p.peer_s.view(p.T, p.k), p.row_s.view(p.T, p.k), p.T, g.shape[1], g.shape[1], p.k), None
+
+
+class _MoECombine(torch.autograd.Function):
+    """Expert outputs ``[total, H]`` on every rank -> ``[T*k, H]``: each (token, slot) pair's output back home
+    (zeros for dropped pairs)."""
+
+    @staticmethod
+    def forward(ctx, y, plan: MoERouting):
+        ctx.plan = plan
+        slot = _publish_sized(plan.group, y, plan.max_total)
+        return gather_rows(slot, plan.peer_s, plan.row_s, plan.T * plan.k, y.shape[1], y.shape[1])
+
+    @staticmethod
+    def backward(ctx, g):
+        p = ctx.plan
+        slot = _publish_sized(p.group, g, p.T * p.k)
+        return gather_rows(slot, p.peer_d, p.slot_d, p.total, g.shape[1], g.shape[1]), None
+
+
+def moe_dispatch(x, plan: MoERouting):
+    return _MoEDispatch.apply(x, plan)
+
+
+def moe_combine(y, plan: MoERouting):
+    return _MoECombine.apply(y, plan)

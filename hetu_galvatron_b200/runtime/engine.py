@@ -170,7 +170,7 @@ def build_model(args, device=None, full_init: bool = False, fused_comm: Optional
     if fused_comm is None:
         fused_comm = bool(int(os.environ.get("HG_FUSED_COMM", "0"))) and device.type == "cuda"
     if fused_zero is None:
-        fused_zero = bool(int(os.environ.get("HG_FUSED_ZERO", "0"))) and device.type == "cuda"
+        fused_zero = bool(int(os.environ.get("HG_FUSED_ZERO", "1"))) and device.type == "cuda"
     stage = build_stage(spec, plan, groups, device, seed=args.train.seed or 1234, full_init=full_init,
                         fused_comm=fused_comm, reduce_in_fp32=args.parallel.reduce_in_fp32 or True,
                         fused_zero=fused_zero)
