@@ -1,0 +1,371 @@
+// bf16 GEMM on CTA pairs: tcgen05.mma.cta_group::2 with a 256 x 256 x 64 tile per two-SM cluster.
+//
+// Compared with the one-CTA kernel (gemm.cu, 128 x 256 tile per SM) each SM stages only half of the B tile: the
+// pair's MMA reads A rows [0,128) / [128,256) from the two CTAs' shared memory and the two halves of B's N range
+// from both, so a 128 x 256 slice of the output costs 32 KB of operand traffic per k-block per SM instead of 48 KB,
+// and six stages fit where four did.
+//
+// Roles per CTA (192 threads): warp 0 TMA producer (one lane), warp 1 TMEM allocator (+ UMMA issuer in the leader
+// CTA only), warps 2-5 epilogue.  Barriers (same shared-memory offsets in both CTAs):
+//   full[s]        leader only; the leader's producer arrives with the byte count of BOTH CTAs' loads, every load
+//                  (from either CTA) completes its bytes on the leader's barrier
+//   empty[s]       both CTAs; signalled by tcgen05.commit with a cluster mask covering the pair
+//   tmem_full[a]   both CTAs; same mechanism, once per tile
+//   tmem_empty[a]  leader only; all 256 epilogue threads of the pair arrive (the peer's through its cluster address)
+// Every wait is bounded (2 s); a CTA that gives up raises its abort flag and the status word, its partner runs into
+// its own limit, and both still meet at the final cluster barrier and free their tensor memory.
+// No operand load uses cluster multicast: each CTA loads exactly the bytes it alone needs.
+#include "gemm_core.cuh"
+
+namespace hg {
+namespace gemm2 {
+
+using namespace hg::gemm;
+
+constexpr int CM = 256;                       // rows of the pair's tile
+constexpr int HALF_N = BN / 2;                // B rows staged by one CTA
+constexpr int STAGES2 = 6;
+constexpr int A2_BYTES = BM * BK * 2;         // 16 KB
+constexpr int B2_BYTES = HALF_N * BK * 2;     // 16 KB
+constexpr int SMEM2_BYTES = STAGES2 * (A2_BYTES + B2_BYTES) + 1024 + 256;
+constexpr uint16_t kPairMask = 0x3;
+
+struct Smem2 {
+  uint8_t* a;
+  uint8_t* b;
+  uint64_t* full;
+  uint64_t* empty;
+  uint64_t* tmem_full;
+  uint64_t* tmem_empty;
+  uint32_t* tmem_base;
+  volatile int* abort;
+};
+
+__device__ __forceinline__ Smem2 carve2(uint8_t* raw) {
+  Smem2 s;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(raw) + 1023) & ~uintptr_t(1023));
+  s.a = base;
+  s.b = base + STAGES2 * A2_BYTES;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(base + STAGES2 * (A2_BYTES + B2_BYTES));
+  s.full = bars;
+  s.empty = bars + STAGES2;
+  s.tmem_full = bars + 2 * STAGES2;
+  s.tmem_empty = bars + 2 * STAGES2 + 2;
+  s.tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
+  s.abort = reinterpret_cast<volatile int*>(s.tmem_base + 1);
+  return s;
+}
+
+// ---- cluster / pair primitives -------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of `local_addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// 2-D tile load into this CTA's shared memory; the bytes complete on the barrier at `bar_cluster_addr`
+// (the leader's).  No multicast: the destination is this CTA only.
+__device__ __forceinline__ void tma_load_2d_pair(void* smem_dst, const CUtensorMap* m, uint32_t bar_cluster_addr, int c0,
+                                                 int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                 uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on the barrier at this shared-memory offset in every CTA of `mask` once the issued MMAs retired.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t mask) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+          smem_u32(bar)),
+      "h"(mask)
+      : "memory");
+}
+
+// ---- roles ------------------------------------------------------------------------------------------------------
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void producer2(const CUtensorMap* tmA, const CUtensorMap* tmB, const Params& p, const Smem2& s,
+                                          uint32_t rank, int first, int step, int num_tiles) {
+  uint32_t stage = 0, phase = 0;
+  bool issued[STAGES2];
+  uint32_t issued_parity[STAGES2];
+#pragma unroll
+  for (int i = 0; i < STAGES2; ++i) { issued[i] = false; issued_parity[i] = 0; }
+  const int num_kb = (p.K + BK - 1) / BK;
+  bool ok = true;
+  for (int tile = first; ok && tile < num_tiles; tile += step) {
+    int tm, tn;
+    tile_coords(p, tile, tm, tn);
+    const int m0 = tm * CM + int(rank) * BM;
+    const int n0 = tn * BN + int(rank) * HALF_N;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      if (*s.abort || !mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }
+      if (rank == 0) mbar_expect_tx(&s.full[stage], 2 * (A2_BYTES + B2_BYTES));
+      const uint32_t bar = map_to_cta(smem_u32(&s.full[stage]), 0);
+      uint8_t* sa = s.a + stage * A2_BYTES;
+      uint8_t* sb = s.b + stage * B2_BYTES;
+      const int k0 = kb * BK;
+      if (A_MN) {
+#pragma unroll
+        for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * SLAB_BYTES, tmA, bar, m0 + j * 64, k0);
+      } else {
+        tma_load_2d_pair(sa, tmA, bar, k0, m0);
+      }
+      if (B_MN) {
+#pragma unroll
+        for (int j = 0; j < HALF_N / 64; ++j) tma_load_2d_pair(sb + j * SLAB_BYTES, tmB, bar, n0 + j * 64, k0);
+      } else {
+        tma_load_2d_pair(sb, tmB, bar, k0, n0);
+      }
+      issued[stage] = true;
+      issued_parity[stage] = phase;
+      if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+    }
+  }
+  if (!ok) {
+    *s.abort = 1;
+    if (rank == 0) {
+      // the leader can see its own copies land; give them a bounded moment before shared memory is released
+#pragma unroll
+      for (int i = 0; i < STAGES2; ++i)
+        if (issued[i])
+          for (uint32_t spin = 0; spin < (1u << 16); ++spin)
+            if (mbar_try_wait(&s.full[i], issued_parity[i])) break;
+    } else {
+      const uint64_t t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);  // 2 ms: far longer than a tile load
+    }
+  }
+}
+
+template <bool A_MN, bool B_MN>
+__device__ __forceinline__ void mma2(const Params& p, const Smem2& s, uint32_t tmem_base, int first, int step,
+                                     int num_tiles) {
+  constexpr uint32_t idesc = make_idesc_bf16(CM, BN, A_MN, B_MN);
+  constexpr uint32_t a_lbo = A_MN ? SLAB_BYTES : 16, a_sbo = 1024, a_kadv = A_MN ? 2048 : 32;
+  constexpr uint32_t b_lbo = B_MN ? SLAB_BYTES : 16, b_sbo = 1024, b_kadv = B_MN ? 2048 : 32;
+  const int num_kb = (p.K + BK - 1) / BK;
+  uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+  bool ok = true;
+  for (int tile = first; ok && tile < num_tiles; tile += step) {
+    if (*s.abort || !mbar_wait(&s.tmem_empty[acc], acc_phase ^ 1, p.status, kTimeoutTmemEmpty, s.abort)) { ok = false; break; }
+    tc_fence_after();
+    const uint32_t d = tmem_base + acc * BN;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      if (*s.abort || !mbar_wait(&s.full[stage], phase, p.status, kTimeoutSmemFull, s.abort)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t sa = smem_u32(s.a + stage * A2_BYTES);
+      const uint32_t sb = smem_u32(s.b + stage * B2_BYTES);
+#pragma unroll
+      for (int k = 0; k < BK / UMMA_K; ++k) {
+        const uint64_t da = make_smem_desc(sa + k * a_kadv, a_lbo, a_sbo);
+        const uint64_t db = make_smem_desc(sb + k * b_kadv, b_lbo, b_sbo);
+        umma_f16_ss_pair(d, da, db, idesc, (kb | k) != 0);
+      }
+      umma_commit_pair(&s.empty[stage], kPairMask);
+      if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+    }
+    if (!ok) break;
+    umma_commit_pair(&s.tmem_full[acc], kPairMask);
+    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+  }
+  if (!ok) *s.abort = 1;
+}
+
+__device__ __forceinline__ void epilogue2(const Params& p, const Smem2& s, uint32_t tmem_base, uint32_t rank, int first,
+                                          int step, int num_tiles) {
+  const int wq = (threadIdx.x >> 5) & 3;
+  const uint32_t lane_off = uint32_t(wq * 32) << 16;
+  uint32_t acc = 0, acc_phase = 0;
+  for (int tile = first; tile < num_tiles; tile += step) {
+    int tm, tn;
+    tile_coords(p, tile, tm, tn);
+    const int row = tm * CM + int(rank) * BM + wq * 32 + lane_id();
+    const int n0 = tn * BN;
+    if (*s.abort || !mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort)) {
+      *s.abort = 1;
+      break;
+    }
+    tc_fence_after();
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; c += 2) {
+      uint32_t r0[32], r1[32];
+      tmem_ld32(tmem_base + lane_off + acc * BN + c * 32, r0);
+      tmem_ld32(tmem_base + lane_off + acc * BN + (c + 1) * 32, r1);
+      tmem_ld_wait();
+      if (row < p.M) {
+        if (n0 + c * 32 < p.N) store_row_chunk(p, row, n0 + c * 32, r0);
+        if (n0 + (c + 1) * 32 < p.N) store_row_chunk(p, row, n0 + (c + 1) * 32, r1);
+      }
+    }
+    tc_fence_before();
+    // the accumulator buffer is free again once all 256 epilogue threads of the pair have read it
+    if (rank == 0) mbar_arrive(&s.tmem_empty[acc]);
+    else mbar_arrive_cluster(map_to_cta(smem_u32(&s.tmem_empty[acc]), 0));
+    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+  }
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(192, 1)
+gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  Smem2 s = carve2(smem_raw);
+  const int warp = threadIdx.x >> 5;
+  const uint32_t rank = cluster_ctarank();
+  const int num_tiles = p.tiles_m * p.tiles_n;
+  const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+#pragma unroll
+    for (int i = 0; i < STAGES2; ++i) {
+      mbar_init(&s.full[i], 1);
+      mbar_init(&s.empty[i], 1);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&s.tmem_full[i], 1);
+      mbar_init(&s.tmem_empty[i], 2 * EPI_WARPS * 32);
+    }
+    *s.abort = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(s.tmem_base, TMEM_COLS);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the partner's barriers exist before anything arrives on them remotely
+  tc_fence_after();
+  const uint32_t tmem_base = *s.tmem_base;
+
+  if (warp == 0) {
+    if (lane_id() == 0) producer2<A_MN, B_MN>(&tmA, &tmB, p, s, rank, pair, pairs, num_tiles);
+  } else if (warp == 1) {
+    if (rank == 0 && lane_id() == 0) mma2<A_MN, B_MN>(p, s, tmem_base, pair, pairs, num_tiles);
+  } else {
+    epilogue2(p, s, tmem_base, rank, pair, pairs, num_tiles);
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // neither CTA frees tensor memory or leaves while its partner may still touch it
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace gemm2
+}  // namespace hg
+
+using namespace hg::gemm;
+using namespace hg::gemm2;
+
+template <bool A_MN, bool B_MN>
+static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int want_pairs, cudaStream_t st) {
+  static int max_pairs = -1;
+  auto k = gemm2_bf16_kernel<A_MN, B_MN>;
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.blockDim = dim3(192, 1, 1);
+  cfg.dynamicSmemBytes = SMEM2_BYTES;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (max_pairs < 0) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+    if (e != cudaSuccess) return int(e);
+    int sms = 0, dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cfg.gridDim = dim3(unsigned(sms / 2 * 2), 1, 1);
+    int n = 0;
+    e = cudaOccupancyMaxActiveClusters(&n, k, &cfg);
+    if (e != cudaSuccess) return int(e);
+    if (n <= 0) return -2;
+    max_pairs = n;
+  }
+  const int pairs = want_pairs < max_pairs ? want_pairs : max_pairs;
+  cfg.gridDim = dim3(unsigned(2 * pairs), 1, 1);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, k, ta, tb, p);
+  return int(e);
+}
+
+extern "C" {
+
+// Same contract as hg_gemm_bf16 (gemm.cu), computed by CTA pairs.  Returns -2 when the device cannot co-schedule a
+// pair of these CTAs (the caller then uses the one-CTA kernel).
+int hg_gemm2_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K, int lda, int ldb,
+                  int ldc, int a_mn, int b_mn, int out_mode, int max_ctas, void* stream) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15))
+    return -1;
+  CUtensorMap ta, tb;
+  int rc;
+  if (a_mn) rc = hg_host::make_tmap_2d_bf16(&ta, A, K, M, lda, 64, 64);
+  else      rc = hg_host::make_tmap_2d_bf16(&ta, A, M, K, lda, BM, 64);
+  if (rc) return rc;
+  if (b_mn) rc = hg_host::make_tmap_2d_bf16(&tb, B, K, N, ldb, 64, 64);
+  else      rc = hg_host::make_tmap_2d_bf16(&tb, B, N, K, ldb, HALF_N, 64);
+  if (rc) return rc;
+  Params p{};
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C;
+  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.out_mode = out_mode;
+  p.tiles_m = (M + CM - 1) / CM;
+  p.tiles_n = (N + BN - 1) / BN;
+  p.group_m = 4;
+  p.status = hg_host::status_ptr();
+  p.ready = nullptr; p.rows_per_flag = 1; p.ready_target = 0; p.m_tile_shift = 0;
+  p.k_ranges = nullptr; p.groups = 1; p.c_group_stride = 0;
+  int pairs = p.tiles_m * p.tiles_n;
+  if (max_ctas > 1 && max_ctas / 2 < pairs) pairs = max_ctas / 2;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (a_mn && b_mn) return launch2<true, true>(ta, tb, p, pairs, st);
+  if (a_mn) return launch2<true, false>(ta, tb, p, pairs, st);
+  if (b_mn) return launch2<false, true>(ta, tb, p, pairs, st);
+  return launch2<false, false>(ta, tb, p, pairs, st);
+}
+
+}  // extern "C"

@@ -64,6 +64,11 @@ def set_aux_loss_scale(scale: float):
 def topk_routing(logits: torch.Tensor, spec: ModelSpec, expert_bias: Optional[torch.Tensor] = None):
     """logits [T, E] (fp32) -> (probs [T, k], idx [T, k]); differentiable in probs."""
     k, E = spec.topk, logits.shape[1]
+    if logits.is_cuda and not (spec.router_groups and spec.router_group_topk) and E <= 256 and k <= 8:
+        # one kernel per direction: scores, selection, probabilities (ops/fused.py::router_topk)
+        probs, idx, _, _ = ops.router_topk(logits, k, spec.router_score, spec.router_pre_softmax, expert_bias,
+                                           spec.router_scaling)
+        return probs, idx
 
     def limited_topk(scores):
         if spec.router_groups and spec.router_group_topk:

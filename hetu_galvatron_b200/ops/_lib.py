@@ -27,12 +27,15 @@ class AttnTensor(ctypes.Structure):
 
 _SIGNATURES = {
     "hg_gemm_bf16": [c_void_p] * 4 + [c_int] * 10 + [c_void_p],
+    "hg_gemm2_bf16": [c_void_p] * 4 + [c_int] * 10 + [c_void_p],
     "hg_grouped_gemm_bf16": [c_void_p] * 4 + [c_int] * 9 + [c_void_p],
     "hg_grouped_wgrad_bf16": [c_void_p] * 4 + [c_int] * 8 + [c_void_p],
     "hg_norm_fwd": [c_void_p] * 8 + [c_int, c_int, c_float, c_int, c_void_p],
     "hg_norm_bwd": [c_void_p] * 10 + [c_int] * 5 + [c_void_p],
     "hg_peer_gather_bf16": [c_void_p, c_int, c_ll, c_ll, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p],
     "hg_peer_gather_rows_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_void_p, c_void_p, c_void_p],
+    "hg_router_topk_fwd": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 5,
+    "hg_router_topk_bwd": [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "hg_zero_reduce_scatter": [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p],
     "hg_zero_adamw_allgather": [c_void_p] * 5 + [c_int, c_ll, c_ll] + [ctypes.c_float] * 5 + [c_int, c_void_p, c_void_p, c_void_p],
     "hg_rope": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,

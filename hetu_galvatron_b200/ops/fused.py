@@ -360,3 +360,72 @@ def cross_entropy(logits: torch.Tensor, targets: torch.Tensor, v0: int = 0, grou
     if logits.stride(1) != 1:
         logits = logits.contiguous()
     return _CrossEntropy.apply(logits, targets.contiguous().long(), v0, group)
+
+
+# ---- top-k router ---------------------------------------------------------------------------------------------
+ROUTER_MODES = {("softmax", False): 0, ("softmax", True): 1, ("sigmoid", False): 2, ("sigmoid", True): 2}
+
+
+class _RouterTopK(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, bias, k, mode, scaling):
+        lib = _lib.load()
+        T, E = logits.shape
+        dev = logits.device
+        probs = torch.empty((T, k), dtype=torch.float32, device=dev)
+        idx = torch.empty((T, k), dtype=torch.int32, device=dev)
+        scores = torch.empty((T, E), dtype=torch.float32, device=dev)
+        counts = torch.zeros(E, dtype=torch.float32, device=dev)
+        rc = lib.hg_router_topk_fwd(logits.data_ptr(), _lib.ptr(bias), T, E, k, mode, float(scaling), probs.data_ptr(),
+                                    idx.data_ptr(), scores.data_ptr(), counts.data_ptr(), _lib.stream())
+        _lib.check(rc, "hg_router_topk_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(scores, probs, idx)
+        ctx.k, ctx.mode, ctx.scaling = k, mode, scaling
+        ctx.mark_non_differentiable(idx, counts)
+        return probs, idx, scores, counts
+
+    @staticmethod
+    def backward(ctx, dprobs, _didx, dscores, _dcounts):
+        scores, probs, idx = ctx.saved_tensors
+        lib = _lib.load()
+        T, E = scores.shape
+        dlogits = torch.empty_like(scores)
+        dprobs = dprobs.contiguous().float()
+        ds = dscores.contiguous().float() if dscores is not None else None
+        rc = lib.hg_router_topk_bwd(scores.data_ptr(), probs.data_ptr(), idx.data_ptr(), dprobs.data_ptr(), _lib.ptr(ds), T,
+                                    E, ctx.k, ctx.mode, float(ctx.scaling), dlogits.data_ptr(), _lib.stream())
+        _lib.check(rc, "hg_router_topk_bwd")
+        _lib.count_launch()
+        return dlogits, None, None, None, None
+
+
+def router_topk(logits: torch.Tensor, k: int, score: str = "softmax", pre_softmax: bool = False,
+                bias: torch.Tensor | None = None, scaling: float | None = None):
+    """``logits [T, E]`` fp32 -> ``(probs [T, k] fp32, idx [T, k] int64, scores [T, E] fp32, counts [E] fp32)``.
+
+    One kernel per direction on CUDA (E <= 256, k <= 8); ``scores`` is the full softmax / sigmoid (differentiable,
+    for the load-balancing losses) and ``counts`` the number of tokens sent to every expert."""
+    mode = ROUTER_MODES[(score, bool(pre_softmax))]
+    if logits.is_cuda and logits.shape[1] <= 256 and k <= 8:
+        probs, idx, scores, counts = _RouterTopK.apply(logits.contiguous().float(), bias, k, mode, scaling or 1.0)
+        return probs, idx.long(), scores, counts
+    if mode == 2:
+        scores = torch.sigmoid(logits)
+        sel = scores + bias if bias is not None else scores
+        idx = sel.topk(k, dim=-1).indices
+        probs = scores.gather(1, idx)
+        if k > 1:
+            probs = probs / (probs.sum(-1, keepdim=True) + 1e-20)
+    else:
+        scores = torch.softmax(logits, dim=-1)
+        if mode == 1:
+            probs, idx = scores.topk(k, dim=-1)
+        else:
+            vals, idx = logits.topk(k, dim=-1)
+            probs = torch.softmax(vals, dim=-1)
+    if scaling:
+        probs = probs * scaling
+    counts = torch.zeros(logits.shape[1], dtype=torch.float32, device=logits.device)
+    counts.index_add_(0, idx.reshape(-1), torch.ones(idx.numel(), dtype=torch.float32, device=logits.device))
+    return probs, idx, scores, counts

@@ -15,6 +15,8 @@ Reference call sites replaced: galvatron/core/runtime/tensor_parallel/layers.py:
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
@@ -30,11 +32,26 @@ def _rowmajor(t: torch.Tensor) -> torch.Tensor:
     return t
 
 
+# CTA-pair kernel (tcgen05.mma.cta_group::2, 256x256 tiles): "auto" uses it for problems of at least one pair tile,
+# "0" never, "1" always.  The one-CTA kernel is the fallback when the device cannot co-schedule a pair.
+_PAIR_MODE = os.environ.get("HG_GEMM_PAIR", "0")
+_pair_ok = True
+
+
+def _use_pair(M: int, N: int, pair) -> bool:
+    if pair is not None:
+        return bool(pair)
+    if not _pair_ok or _PAIR_MODE == "0":
+        return False
+    return _PAIR_MODE == "1" or (M >= 256 and N >= 256)
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False, out: torch.Tensor | None = None,
-         out_mode: int = OUT_BF16, bias: torch.Tensor | None = None, max_ctas: int = 0) -> torch.Tensor:
+         out_mode: int = OUT_BF16, bias: torch.Tensor | None = None, max_ctas: int = 0, pair=None) -> torch.Tensor:
     """``C[M,N] = op(A) op(B)`` with fp32 accumulation.
 
     ``a`` is ``[M,K]`` (or ``[K,M]`` when ``a_mn``), ``b`` is ``[N,K]`` (or ``[K,N]`` when ``b_mn``).
+    ``pair``: force (True) / forbid (False) the CTA-pair kernel; ``None`` follows ``HG_GEMM_PAIR``.
     """
     if not a.is_cuda:
         A = a.t() if a_mn else a
@@ -71,6 +88,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         if out.shape[0] != M or out.shape[1] != N or out.stride(1) != 1:
             raise ValueError("bad output tensor")
     lib = _lib.load()
+    if _use_pair(M, N, pair):
+        rc = lib.hg_gemm2_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K, a.stride(0),
+                               b.stride(0), out.stride(0), int(a_mn), int(b_mn), out_mode, max_ctas, _lib.stream())
+        if rc == 0:
+            _lib.count_launch()
+            return out
+        if rc != -2 or pair:
+            raise _lib.KernelError("hg_gemm2_bf16 failed with code %d (M=%d N=%d K=%d a_mn=%d b_mn=%d)" % (rc, M, N, K, a_mn, b_mn))
+        global _pair_ok
+        _pair_ok = False  # this device cannot co-schedule the pair: one-CTA kernel from now on
     rc = lib.hg_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), _lib.ptr(bias), M, N, K, a.stride(0),
                           b.stride(0), out.stride(0), int(a_mn), int(b_mn), out_mode, max_ctas, _lib.stream())
     if rc != 0:

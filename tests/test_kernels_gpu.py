@@ -274,3 +274,55 @@ def test_bounded_wait_reports_status():
     assert code == 5
     x = torch.ones(4, device=DEV)
     assert (x + 1).sum().item() == 8
+
+
+@pytest.mark.parametrize("score,pre", [("softmax", False), ("softmax", True), ("sigmoid", False)])
+@pytest.mark.parametrize("E,k", [(8, 2), (64, 6), (160, 8)])
+def test_router_topk(score, pre, E, k):
+    """The fused router kernel against the plain PyTorch formulation, values and gradients (through both the
+    selected probabilities and the full score matrix used by load-balancing losses)."""
+    torch.manual_seed(E + k)
+    T = 777
+    logits = torch.randn(T, E, device=DEV) * 2.0
+    bias = torch.randn(E, device=DEV) * 0.1 if score == "sigmoid" else None
+    wp = torch.randn(T, k, device=DEV)
+    ws = torch.randn(T, E, device=DEV)
+    a = logits.clone().requires_grad_()
+    probs, idx, scores, counts = ops.router_topk(a, k, score, pre, bias, 1.5)
+    ((probs * wp).sum() + (scores * ws).sum()).backward()
+    b = logits.clone().requires_grad_()
+    if score == "sigmoid":
+        sc = torch.sigmoid(b)
+        ridx = (sc + bias).topk(k, dim=-1).indices
+        rp = sc.gather(1, ridx)
+        rp = rp / (rp.sum(-1, keepdim=True) + 1e-20)
+    else:
+        sc = torch.softmax(b, dim=-1)
+        if pre:
+            rp, ridx = sc.topk(k, dim=-1)
+        else:
+            v, ridx = b.topk(k, dim=-1)
+            rp = torch.softmax(v, dim=-1)
+    rp = rp * 1.5
+    ((rp * wp).sum() + (sc * ws).sum()).backward()
+    assert torch.equal(idx, ridx)
+    assert torch.allclose(probs, rp, atol=1e-5, rtol=1e-4)
+    assert torch.allclose(scores, sc, atol=1e-6, rtol=1e-4)
+    assert torch.equal(counts, torch.bincount(ridx.reshape(-1), minlength=E).float())
+    assert rel_err(a.grad, b.grad) < 1e-4
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (4096, 4096, 1024), (1000, 776, 520), (304, 264, 72)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True), (True, False)])
+def test_gemm_cta_pair_variants(M, N, K, a_mn, b_mn):
+    """The CTA-pair (cta_group::2) kernel against fp32 matmul, every operand layout, ragged edges included."""
+    torch.manual_seed(1)
+    a = torch.randn((K, M) if a_mn else (M, K), device=DEV, dtype=torch.bfloat16)
+    b = torch.randn((K, N) if b_mn else (N, K), device=DEV, dtype=torch.bfloat16)
+    ref = (a.t() if a_mn else a).float() @ (b if b_mn else b.t()).float()
+    out = ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, pair=True)
+    assert rel_err(out, ref) < 5e-3
+    acc = torch.randn(M, N, device=DEV)
+    want = acc + ref
+    ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, out_mode=OUT_F32_ACC, pair=True)
+    assert rel_err(acc, want) < 1e-3
