@@ -276,10 +276,46 @@ class GalvatronMoEMLP(nn.Module):
         self.experts.reset_parameters(seed, full_init)
 
     def forward(self, x2d: torch.Tensor, probs: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        """``x2d [T, H]``, ``probs / idx [T, k]`` -> ``[T, H]``.
+
+        Expert tensor parallelism (each expert's FFN dimension split over the ``tp_of_ep`` group): the tokens of the
+        group are gathered, every rank runs the routed experts on its weight slice, and the partial sums are
+        reduce-scattered back to the token owners (moe/token_dispatcher.py:560-600 does the gather after the
+        all-to-all; gathering first keeps one code path for both dispatchers).
+        All-gather dispatcher: tokens, probabilities and indices of the whole expert-parallel group are gathered,
+        each rank serves the pairs routed to its local experts, and a reduce-scatter returns the weighted sums
+        (moe/token_dispatcher.py:116-284)."""
+        s, c = self.spec, self.ctx
+        etp = c.etp_size
+        if etp > 1:
+            x2d = mp.gather_first_dim(x2d, c.tp_of_ep, grad_is_partial=True)
+            probs = mp.gather_first_dim(probs, c.tp_of_ep, grad_is_partial=True)
+            idx = mp.all_gather_first(idx.contiguous(), c.tp_of_ep)
+        if s.dispatcher == "allgather" and c.ep_size > 1:
+            E_loc = self.experts.E_loc
+            lo = c.ep_rank * E_loc
+            xa = mp.gather_first_dim(x2d, c.ep, grad_is_partial=True)
+            pa = mp.gather_first_dim(probs, c.ep, grad_is_partial=True)
+            ia = mp.all_gather_first(idx.contiguous(), c.ep)
+            local = (ia >= lo) & (ia < lo + E_loc)
+            il = torch.where(local, ia - lo, torch.full_like(ia, -1))
+            out = self._routed(xa, pa, il, local_only=True)
+            out = mp.reduce_scatter_first_dim(out, c.ep)
+        else:
+            out = self._routed(x2d, probs, idx)
+        if etp > 1:
+            out = mp.reduce_scatter_first_dim(out, c.tp_of_ep)
+        return out
+
+    def _routed(self, x2d: torch.Tensor, probs: torch.Tensor, idx: torch.Tensor, local_only: bool = False) -> torch.Tensor:
+        """Dispatch to the experts and combine.  ``local_only``: ``idx`` already names local experts (``-1`` for
+        pairs served elsewhere) and no exchange is needed."""
         s, c = self.spec, self.ctx
         T, H = x2d.shape
         k, E, ep, E_loc = s.topk, s.experts, c.ep_size, self.experts.E_loc
-        if ep > 1 and getattr(c, "fused_comm", False) and c.etp_size == 1:
+        if local_only:
+            E, ep = E_loc, 1
+        if ep > 1 and getattr(c, "fused_comm", False):
             from ..parallel import fused_a2a as fa
 
             if fa.usable(x2d, c.ep):
@@ -295,7 +331,7 @@ class GalvatronMoEMLP(nn.Module):
         valid = flat_e >= 0
         sort_key = torch.where(valid, flat_e, torch.full_like(flat_e, E))
         order = torch.argsort(sort_key, stable=True)               # expert-major, token-minor
-        n_valid = int(valid.sum().item()) if s.capacity_factor is not None else T * k
+        n_valid = int(valid.sum().item()) if (s.capacity_factor is not None or local_only) else T * k
         order = order[:n_valid]
         tok_of = order // k
         e_sorted = flat_e[order]
@@ -324,8 +360,6 @@ class GalvatronMoEMLP(nn.Module):
         dest = starts[b_exp] + within[b_exp, b_src] + (rows - src_block_start.reshape(-1)[blk])
         buf = recv.new_zeros((max(total, SEG_ALIGN), H)).index_copy(0, dest, recv)
         row_start = starts.to(torch.int32)
-        if c.etp_size > 1:
-            raise NotImplementedError("expert tensor parallelism > 1 is planned; use etp = 1")
         out_buf = self.experts(buf, row_start)
         back = out_buf.index_select(0, dest)
         if ep > 1:
@@ -344,14 +378,25 @@ class GalvatronMoEAttention(nn.Module):
         super().__init__()
         self.attn = GalvatronAttention(spec, ctx, device, name + ".attn")
         self.pre_router_norm = Norm(spec, device)
+        # shared experts are dense parameters (replicated over the expert-parallel group, sharded over tp), so they
+        # live in this unit and are reduced over the layer's full data-parallel group (moe/mlp.py:215-400)
+        self.shared_experts = None
+        if spec.shared_ffn > 0:
+            from .modules import MLP
+
+            self.shared_experts = MLP(spec, ctx, device, name + ".mlp.shared_experts", ffn=spec.shared_ffn)
 
     def reset_parameters(self, seed=1234, full_init=False):
         self.attn.reset_parameters(seed, full_init)
         self.pre_router_norm.reset_parameters()
+        if self.shared_experts is not None:
+            self.shared_experts.reset_parameters(seed, full_init)
 
     def forward(self, x):
         a = self.attn(x)
         n, h = self.pre_router_norm(a, residual=x)
+        if self.shared_experts is not None:
+            return n, h, self.shared_experts(n)
         return n, h
 
 
@@ -387,12 +432,15 @@ class MoELayerRunner(nn.Module):
             w.finish_backward()
 
     def forward(self, x):
-        n, h = self.attention(x)
+        res = self.attention(x)
+        n, h = res[0], res[1]
         S, B, H = n.shape
         n2 = n.reshape(S * B, H)
         probs, idx = self.router(n2)
-        y = self.mlp(n2, probs, idx)
-        return ops_add(h, y.view(S, B, H))
+        y = self.mlp(n2, probs, idx).view(S, B, H)
+        if len(res) > 2:
+            y = y + res[2]
+        return ops_add(h, y)
 
 
 def wrap_moe_units(layer: GalvatronMoEDecoderLayer, lp, ctx: LayerCtx, plan, reduce_in_fp32: bool,

@@ -41,6 +41,7 @@ class ModelSpec:
     # MoE
     experts: int = 0
     moe_ffn: int = 0
+    shared_ffn: int = 0              # > 0: a dense MLP of this width runs on every token beside the routed experts
     topk: int = 2
     router_score: str = "softmax"
     router_pre_softmax: bool = False
@@ -133,6 +134,7 @@ def spec_from_args(args) -> ModelSpec:
         router_dtype=m.moe_router_dtype, aux_loss_coeff=m.moe_aux_loss_coeff, z_loss_coeff=m.moe_z_loss_coeff,
         load_balancing=m.moe_router_load_balancing_type, capacity_factor=m.moe_expert_capacity_factor,
         pad_to_capacity=m.moe_pad_expert_input_to_capacity, drop_policy=m.moe_token_drop_policy,
+        shared_ffn=int(getattr(m, "moe_shared_expert_intermediate_size", 0) or 0),
         dispatcher=m.moe_token_dispatcher_type, grouped_gemm=m.moe_grouped_gemm, jitter_eps=m.moe_input_jitter_eps,
     )
 

@@ -133,5 +133,28 @@ def test_moe_expert_parallel():
     check(2, {"parallel": {"global_ep_deg": 2}, "model": model}, base, key="moe", rtol=1e-3, norm_rtol=2e-2)
 
 
+MOE = {"num_moe_experts": 4, "moe_ffn_hidden_size": 256, "moe_router_topk": 2, "is_moe_model": True,
+       "moe_token_dispatcher_type": "alltoall", "moe_aux_loss_coeff": 1e-2}
+
+
+def test_moe_allgather_dispatcher():
+    base = {"chunks": 1, "model": MOE}
+    check(2, {"parallel": {"global_ep_deg": 2}, "model": dict(MOE, moe_token_dispatcher_type="allgather")}, base,
+          key="moe", rtol=1e-3, norm_rtol=2e-2)
+
+
+def test_moe_expert_tensor_parallel():
+    base = {"chunks": 1, "model": MOE}
+    check(4, {"parallel": {"global_ep_deg": 2, "global_tp_of_ep_deg": 2}, "model": MOE}, base, key="moe", rtol=1e-3,
+          norm_rtol=2e-2)
+
+
+def test_moe_shared_experts():
+    model = dict(MOE, moe_shared_expert_intermediate_size=128)
+    base = {"chunks": 1, "model": model}
+    check(2, {"parallel": {"global_ep_deg": 2}, "model": model}, base, key="moe_shared", rtol=1e-3, norm_rtol=2e-2)
+    check(2, {"parallel": {"global_tp_deg": 2, "vocab_tp": 2}, "model": model}, base, key="moe_shared", rtol=1e-3, norm_rtol=2e-2)
+
+
 if __name__ == "__main__":
     worker_main(REGISTRY)
