@@ -24,8 +24,10 @@ def main(argv=None):
     args = load_config(argv[0], argv[1:], mode="search")
     resolve_model_config(args)
     engine = GalvatronSearchEngine(args)
-    here = os.path.dirname(os.path.abspath(argv[0]))
-    engine.set_search_engine_info(here, model_layer_configs(args), model_name(args))
+    # profiled JSON files are read from <dir>/configs/ and the result is written there (the directory the profilers
+    # were run from: HG_PROFILE_DIR, else the current directory)
+    work_dir = os.environ.get("HG_PROFILE_DIR") or os.getcwd()
+    engine.set_search_engine_info(work_dir, model_layer_configs(args), model_name(args))
     engine.initialize_search_engine()
     return engine.parallelism_optimization()
 

@@ -123,8 +123,13 @@ class ModelProfiler(BaseProfiler):
         return self.basic_overrides_dict
 
     def get_envs_dict(self) -> Dict[str, Any]:
-        # stream issue order is explicit in this framework; the variable is kept for launchers that expect it
-        return {"CUDA_DEVICE_MAX_CONNECTIONS": 1}
+        # stream issue order is explicit in this framework; the variable is kept for launchers that expect it.
+        # Memory runs keep the gradient / parameter buffers in the caching allocator (not in symmetric memory) so
+        # that the allocator statistics the runtime profiler reads see them.
+        env = {"CUDA_DEVICE_MAX_CONNECTIONS": 1}
+        if self.args.profile_type == "memory":
+            env["HG_FUSED_ZERO"] = 0
+        return env
 
     @staticmethod
     def dict_to_str(d: Dict, sep: str = "=") -> str:

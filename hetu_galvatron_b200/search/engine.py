@@ -328,8 +328,18 @@ class GalvatronSearchEngine:
         return self.time_config, self.memory_config
 
     def _hw_file(self, override: Optional[str], name: str) -> str:
-        base = override if override is not None else os.path.join(self.path, "../../profile_hardware/hardware_configs/")
-        return base if base.endswith(".json") else os.path.join(base, name)
+        if override is not None:
+            return override if override.endswith(".json") else os.path.join(override, name)
+        # default: next to the search configuration, then the reference's tree layout, then the profile measured
+        # on 8 x B200 that ships with the package
+        here = os.path.dirname(os.path.abspath(__file__))
+        candidates = [os.path.join(self.path, "hardware_configs"),
+                      os.path.join(self.path, "../../profile_hardware/hardware_configs/"),
+                      os.path.join(here, "..", "profiler", "hardware_configs")]
+        for base in candidates:
+            if os.path.exists(os.path.join(base, name)):
+                return os.path.join(base, name)
+        return os.path.join(candidates[0], name)
 
     def get_profiled_hardware_configs(self):
         prof, hw = self.args.profiling_info, self.args.hardware_info
