@@ -115,6 +115,8 @@ GalvatronModelArgs = _build("GalvatronModelArgs", {
     "rotary_base": (O[int], 10000),
     "rotary_percent": (O[float], 1.0),
     "rotary_interleaved": (bool, False),
+    "use_rope_scaling": (bool, False),
+    "rope_scaling_factor": (float, 8.0),
     "rotary_seq_len_interpolation_factor": (O[int], None),
     "mrope_section": (O[List[int]], None),
     "make_vocab_size_divisible_by": (O[int], 128),

@@ -159,7 +159,8 @@ class SelfAttention(nn.Module):
             pos, off = local_positions(c, S_full, S_att, row0, qkv.device)
             if pos is not None:
                 pos = pos.repeat_interleave(B)
-            cos, sin = ops.rope_tables(max(S_full, 1), self.rot_dim, s.rope_base, str(qkv.device), s.rope_interp)
+            cos, sin = ops.rope_tables(max(S_full, 1), self.rot_dim, s.rope_base, str(qkv.device), s.rope_interp,
+                                        s.rope_scaling_factor)
             qkv2 = ops.rope_packed(qkv2, self.rope_slots, self.hd, cos, sin, B, pos, off)
         if c.sp_size == 1 and c.cp_size == 1:
             ctxv = ops.flash_attention_packed(qkv2, S_att, B, self.nh, self.ng, self.hd, causal=True)

@@ -32,6 +32,7 @@ class ModelSpec:
     rope_base: float = 10000.0
     rope_pct: float = 1.0
     rope_interp: float = 1.0
+    rope_scaling_factor: float = 0.0  # > 0: Llama-3.x frequency scaling with this factor
     bias: bool = False               # bias on every linear
     qkv_bias: bool = False
     tied: bool = False               # embedding and LM head share one weight
@@ -126,6 +127,8 @@ def spec_from_args(args) -> ModelSpec:
         rope_interp=float(m.rotary_seq_len_interpolation_factor or 1.0), bias=m.add_bias_linear,
         qkv_bias=m.add_qkv_bias or m.add_bias_linear, tied=not m.untie_embeddings_and_output_weights,
         init_std=(tr.init_method_std if tr is not None else 0.02), dtype=dtype,
+        rope_scaling_factor=(float(getattr(m, "rope_scaling_factor", 8.0) or 8.0)
+                             if getattr(m, "use_rope_scaling", False) else 0.0),
         hidden_dropout=float(getattr(m, "hidden_dropout", 0.0) or 0.0),
         experts=m.num_moe_experts or 0, moe_ffn=m.moe_ffn_hidden_size or m.ffn_hidden_size or 0,
         topk=m.moe_router_topk, router_score=m.moe_router_score_function, router_pre_softmax=m.moe_router_pre_softmax,

@@ -101,13 +101,42 @@ def norm(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None, eps: f
 # --------------------------------------------------------------------------------------------
 # RoPE
 # --------------------------------------------------------------------------------------------
-@lru_cache(maxsize=16)
-def rope_tables(max_pos: int, rot_dim: int, base: float, device: str, interp: float = 1.0):
-    """fp32 ``cos``/``sin`` tables ``[max_pos, rot_dim/2]`` (inv_freq = base^(-2i/dim), positions / interp)."""
+_ROPE_CACHE: dict = {}
+
+
+def llama3_scale_inv_freq(inv: torch.Tensor, factor: float = 8.0, low_freq_factor: float = 1.0,
+                          high_freq_factor: float = 4.0, original_max_pos: int = 8192) -> torch.Tensor:
+    """Llama-3.x frequency scaling: wavelengths beyond ``original_max_pos / low_freq_factor`` are stretched by
+    ``factor``, those below ``original_max_pos / high_freq_factor`` are kept, the band in between is blended
+    (galvatron/core/runtime/transformer/rotary_pos_embedding.py:124-157)."""
+    import math
+
+    wavelen = 2 * math.pi / inv
+    low_wl, high_wl = original_max_pos / low_freq_factor, original_max_pos / high_freq_factor
+    out = torch.where(wavelen > low_wl, inv / factor, inv)
+    smooth = (original_max_pos / wavelen - low_freq_factor) / (high_freq_factor - low_freq_factor)
+    blended = (1 - smooth) * inv / factor + smooth * inv
+    medium = ~(wavelen < high_wl) & ~(wavelen > low_wl)
+    return torch.where(medium, blended, out)
+
+
+def rope_tables(max_pos: int, rot_dim: int, base: float, device: str, interp: float = 1.0, llama3_factor: float = 0.0):
+    """fp32 ``cos``/``sin`` tables ``[max_pos, rot_dim/2]`` (inv_freq = base^(-2i/dim), positions / interp; optional
+    Llama-3 frequency scaling).  Cached per argument tuple: every layer of a model shares one pair."""
+    key = (max_pos, rot_dim, float(base), str(device), float(interp), float(llama3_factor or 0.0))
+    hit = _ROPE_CACHE.get(key)
+    if hit is not None:
+        return hit
     inv = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float32) / rot_dim))
+    if llama3_factor:
+        inv = llama3_scale_inv_freq(inv, llama3_factor)
     pos = torch.arange(max_pos, dtype=torch.float32) / interp
     f = torch.outer(pos, inv)
-    return f.cos().to(device).contiguous(), f.sin().to(device).contiguous()
+    out = (f.cos().to(device).contiguous(), f.sin().to(device).contiguous())
+    if len(_ROPE_CACHE) > 64:
+        _ROPE_CACHE.clear()
+    _ROPE_CACHE[key] = out
+    return out
 
 
 def _rope_ref(t, cos, sin, pos, sign=1.0):

@@ -87,3 +87,15 @@ def adamw_allgather_peer(master, grad, exp_avg, exp_avg_sq, targets, dst_off: in
                                      float(weight_decay), int(step), _lib.ptr(gscale), _lib.ptr(skip), _lib.stream())
     _lib.check(rc, "hg_zero_adamw_allgather")
     _lib.count_launch()
+
+
+def all_gather_peer(shards: SymmetricBuffer, shard_numel: int, out: torch.Tensor):
+    """``out[r*S:(r+1)*S] = shard_r`` for every rank ``r``: this rank pulls all shards through their peer mappings
+    (bf16, ``S`` a multiple of 8).  The shards must be quiescent (see ``ShardedUnit``: they change only inside the
+    optimizer step, which ends with a rendezvous)."""
+    lib = _lib.load()
+    rc = lib.hg_peer_gather_bf16(shards.ptr_array(), shards.t, 1, shard_numel, 0, shard_numel, out.data_ptr(), shard_numel,
+                                 shard_numel, _lib.stream())
+    _lib.check(rc, "hg_peer_gather_bf16")
+    _lib.count_launch()
+    return out

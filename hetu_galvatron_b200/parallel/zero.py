@@ -123,8 +123,19 @@ class ShardedUnit:
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
         self.grad_shard = None  # fp32 view / buffer holding this rank's reduced gradient
+        self._sym_shard = None
         if self.dp_type == "zero3":
-            self.shard_lp = self.flat[lo:hi].clone()
+            if self.fused and self.dtype == torch.bfloat16:
+                # the bf16 shard is what peers pull from when they re-assemble the unit's parameters: it changes only
+                # in the optimizer step, which ends with a rendezvous, so gathers need no synchronisation of their own
+                from . import fused_zero as fz
+
+                self._sym_shard = fz.SymmetricBuffer(self.shard_numel, self.dtype, dev, self.pg)
+                self.shard_lp = self._sym_shard.tensor
+                self.shard_lp.copy_(self.flat[lo:hi])
+                self.sync_peers()
+            else:
+                self.shard_lp = self.flat[lo:hi].clone()
             self.release()
         else:
             self.shard_lp = self.flat[lo:hi]
@@ -159,6 +170,8 @@ class ShardedUnit:
         self.master.copy_(self.flat[lo:hi])
         if self.dp_type == "zero3":
             self.shard_lp.copy_(self.flat[lo:hi])
+            if self._sym_shard is not None:
+                self.sync_peers()        # peers pull from this shard
 
     # ---- ZeRO-3 gather / release --------------------------------------------------------------------
     def gather(self):
@@ -172,6 +185,10 @@ class ShardedUnit:
             parts = [torch.empty_like(self.shard_lp) for _ in range(self.n)]
             dist.all_gather(parts, self.shard_lp, group=self.pg)
             self.flat.copy_(torch.cat(parts))
+        elif self._sym_shard is not None:
+            from . import fused_zero as fz
+
+            fz.all_gather_peer(self._sym_shard, self.shard_numel, self.flat)   # pull every rank's shard over NVLink
         else:
             dist.all_gather_into_tensor(self.flat, self.shard_lp, group=self.pg)
         self.gathered = True

@@ -112,6 +112,78 @@ def pp_division_even(layernum_list: Sequence[int], pp_deg: int) -> List[int]:
     return [avg] * (pp_deg - 1) + [total - avg * (pp_deg - 1)]
 
 
+def balance_stages(layer_costs: Sequence[float], other_costs: Sequence[float], pp_deg: int):
+    """Split ``len(layer_costs)`` consecutive layers over ``pp_deg`` stages so that stage memory
+    (``other_costs[stage]`` + its layers) is even: a stage takes layers until it is within half a layer of the
+    average, no early stage may exceed 1.3x the average, and no stage is left empty.  Returns (division, stage costs)."""
+    n = len(layer_costs)
+    avg = (float(np.sum(layer_costs)) + float(np.sum(other_costs))) / pp_deg
+    division = [0] * pp_deg
+    acc = [float(x) for x in other_costs]
+    idx = 0
+    for i in range(pp_deg):
+        while idx < n and not (i < pp_deg - 1 and avg - acc[i] < 0.5 * layer_costs[idx]):
+            acc[i] += layer_costs[idx]
+            division[i] += 1
+            idx += 1
+    for i in range(pp_deg - 1):
+        left, right = int(np.sum(division[:i])), int(np.sum(division[:i + 1]))
+        cur = float(np.sum(layer_costs[left:right])) + other_costs[i]
+        while cur > avg * 1.3 and division[i] > 0:
+            division[i] -= 1
+            division[i + 1] += 1
+            right -= 1
+            cur -= layer_costs[right]
+    for i in range(pp_deg - 1):
+        while division[i] <= 0:
+            division[i] += 1
+            division[i + 1] -= 1
+    for i in range(pp_deg - 1, 0, -1):
+        while division[i] <= 0:
+            division[i] += 1
+            division[i - 1] -= 1
+    stage = []
+    for i in range(pp_deg):
+        left, right = int(np.sum(division[:i])), int(np.sum(division[:i + 1]))
+        stage.append(float(other_costs[i]) + float(np.sum(layer_costs[left:right])))
+    return division, stage
+
+
+def pp_division_memory_balanced(model_args_list, train_args_list, parallel_args_list, profile_model_args_list,
+                                layer_num: Sequence[int], pp_deg: int, bsz: int, mbsz: int, strategies):
+    """Pipeline division balanced by the memory of the cheapest uniform strategy (tp 1, ZeRO-2 over the remaining
+    ranks, GPipe accounting), for models with several layer types
+    (galvatron/core/search_engine/search_engine.py:954-1058).  Returns ``(division, stage memory)`` or
+    ``(None, None)`` when no strategy uses ``pp_deg`` stages."""
+    import copy as _copy
+
+    from .cost_model import EmbeddingLMHeadMemoryCost, LayerMemoryCost
+    from .strategy import DPType, EmbeddingLMHeadStrategy, LayerStrategy
+
+    if pp_deg == 1:
+        return [int(np.sum(layer_num))], None
+    cand = [s for s in strategies if s.pp_size == pp_deg]
+    if not cand:
+        return None, None
+    world = cand[0].world_size
+    pa = [_copy.deepcopy(p) for p in parallel_args_list]
+    for p in pa:
+        p.pipeline_type = "gpipe"
+    chunks = max(1, bsz // mbsz)
+    per_type = []
+    for i in range(len(layer_num)):
+        st = LayerStrategy(pp_size=pp_deg, tp_size=1, sp_size=1, dp_size=world // pp_deg, dp_type=DPType.ZERO2, checkpoint=False)
+        per_type.append(LayerMemoryCost(st, bsz, chunks, 0, model_args_list[i], train_args_list[i], pa[i],
+                                        profile_model_args_list[i]).get_memory_cost()["enc_total"])
+    est = EmbeddingLMHeadStrategy(pp_size=pp_deg, tp_size=1, sp_size=1, dp_size=world // pp_deg, dp_type=DPType.ZERO2)
+    other = EmbeddingLMHeadMemoryCost(est, bsz, chunks, model_args_list[0], train_args_list[0], pa[0],
+                                      profile_model_args_list[0]).get_memory_cost()["enc_total"]
+    layers: List[float] = []
+    for i, n in enumerate(layer_num):
+        layers += [per_type[i]] * int(n)
+    return balance_stages(layers, other, pp_deg)
+
+
 def _task_logger(log_dir: str, gbsz, chunks, pp, buffer_tp, mode) -> logging.Logger:
     d = os.path.join(log_dir, "search_gbsz%d_chunks%d" % (gbsz, chunks))
     os.makedirs(d, exist_ok=True)

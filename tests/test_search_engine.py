@@ -118,3 +118,18 @@ def test_native_dp_core_matches_python():
             assert total[k] == outs[0][0][k] or (np.isinf(total[k]) and np.isinf(outs[0][0][k]))
             assert [int(x) for x in res[k]] == [int(x) for x in outs[0][1][k]]
             assert int(remain[k]) == int(outs[0][2][k])
+
+
+def test_memory_balanced_stage_division():
+    from hetu_galvatron_b200.search.engine import balance_stages, pp_division_even
+
+    # a heavy first stage (embedding) pushes layers to the later stages; nothing is left empty
+    div, cost = balance_stages([10.0] * 12, [35.0, 0.0, 0.0, 15.0], 4)
+    assert sum(div) == 12 and min(div) >= 1 and div[0] < div[1]
+    assert max(cost) <= 1.3 * (120 + 50) / 4 + 10.0
+    # uniform costs without extras reproduce the even split
+    div, _ = balance_stages([1.0] * 8, [0.0] * 4, 4)
+    assert div == pp_division_even([8], 4)
+    # more stages than a greedy fill would populate: every stage still gets a layer
+    div, _ = balance_stages([5.0, 1.0, 1.0, 1.0], [0.0, 0.0, 0.0, 0.0], 4)
+    assert div == [1, 1, 1, 1]
