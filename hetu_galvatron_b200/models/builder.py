@@ -112,7 +112,8 @@ def build_stage(spec: ModelSpec, plan: HybridPlan, groups: ModelGroups, device, 
         # (also across a stage boundary: the receiver re-lays-out what the sender shipped in its own layout)
         if prev_lp is not None:
             re = build_reshard(groups.factory, plan.world_size, plan.pp_deg, groups.rank,
-                               groups.per_layer[prev_lp.index], groups.per_layer[lp.index], prev_lp, lp)
+                               groups.per_layer[prev_lp.index], groups.per_layer[lp.index], prev_lp, lp,
+                               peer=fused_comm)
         else:
             re = None
         if lp.stage == groups.stage:

@@ -55,12 +55,75 @@ def apply_zigzag(x: torch.Tensor, cp: int) -> torch.Tensor:
     return torch.cat([chunks[c] for c in zigzag_order(cp)], dim=0)
 
 
+# ---- one-kernel resharding over peer memory -------------------------------------------------------------------
+def _global_pos(i: torch.Tensor, s_local: torch.Tensor, width: int, cp: int, S: int) -> torch.Tensor:
+    """Natural sequence position of local row ``s_local`` on sequence-shard index ``i`` (``i = c * width + t``)."""
+    g = width * cp
+    c, t = i // width, i % width
+    p = t * (S // g) + s_local                      # position inside the cp rank's part
+    if cp == 1:
+        return p
+    half = S // (2 * cp)
+    return torch.where(p < half, c * half + p, (2 * cp - 1 - c) * half + (p - half))
+
+
+def _owner(pos: torch.Tensor, width: int, cp: int, S: int):
+    """Inverse of :func:`_global_pos`: (sequence-shard index, local row) holding natural position ``pos``."""
+    g = width * cp
+    if cp == 1:
+        p, c = pos, torch.zeros_like(pos)
+    else:
+        half = S // (2 * cp)
+        chunk = pos // half
+        first = chunk < cp
+        c = torch.where(first, chunk, 2 * cp - 1 - chunk)
+        p = torch.where(first, pos - chunk * half, half + pos - chunk * half)
+    per = S // g
+    return c * width + p // per, p % per
+
+
+def pull_lists(S: int, rows_dst: int, b_dst: int, b_src: int, j_dst: int, src, dst, device):
+    """For every output row ``(s', b')`` of block rank ``j_dst``: the block rank and the row that hold it in the
+    source layout.  ``src`` / ``dst`` are ``(width, cp)``; rows are numbered ``s * batch + b``."""
+    (w_s, cp_s), (w_d, cp_d) = src, dst
+    g_s, g_d = w_s * cp_s, w_d * cp_d
+    a_d, i_d = j_dst // g_d, j_dst % g_d
+    s_loc = torch.arange(rows_dst, device=device).repeat_interleave(b_dst)
+    b_loc = torch.arange(b_dst, device=device).repeat(rows_dst)
+    pos = _global_pos(torch.full_like(s_loc, i_d), s_loc, w_d, cp_d, S)
+    sample = a_d * b_dst + b_loc
+    a_s, b_s = sample // b_src, sample % b_src
+    i_s, s_s = _owner(pos, w_s, cp_s, S)
+    return (a_s * g_s + i_s).to(torch.int32), (s_s * b_src + b_s).to(torch.int32)
+
+
+class _PeerReshard(torch.autograd.Function):
+    """Forward pulls the rows of the new layout from the block's ranks; backward pulls the gradient rows of the old
+    layout the same way (the move is a permutation inside the block, so no reduction is needed)."""
+
+    @staticmethod
+    def forward(ctx, x, mod, S):
+        ctx.mod, ctx.S, ctx.shape = mod, S, x.shape
+        return mod._pull(x, S, mod.src, mod.dst)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.mod._pull(g, ctx.S, ctx.mod.dst, ctx.mod.src), None, None
+
+
 class Reshard(nn.Module):
-    """Moves ``[S/g_old, B/d_old, H]`` to ``[S/g_new, B/d_new, H]``."""
+    """Moves ``[S/g_old, B/d_old, H]`` to ``[S/g_new, B/d_new, H]``.
+
+    With ``peer`` set (bf16 activations on a GPU, block of at most 8 ranks) the whole move is one pull kernel over
+    NVLink peer memory: every rank publishes its tensor, computes for each of its new rows which block rank holds
+    it, and gathers them (``parallel/fused_a2a.py``)."""
 
     def __init__(self, old_groups, new_groups, old_width: int, old_cp: int, new_width: int, new_cp: int,
-                 fused: Optional[CommGroup], rank_in_stage: int):
+                 fused: Optional[CommGroup], rank_in_stage: int, peer: bool = False):
         super().__init__()
+        self.peer = peer
+        self.src, self.dst = (old_width, old_cp), (new_width, new_cp)
+        self._lists = {}
         self.old, self.new = old_groups, new_groups
         self.g_old, self.g_new = old_width * old_cp, new_width * new_cp
         self.cp_old, self.cp_new = old_cp, new_cp
@@ -68,10 +131,31 @@ class Reshard(nn.Module):
         self.j = rank_in_stage % max(self.g_old, self.g_new)  # index inside the larger block
         self.identity = (old_width == new_width and old_cp == new_cp)
 
+    def _pull(self, x: torch.Tensor, S: int, src, dst) -> torch.Tensor:
+        from . import fused_a2a as fa
+
+        g_s, g_d = src[0] * src[1], dst[0] * dst[1]
+        big = max(g_s, g_d)
+        grp = self.old.tsp_cp if self.g_old >= self.g_new else self.new.tsp_cp   # the block
+        rows_s, b_s, H = x.shape
+        b_d = b_s * g_d // g_s
+        rows_d = S // g_d
+        key = (S, rows_s, b_s, src, dst)
+        lists = self._lists.get(key)
+        if lists is None:
+            lists = self._lists[key] = pull_lists(S, rows_d, b_d, b_s, self.j % big if big else 0, src, dst, x.device)
+        slot = fa.staging_for(grp, x.numel() * 2, x.device).publish(x.contiguous())
+        out = fa.gather_rows(slot, lists[0], lists[1], rows_d * b_d, H, H)
+        return out.view(rows_d, b_d, H)
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         if self.identity:
             return x
         floating = x.is_floating_point()
+        if self.peer and floating and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and x.shape[-1] % 8 == 0 \
+                and max(self.g_old, self.g_new) <= 8:
+            S = x.shape[0] * self.g_old
+            return _PeerReshard.apply(x, self, S)
         gather = (lambda t, g: mp.gather_first_dim(t, g, grad_is_partial=True)) if floating else \
             (lambda t, g: mp.all_gather_first(t, g))
         # 1. full sequence of my batch shard, natural order
@@ -97,7 +181,7 @@ class Reshard(nn.Module):
 
 
 def build_reshard(factory: GroupFactory, world: int, pp: int, rank: int, old_groups, new_groups, old_plan,
-                  new_plan) -> Optional[Reshard]:
+                  new_plan, peer: bool = False) -> Optional[Reshard]:
     ow, ocp = max(old_plan.tp, old_plan.sp), old_plan.cp
     nw, ncp = max(new_plan.tp, new_plan.sp), new_plan.cp
     if ow == nw and ocp == ncp:
@@ -110,4 +194,4 @@ def build_reshard(factory: GroupFactory, world: int, pp: int, rank: int, old_gro
         lay = Layout(("pp", "blk", "a", "i"), (pp, world // pp // big, big // small, small))
         fused = factory.make(lay.groups(("a",)))
     stage_ranks = world // pp
-    return Reshard(old_groups, new_groups, ow, ocp, nw, ncp, fused, rank % stage_ranks)
+    return Reshard(old_groups, new_groups, ow, ocp, nw, ncp, fused, rank % stage_ranks, peer=peer)

@@ -168,6 +168,10 @@ MOE = {"num_moe_experts": 4, "moe_ffn_hidden_size": 256, "moe_router_topk": 2, "
 @pytest.mark.parametrize("name,cfg", [
     ("moe_ep2", {"parallel": {"global_ep_deg": 2}, "model": MOE}),
     ("ulysses_sp2", {"parallel": {"global_tp_deg": 2, "use_ulysses": True}}),
+    ("reshard_tp_1_2_2_1", {"parallel": {"galvatron_config_path": {
+        "pp_deg": 1, "tp_sizes_enc": "1,2", "tp_consecutive_flags": "1,1", "dp_types_enc": "0,0", "use_sp": "0,0",
+        "checkpoint": "0,0", "global_bsz": 8, "chunks": 2, "pp_division": "2", "pipeline_type": "gpipe",
+        "default_dp_type": "ddp", "vtp": 1, "vsp": 0, "embed_sdp": 0}}}),
 ])
 def test_model_training_matches_nccl_path(name, cfg):
     _need(2)

@@ -373,3 +373,28 @@ def test_rng_tracker_streams():
     with pytest.raises(KeyError):
         with t3.fork("missing"):
             pass
+
+
+# ---- resharding index algebra ------------------------------------------------------------------------------------
+@pytest.mark.parametrize("src,dst", [((1, 1), (2, 1)), ((4, 1), (2, 1)), ((1, 2), (2, 1)), ((2, 2), (1, 1)),
+                                     ((2, 1), (1, 4)), ((1, 4), (4, 1)), ((2, 2), (4, 1))])
+def test_reshard_pull_lists_match_the_collective_formulation(src, dst):
+    """For every rank of a block, the (rank, row) list of the one-kernel resharding selects exactly the rows that
+    "gather sequence -> undo zig-zag -> re-split batch -> zig-zag -> slice" produces."""
+    from hetu_galvatron_b200.parallel.reshard import apply_zigzag, pull_lists
+
+    def held(full, width, cp, i):
+        return apply_zigzag(full, cp).chunk(width * cp, dim=0)[i].contiguous()
+
+    S, H = 32, 1
+    g_s, g_d = src[0] * src[1], dst[0] * dst[1]
+    big = max(g_s, g_d)
+    samples = 4 * big
+    data = torch.arange(S * samples, dtype=torch.float32).view(S, samples, H)
+    b_s, b_d = samples // (big // g_s), samples // (big // g_d)
+    srcs = [held(data[:, (j // g_s) * b_s:(j // g_s + 1) * b_s], src[0], src[1], j % g_s).reshape(-1, H) for j in range(big)]
+    flat = torch.stack(srcs)
+    for j in range(big):
+        want = held(data[:, (j // g_d) * b_d:(j // g_d + 1) * b_d], dst[0], dst[1], j % g_d)
+        peer, row = pull_lists(S, S // g_d, b_d, b_s, j, src, dst, "cpu")
+        assert torch.equal(flat[peer.long(), row.long()].view(S // g_d, b_d, H), want)
