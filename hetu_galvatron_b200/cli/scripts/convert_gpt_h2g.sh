@@ -1,0 +1,3 @@
+#!/bin/bash
+# HuggingFace checkpoint -> per-module split files.  Usage: convert_gpt_h2g.sh <hf checkpoint dir> <output dir>
+python3 -m hetu_galvatron_b200.cli.checkpoint_convert_h2g --model_type gpt --input_checkpoint "$1" --output_dir "$2"

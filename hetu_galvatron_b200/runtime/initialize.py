@@ -68,6 +68,7 @@ def initialize_galvatron(args, backend: str = None):
         dist.init_process_group(be, **kw)
     set_seed(args.train.seed or 1234)
     state.set_global_memory_buffer()
+    state.set_writers(args, is_last_rank=(args.rank == args.world_size - 1))
     from .rerun import initialize_rerun_state_machine
 
     initialize_rerun_state_machine()

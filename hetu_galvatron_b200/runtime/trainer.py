@@ -27,6 +27,16 @@ from .rerun import RerunDataIterator, get_rerun_state_machine
 from .scheduler import get_optimizer_param_scheduler
 
 
+def _nvtx_push(name: str):
+    if torch.cuda.is_available():
+        torch.cuda.nvtx.range_push(name)
+
+
+def _nvtx_pop():
+    if torch.cuda.is_available():
+        torch.cuda.nvtx.range_pop()
+
+
 def get_optimizer_and_param_scheduler(model, args):
     t = args.train
     opt = ShardedAdamW(model.sharded_units, lr=t.lr, betas=(t.adam_beta1, t.adam_beta2), eps=t.adam_eps,
@@ -75,21 +85,29 @@ def train(args, max_iters: Optional[int] = None, profile_window=(10, 20)):
         forward_only = bool(args.profile.profile_forward)
         loss = None
         while machine.should_run_forward_backward(train_it):
+            _nvtx_push("forward_backward")
             tokens, kw, loss_fn = get_batch(train_it, model.device)
             optimizer.zero_grad()
             loss = model.forward_backward([tokens], it, profiler, loss_fn, labels=kw.get("labels"),
                                           loss_mask=kw.get("loss_mask"), forward_only=forward_only)
             if loss is not None and machine.get_mode().value != "disabled":
                 machine.validate_result(loss, machine.is_unexpectedly_large(1e4), "loss", tolerance=0.0, fatal=True)
+            _nvtx_pop()
         if not forward_only:
+            _nvtx_push("optimizer")
             model.sync_tied_embedding_grads()
             optimizer.step()
+            _nvtx_pop()
             if scheduler is not None:
                 scheduler.step(increment=gbsz)
         profiler.profile_memory(it, "After optimizer_step")
         lr = optimizer.param_groups[0]["lr"]
         loss_val = float(loss) if loss is not None else None
         losses.append(loss_val)
+        if loss_val is not None:
+            from ..parallel import state as _state
+
+            _state.log_scalars(it + 1, **{"train/loss": loss_val, "train/lr": lr})
         profiler.post_profile_memory(it)
         profiler.profile_time_end(it, loss_val, lr, optimizer.grad_norm() if (optimizer.clip_grad > 0 and not forward_only) else None)
         save, leave, code = machine.should_checkpoint_and_exit()

@@ -40,3 +40,34 @@ def print_loss(loss, ep: int, iter: int):
         print("(Iteration %d): Loss = %.3f" % (iter, float(loss)))
     else:
         print("[Epoch %d] (Iteration %d): Loss = %.3f" % (ep, iter, float(loss)))
+
+
+def distributed_dataloader(dataset, global_bsz: int, shuffle: bool = True, group=None, collate_fn=None):
+    """A ``DataLoader`` with a ``DistributedSampler`` over ``group`` (default: all ranks); batch = global / ranks
+    (galvatron/utils/training_utils.py:13-23)."""
+    from torch.utils.data import DataLoader
+    from torch.utils.data.distributed import DistributedSampler
+
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    sampler = DistributedSampler(dataset, shuffle=shuffle, num_replicas=world, rank=rank)
+    return DataLoader(dataset, batch_size=max(1, global_bsz // world), sampler=sampler, collate_fn=collate_fn)
+
+
+def divide(numerator: int, denominator: int) -> int:
+    if numerator % denominator:
+        raise ValueError("%d is not divisible by %d" % (numerator, denominator))
+    return numerator // denominator
+
+
+class VocabUtility:
+    """Vocabulary range ``[first, last)`` owned by a rank of a vocab-parallel group
+    (galvatron/core/runtime/tensor_parallel/utils.py:32-82)."""
+
+    @staticmethod
+    def vocab_range_from_per_partition_vocab_size(per_partition: int, rank: int, world_size: int = None):
+        return rank * per_partition, (rank + 1) * per_partition
+
+    @staticmethod
+    def vocab_range_from_global_vocab_size(global_vocab: int, rank: int, world_size: int):
+        return VocabUtility.vocab_range_from_per_partition_vocab_size(divide(global_vocab, world_size), rank, world_size)
