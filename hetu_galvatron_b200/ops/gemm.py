@@ -34,7 +34,7 @@ def _rowmajor(t: torch.Tensor) -> torch.Tensor:
 
 # CTA-pair kernel (tcgen05.mma.cta_group::2, 256x256 tiles): "auto" uses it for problems of at least one pair tile,
 # "0" never, "1" always.  The one-CTA kernel is the fallback when the device cannot co-schedule a pair.
-_PAIR_MODE = os.environ.get("HG_GEMM_PAIR", "0")
+_PAIR_MODE = os.environ.get("HG_GEMM_PAIR", "auto")
 _pair_ok = True
 
 
