@@ -168,6 +168,7 @@ GalvatronProfileArgs = _build("GalvatronProfileArgs", {
     "profile_forward": (Literal[0, 1], 0),
     "save_profiled_memory": (int, 0),
     "exit_after_profiling": (Literal[0, 1], 1),
+    "save_profiled_iteration_time": (int, 0),   # write the whole-iteration time (fwd + bwd + optimizer) for the refit
 }, doc="In-training profiling switches.")
 
 CommonTrainArgs = _build("CommonTrainArgs", {

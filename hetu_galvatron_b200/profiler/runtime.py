@@ -276,6 +276,9 @@ class RuntimeProfiler(BaseProfiler):
         if a.profile.profile_forward:
             save_profiled_time(self.time_profiling_path(), avg * 1e3, a.train.global_batch_size, self.layernum_list,
                                self.seqlen_list)
+        elif getattr(a.profile, "save_profiled_iteration_time", 0) and self.rank == 0:
+            save_profiled_time(self._config_path("iteration"), avg * 1e3, a.train.global_batch_size, self.layernum_list,
+                               self.seqlen_list)
         if self.exit:
             sys.exit(0)
         span = self.end_iter - self.start_iter

@@ -41,6 +41,9 @@ def load_native_core():
             return None
 
 
+MEM_TABLE_ROWS = 32768
+
+
 class DPAlg:
     """One stage's knapsack: memory budget ``max_mem`` MB, ``layer_num`` layers, ``S`` strategies."""
 
@@ -274,25 +277,30 @@ class DpOnModel:
                                  self.hwargs[t], self.logger).gen_result()[0] for s in strategies]
             intra[start:start + n] = np.array(row, dtype=np.float64).reshape(1, -1).repeat(n, axis=0)
             start += n
+        # The knapsack table has one row per memory unit.  Budgets up to MEM_TABLE_ROWS MB use 1 MB units (what the
+        # reference does for its 24-40 GB budgets); a 180 GB part uses coarser units so that the table keeps that
+        # size.  Every amount is rounded up to whole units, so the plan can only over-estimate memory (by less than
+        # one unit per layer).
+        unit = max(1, math.ceil(self.max_mem / MEM_TABLE_ROWS))
+        budget = self.max_mem // unit
         memory = [np.zeros((total, S)) for _ in range(pp_size)]
         for stage in range(pp_size):
             start = 0
             for t, n in enumerate(self.layer_num):
                 st = 0 if self.pipeline_type == "gpipe" else stage
-                row = np.ceil(np.array([self._layer_memory(s, gbsz, chunks, st, t) for s in strategies])).astype(np.int32)
+                row = np.ceil(np.array([self._layer_memory(s, gbsz, chunks, st, t) for s in strategies]) / unit).astype(np.int32)
                 memory[stage][start:start + n] = row.reshape(1, -1).repeat(n, axis=0)
                 start += n
         inter = self._transition_costs(gbsz, chunks, pp_size, strategies)
         embed = [self._embed_costs(es, gbsz, chunks) for es in embed_strategies]
         opt = self._empty(pp_size)
         for es, ((other_sync, other_nosync), other_mem) in zip(embed_strategies, embed):
-            other_mem = np.ceil(other_mem).astype(int)
+            other_mem = np.ceil((np.asarray(other_mem, dtype=np.float64) + float(global_mb)) / unit).astype(int)
             key = es.tp_sp_size
             chosen, remain_l, used_l, start = [], [], [], 0
             for stage in range(pp_size):
                 n = division[stage]
-                alg = DPAlg(self.max_mem, {key: int(other_mem[stage]) + int(global_mb)}, {key: other_sync[stage]}, n, S,
-                            threads=self.threads)
+                alg = DPAlg(budget, {key: int(other_mem[stage])}, {key: other_sync[stage]}, n, S, threads=self.threads)
                 alg.set_v_and_cost(memory[stage][start:start + n], intra[start:start + n], inter[start:start + n])
                 _, picks, remain = alg.fit()
                 picks, remain = picks[key], remain[key]
@@ -301,8 +309,8 @@ class DpOnModel:
                     used_l.append(np.inf)
                 else:
                     chosen.append([strategies[i] for i in picks])
-                    used_l.append(self.max_mem - remain + self.mem_cache)
-                remain_l.append(remain)
+                    used_l.append((budget - remain) * unit + self.mem_cache)
+                remain_l.append(remain if remain == -1 else remain * unit)
                 start += n
             if any(c is None for c in chosen):
                 self.log("embedding/lm-head %s: no solution" % es)
