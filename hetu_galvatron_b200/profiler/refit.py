@@ -12,8 +12,11 @@ in ``configs/computation_profiling_*.json`` and writes
 
     hardware_configs/b200_refit.json   {"backward_forward_ratio": r, ...}
 
-where ``1 + r = (T_full(Lmax) - T_full(Lmin)) / (T_fwd(Lmax) - T_fwd(Lmin))``.  The search engine picks the file up
-from the hardware-profile directory.
+where ``1 + r = (T_full(Lmax) - T_full(Lmin) - o * dL) / (T_fwd(Lmax) - T_fwd(Lmin))`` and ``o`` is the optimizer step
+of one layer, which does not scale with the batch and is therefore kept as its own term
+(``optimizer_ms_per_layer``): AdamW and the gradient norm stream 34 bytes per parameter against the 18 bytes of model
+state the memory profile reports, at the measured copy bandwidth.  The search engine picks the file up from the
+hardware-profile directory.
 """
 from __future__ import annotations
 
@@ -28,16 +31,33 @@ from ..utils.config_utils import read_json_config, write_json_config
 from .model import ModelProfiler
 
 
-def ratio_from_times(fwd: Dict[str, float], full: Dict[str, float], lmin: int, lmax: int, bsz: int, seq: int) -> float:
+def optimizer_ms_per_layer(parameter_size_mb: float, hbm_gbs: float) -> float:
+    """``parameter_size_mb`` is the memory profile's figure (model-state MB / 4).  Bytes streamed per step: read
+    fp32 gradient, master, two moments, write master, two moments (28) + bf16 parameter (2) + gradient-norm read (4)."""
+    state_mb = 4.0 * parameter_size_mb
+    return state_mb * (34.0 / 18.0) / 1024.0 / hbm_gbs * 1e3
+
+
+def ratio_from_times(fwd: Dict[str, float], full: Dict[str, float], lmin: int, lmax: int, bsz: int, seq: int,
+                     optimizer_ms: float = 0.0) -> float:
     k = lambda L: "layernum%d_bsz%d_seq%d" % (L, bsz, seq)  # noqa: E731
     d_fwd = fwd[k(lmax)] - fwd[k(lmin)]
-    d_full = full[k(lmax)] - full[k(lmin)]
+    d_full = full[k(lmax)] - full[k(lmin)] - optimizer_ms * (lmax - lmin)
     if d_fwd <= 0 or d_full <= d_fwd:
         raise ValueError("inconsistent timings: forward %s, full %s" % (d_fwd, d_full))
     return d_full / d_fwd - 1.0
 
 
-def main(argv=None, run=os.system, out_dir: Optional[str] = None):
+def measured_hbm_gbs(default: float = 6500.0) -> float:
+    here = os.path.dirname(os.path.abspath(__file__))
+    for up in (os.path.join(here, "..", ".."), os.getcwd()):
+        p = os.path.join(up, "MEASURED_PEAKS.json")
+        if os.path.exists(p):
+            return float(json.load(open(p)).get("hbm_gbs", default))
+    return default
+
+
+def main(argv=None, run=os.system, out_dir: Optional[str] = None, no_launch: bool = False):
     argv = list(sys.argv[1:] if argv is None else argv)
     if not argv:
         raise SystemExit(__doc__)
@@ -56,17 +76,26 @@ def main(argv=None, run=os.system, out_dir: Optional[str] = None):
                  "runtime.train.global_batch_size": bsz, "runtime.train.seq_length": seq})
     log_dir = os.path.join(work, "logs/profile_refit")
     os.makedirs(log_dir, exist_ok=True)
-    for L in (lmin, lmax):
-        ov = dict(base)
-        ov["runtime.model.num_layers"] = L
-        run(prof._command(ov, log_dir, "full_layernum_%d" % L))
+    if not no_launch:
+        for L in (lmin, lmax):
+            ov = dict(base)
+            ov["runtime.model.num_layers"] = L
+            run(prof._command(ov, log_dir, "full_layernum_%d" % L))
     fwd = read_json_config(prof.time_profiling_path())
     full = read_json_config(prof._config_path("iteration"))
-    r = ratio_from_times(fwd, full, lmin, lmax, bsz, seq)
+    opt_ms = 0.0
+    mem_path = prof.memory_profiling_path()
+    if os.path.exists(mem_path):
+        mem = read_json_config(mem_path)
+        for key in ("layertype_0_sp", "layertype_0"):
+            if key in mem and str(seq) in mem[key]:
+                opt_ms = optimizer_ms_per_layer(mem[key][str(seq)]["parameter_size"], measured_hbm_gbs())
+                break
+    r = ratio_from_times(fwd, full, lmin, lmax, bsz, seq, opt_ms)
     out_dir = out_dir or os.path.join(work, "hardware_configs")
     path = os.path.join(out_dir, "b200_refit.json")
     cfg = read_json_config(path) if os.path.exists(path) else {}
-    cfg.update({"backward_forward_ratio": r, "measured_with": {"model": model_name(args), "bsz": bsz, "seq": seq,
+    cfg.update({"backward_forward_ratio": r, "optimizer_ms_per_layer": opt_ms, "measured_with": {"model": model_name(args), "bsz": bsz, "seq": seq,
                                                                 "layers": [lmin, lmax]}})
     write_json_config(cfg, path)
     print("backward / forward ratio %.4f written to %s" % (r, path))

@@ -83,6 +83,8 @@ class ProfileHardwareArgs:
     all2all_message_size_to_latency_dict_dict: dict = field(default_factory=dict)
     # B200 refit: fraction of the TP/SP collective time that the fused compute+collective kernels hide
     fused_comm_hidden_fraction: float = 0.0
+    # B200 refit: optimizer step of one unsharded layer in ms (memory-bound AdamW + norm; scales with 1/sdp under ZeRO)
+    optimizer_ms_per_layer: float = 0.0
 
 
 def _line(x, m, c):
@@ -201,6 +203,9 @@ class LayerTimeCost:
             res = self.fct + a + b + self.tp_time + hw.extra_overhead
         if s.dp_type == DPType.ZERO3:
             res = res + self.zero3_gather_msg * self.dc
+        if hw.optimizer_ms_per_layer:
+            shard = s.sdp_size if s.dp_type in (DPType.ZERO2, DPType.ZERO3) else 1
+            res = res + hw.optimizer_ms_per_layer * self.L / (s.tp_size * shard)
         if s.pp_size > 1 and self.p2p_coe is not None:
             res = res + self.p2p_msg * self.p2p_coe
         return res * 0.001 * hw.costmodel_coe / self.L

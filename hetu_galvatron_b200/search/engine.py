@@ -437,6 +437,7 @@ class GalvatronSearchEngine:
             r = read_json_config(refit)
             self.bwd_fwd_ratio = r.get("backward_forward_ratio")
             self.fused_hidden = r.get("fused_comm_hidden_fraction", 0.0)
+            self.optimizer_ms = r.get("optimizer_ms_per_layer", 0.0)
         return self.allreduce_bandwidth, self.p2p_bandwidth, self.overlap_coe, self.sp_allreduce, self.sp_all2all
 
     def set_cost_models(self):
@@ -465,7 +466,8 @@ class GalvatronSearchEngine:
                 allreduce_message_size_to_latency_dict_dict=self.allreduce_latency,
                 allgather_message_size_to_latency_dict_dict=self.allgather_latency,
                 all2all_message_size_to_latency_dict_dict=self.all2all_latency,
-                fused_comm_hidden_fraction=getattr(self, "fused_hidden", 0.0)))
+                fused_comm_hidden_fraction=getattr(self, "fused_hidden", 0.0),
+                optimizer_ms_per_layer=getattr(self, "optimizer_ms", 0.0)))
 
     # ---- the sweep -----------------------------------------------------------------------------------------------
     def set_searching_bsz(self):
