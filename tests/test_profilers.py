@@ -171,6 +171,35 @@ def test_profile_entry_points(tmp_path, monkeypatch):
     assert (tmp_path / "scripts" / "profile_allreduce.sh").exists()
 
 
+def test_refit_ratio_and_optimizer_term():
+    from hetu_galvatron_b200.profiler import refit
+    from hetu_galvatron_b200.search.cost_model import (LayerTimeCost, ModelArgs, ParallelArgs, ProfileHardwareArgs,
+                                                       ProfileModelArgs, TrainArgs)
+    from hetu_galvatron_b200.search.strategy import DPType, LayerStrategy
+
+    fwd = {"layernum2_bsz2_seq4096": 10.0, "layernum4_bsz2_seq4096": 18.0}
+    full = {"layernum2_bsz2_seq4096": 40.0, "layernum4_bsz2_seq4096": 70.0}
+    assert refit.ratio_from_times(fwd, full, 2, 4, 2, 4096) == pytest.approx(30.0 / 8.0 - 1.0)
+    assert refit.ratio_from_times(fwd, full, 2, 4, 2, 4096, optimizer_ms=1.0) == pytest.approx(28.0 / 8.0 - 1.0)
+    with pytest.raises(ValueError):
+        refit.ratio_from_times(fwd, fwd, 2, 4, 2, 4096)
+    # 18 bytes of state per parameter are streamed as 34 bytes per step
+    assert refit.optimizer_ms_per_layer(900.0, 6500.0) == pytest.approx(3600.0 * 34 / 18 / 1024 / 6500 * 1e3)
+
+    def cost(opt_ms, ratio, dp_type, dp):
+        hw = ProfileHardwareArgs(allreduce_latency_per_MB_dict={"%d_1" % dp: 0.0, "%d_0" % dp: 0.0, "1_1": 0.0},
+                                 optimizer_ms_per_layer=opt_ms)
+        pm = ProfileModelArgs(forward_computation_time=2.0, backward_forward_ratio=ratio)
+        st = LayerStrategy(pp_size=1, tp_size=1, sp_size=1, dp_size=dp, dp_type=dp_type, checkpoint=False)
+        return LayerTimeCost(st, 8 * dp, 1, ModelArgs(parameter_size=48, seq_length=1024, hidden_size=1024, layer_num=4),
+                             TrainArgs(), ParallelArgs(), pm, hw).gen_result()[0]
+
+    base = cost(0.0, 2.0, DPType.DDP, 1)
+    assert cost(0.0, 3.0, DPType.DDP, 1) == pytest.approx(base * 4.0 / 3.0)       # fwd * (1 + ratio)
+    assert cost(1.0, 2.0, DPType.DDP, 1) == pytest.approx(base + 1e-3)            # + 1 ms per layer, unsharded
+    assert cost(8.0, 2.0, DPType.ZERO2, 8) - cost(0.0, 2.0, DPType.ZERO2, 8) == pytest.approx(1e-3)  # / sdp under ZeRO
+
+
 RUNTIME_YAML = """
 runtime:
   parallel: {mixed_precision: fp32}
