@@ -16,6 +16,12 @@ namespace hg {
 namespace attn {
 
 constexpr int kThreads = 192;  // warp 0: TMA, warp 1: UMMA, warps 2-5: softmax / epilogue
+// Backward kernels: two softmax warpgroups (warps 2-5 and 6-9).  Thread == accumulator row in both; warpgroup g owns
+// columns [32g, 32g+32) of every 64-column score step, which halves the exp2 / FMA work per thread so that the
+// score pipeline keeps up with the tensor core.  (TMEM lanes a warp may touch are 32*(warp%4)..: warps w and w+4
+// share a lane quarter.)
+constexpr int kBwdThreads = 320;
+constexpr int kBwdSoftmaxThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
@@ -371,7 +377,7 @@ struct DkvSmem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                      const BwdParams p) {
@@ -414,12 +420,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(&qd_full[i], 1);
       mbar_init(&qd_empty[i], 1);
       mbar_init(&st_full[i], 1);
-      mbar_init(&st_empty[i], 128);
+      mbar_init(&st_empty[i], kBwdSoftmaxThreads);
     }
-    mbar_init(pds_full, 128);
+    mbar_init(pds_full, kBwdSoftmaxThreads);
     mbar_init(pds_empty, 1);
-    mbar_init(&stats_full[0], 128);
-    mbar_init(&stats_full[1], 128);
+    mbar_init(&stats_full[0], kBwdSoftmaxThreads);
+    mbar_init(&stats_full[1], kBwdSoftmaxThreads);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -503,8 +509,10 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     }
   } else {
     const int wq = warp & 3;
+    const int half = (warp - 2) >> 2;     // which 32 of the step's 64 query columns this warpgroup owns
+    const int c0 = half * 32;
     const int row = wq * 32 + lane_id();  // key row inside the block
-    const int tid = threadIdx.x - 64;     // 0..127 among the softmax threads
+    const int tid = threadIdx.x - 64;     // 0..255 among the softmax threads
     const uint32_t lane_off = uint32_t(wq * 32) << 16;
     const float sl2 = p.scale * kLog2e;
     const int k_pos = p.k_pos0 + k0 + row;
@@ -519,34 +527,35 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         float* dst = sStats + st * 128;
         const int q = qrow + (tid & 63);
         const size_t idx = (size_t(b) * p.nheads + h) * p.Sq + q;
-        float v = 0.f;
-        if (q < p.Sq) v = (tid < 64) ? p.LSE[idx] * kLog2e : p.D[idx];
-        else v = (tid < 64) ? INFINITY : 0.f;   // rows past the end: exp2(-inf) = 0
-        dst[tid] = v;
+        if (tid < 128) {
+          float v = 0.f;
+          if (q < p.Sq) v = (tid < 64) ? p.LSE[idx] * kLog2e : p.D[idx];
+          else v = (tid < 64) ? INFINITY : 0.f;   // rows past the end: exp2(-inf) = 0
+          dst[tid] = v;
+        }
       }
       mbar_arrive(&stats_full[st]);
       if (*abort_flag || !mbar_wait_warp(&stats_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
       if (*abort_flag || !mbar_wait_warp(&st_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      float pt[64], ds[64];
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
+      float pt[32], ds[32];
+      {
         uint32_t r0[32], r1[32];
-        tmem_ld32(tST[st] + lane_off + c * 32, r0);
-        tmem_ld32(tDPT[st] + lane_off + c * 32, r1);
+        tmem_ld32(tST[st] + lane_off + c0, r0);
+        tmem_ld32(tDPT[st] + lane_off + c0, r1);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) { pt[c * 32 + i] = __uint_as_float(r0[i]); ds[c * 32 + i] = __uint_as_float(r1[i]); }
+        for (int i = 0; i < 32; ++i) { pt[i] = __uint_as_float(r0[i]); ds[i] = __uint_as_float(r1[i]); }
       }
       tc_fence_before();
       mbar_arrive(&st_empty[st]);
-      const float* lse2 = sStats + st * 128;
+      const float* lse2 = sStats + st * 128 + c0;
       const float* dd = lse2 + 64;
       const bool need_mask = p.causal && (p.q_pos0 + qrow < p.k_pos0 + k0 + 127);
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
+      for (int i = 0; i < 32; ++i) {
         float pv = exp2f(pt[i] * sl2 - lse2[i]);
-        if (!k_valid || (need_mask && (k_pos > p.q_pos0 + qrow + i))) pv = 0.f;
+        if (!k_valid || (need_mask && (k_pos > p.q_pos0 + qrow + c0 + i))) pv = 0.f;
         pt[i] = pv;
         ds[i] = pv * (ds[i] - dd[i]);
       }
@@ -554,14 +563,14 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         if (!mbar_wait_warp(pds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
       }
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
+      for (int cc = 0; cc < 4; ++cc) {
         uint4 u, w;
         u.x = pack_bf16(pt[cc * 8 + 0], pt[cc * 8 + 1]); u.y = pack_bf16(pt[cc * 8 + 2], pt[cc * 8 + 3]);
         u.z = pack_bf16(pt[cc * 8 + 4], pt[cc * 8 + 5]); u.w = pack_bf16(pt[cc * 8 + 6], pt[cc * 8 + 7]);
         w.x = pack_bf16(ds[cc * 8 + 0], ds[cc * 8 + 1]); w.y = pack_bf16(ds[cc * 8 + 2], ds[cc * 8 + 3]);
         w.z = pack_bf16(ds[cc * 8 + 4], ds[cc * 8 + 5]); w.w = pack_bf16(ds[cc * 8 + 6], ds[cc * 8 + 7]);
-        *reinterpret_cast<uint4*>(sPT + sw128_offset(row, cc)) = u;
-        *reinterpret_cast<uint4*>(sDST + sw128_offset(row, cc)) = w;
+        *reinterpret_cast<uint4*>(sPT + sw128_offset(row, half * 4 + cc)) = u;
+        *reinterpret_cast<uint4*>(sDST + sw128_offset(row, half * 4 + cc)) = w;
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -575,7 +584,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (n_it == 0) {
       if (krow < p.Skv) {
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
+        for (int i = half; i < HD / 8; i += 2) {
           reinterpret_cast<uint4*>(dk)[i] = make_uint4(0, 0, 0, 0);
           reinterpret_cast<uint4*>(dv)[i] = make_uint4(0, 0, 0, 0);
         }
@@ -583,7 +592,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     } else if (ok && !*abort_flag && mbar_wait_warp(pds_empty, (n_it - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half; c < HD / 32; c += 2) {   // the two warpgroups take alternate 32-column chunks
         uint32_t r0[32], r1[32];
         tmem_ld32(tDV + lane_off + c * 32, r0);
         tmem_ld32(tDK + lane_off + c * 32, r1);
@@ -630,7 +639,7 @@ struct DqSmem {
 };
 
 template <int HD>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const BwdParams p) {
@@ -667,9 +676,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], kBwdSoftmaxThreads);
     }
-    mbar_init(ds_full, 128);
+    mbar_init(ds_full, kBwdSoftmaxThreads);
     mbar_init(ds_empty, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -747,6 +756,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     }
   } else {
     const int wq = warp & 3;
+    const int half = (warp - 2) >> 2;     // which 32 of the step's 64 key columns this warpgroup owns
+    const int c0 = half * 32;
     const int row = wq * 32 + lane_id();
     const uint32_t lane_off = uint32_t(wq * 32) << 16;
     const float sl2 = p.scale * kLog2e;
@@ -763,24 +774,23 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const int st = it & 1;
       if (*abort_flag || !mbar_wait_warp(&s_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      float ds[64];
+      float ds[32];
       {
-        float sv[64];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        float sv[32];
+        {
           uint32_t r0[32], r1[32];
-          tmem_ld32(tS[st] + lane_off + c * 32, r0);
-          tmem_ld32(tDP[st] + lane_off + c * 32, r1);
+          tmem_ld32(tS[st] + lane_off + c0, r0);
+          tmem_ld32(tDP[st] + lane_off + c0, r1);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) { sv[c * 32 + i] = __uint_as_float(r0[i]); ds[c * 32 + i] = __uint_as_float(r1[i]); }
+          for (int i = 0; i < 32; ++i) { sv[i] = __uint_as_float(r0[i]); ds[i] = __uint_as_float(r1[i]); }
         }
         tc_fence_before();
         mbar_arrive(&s_empty[st]);
-        const int kbase = it * 64;
-        const bool need_mask = (p.causal && (p.k_pos0 + kbase + 63 > p.q_pos0 + q0)) || (kbase + 64 > p.Skv);
+        const int kbase = it * 64 + c0;
+        const bool need_mask = (p.causal && (p.k_pos0 + kbase + 31 > p.q_pos0 + q0)) || (kbase + 32 > p.Skv);
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < 32; ++i) {
           float pv = exp2f(sv[i] * sl2 - lse2);
           if (need_mask && ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos)))) pv = 0.f;
           ds[i] = pv * (ds[i] - dsum);
@@ -790,11 +800,11 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!mbar_wait_warp(ds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
       }
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
+      for (int cc = 0; cc < 4; ++cc) {
         uint4 w;
         w.x = pack_bf16(ds[cc * 8 + 0], ds[cc * 8 + 1]); w.y = pack_bf16(ds[cc * 8 + 2], ds[cc * 8 + 3]);
         w.z = pack_bf16(ds[cc * 8 + 4], ds[cc * 8 + 5]); w.w = pack_bf16(ds[cc * 8 + 6], ds[cc * 8 + 7]);
-        *reinterpret_cast<uint4*>(sDS + sw128_offset(row, cc)) = w;
+        *reinterpret_cast<uint4*>(sDS + sw128_offset(row, half * 4 + cc)) = w;
       }
       fence_proxy_async_smem();
       tc_fence_before();
@@ -805,12 +815,12 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (n_it == 0) {
       if (srow < p.Sq) {
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4*>(dq)[i] = make_uint4(0, 0, 0, 0);
+        for (int i = half; i < HD / 8; i += 2) reinterpret_cast<uint4*>(dq)[i] = make_uint4(0, 0, 0, 0);
       }
     } else if (ok && !*abort_flag && mbar_wait_warp(ds_empty, (n_it - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
       tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < HD / 32; ++c) {
+      for (int c = half; c < HD / 32; c += 2) {   // the two warpgroups take alternate 32-column chunks
         uint32_t r[32];
         tmem_ld32(tDQ + lane_off + c * 32, r);
         tmem_ld_wait();
@@ -949,11 +959,11 @@ int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
     if (hd == 128) {
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(flash_bwd_dkv_kernel<128>, DkvSmem<128>::kTotal))) return rc; cfg = true; }
-      flash_bwd_dkv_kernel<128><<<grid, kThreads, DkvSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+      flash_bwd_dkv_kernel<128><<<grid, kBwdThreads, DkvSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
     } else {
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(flash_bwd_dkv_kernel<64>, DkvSmem<64>::kTotal))) return rc; cfg = true; }
-      flash_bwd_dkv_kernel<64><<<grid, kThreads, DkvSmem<64>::kTotal, st>>>(tq, tk, tv, tdo, p);
+      flash_bwd_dkv_kernel<64><<<grid, kBwdThreads, DkvSmem<64>::kTotal, st>>>(tq, tk, tv, tdo, p);
     }
   }
   {
@@ -966,11 +976,11 @@ int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
     if (hd == 128) {
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(flash_bwd_dq_kernel<128>, DqSmem<128>::kTotal))) return rc; cfg = true; }
-      flash_bwd_dq_kernel<128><<<grid, kThreads, DqSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+      flash_bwd_dq_kernel<128><<<grid, kBwdThreads, DqSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
     } else {
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(flash_bwd_dq_kernel<64>, DqSmem<64>::kTotal))) return rc; cfg = true; }
-      flash_bwd_dq_kernel<64><<<grid, kThreads, DqSmem<64>::kTotal, st>>>(tq, tk, tv, tdo, p);
+      flash_bwd_dq_kernel<64><<<grid, kBwdThreads, DqSmem<64>::kTotal, st>>>(tq, tk, tv, tdo, p);
     }
   }
   return int(cudaGetLastError());
