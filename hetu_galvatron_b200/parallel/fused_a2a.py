@@ -46,7 +46,8 @@ class A2AStaging:
         self.calls += 1
         slot = self.slots[self.calls & 1]
         nbytes = x.numel() * x.element_size()
-        slot.tensor[:nbytes].view(x.dtype).copy_(x.reshape(-1))
+        # one pass even when ``x`` is a strided view (e.g. q / k / v inside the packed QKV buffer)
+        slot.tensor[:nbytes].view(x.dtype).view(x.shape).copy_(x)
         peer_barrier(self.group.group, self.device)
         return slot
 
@@ -82,7 +83,7 @@ def _seq_to_heads(x: torch.Tensor, group, p: int, rep: int) -> torch.Tensor:
     d = group.rank
     m = max(1, n * rep // p)
     first_head = (d // rep) if rep > 1 else d * m
-    slot = staging_for(group, x.numel() * 2, x.device).publish(x.contiguous())
+    slot = staging_for(group, x.numel() * 2, x.device).publish(x)
     out = torch.empty((p * S, B, m, hd), dtype=x.dtype, device=x.device)
     _gather(slot, S * B, m * hd, first_head * hd, n * hd, out, S * B * m * hd, m * hd)
     return out
@@ -93,7 +94,7 @@ def _heads_to_seq(y: torch.Tensor, group, p: int) -> torch.Tensor:
     Sp, B, m, hd = y.shape
     S = Sp // p
     d = group.rank
-    slot = staging_for(group, y.numel() * 2, y.device).publish(y.contiguous())
+    slot = staging_for(group, y.numel() * 2, y.device).publish(y)
     out = torch.empty((S, B, p * m, hd), dtype=y.dtype, device=y.device)
     _gather(slot, S * B, m * hd, d * S * B * m * hd, m * hd, out, m * hd, p * m * hd)
     return out
@@ -211,7 +212,7 @@ class MoERouting:
 def _publish_sized(group, x: torch.Tensor, rows_bound: int) -> SymmetricBuffer:
     """Publish ``x [rows, width]``; the staging is sized by ``rows_bound`` (the same number on every rank)."""
     st = staging_for(group, rows_bound * x.shape[1] * 2, x.device)
-    return st.publish(x.contiguous())
+    return st.publish(x)
 
 
 class _MoEDispatch(torch.autograd.Function):

@@ -144,7 +144,7 @@ class Reshard(nn.Module):
         lists = self._lists.get(key)
         if lists is None:
             lists = self._lists[key] = pull_lists(S, rows_d, b_d, b_s, self.j % big if big else 0, src, dst, x.device)
-        slot = fa.staging_for(grp, x.numel() * 2, x.device).publish(x.contiguous())
+        slot = fa.staging_for(grp, x.numel() * 2, x.device).publish(x)
         out = fa.gather_rows(slot, lists[0], lists[1], rows_d * b_d, H, H)
         return out.view(rows_d, b_d, H)
 
