@@ -55,7 +55,16 @@ def get_runtime_profiler(args, model, start_iter: int = 10, end_iter: int = 20) 
     return prof
 
 
-def train(args, max_iters: Optional[int] = None, profile_window=(10, 20)):
+def _profile_window(default):
+    """``HG_PROFILE_WINDOW="start,end"`` moves the iterations that the runtime profiler times (default 10..20)."""
+    v = os.environ.get("HG_PROFILE_WINDOW")
+    if not v:
+        return default
+    a, b = (int(x) for x in v.split(","))
+    return a, b
+
+
+def train(args, max_iters: Optional[int] = None, profile_window=None):
     """Runs ``args.train.train_iters`` iterations (or ``max_iters``); returns the list of per-iteration losses seen
     on this rank (``None`` entries on ranks that do not hold the last pipeline stage)."""
     resolve_model_config(args)
@@ -75,6 +84,7 @@ def train(args, max_iters: Optional[int] = None, profile_window=(10, 20)):
     train_it, valid_it, _ = get_train_valid_test_data_iterators(args, model)
     machine = get_rerun_state_machine()
     train_it = RerunDataIterator(train_it)
+    profile_window = profile_window or _profile_window((10, 20))
     profiler = get_runtime_profiler(args, model, start_iter=profile_window[0], end_iter=profile_window[1])
     profiler.profile_memory(0, "After creating model")
     total = max_iters if max_iters is not None else (args.train.train_iters or 0)
