@@ -371,9 +371,9 @@ template <int HD>
 struct DkvSmem {
   static constexpr int kKV = 128 * HD * 2;     // resident K or V
   static constexpr int kQD = 64 * HD * 2;      // one stage of Q or dO
-  static constexpr int kPT = 128 * 64 * 2;     // P^T or dS^T
+  static constexpr int kPT = 128 * 64 * 2;     // one P^T or dS^T buffer (two of each: written for step i+1 while step i is multiplied)
   static constexpr int kStats = 2 * 2 * 64 * 4;  // lse2/D, double buffered
-  static constexpr int kTotal = 2 * kKV + 4 * kQD + 2 * kPT + kStats + 1024 + 256;
+  static constexpr int kTotal = 2 * kKV + 4 * kQD + 4 * kPT + kStats + 1024 + 256;
 };
 
 template <int HD>
@@ -388,18 +388,18 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* sQ = sV + DkvSmem<HD>::kKV;            // 2 stages
   uint8_t* sDO = sQ + 2 * DkvSmem<HD>::kQD;       // 2 stages
   uint8_t* sPT = sDO + 2 * DkvSmem<HD>::kQD;
-  uint8_t* sDST = sPT + DkvSmem<HD>::kPT;
-  float* sStats = reinterpret_cast<float*>(sDST + DkvSmem<HD>::kPT);  // [2][2][64]
+  uint8_t* sDST = sPT + 2 * DkvSmem<HD>::kPT;
+  float* sStats = reinterpret_cast<float*>(sDST + 2 * DkvSmem<HD>::kPT);  // [2][2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStats) + DkvSmem<HD>::kStats);
   uint64_t* kv_full = bars;        // 1
   uint64_t* qd_full = bars + 1;    // 2
   uint64_t* qd_empty = bars + 3;   // 2
   uint64_t* st_full = bars + 5;    // 2
   uint64_t* st_empty = bars + 7;   // 2
-  uint64_t* pds_full = bars + 9;   // 1
-  uint64_t* pds_empty = bars + 10; // 1
-  uint64_t* stats_full = bars + 11; // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* pds_full = bars + 9;   // 2
+  uint64_t* pds_empty = bars + 11; // 2
+  uint64_t* stats_full = bars + 13; // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -421,9 +421,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       mbar_init(&qd_empty[i], 1);
       mbar_init(&st_full[i], 1);
       mbar_init(&st_empty[i], kBwdSoftmaxThreads);
+      mbar_init(&pds_full[i], kBwdSoftmaxThreads);
+      mbar_init(&pds_empty[i], 1);
     }
-    mbar_init(pds_full, kBwdSoftmaxThreads);
-    mbar_init(pds_empty, 1);
     mbar_init(&stats_full[0], kBwdSoftmaxThreads);
     mbar_init(&stats_full[1], kBwdSoftmaxThreads);
     *abort_flag = 0;
@@ -493,17 +493,18 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       for (int it = 0; ok && it < n_it; ++it) {
         if (it + 1 < n_it) { ok = issue_st(it + 1); if (!ok) break; }
         const int st = it & 1;
-        if (*abort_flag || !mbar_wait(pds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        if (*abort_flag || !mbar_wait(&pds_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t aQ = smem_u32(sQ + st * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + st * DkvSmem<HD>::kQD);
+        const uint32_t aPTs = aPT + st * DkvSmem<HD>::kPT, aDSTs = aDST + st * DkvSmem<HD>::kPT;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_f16_ss(tDV, kmajor_desc(aPT, 128, kk), mnmajor_desc(aDO, 64, kk), idesc_acc, (it | kk) != 0);
+          umma_f16_ss(tDV, kmajor_desc(aPTs, 128, kk), mnmajor_desc(aDO, 64, kk), idesc_acc, (it | kk) != 0);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_f16_ss(tDK, kmajor_desc(aDST, 128, kk), mnmajor_desc(aQ, 64, kk), idesc_acc, (it | kk) != 0);
+          umma_f16_ss(tDK, kmajor_desc(aDSTs, 128, kk), mnmajor_desc(aQ, 64, kk), idesc_acc, (it | kk) != 0);
         umma_commit(&qd_empty[st]);
-        umma_commit(pds_empty);
+        umma_commit(&pds_empty[st]);
       }
       if (!ok) *abort_flag = 1;
     }
@@ -559,9 +560,11 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         pt[i] = pv;
         ds[i] = pv * (ds[i] - dd[i]);
       }
-      if (it > 0) {
-        if (!mbar_wait_warp(pds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      if (it >= 2) {   // these buffers were last read by the dV / dK products of step it-2
+        if (!mbar_wait_warp(&pds_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
       }
+      uint8_t* sPTs = sPT + st * DkvSmem<HD>::kPT;
+      uint8_t* sDSTs = sDST + st * DkvSmem<HD>::kPT;
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         uint4 u, w;
@@ -569,12 +572,12 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         u.z = pack_bf16(pt[cc * 8 + 4], pt[cc * 8 + 5]); u.w = pack_bf16(pt[cc * 8 + 6], pt[cc * 8 + 7]);
         w.x = pack_bf16(ds[cc * 8 + 0], ds[cc * 8 + 1]); w.y = pack_bf16(ds[cc * 8 + 2], ds[cc * 8 + 3]);
         w.z = pack_bf16(ds[cc * 8 + 4], ds[cc * 8 + 5]); w.w = pack_bf16(ds[cc * 8 + 6], ds[cc * 8 + 7]);
-        *reinterpret_cast<uint4*>(sPT + sw128_offset(row, half * 4 + cc)) = u;
-        *reinterpret_cast<uint4*>(sDST + sw128_offset(row, half * 4 + cc)) = w;
+        *reinterpret_cast<uint4*>(sPTs + sw128_offset(row, half * 4 + cc)) = u;
+        *reinterpret_cast<uint4*>(sDSTs + sw128_offset(row, half * 4 + cc)) = w;
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(pds_full);
+      mbar_arrive(&pds_full[st]);
     }
     // ---- epilogue ----
     const int krow = k0 + row;
@@ -589,7 +592,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
           reinterpret_cast<uint4*>(dv)[i] = make_uint4(0, 0, 0, 0);
         }
       }
-    } else if (ok && !*abort_flag && mbar_wait_warp(pds_empty, (n_it - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
+    } else if (ok && !*abort_flag &&
+               mbar_wait_warp(&pds_empty[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, p.status, kTimeoutOther, abort_flag)) {
       tc_fence_after();
 #pragma unroll
       for (int c = half; c < HD / 32; c += 2) {   // the two warpgroups take alternate 32-column chunks
@@ -634,8 +638,8 @@ template <int HD>
 struct DqSmem {
   static constexpr int kQ = 128 * HD * 2;     // resident Q or dO
   static constexpr int kKV = 64 * HD * 2;     // one stage of K or V
-  static constexpr int kDS = 128 * 64 * 2;
-  static constexpr int kTotal = 2 * kQ + 4 * kKV + kDS + 1024 + 256;
+  static constexpr int kDS = 128 * 64 * 2;    // one dS buffer (two are kept so that step i+1 is written while step i is multiplied)
+  static constexpr int kTotal = 2 * kQ + 4 * kKV + 2 * kDS + 1024 + 256;
 };
 
 template <int HD>
@@ -650,15 +654,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* sK = sDO + DqSmem<HD>::kQ;            // 2 stages
   uint8_t* sV = sK + 2 * DqSmem<HD>::kKV;        // 2 stages
   uint8_t* sDS = sV + 2 * DqSmem<HD>::kKV;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + DqSmem<HD>::kDS);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + 2 * DqSmem<HD>::kDS);
   uint64_t* qdo_full = bars;       // 1
   uint64_t* kv_full = bars + 1;    // 2
   uint64_t* kv_empty = bars + 3;   // 2
   uint64_t* s_full = bars + 5;     // 2
   uint64_t* s_empty = bars + 7;    // 2
-  uint64_t* ds_full = bars + 9;    // 1
-  uint64_t* ds_empty = bars + 10;  // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+  uint64_t* ds_full = bars + 9;    // 2
+  uint64_t* ds_empty = bars + 11;  // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -677,9 +681,9 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&kv_empty[i], 1);
       mbar_init(&s_full[i], 1);
       mbar_init(&s_empty[i], kBwdSoftmaxThreads);
+      mbar_init(&ds_full[i], kBwdSoftmaxThreads);
+      mbar_init(&ds_empty[i], 1);
     }
-    mbar_init(ds_full, kBwdSoftmaxThreads);
-    mbar_init(ds_empty, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -743,14 +747,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       for (int it = 0; ok && it < n_it; ++it) {
         if (it + 1 < n_it) { ok = issue_s(it + 1); if (!ok) break; }
         const int st = it & 1;
-        if (*abort_flag || !mbar_wait(ds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        if (*abort_flag || !mbar_wait(&ds_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t aK = smem_u32(sK + st * DqSmem<HD>::kKV);
+        const uint32_t aDSs = aDS + st * DqSmem<HD>::kDS;
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)
-          umma_f16_ss(tDQ, kmajor_desc(aDS, 128, kk), mnmajor_desc(aK, 64, kk), idesc_dq, (it | kk) != 0);
+          umma_f16_ss(tDQ, kmajor_desc(aDSs, 128, kk), mnmajor_desc(aK, 64, kk), idesc_dq, (it | kk) != 0);
         umma_commit(&kv_empty[st]);
-        umma_commit(ds_empty);
+        umma_commit(&ds_empty[st]);
       }
       if (!ok) *abort_flag = 1;
     }
@@ -796,19 +801,20 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
           ds[i] = pv * (ds[i] - dsum);
         }
       }
-      if (it > 0) {
-        if (!mbar_wait_warp(ds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      if (it >= 2) {   // this buffer was last read by the dQ product of step it-2
+        if (!mbar_wait_warp(&ds_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
       }
+      uint8_t* sDSs = sDS + st * DqSmem<HD>::kDS;
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         uint4 w;
         w.x = pack_bf16(ds[cc * 8 + 0], ds[cc * 8 + 1]); w.y = pack_bf16(ds[cc * 8 + 2], ds[cc * 8 + 3]);
         w.z = pack_bf16(ds[cc * 8 + 4], ds[cc * 8 + 5]); w.w = pack_bf16(ds[cc * 8 + 6], ds[cc * 8 + 7]);
-        *reinterpret_cast<uint4*>(sDS + sw128_offset(row, half * 4 + cc)) = w;
+        *reinterpret_cast<uint4*>(sDSs + sw128_offset(row, half * 4 + cc)) = w;
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      mbar_arrive(&ds_full[st]);
     }
     const int dqslot = p.dqmap.slot(h, p.qpg);
     __nv_bfloat16* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
@@ -817,7 +823,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
         for (int i = half; i < HD / 8; i += 2) reinterpret_cast<uint4*>(dq)[i] = make_uint4(0, 0, 0, 0);
       }
-    } else if (ok && !*abort_flag && mbar_wait_warp(ds_empty, (n_it - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
+    } else if (ok && !*abort_flag &&
+               mbar_wait_warp(&ds_empty[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, p.status, kTimeoutOther, abort_flag)) {
       tc_fence_after();
 #pragma unroll
       for (int c = half; c < HD / 32; c += 2) {   // the two warpgroups take alternate 32-column chunks
