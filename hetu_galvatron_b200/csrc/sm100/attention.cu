@@ -855,6 +855,232 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
+
+// =================================================================================================
+// Backward, part 2 with 128-key steps (head dim 128).  A tcgen05.mma of shape 128 x N x 16 occupies the tensor core
+// for the same time whatever N <= 256 is, so the score products are issued with N = 128 instead of 64: per 128 keys
+// the kernel issues 24 MMAs (8 S, 8 dP, 8 dQ) where the 64-key version issues 40.  Shared memory then holds two
+// 128-row K/V stages (128 KB), Q and dO (64 KB) and one dS buffer (32 KB, two 64-column slabs, one per softmax
+// warpgroup); tensor memory holds one S / dP pair (256 columns) and dQ (128).  The S product of step i+1 is issued
+// as soon as the softmax threads have loaded step i into registers, so it still overlaps their arithmetic.
+// =================================================================================================
+template <int HD>
+struct Dq128Smem {
+  static constexpr int kQ = 128 * HD * 2;      // resident Q or dO
+  static constexpr int kKV = 128 * HD * 2;     // one stage of K or V
+  static constexpr int kDS = 128 * 128 * 2;    // dS: two K-major slabs of [128 rows x 64 keys]
+  static constexpr int kTotal = 2 * kQ + 4 * kKV + kDS + 1024 + 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                       const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  using L = Dq128Smem<HD>;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;
+  uint8_t* sDO = sQ + L::kQ;
+  uint8_t* sK = sDO + L::kQ;            // 2 stages
+  uint8_t* sV = sK + 2 * L::kKV;        // 2 stages
+  uint8_t* sDS = sV + 2 * L::kKV;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + L::kDS);
+  uint64_t* qdo_full = bars;       // 1
+  uint64_t* kv_full = bars + 1;    // 2
+  uint64_t* kv_empty = bars + 3;   // 2
+  uint64_t* s_full = bars + 5;     // 1
+  uint64_t* s_empty = bars + 6;    // 1
+  uint64_t* ds_full = bars + 7;    // 1
+  uint64_t* ds_empty = bars + 8;   // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int qb = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb * 128;
+  int kv_len = p.Skv;
+  if (p.causal) kv_len = min(p.Skv, p.q_pos0 + q0 + 127 - p.k_pos0 + 1);
+  const int n_it = kv_len > 0 ? (kv_len + 127) / 128 : 0;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+    mbar_init(qdo_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&kv_full[i], 1);
+      mbar_init(&kv_empty[i], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(s_empty, kBwdSoftmaxThreads);
+    mbar_init(ds_full, kBwdSoftmaxThreads);
+    mbar_init(ds_empty, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+
+  const int qslot = p.qmap.slot(h, p.qpg), kslot = p.kmap.slot(h, p.qpg), vslot = p.vmap.slot(h, p.qpg),
+            doslot = p.domap.slot(h, p.qpg);
+
+  if (warp == 0) {
+    if (lane_id() == 0 && n_it > 0) {
+      mbar_expect_tx(qdo_full, 2 * L::kQ);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        tma_load_4d(sQ + c * 128 * 128, &tmQ, qdo_full, c * 64, qslot, q0, b);
+        tma_load_4d(sDO + c * 128 * 128, &tmDO, qdo_full, c * 64, doslot, q0, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int st = it & 1;
+        if (*abort_flag || !mbar_wait(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        mbar_expect_tx(&kv_full[st], 2 * L::kKV);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c) {
+          tma_load_4d(sK + st * L::kKV + c * 128 * 128, &tmK, &kv_full[st], c * 64, kslot, it * 128, b);
+          tma_load_4d(sV + st * L::kKV + c * 128 * 128, &tmV, &kv_full[st], c * 64, vslot, it * 128, b);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane_id() == 0 && n_it > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
+      bool ok = mbar_wait(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      auto issue_s = [&](int it) -> bool {
+        const int st = it & 1;
+        if (*abort_flag || !mbar_wait(&kv_full[st], (it >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait(s_empty, (it & 1) ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * L::kKV), aV = smem_u32(sV + st * L::kKV);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_f16_ss(tS, kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 128, kk), idesc_s, kk != 0);
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+          umma_f16_ss(tDP, kmajor_desc(aDO, 128, kk), kmajor_desc(aV, 128, kk), idesc_s, kk != 0);
+        umma_commit(s_full);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int it = 0; ok && it < n_it; ++it) {
+        if (it + 1 < n_it) { ok = issue_s(it + 1); if (!ok) break; }
+        const int st = it & 1;
+        if (*abort_flag || !mbar_wait(ds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t aK = smem_u32(sK + st * L::kKV);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          umma_f16_ss(tDQ, kmajor_desc(aDS, 128, kk), mnmajor_desc(aK, 128, kk), idesc_dq, (it | kk) != 0);
+        umma_commit(&kv_empty[st]);
+        umma_commit(ds_empty);
+      }
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    const int wq = warp & 3;
+    const int half = (warp - 2) >> 2;     // which 64 of the step's 128 key columns this warpgroup owns
+    const int c0 = half * 64;
+    const int row = wq * 32 + lane_id();
+    const uint32_t lane_off = uint32_t(wq * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    const int srow = q0 + row;
+    const int q_pos = p.q_pos0 + srow;
+    float lse2 = INFINITY, dsum = 0.f;
+    if (srow < p.Sq) {
+      const size_t idx = (size_t(b) * p.nheads + h) * p.Sq + srow;
+      lse2 = p.LSE[idx] * kLog2e;
+      dsum = p.D[idx];
+    }
+    uint8_t* sDSh = sDS + half * (128 * 128);   // this warpgroup's slab
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      if (*abort_flag || !mbar_wait_warp(s_full, it & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      float ds[64];
+      {
+        float sv[64];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          uint32_t r0[32], r1[32];
+          tmem_ld32(tS + lane_off + c0 + c * 32, r0);
+          tmem_ld32(tDP + lane_off + c0 + c * 32, r1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) { sv[c * 32 + i] = __uint_as_float(r0[i]); ds[c * 32 + i] = __uint_as_float(r1[i]); }
+        }
+        tc_fence_before();
+        mbar_arrive(s_empty);
+        const int kbase = it * 128 + c0;
+        const bool need_mask = (p.causal && (p.k_pos0 + kbase + 63 > p.q_pos0 + q0)) || (kbase + 64 > p.Skv);
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          float pv = exp2f(sv[i] * sl2 - lse2);
+          if (need_mask && ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos)))) pv = 0.f;
+          ds[i] = pv * (ds[i] - dsum);
+        }
+      }
+      if (it > 0) {
+        if (!mbar_wait_warp(ds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      }
+#pragma unroll
+      for (int cc = 0; cc < 8; ++cc) {
+        uint4 w;
+        w.x = pack_bf16(ds[cc * 8 + 0], ds[cc * 8 + 1]); w.y = pack_bf16(ds[cc * 8 + 2], ds[cc * 8 + 3]);
+        w.z = pack_bf16(ds[cc * 8 + 4], ds[cc * 8 + 5]); w.w = pack_bf16(ds[cc * 8 + 6], ds[cc * 8 + 7]);
+        *reinterpret_cast<uint4*>(sDSh + sw128_offset(row, cc)) = w;
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    const int dqslot = p.dqmap.slot(h, p.qpg);
+    __nv_bfloat16* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
+    if (n_it == 0) {
+      if (srow < p.Sq) {
+#pragma unroll
+        for (int i = half; i < HD / 8; i += 2) reinterpret_cast<uint4*>(dq)[i] = make_uint4(0, 0, 0, 0);
+      }
+    } else if (ok && !*abort_flag && mbar_wait_warp(ds_empty, (n_it - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
+      tc_fence_after();
+#pragma unroll
+      for (int c = half; c < HD / 32; c += 2) {
+        uint32_t r[32];
+        tmem_ld32(tDQ + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (srow < p.Sq) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(r[q * 8 + 0]) * p.scale, __uint_as_float(r[q * 8 + 1]) * p.scale);
+            u.y = pack_bf16(__uint_as_float(r[q * 8 + 2]) * p.scale, __uint_as_float(r[q * 8 + 3]) * p.scale);
+            u.z = pack_bf16(__uint_as_float(r[q * 8 + 4]) * p.scale, __uint_as_float(r[q * 8 + 5]) * p.scale);
+            u.w = pack_bf16(__uint_as_float(r[q * 8 + 6]) * p.scale, __uint_as_float(r[q * 8 + 7]) * p.scale);
+            reinterpret_cast<uint4*>(dq + c * 32)[q] = u;
+          }
+        }
+      }
+    } else {
+      *abort_flag = 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
 }  // namespace attn
 }  // namespace hg
 
@@ -975,15 +1201,16 @@ int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
   }
   {
     CUtensorMap tq, tk, tv, tdo;
+    const int kv_rows = (hd == 128) ? 128 : 64;   // keys per step of the dQ kernel
     if ((rc = make_map(&tq, q->ptr, hd, q->slots, Sq, B, q->ss, q->sb, 128))) return rc;
-    if ((rc = make_map(&tk, k->ptr, hd, k->slots, Skv, B, k->ss, k->sb, 64))) return rc;
-    if ((rc = make_map(&tv, v->ptr, hd, v->slots, Skv, B, v->ss, v->sb, 64))) return rc;
+    if ((rc = make_map(&tk, k->ptr, hd, k->slots, Skv, B, k->ss, k->sb, kv_rows))) return rc;
+    if ((rc = make_map(&tv, v->ptr, hd, v->slots, Skv, B, v->ss, v->sb, kv_rows))) return rc;
     if ((rc = make_map(&tdo, d_o->ptr, hd, d_o->slots, Sq, B, d_o->ss, d_o->sb, 128))) return rc;
     dim3 grid((Sq + 127) / 128, nheads, B);
     if (hd == 128) {
       static bool cfg = false;
-      if (!cfg) { if ((rc = set_smem(flash_bwd_dq_kernel<128>, DqSmem<128>::kTotal))) return rc; cfg = true; }
-      flash_bwd_dq_kernel<128><<<grid, kBwdThreads, DqSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+      if (!cfg) { if ((rc = set_smem(flash_bwd_dq128_kernel<128>, Dq128Smem<128>::kTotal))) return rc; cfg = true; }
+      flash_bwd_dq128_kernel<128><<<grid, kBwdThreads, Dq128Smem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
     } else {
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(flash_bwd_dq_kernel<64>, DqSmem<64>::kTotal))) return rc; cfg = true; }
