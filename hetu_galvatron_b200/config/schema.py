@@ -140,6 +140,7 @@ GalvatronModelArgs = _build("GalvatronModelArgs", {
     "moe_router_num_groups": (O[int], None),
     "moe_router_group_topk": (O[int], None),
     "moe_router_enable_expert_bias": (bool, False),
+    "moe_router_bias_update_rate": (float, 1.0e-3),
     "moe_router_dtype": (O[Literal["fp32", "fp64"]], None),
     "deterministic_mode": (bool, False),
     "moe_aux_loss_coeff": (float, 0.0),

@@ -134,6 +134,50 @@ def switch_aux_loss(logits, idx, E, k, coeff, group=None):
     return (agg * counts).sum() * (E * coeff / (k * total_T * T))
 
 
+def sequence_aux_loss(logits, idx, E, k, coeff, batch: int):
+    """Load-balancing loss computed per sequence and averaged over the batch (rows are ordered ``s * batch + b``):
+    for every sequence, ``sum_e mean_prob_e * fraction_e * E / k`` (moe/moe_utils.py:62-112)."""
+    T = logits.shape[0]
+    S = T // batch
+    scores = torch.softmax(logits, dim=-1).view(S, batch, E)
+    valid = (idx >= 0)
+    onehot = torch.zeros(T, E, dtype=torch.float32, device=logits.device)
+    onehot.scatter_add_(1, idx.clamp(min=0), valid.to(torch.float32))
+    frac = onehot.view(S, batch, E).sum(0) / (S * k)            # [batch, E] fraction of the sequence's slots
+    mean_prob = scores.mean(0)                                     # [batch, E]
+    return (mean_prob * frac).sum(-1).mean() * (E * coeff)
+
+
+def sinkhorn(cost: torch.Tensor, tol: float = 1e-4, max_iter: int = 100) -> torch.Tensor:
+    """Sinkhorn-Knopp normalisation of ``exp(cost)`` towards uniform row and column sums (moe/moe_utils.py:14-59)."""
+    cost = torch.exp(cost)
+    d0 = torch.ones(cost.size(0), device=cost.device, dtype=cost.dtype)
+    d1 = torch.ones(cost.size(1), device=cost.device, dtype=cost.dtype)
+    eps = 1e-8
+    err = 1e9
+    it = 0
+    while err > tol and it < max_iter:
+        d1_old = d1
+        d0 = (1.0 / d0.size(0)) / (torch.sum(d1 * cost, 1) + eps)
+        d1 = (1.0 / d1.size(0)) / (torch.sum(d0.unsqueeze(1) * cost, 0) + eps)
+        err = float(torch.mean(torch.abs(d1_old - d1)))
+        it += 1
+    return d1 * cost * d0.unsqueeze(1)
+
+
+def sinkhorn_routing(logits: torch.Tensor, k: int, training: bool):
+    """Selection by the balanced assignment (no gradient), probabilities from the raw logits: sigmoid for top-1,
+    softmax otherwise (moe/router.py:236-262)."""
+    act = (lambda x: torch.sigmoid(x)) if k == 1 else (lambda x: torch.softmax(x, dim=-1, dtype=torch.float32))
+    if training:
+        with torch.no_grad():
+            idx = sinkhorn(logits.float()).topk(k, dim=1).indices
+        return act(logits).gather(1, idx), idx
+    scores = act(logits)
+    probs, idx = scores.topk(k, dim=1)
+    return probs, idx
+
+
 def z_loss(logits, coeff):
     return torch.logsumexp(logits, dim=-1).pow(2).mean() * coeff
 
@@ -153,6 +197,19 @@ class GalvatronMoERouter(nn.Module):
         init_normal_sharded_(self.router.weight, self.spec.init_std, (self.spec.experts, self.spec.hidden), None, 0, 1,
                              seed, self.name + ".router.weight", full_init)
 
+    def update_expert_bias(self, rate: float, group=None):
+        """Aux-loss-free balancing: after an optimizer step, raise the selection bias of under-loaded experts and
+        lower that of over-loaded ones by ``rate`` (token counts summed over ``group``), then reset the counters
+        (moe/moe_utils.py:547-571)."""
+        if not hasattr(self.router, "expert_bias"):
+            return
+        with torch.no_grad():
+            load = self.router.local_tokens_per_expert.clone()
+            if group is not None and dist.is_initialized():
+                dist.all_reduce(load, group=group)
+            self.router.expert_bias += torch.sign(load.mean() - load) * rate
+            self.router.local_tokens_per_expert.zero_()
+
     def forward(self, x2d: torch.Tensor):
         """x2d [T, H] -> (probs [T, k] fp32, idx [T, k] int64 with -1 for dropped, x2d possibly carrying aux losses)."""
         s = self.spec
@@ -165,11 +222,17 @@ class GalvatronMoERouter(nn.Module):
         if s.z_loss_coeff and self.training:
             logits = _AuxLossScaler.apply(logits, z_loss(logits, s.z_loss_coeff))
         bias = getattr(self.router, "expert_bias", None)
-        probs, idx = topk_routing(logits, s, bias)
+        if s.load_balancing == "sinkhorn":
+            probs, idx = sinkhorn_routing(logits, s.topk, self.training)
+        else:
+            probs, idx = topk_routing(logits, s, bias)
         if s.capacity_factor is not None:
             cap = math.ceil(x2d.shape[0] * s.topk / s.experts * s.capacity_factor)
             probs, idx = apply_capacity(probs, idx, s.experts, cap, s.drop_policy)
-        if s.aux_loss_coeff and s.load_balancing in ("aux_loss", "seq_aux_loss") and self.training:
+        if s.aux_loss_coeff and s.load_balancing == "seq_aux_loss" and self.training and getattr(self, "batch_hint", 0):
+            probs = _AuxLossScaler.apply(probs, sequence_aux_loss(logits, idx, s.experts, s.topk, s.aux_loss_coeff,
+                                                                  self.batch_hint))
+        elif s.aux_loss_coeff and s.load_balancing in ("aux_loss", "seq_aux_loss") and self.training:
             grp = self.ctx.tp if self.ctx.tp_size > 1 else (self.ctx.sp if self.ctx.sp_size > 1 else None)
             probs = _AuxLossScaler.apply(probs, switch_aux_loss(logits, idx, s.experts, s.topk, s.aux_loss_coeff, grp))
         if bias is not None:
@@ -436,6 +499,7 @@ class MoELayerRunner(nn.Module):
         n, h = res[0], res[1]
         S, B, H = n.shape
         n2 = n.reshape(S * B, H)
+        self.router.inner.batch_hint = B
         probs, idx = self.router(n2)
         y = self.mlp(n2, probs, idx).view(S, B, H)
         if len(res) > 2:

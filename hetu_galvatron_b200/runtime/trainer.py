@@ -37,6 +37,20 @@ def _nvtx_pop():
         torch.cuda.nvtx.range_pop()
 
 
+def _update_expert_bias(model, args):
+    """Aux-loss-free load balancing: nudge every router's selection bias after the optimizer step."""
+    m = args.model
+    if not getattr(m, "moe_router_enable_expert_bias", False):
+        return
+    rate = getattr(m, "moe_router_bias_update_rate", 1e-3) or 1e-3
+    for unit in model.model.units:
+        router = getattr(unit, "router", None)
+        if router is not None and hasattr(router.inner, "update_expert_bias"):
+            ctx = router.inner.ctx
+            grp = ctx.sdp.group if (ctx.sdp is not None and ctx.sdp.size > 1) else None
+            router.inner.update_expert_bias(rate, grp)
+
+
 def get_optimizer_and_param_scheduler(model, args):
     t = args.train
     opt = ShardedAdamW(model.sharded_units, lr=t.lr, betas=(t.adam_beta1, t.adam_beta2), eps=t.adam_eps,
@@ -107,6 +121,7 @@ def train(args, max_iters: Optional[int] = None, profile_window=None):
             _nvtx_push("optimizer")
             model.sync_tied_embedding_grads()
             optimizer.step()
+            _update_expert_bias(model, args)
             _nvtx_pop()
             if scheduler is not None:
                 scheduler.step(increment=gbsz)

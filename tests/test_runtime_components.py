@@ -398,3 +398,50 @@ def test_reshard_pull_lists_match_the_collective_formulation(src, dst):
         want = held(data[:, (j // g_d) * b_d:(j // g_d + 1) * b_d], dst[0], dst[1], j % g_d)
         peer, row = pull_lists(S, S // g_d, b_d, b_s, j, src, dst, "cpu")
         assert torch.equal(flat[peer.long(), row.long()].view(S // g_d, b_d, H), want)
+
+
+# ---- MoE router extras ---------------------------------------------------------------------------------------------
+def test_sinkhorn_balances_and_routes():
+    from hetu_galvatron_b200.models import moe
+
+    torch.manual_seed(0)
+    logits = torch.randn(64, 8) + torch.tensor([3.0, 0, 0, 0, 0, 0, 0, 0])   # expert 0 is everybody's favourite
+    norm = moe.sinkhorn(logits)
+    assert torch.allclose(norm.sum(0), torch.full((8,), 1 / 8), atol=2e-3)      # balanced columns
+    probs, idx = moe.sinkhorn_routing(logits.clone().requires_grad_(), 2, training=True)
+    greedy = logits.topk(2, dim=1).indices
+    assert (idx == 0).sum() < (greedy == 0).sum()                               # fewer tokens pile on expert 0
+    assert probs.requires_grad and torch.allclose(probs, torch.softmax(logits, -1).gather(1, idx))
+    p1, i1 = moe.sinkhorn_routing(logits, 1, training=False)
+    assert torch.equal(i1, torch.sigmoid(logits).topk(1, dim=1).indices)
+
+
+def test_sequence_aux_loss_matches_per_sequence_formula():
+    from hetu_galvatron_b200.models import moe
+
+    torch.manual_seed(1)
+    S, B, E, k = 16, 3, 4, 2
+    logits = torch.randn(S * B, E)
+    idx = logits.topk(k, dim=1).indices
+    got = moe.sequence_aux_loss(logits, idx, E, k, 0.01, B)
+    sc = torch.softmax(logits, -1).view(S, B, E)
+    want = 0.0
+    for b in range(B):
+        counts = torch.bincount(idx.view(S, B, k)[:, b].reshape(-1), minlength=E).float()
+        want += (sc[:, b].mean(0) * counts / (S * k)).sum() * E * 0.01
+    assert got.item() == pytest.approx(float(want) / B, rel=1e-5)
+
+
+def test_expert_bias_update_moves_towards_balance():
+    from types import SimpleNamespace
+
+    from hetu_galvatron_b200.models import moe
+
+    r = moe.GalvatronMoERouter.__new__(moe.GalvatronMoERouter)
+    torch.nn.Module.__init__(r)
+    r.router = torch.nn.Module()
+    r.router.register_buffer("expert_bias", torch.zeros(4))
+    r.router.register_buffer("local_tokens_per_expert", torch.tensor([10.0, 2.0, 4.0, 4.0]))
+    r.update_expert_bias(0.1)
+    assert torch.allclose(r.router.expert_bias, torch.tensor([-0.1, 0.1, 0.1, 0.1]))
+    assert float(r.router.local_tokens_per_expert.sum()) == 0.0
