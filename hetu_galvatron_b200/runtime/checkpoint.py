@@ -140,7 +140,7 @@ def shard_from_hf(kind: str, hf: Dict[str, torch.Tensor], spec: ModelSpec, tp_ra
         if "bias" in hf:
             out["norm.bias"] = hf["bias"]
     elif kind in ("decoder", "moe_attention"):
-        pre = "attn." if kind == "decoder" else "attn.attn."
+        pre = "attn."   # GalvatronDecoderLayer.attn and GalvatronMoEAttention.attn are both a GalvatronAttention
         if "self_attn.q_proj.weight" in hf:  # llama-style names
             qkv = pack_qkv(hf["self_attn.q_proj.weight"], hf["self_attn.k_proj.weight"], hf["self_attn.v_proj.weight"],
                            nh, ng, hd)
@@ -175,16 +175,25 @@ def shard_from_hf(kind: str, hf: Dict[str, torch.Tensor], spec: ModelSpec, tp_ra
             out["ffn.mlp.linear_fc2.weight"] = _cols(hf["mlp.c_proj.weight"].t(), tp_rank, tp)
             out["ffn.mlp.linear_fc2.bias"] = hf["mlp.c_proj.bias"]
     elif kind == "moe_router":
-        out["router.weight"] = hf["block_sparse_moe.gate.weight"].float()
+        # classic Mixtral checkpoints name the gate block_sparse_moe.gate; newer transformers releases mlp.gate
+        key = "block_sparse_moe.gate.weight" if "block_sparse_moe.gate.weight" in hf else "mlp.gate.weight"
+        out["router.weight"] = hf[key].float()
     elif kind == "moe_mlp":
         e_loc = spec.experts // ep
         fc1, fc2 = [], []
+        fused = "mlp.experts.gate_up_proj" in hf   # newer layout: [E, 2F, H] (gate rows, then up rows) and [E, H, F]
         for j in range(e_loc):
             e = ep_rank * e_loc + j
-            base = "block_sparse_moe.experts.%d." % e
-            gate, up = _rows(hf[base + "w1.weight"], tp_rank, tp), _rows(hf[base + "w3.weight"], tp_rank, tp)
+            if fused:
+                gu = hf["mlp.experts.gate_up_proj"][e]
+                F = gu.shape[0] // 2
+                w1, w3, w2 = gu[:F], gu[F:], hf["mlp.experts.down_proj"][e]
+            else:
+                base = "block_sparse_moe.experts.%d." % e
+                w1, w3, w2 = hf[base + "w1.weight"], hf[base + "w3.weight"], hf[base + "w2.weight"]
+            gate, up = _rows(w1, tp_rank, tp), _rows(w3, tp_rank, tp)
             fc1.append(torch.cat([gate, up], dim=0))
-            fc2.append(_cols(hf[base + "w2.weight"], tp_rank, tp))
+            fc2.append(_cols(w2, tp_rank, tp))
         out["experts.linear_fc1.weight"] = torch.stack(fc1)
         out["experts.linear_fc2.weight"] = torch.stack(fc2)
     else:
@@ -247,7 +256,7 @@ def load_hf_split(model, load_dir: str):
             tp_rank, tp = ctx.etp_rank, ctx.etp_size
         sd = shard_from_hf(kind, hf, spec, tp_rank, tp, ep_rank, ep)
         unit.gather()
-        _copy_into(module, sd, strict=False)
+        _copy_into(module, sd, strict=True)   # a key the module does not have is a naming bug, not something to skip
         unit.reload_master()
         unit.release()
 

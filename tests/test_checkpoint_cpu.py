@@ -72,7 +72,36 @@ def train_and_resume(cfg):
     return train(args)
 
 
-REGISTRY = {"loss_from_split": loss_from_split, "train_and_resume": train_and_resume}
+def moe_args(parallel=None, model=None):
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+
+    p = dict(mixed_precision="fp32")
+    p.update(parallel or {})
+    m = dict(model_size="mixtral-test", hidden_size=H, num_layers=L, num_attention_heads=NH, num_query_groups=NKV,
+             vocab_size=V, normalization="RMSNorm", gated_linear_unit=True, activation_func="torch.nn.functional.silu",
+             untie_embeddings_and_output_weights=True, make_vocab_size_divisible_by=8, norm_epsilon=1e-5,
+             is_moe_model=True, num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=FFN, rotary_base=1000000)
+    m.update(model or {})
+    return GalvatronRuntimeArgs(parallel=p, model=m, data=dict(use_random_dataset=True),
+                                train=dict(seq_length=SEQ, global_batch_size=GB, chunks=1, lr=1e-3, seed=3))
+
+
+def moe_loss_from_split(cfg):
+    from hetu_galvatron_b200.runtime import checkpoint as ck
+    from hetu_galvatron_b200.runtime.engine import build_model
+
+    model = build_model(moe_args(cfg.get("parallel"), cfg.get("model")), device=torch.device("cpu"))
+    ck.load_hf_split(model, cfg["dir"])
+    tok = batch()
+    B = model.local_batch_size()
+    d = model.vocab_ctx.dp.rank if model.vocab_ctx.dp is not None else 0
+    mine = tok[d * B:(d + 1) * B]
+    loss = model.forward_backward(mine[:, :-1], 0, labels=mine[:, 1:], forward_only=True)
+    return float(loss) if loss is not None else None
+
+
+REGISTRY = {"loss_from_split": loss_from_split, "train_and_resume": train_and_resume,
+            "moe_loss_from_split": moe_loss_from_split}
 
 
 @pytest.fixture(scope="module")
@@ -90,6 +119,40 @@ def split_dir(tmp_path_factory):
         ref = m(input_ids=tok[:, :-1], labels=None).logits.float()
     loss = torch.nn.functional.cross_entropy(ref.reshape(-1, V), tok[:, 1:].reshape(-1)).item()
     return str(d), loss, m
+
+
+@pytest.fixture(scope="module")
+def mixtral_split(tmp_path_factory):
+    from transformers import MixtralConfig, MixtralForCausalLM
+
+    from hetu_galvatron_b200.runtime import checkpoint as ck
+
+    torch.manual_seed(21)
+    cfg = MixtralConfig(hidden_size=H, num_hidden_layers=L, num_attention_heads=NH, num_key_value_heads=NKV,
+                        intermediate_size=FFN, vocab_size=V, rms_norm_eps=1e-5, max_position_embeddings=SEQ,
+                        num_local_experts=4, num_experts_per_tok=2, tie_word_embeddings=False, router_aux_loss_coef=0.0,
+                        sliding_window=None, rope_theta=1000000.0)
+    m = MixtralForCausalLM(cfg).eval()
+    d = tmp_path_factory.mktemp("mixtral_split")
+    ck.convert_hf_to_split(m.state_dict(), "mixtral", str(d))
+    tok = batch()
+    with torch.no_grad():
+        logits = m(input_ids=tok[:, :-1]).logits.float()
+    loss = torch.nn.functional.cross_entropy(logits.reshape(-1, V), tok[:, 1:].reshape(-1)).item()
+    return str(d), loss
+
+
+@pytest.mark.parametrize("world,parallel,model", [
+    (1, {}, {}),
+    (2, dict(global_ep_deg=2), dict(moe_token_dispatcher_type="alltoall")),
+    (2, dict(global_ep_deg=2), dict(moe_token_dispatcher_type="allgather")),
+])
+def test_mixtral_hf_weights_give_hf_loss(mixtral_split, world, parallel, model):
+    """Router, dispatch, experts and combine against HuggingFace's Mixtral with the same weights."""
+    d, hf_loss = mixtral_split
+    res = run_distributed(__file__, "moe_loss_from_split", world, {"dir": d, "parallel": parallel, "model": model})
+    seen = [r for r in res if r is not None]
+    assert seen and all(abs(r - hf_loss) / hf_loss < 1e-4 for r in seen), (res, hf_loss)
 
 
 def test_qkv_pack_roundtrip():
