@@ -138,12 +138,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (*abort_flag || !mbar_wait(&k_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
         mbar_expect_tx(&k_full[st], FwdSmem<HD>::kKV);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
           tma_load_4d(sK + st * FwdSmem<HD>::kKV + c * 128 * 128, &tmK, &k_full[st], c * 64, kslot, j * 128, b);
-        if (*abort_flag || !mbar_wait(&v_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (!mbar_wait(&v_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
         mbar_expect_tx(&v_full[st], FwdSmem<HD>::kKV);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
@@ -151,38 +151,46 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane_id() == 0 && n_kv > 0) {
+    if (n_kv > 0) {
+      // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
-      bool ok = mbar_wait(q_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      bool ok = mbar_wait_warp(q_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       auto issue_s = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (*abort_flag || !mbar_wait(&k_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
-        if (!mbar_wait(&s_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
+        if (!mbar_wait_warp(&k_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait_warp(&s_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
         tc_fence_after();
         const uint32_t aK = smem_u32(sK + st * FwdSmem<HD>::kKV);
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16_ss(tS[st], kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 128, kk), idesc_s, kk != 0);
-        umma_commit(&s_full[st]);
-        umma_commit(&k_empty[st]);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tS[st], kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 128, kk), idesc_s, kk != 0);
+          umma_commit(&s_full[st]);
+          umma_commit(&k_empty[st]);
+        }
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int j = 0; ok && j < n_kv; ++j) {
         if (j + 1 < n_kv) { ok = issue_s(j + 1); if (!ok) break; }
         const int st = j & 1;
-        if (*abort_flag || !mbar_wait(p_full, j & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
-        if (!mbar_wait(&v_full[st], (j >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(p_full, j & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(&v_full[st], (j >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t aV = smem_u32(sV + st * FwdSmem<HD>::kKV);
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16_ss(tO, kmajor_desc(aP, 128, kk), mnmajor_desc(aV, 128, kk), idesc_o, (j | kk) != 0);
-        umma_commit(&v_empty[st]);
-        umma_commit(o_done);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_f16_ss(tO, kmajor_desc(aP, 128, kk), mnmajor_desc(aV, 128, kk), idesc_o, (j | kk) != 0);
+          umma_commit(&v_empty[st]);
+          umma_commit(o_done);
+        }
+        __syncwarp();
       }
       if (!ok) *abort_flag = 1;
     }
@@ -197,7 +205,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     bool ok = true;
     for (int j = 0; j < n_kv; ++j) {
       const int st = j & 1;
-      if (*abort_flag || !mbar_wait_warp(&s_full[st], (j >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full[st], (j >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
       float s[128];
 #pragma unroll
@@ -457,7 +465,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int st = it & 1;
         const int h = h0 + it / steps_per_head;
         const int qrow = (qs0 + it % steps_per_head) * 64;
-        if (*abort_flag || !mbar_wait(&qd_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (!mbar_wait(&qd_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
         mbar_expect_tx(&qd_full[st], 2 * DkvSmem<HD>::kQD);
         const int qslot = p.qmap.slot(h, p.qpg), doslot = p.domap.slot(h, p.qpg);
 #pragma unroll
@@ -468,43 +476,51 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
     }
   } else if (warp == 1) {
-    if (lane_id() == 0 && n_it > 0) {
+    if (n_it > 0) {
+      // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
       constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, HD, false, true);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), aDST = smem_u32(sDST);
-      bool ok = mbar_wait(kv_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      bool ok = mbar_wait_warp(kv_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       auto issue_st = [&](int it) -> bool {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (*abort_flag || !mbar_wait(&qd_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
-        if (!mbar_wait(&st_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
+        if (!mbar_wait_warp(&qd_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait_warp(&st_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
         tc_fence_after();
         const uint32_t aQ = smem_u32(sQ + st * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + st * DkvSmem<HD>::kQD);
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16_ss(tST[st], kmajor_desc(aK, 128, kk), kmajor_desc(aQ, 64, kk), idesc_st, kk != 0);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tST[st], kmajor_desc(aK, 128, kk), kmajor_desc(aQ, 64, kk), idesc_st, kk != 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16_ss(tDPT[st], kmajor_desc(aV, 128, kk), kmajor_desc(aDO, 64, kk), idesc_st, kk != 0);
-        umma_commit(&st_full[st]);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tDPT[st], kmajor_desc(aV, 128, kk), kmajor_desc(aDO, 64, kk), idesc_st, kk != 0);
+          umma_commit(&st_full[st]);
+        }
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_st(0);
       for (int it = 0; ok && it < n_it; ++it) {
         if (it + 1 < n_it) { ok = issue_st(it + 1); if (!ok) break; }
         const int st = it & 1;
-        if (*abort_flag || !mbar_wait(&pds_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(&pds_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t aQ = smem_u32(sQ + st * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + st * DkvSmem<HD>::kQD);
         const uint32_t aPTs = aPT + st * DkvSmem<HD>::kPT, aDSTs = aDST + st * DkvSmem<HD>::kPT;
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16_ss(tDV, kmajor_desc(aPTs, 128, kk), mnmajor_desc(aDO, 64, kk), idesc_acc, (it | kk) != 0);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ss(tDV, kmajor_desc(aPTs, 128, kk), mnmajor_desc(aDO, 64, kk), idesc_acc, (it | kk) != 0);
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16_ss(tDK, kmajor_desc(aDSTs, 128, kk), mnmajor_desc(aQ, 64, kk), idesc_acc, (it | kk) != 0);
-        umma_commit(&qd_empty[st]);
-        umma_commit(&pds_empty[st]);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ss(tDK, kmajor_desc(aDSTs, 128, kk), mnmajor_desc(aQ, 64, kk), idesc_acc, (it | kk) != 0);
+          umma_commit(&qd_empty[st]);
+          umma_commit(&pds_empty[st]);
+        }
+        __syncwarp();
       }
       if (!ok) *abort_flag = 1;
     }
@@ -536,8 +552,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         }
       }
       mbar_arrive(&stats_full[st]);
-      if (*abort_flag || !mbar_wait_warp(&stats_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
-      if (*abort_flag || !mbar_wait_warp(&st_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&stats_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&st_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
       float pt[32], ds[32];
       {
@@ -712,7 +728,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1;
-        if (*abort_flag || !mbar_wait(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (!mbar_wait(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
         mbar_expect_tx(&kv_full[st], 2 * DqSmem<HD>::kKV);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c) {
@@ -722,40 +738,48 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       }
     }
   } else if (warp == 1) {
-    if (lane_id() == 0 && n_it > 0) {
+    if (n_it > 0) {
+      // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
-      bool ok = mbar_wait(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      bool ok = mbar_wait_warp(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       auto issue_s = [&](int it) -> bool {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (*abort_flag || !mbar_wait(&kv_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
-        if (!mbar_wait(&s_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
+        if (!mbar_wait_warp(&kv_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait_warp(&s_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
         tc_fence_after();
         const uint32_t aK = smem_u32(sK + st * DqSmem<HD>::kKV), aV = smem_u32(sV + st * DqSmem<HD>::kKV);
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16_ss(tS[st], kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 64, kk), idesc_s, kk != 0);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tS[st], kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 64, kk), idesc_s, kk != 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16_ss(tDP[st], kmajor_desc(aDO, 128, kk), kmajor_desc(aV, 64, kk), idesc_s, kk != 0);
-        umma_commit(&s_full[st]);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tDP[st], kmajor_desc(aDO, 128, kk), kmajor_desc(aV, 64, kk), idesc_s, kk != 0);
+          umma_commit(&s_full[st]);
+        }
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int it = 0; ok && it < n_it; ++it) {
         if (it + 1 < n_it) { ok = issue_s(it + 1); if (!ok) break; }
         const int st = it & 1;
-        if (*abort_flag || !mbar_wait(&ds_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(&ds_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t aK = smem_u32(sK + st * DqSmem<HD>::kKV);
         const uint32_t aDSs = aDS + st * DqSmem<HD>::kDS;
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk)
-          umma_f16_ss(tDQ, kmajor_desc(aDSs, 128, kk), mnmajor_desc(aK, 64, kk), idesc_dq, (it | kk) != 0);
-        umma_commit(&kv_empty[st]);
-        umma_commit(&ds_empty[st]);
+          for (int kk = 0; kk < 4; ++kk)
+            umma_f16_ss(tDQ, kmajor_desc(aDSs, 128, kk), mnmajor_desc(aK, 64, kk), idesc_dq, (it | kk) != 0);
+          umma_commit(&kv_empty[st]);
+          umma_commit(&ds_empty[st]);
+        }
+        __syncwarp();
       }
       if (!ok) *abort_flag = 1;
     }
@@ -777,7 +801,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const int st = it & 1;
-      if (*abort_flag || !mbar_wait_warp(&s_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(&s_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
       float ds[32];
       {
@@ -941,7 +965,7 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1;
-        if (*abort_flag || !mbar_wait(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (!mbar_wait(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
         mbar_expect_tx(&kv_full[st], 2 * L::kKV);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c) {
@@ -951,38 +975,46 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
     }
   } else if (warp == 1) {
-    if (lane_id() == 0 && n_it > 0) {
+    if (n_it > 0) {
+      // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
-      bool ok = mbar_wait(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      bool ok = mbar_wait_warp(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       auto issue_s = [&](int it) -> bool {
         const int st = it & 1;
-        if (*abort_flag || !mbar_wait(&kv_full[st], (it >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) return false;
-        if (!mbar_wait(s_empty, (it & 1) ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
+        if (!mbar_wait_warp(&kv_full[st], (it >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait_warp(s_empty, (it & 1) ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
         tc_fence_after();
         const uint32_t aK = smem_u32(sK + st * L::kKV), aV = smem_u32(sV + st * L::kKV);
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16_ss(tS, kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 128, kk), idesc_s, kk != 0);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tS, kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 128, kk), idesc_s, kk != 0);
 #pragma unroll
-        for (int kk = 0; kk < HD / 16; ++kk)
-          umma_f16_ss(tDP, kmajor_desc(aDO, 128, kk), kmajor_desc(aV, 128, kk), idesc_s, kk != 0);
-        umma_commit(s_full);
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tDP, kmajor_desc(aDO, 128, kk), kmajor_desc(aV, 128, kk), idesc_s, kk != 0);
+          umma_commit(s_full);
+        }
+        __syncwarp();
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int it = 0; ok && it < n_it; ++it) {
         if (it + 1 < n_it) { ok = issue_s(it + 1); if (!ok) break; }
         const int st = it & 1;
-        if (*abort_flag || !mbar_wait(ds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        if (!mbar_wait_warp(ds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint32_t aK = smem_u32(sK + st * L::kKV);
+        if (issuer) {
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          umma_f16_ss(tDQ, kmajor_desc(aDS, 128, kk), mnmajor_desc(aK, 128, kk), idesc_dq, (it | kk) != 0);
-        umma_commit(&kv_empty[st]);
-        umma_commit(ds_empty);
+          for (int kk = 0; kk < 8; ++kk)
+            umma_f16_ss(tDQ, kmajor_desc(aDS, 128, kk), mnmajor_desc(aK, 128, kk), idesc_dq, (it | kk) != 0);
+          umma_commit(&kv_empty[st]);
+          umma_commit(ds_empty);
+        }
+        __syncwarp();
       }
       if (!ok) *abort_flag = 1;
     }
@@ -1004,7 +1036,7 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     uint8_t* sDSh = sDS + half * (128 * 128);   // this warpgroup's slab
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
-      if (*abort_flag || !mbar_wait_warp(s_full, it & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(s_full, it & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
       float ds[64];
       {

@@ -97,7 +97,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0) {
     if (lane_id() == 0) producer_loop<false, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);
   } else if (warp == 1) {
-    if (lane_id() == 0) mma_loop<false, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
+    mma_loop<false, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else if (warp < 6) {
     epilogue_loop(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
   } else {
@@ -183,7 +183,7 @@ __device__ __forceinline__ void rs_epilogue_loop(const Params& p, const RsParams
     const TileInfo ti = tile_info(p, tile);
     const int d = ti.m0 / rs.slab_rows;              // owner of this tile's rows
     const int mblk = (ti.m0 - d * rs.slab_rows) / BM;
-    if (alive && (*s.abort || !mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort))) {
+    if (alive && (!mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort))) {
       *s.abort = 1;
       alive = false;
     }
@@ -313,7 +313,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   if (warp == 0) {
     if (lane_id() == 0) producer_loop<false, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);
   } else if (warp == 1) {
-    if (lane_id() == 0) mma_loop<false, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
+    mma_loop<false, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else if (warp < 6) {
     rs_epilogue_loop(p, rs, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
     if (!*s.abort) rs_reduce_phase(p, rs, s);

@@ -30,7 +30,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (warp == 0) {
     if (lane_id() == 0) producer_loop<A_MN, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);
   } else if (warp == 1) {
-    if (lane_id() == 0) mma_loop<A_MN, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
+    mma_loop<A_MN, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else {
     epilogue_loop(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);
   }
@@ -103,7 +103,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       bool ok = true;
       for_each_tile([&](int g, int m0, int m_end, int n0) {
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (*s.abort || !mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; return false; }
+          if (!mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; return false; }
           mbar_expect_tx(&s.full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
           uint8_t* sa = s.a + stage * A_STAGE_BYTES;
           uint8_t* sb = s.b + stage * B_STAGE_BYTES;
@@ -123,39 +123,43 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
       if (!ok) *s.abort = 1;
     }
   } else if (warp == 1) {
-    if (lane_id() == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, false, B_MN);
-      constexpr uint32_t b_lbo = B_MN ? SLAB_BYTES : 16, b_kadv = B_MN ? 2048 : 32;
-      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-      bool ok = true;
-      for_each_tile([&](int, int, int, int) {
-        if (*s.abort || !mbar_wait(&s.tmem_empty[acc], acc_phase ^ 1, p.status, kTimeoutTmemEmpty, s.abort)) { ok = false; return false; }
+    // the whole warp walks the tile list; one elected lane issues the MMAs (see mma_loop in gemm_core.cuh)
+    constexpr uint32_t idesc = make_idesc_bf16(BM, BN, false, B_MN);
+    constexpr uint32_t b_lbo = B_MN ? SLAB_BYTES : 16, b_kadv = B_MN ? 2048 : 32;
+    uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+    bool ok = true;
+    const bool issuer = elect_one() != 0;
+    for_each_tile([&](int, int, int, int) {
+      if (!mbar_wait_warp(&s.tmem_empty[acc], acc_phase ^ 1, p.status, kTimeoutTmemEmpty, s.abort)) { ok = false; return false; }
+      tc_fence_after();
+      const uint32_t d = tmem_base + acc * BN;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_warp(&s.full[stage], phase, p.status, kTimeoutSmemFull, s.abort)) { ok = false; return false; }
         tc_fence_after();
-        const uint32_t d = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (*s.abort || !mbar_wait(&s.full[stage], phase, p.status, kTimeoutSmemFull, s.abort)) { ok = false; return false; }
-          tc_fence_after();
-          const uint32_t sa = smem_u32(s.a + stage * A_STAGE_BYTES);
-          const uint32_t sb = smem_u32(s.b + stage * B_STAGE_BYTES);
+        const uint32_t sa = smem_u32(s.a + stage * A_STAGE_BYTES);
+        const uint32_t sb = smem_u32(s.b + stage * B_STAGE_BYTES);
+        if (issuer) {
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
             umma_f16_ss(d, make_smem_desc(sa + k * 32, 16, 1024), make_smem_desc(sb + k * b_kadv, b_lbo, 1024), idesc,
                         (kb | k) != 0);
           umma_commit(&s.empty[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        umma_commit(&s.tmem_full[acc]);
-        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-        return true;
-      });
-      if (!ok) *s.abort = 1;
-    }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      if (issuer) umma_commit(&s.tmem_full[acc]);
+      __syncwarp();
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      return true;
+    });
+    if (!ok) *s.abort = 1;
   } else {
     const int wq = warp & 3;
     const uint32_t lane_off = uint32_t(wq * 32) << 16;
     uint32_t acc = 0, acc_phase = 0;
     for_each_tile([&](int, int m0, int m_end, int n0) {
-      if (*s.abort || !mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort)) { *s.abort = 1; return false; }
+      if (!mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort)) { *s.abort = 1; return false; }
       tc_fence_after();
       const int row = m0 + wq * 32 + lane_id();
 #pragma unroll 1

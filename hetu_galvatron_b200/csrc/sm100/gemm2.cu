@@ -6,7 +6,7 @@
 // and six stages fit where four did.
 //
 // Roles per CTA (192 threads): warp 0 TMA producer (one lane), warp 1 TMEM allocator (+ UMMA issuer in the leader
-// CTA only), warps 2-5 epilogue.  Barriers (same shared-memory offsets in both CTAs):
+// CTA only: the warp walks the loop, one elected lane issues), warps 2-5 epilogue.  Barriers (same shared-memory offsets in both CTAs):
 //   full[s]        leader only; the leader's producer arrives with the byte count of BOTH CTAs' loads, every load
 //                  (from either CTA) completes its bytes on the leader's barrier
 //   empty[s]       both CTAs; signalled by tcgen05.commit with a cluster mask covering the pair
@@ -132,7 +132,7 @@ __device__ __forceinline__ void producer2(const CUtensorMap* tmA, const CUtensor
     const int m0 = tm * CM + int(rank) * BM;
     const int n0 = tn * BN + int(rank) * HALF_N;
     for (int kb = 0; kb < num_kb; ++kb) {
-      if (*s.abort || !mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }
+      if (!mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }
       if (rank == 0) mbar_expect_tx(&s.full[stage], 2 * (A2_BYTES + B2_BYTES));
       const uint32_t bar = map_to_cta(smem_u32(&s.full[stage]), 0);
       uint8_t* sa = s.a + stage * A2_BYTES;
@@ -180,26 +180,31 @@ __device__ __forceinline__ void mma2(const Params& p, const Smem2& s, uint32_t t
   const int num_kb = (p.K + BK - 1) / BK;
   uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
   bool ok = true;
+  const bool issuer = elect_one() != 0;   // the warp walks the loop together; only this lane issues (see gemm_core.cuh)
   for (int tile = first; ok && tile < num_tiles; tile += step) {
-    if (*s.abort || !mbar_wait(&s.tmem_empty[acc], acc_phase ^ 1, p.status, kTimeoutTmemEmpty, s.abort)) { ok = false; break; }
+    if (!mbar_wait_warp(&s.tmem_empty[acc], acc_phase ^ 1, p.status, kTimeoutTmemEmpty, s.abort)) { ok = false; break; }
     tc_fence_after();
     const uint32_t d = tmem_base + acc * BN;
     for (int kb = 0; kb < num_kb; ++kb) {
-      if (*s.abort || !mbar_wait(&s.full[stage], phase, p.status, kTimeoutSmemFull, s.abort)) { ok = false; break; }
+      if (!mbar_wait_warp(&s.full[stage], phase, p.status, kTimeoutSmemFull, s.abort)) { ok = false; break; }
       tc_fence_after();
       const uint32_t sa = smem_u32(s.a + stage * A2_BYTES);
       const uint32_t sb = smem_u32(s.b + stage * B2_BYTES);
+      if (issuer) {
 #pragma unroll
-      for (int k = 0; k < BK / UMMA_K; ++k) {
-        const uint64_t da = make_smem_desc(sa + k * a_kadv, a_lbo, a_sbo);
-        const uint64_t db = make_smem_desc(sb + k * b_kadv, b_lbo, b_sbo);
-        umma_f16_ss_pair(d, da, db, idesc, (kb | k) != 0);
+        for (int k = 0; k < BK / UMMA_K; ++k) {
+          const uint64_t da = make_smem_desc(sa + k * a_kadv, a_lbo, a_sbo);
+          const uint64_t db = make_smem_desc(sb + k * b_kadv, b_lbo, b_sbo);
+          umma_f16_ss_pair(d, da, db, idesc, (kb | k) != 0);
+        }
+        umma_commit_pair(&s.empty[stage], kPairMask);
       }
-      umma_commit_pair(&s.empty[stage], kPairMask);
+      __syncwarp();
       if (++stage == STAGES2) { stage = 0; phase ^= 1; }
     }
     if (!ok) break;
-    umma_commit_pair(&s.tmem_full[acc], kPairMask);
+    if (issuer) umma_commit_pair(&s.tmem_full[acc], kPairMask);
+    __syncwarp();
     if (++acc == 2) { acc = 0; acc_phase ^= 1; }
   }
   if (!ok) *s.abort = 1;
@@ -215,7 +220,7 @@ __device__ __forceinline__ void epilogue2(const Params& p, const Smem2& s, uint3
     tile_coords(p, tile, tm, tn);
     const int row = tm * CM + int(rank) * BM + wq * 32 + lane_id();
     const int n0 = tn * BN;
-    if (*s.abort || !mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort)) {
+    if (!mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort)) {
       *s.abort = 1;
       break;
     }
@@ -278,7 +283,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   if (warp == 0) {
     if (lane_id() == 0) producer2<A_MN, B_MN>(&tmA, &tmB, p, s, rank, pair, pairs, num_tiles);
   } else if (warp == 1) {
-    if (rank == 0 && lane_id() == 0) mma2<A_MN, B_MN>(p, s, tmem_base, pair, pairs, num_tiles);
+    if (rank == 0) mma2<A_MN, B_MN>(p, s, tmem_base, pair, pairs, num_tiles);
   } else {
     epilogue2(p, s, tmem_base, rank, pair, pairs, num_tiles);
   }
