@@ -25,6 +25,15 @@ constexpr int kBwdSoftmaxThreads = 256;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
+// 2^x on the special-function unit: one instruction, results below 2^-126 flush to zero, 2^-inf = 0.
+// (exp2f() wraps the same instruction in range handling that costs several more per element, and the score
+// loops below run it tens of thousands of times per step.)
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // Head -> slot mapping inside the (possibly packed) tensor:  slot = (h / qpg) * gs + (h % qpg) * hs + off
 struct SlotMap {
   int gs, hs, off;
@@ -131,23 +140,25 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int qslot = p.qmap.slot(h, p.qpg), kslot = p.kmap.slot(h, p.qpg), vslot = p.vmap.slot(h, p.qpg);
 
   if (warp == 0) {
-    if (lane_id() == 0 && n_kv > 0) {
-      mbar_expect_tx(q_full, FwdSmem<HD>::kQ);
+    if (n_kv > 0) {
+      // the whole warp walks the loop, one elected lane issues the copies (see producer_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
+      if (issuer) mbar_expect_tx(q_full, FwdSmem<HD>::kQ);
 #pragma unroll
-      for (int j = 0; j < HD / 64; ++j) tma_load_4d(sQ + j * 128 * 128, &tmQ, q_full, j * 64, qslot, q0, b);
+      for (int j = 0; j < HD / 64; ++j) if (issuer) tma_load_4d(sQ + j * 128 * 128, &tmQ, q_full, j * 64, qslot, q0, b);
       for (int j = 0; j < n_kv; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
-        mbar_expect_tx(&k_full[st], FwdSmem<HD>::kKV);
+        if (!mbar_wait_warp(&k_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&k_full[st], FwdSmem<HD>::kKV);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sK + st * FwdSmem<HD>::kKV + c * 128 * 128, &tmK, &k_full[st], c * 64, kslot, j * 128, b);
-        if (!mbar_wait(&v_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
-        mbar_expect_tx(&v_full[st], FwdSmem<HD>::kKV);
+          if (issuer) tma_load_4d(sK + st * FwdSmem<HD>::kKV + c * 128 * 128, &tmK, &k_full[st], c * 64, kslot, j * 128, b);
+        if (!mbar_wait_warp(&v_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&v_full[st], FwdSmem<HD>::kKV);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c)
-          tma_load_4d(sV + st * FwdSmem<HD>::kKV + c * 128 * 128, &tmV, &v_full[st], c * 64, vslot, j * 128, b);
+          if (issuer) tma_load_4d(sV + st * FwdSmem<HD>::kKV + c * 128 * 128, &tmV, &v_full[st], c * 64, vslot, j * 128, b);
       }
     }
   } else if (warp == 1) {
@@ -228,26 +239,33 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           if (dead) s[i] = -INFINITY;
         }
       }
-      float mx = s[0];
+      float mx4[4] = {s[0], s[1], s[2], s[3]};   // four chains: a single one is 127 dependent instructions long
 #pragma unroll
-      for (int i = 1; i < 128; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 4; i < 128; i += 4) {
+        mx4[0] = fmaxf(mx4[0], s[i]); mx4[1] = fmaxf(mx4[1], s[i + 1]);
+        mx4[2] = fmaxf(mx4[2], s[i + 2]); mx4[3] = fmaxf(mx4[3], s[i + 3]);
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx *= sl2;
       // lazy rescale: keep the running reference max unless the new max exceeds it by more than 2^8
       float alpha = 1.f;
       bool rescale = false;
       if (mx > m_used + 8.f) {
-        alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - mx);
+        alpha = (m_used == -INFINITY) ? 0.f : ex2(m_used - mx);
         m_used = mx;
         rescale = (j > 0);
       }
-      const float mref = (m_used == -INFINITY) ? 0.f : m_used;
-      float sum = 0.f;
+      const float nmref = (m_used == -INFINITY) ? 0.f : -m_used;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int i = 0; i < 128; ++i) {
-        s[i] = exp2f(s[i] * sl2 - mref);
-        sum += s[i];
+      for (int i = 0; i < 128; i += 4) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          s[i + u] = ex2(fmaf(s[i + u], sl2, nmref));
+          sum4[u] += s[i + u];
+        }
       }
-      l = l * alpha + sum;
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       if (j > 0) {
         if (!mbar_wait_warp(o_done, (j - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -379,9 +397,11 @@ template <int HD>
 struct DkvSmem {
   static constexpr int kKV = 128 * HD * 2;     // resident K or V
   static constexpr int kQD = 64 * HD * 2;      // one stage of Q or dO
+  static constexpr int kQDStages = 3;          // a stage is held from its S^T product to its dK product, i.e. for more
+                                               // than a step: with two stages every load was waited for in full
   static constexpr int kPT = 128 * 64 * 2;     // one P^T or dS^T buffer (two of each: written for step i+1 while step i is multiplied)
   static constexpr int kStats = 2 * 2 * 64 * 4;  // lse2/D, double buffered
-  static constexpr int kTotal = 2 * kKV + 4 * kQD + 4 * kPT + kStats + 1024 + 256;
+  static constexpr int kTotal = 2 * kKV + 2 * kQDStages * kQD + 4 * kPT + kStats + 1024 + 256;
 };
 
 template <int HD>
@@ -393,21 +413,22 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sK = base;
   uint8_t* sV = sK + DkvSmem<HD>::kKV;
-  uint8_t* sQ = sV + DkvSmem<HD>::kKV;            // 2 stages
-  uint8_t* sDO = sQ + 2 * DkvSmem<HD>::kQD;       // 2 stages
-  uint8_t* sPT = sDO + 2 * DkvSmem<HD>::kQD;
+  constexpr int NQ = DkvSmem<HD>::kQDStages;
+  uint8_t* sQ = sV + DkvSmem<HD>::kKV;            // NQ stages
+  uint8_t* sDO = sQ + NQ * DkvSmem<HD>::kQD;      // NQ stages
+  uint8_t* sPT = sDO + NQ * DkvSmem<HD>::kQD;
   uint8_t* sDST = sPT + 2 * DkvSmem<HD>::kPT;
   float* sStats = reinterpret_cast<float*>(sDST + 2 * DkvSmem<HD>::kPT);  // [2][2][64]
   uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStats) + DkvSmem<HD>::kStats);
   uint64_t* kv_full = bars;        // 1
-  uint64_t* qd_full = bars + 1;    // 2
-  uint64_t* qd_empty = bars + 3;   // 2
-  uint64_t* st_full = bars + 5;    // 2
-  uint64_t* st_empty = bars + 7;   // 2
-  uint64_t* pds_full = bars + 9;   // 2
-  uint64_t* pds_empty = bars + 11; // 2
-  uint64_t* stats_full = bars + 13; // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  uint64_t* qd_full = bars + 1;    // 3
+  uint64_t* qd_empty = bars + 4;   // 3
+  uint64_t* st_full = bars + 7;    // 2
+  uint64_t* st_empty = bars + 9;   // 2
+  uint64_t* pds_full = bars + 11;  // 2
+  uint64_t* pds_empty = bars + 13; // 2
+  uint64_t* stats_full = bars + 15; // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 17);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -424,9 +445,11 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
     mbar_init(kv_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < NQ; ++i) {
       mbar_init(&qd_full[i], 1);
       mbar_init(&qd_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&st_full[i], 1);
       mbar_init(&st_empty[i], kBwdSoftmaxThreads);
       mbar_init(&pds_full[i], kBwdSoftmaxThreads);
@@ -454,25 +477,30 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
   const int kslot = p.kmap.slot(h0, p.qpg), vslot = p.vmap.slot(h0, p.qpg);
 
   if (warp == 0) {
-    if (lane_id() == 0 && n_it > 0) {
-      mbar_expect_tx(kv_full, 2 * DkvSmem<HD>::kKV);
+    if (n_it > 0) {
+      // the whole warp walks the loop, one elected lane issues the copies (see producer_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
+      if (issuer) mbar_expect_tx(kv_full, 2 * DkvSmem<HD>::kKV);
 #pragma unroll
       for (int c = 0; c < HD / 64; ++c) {
-        tma_load_4d(sK + c * 128 * 128, &tmK, kv_full, c * 64, kslot, k0, b);
-        tma_load_4d(sV + c * 128 * 128, &tmV, kv_full, c * 64, vslot, k0, b);
+        if (issuer) tma_load_4d(sK + c * 128 * 128, &tmK, kv_full, c * 64, kslot, k0, b);
+        if (issuer) tma_load_4d(sV + c * 128 * 128, &tmV, kv_full, c * 64, vslot, k0, b);
       }
+      int st = 0;            // ring slot and its phase, and the (head, query step) of the iteration
+      uint32_t ph = 0;
+      int h = h0, qs = qs0;
       for (int it = 0; it < n_it; ++it) {
-        const int st = it & 1;
-        const int h = h0 + it / steps_per_head;
-        const int qrow = (qs0 + it % steps_per_head) * 64;
-        if (!mbar_wait(&qd_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
-        mbar_expect_tx(&qd_full[st], 2 * DkvSmem<HD>::kQD);
+        const int qrow = qs * 64;
+        if (!mbar_wait_warp(&qd_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&qd_full[st], 2 * DkvSmem<HD>::kQD);
         const int qslot = p.qmap.slot(h, p.qpg), doslot = p.domap.slot(h, p.qpg);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c) {
-          tma_load_4d(sQ + st * DkvSmem<HD>::kQD + c * 64 * 128, &tmQ, &qd_full[st], c * 64, qslot, qrow, b);
-          tma_load_4d(sDO + st * DkvSmem<HD>::kQD + c * 64 * 128, &tmDO, &qd_full[st], c * 64, doslot, qrow, b);
+          if (issuer) tma_load_4d(sQ + st * DkvSmem<HD>::kQD + c * 64 * 128, &tmQ, &qd_full[st], c * 64, qslot, qrow, b);
+          if (issuer) tma_load_4d(sDO + st * DkvSmem<HD>::kQD + c * 64 * 128, &tmDO, &qd_full[st], c * 64, doslot, qrow, b);
         }
+        if (++st == NQ) { st = 0; ph ^= 1; }
+        if (++qs == n_qs) { qs = qs0; ++h; }
       }
     }
   } else if (warp == 1) {
@@ -483,13 +511,16 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       constexpr uint32_t idesc_acc = make_idesc_bf16(128, HD, false, true);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), aDST = smem_u32(sDST);
       bool ok = mbar_wait_warp(kv_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      int qs_s = 0, qs_d = 0;          // Q / dO ring slot of the next S^T issue and of the next dV / dK issue
+      uint32_t qph_s = 0;
       auto issue_st = [&](int it) -> bool {
         const int st = it & 1;
         const uint32_t ph = (it >> 1) & 1;
-        if (!mbar_wait_warp(&qd_full[st], ph, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait_warp(&qd_full[qs_s], qph_s, p.status, kTimeoutSmemFull, abort_flag)) return false;
         if (!mbar_wait_warp(&st_empty[st], ph ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ + st * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + st * DkvSmem<HD>::kQD);
+        const uint32_t aQ = smem_u32(sQ + qs_s * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + qs_s * DkvSmem<HD>::kQD);
+        if (++qs_s == NQ) { qs_s = 0; qph_s ^= 1; }
         if (issuer) {
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk)
@@ -508,7 +539,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
         const int st = it & 1;
         if (!mbar_wait_warp(&pds_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t aQ = smem_u32(sQ + st * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + st * DkvSmem<HD>::kQD);
+        const uint32_t aQ = smem_u32(sQ + qs_d * DkvSmem<HD>::kQD), aDO = smem_u32(sDO + qs_d * DkvSmem<HD>::kQD);
         const uint32_t aPTs = aPT + st * DkvSmem<HD>::kPT, aDSTs = aDST + st * DkvSmem<HD>::kPT;
         if (issuer) {
 #pragma unroll
@@ -517,10 +548,11 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk)
             umma_f16_ss(tDK, kmajor_desc(aDSTs, 128, kk), mnmajor_desc(aQ, 64, kk), idesc_acc, (it | kk) != 0);
-          umma_commit(&qd_empty[st]);
+          umma_commit(&qd_empty[qs_d]);
           umma_commit(&pds_empty[st]);
         }
         __syncwarp();
+        if (++qs_d == NQ) qs_d = 0;
       }
       if (!ok) *abort_flag = 1;
     }
@@ -535,23 +567,36 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     const int k_pos = p.k_pos0 + k0 + row;
     const bool k_valid = (k0 + row) < p.Skv;
     bool ok = true;
-    for (int it = 0; it < n_it; ++it) {
-      const int st = it & 1;
-      const int h = h0 + it / steps_per_head;
-      const int qrow = (qs0 + it % steps_per_head) * 64;
-      // per-query statistics of this step -> shared memory
-      {
-        float* dst = sStats + st * 128;
-        const int q = qrow + (tid & 63);
-        const size_t idx = (size_t(b) * p.nheads + h) * p.Sq + q;
-        if (tid < 128) {
-          float v = 0.f;
-          if (q < p.Sq) v = (tid < 64) ? p.LSE[idx] * kLog2e : p.D[idx];
-          else v = (tid < 64) ? INFINITY : 0.f;   // rows past the end: exp2(-inf) = 0
-          dst[tid] = v;
+    // Per-query statistics (-LSE * log2 e and D) of a step, fetched one step ahead so that the global-memory
+    // latency is hidden behind the previous step's work: thread t < 64 carries -lse2 of query t, 64 <= t < 128 D.
+    int ld_h = h0, ld_qs = qs0, ld_it = 0;   // (head, query step) of the next statistics fetch; no division in the loop
+    auto load_stat = [&]() -> float {
+      float v = 0.f;
+      if (tid < 128 && ld_it < n_it) {
+        const int q = ld_qs * 64 + (tid & 63);
+        if (q >= p.Sq) {
+          v = (tid < 64) ? -INFINITY : 0.f;   // rows past the end: 2^-inf = 0
+        } else {
+          const float* src = (tid < 64) ? p.LSE : p.D;
+          v = src[(size_t(b) * p.nheads + ld_h) * p.Sq + q];
+          if (tid < 64) v *= -kLog2e;
         }
       }
-      mbar_arrive(&stats_full[st]);
+      ++ld_it;
+      if (++ld_qs == n_qs) { ld_qs = qs0; ++ld_h; }
+      return v;
+    };
+    float stat_next = load_stat();
+    if (n_it > 0) {
+      if (tid < 128) sStats[tid] = stat_next;
+      mbar_arrive(&stats_full[0]);
+      stat_next = load_stat();
+    }
+    int cur_qs = qs0;
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it & 1;
+      const int qrow = cur_qs * 64;
+      if (++cur_qs == n_qs) cur_qs = qs0;
       if (!mbar_wait_warp(&stats_full[st], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
       if (!mbar_wait_warp(&st_full[st], (it >> 1) & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
@@ -566,15 +611,33 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       }
       tc_fence_before();
       mbar_arrive(&st_empty[st]);
-      const float* lse2 = sStats + st * 128 + c0;
-      const float* dd = lse2 + 64;
-      const bool need_mask = p.causal && (p.q_pos0 + qrow < p.k_pos0 + k0 + 127);
+      {
+        const float4* nl4 = reinterpret_cast<const float4*>(sStats + st * 128 + c0);   // -lse2
+        const float4* dd4 = nl4 + 16;                                                  // D
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        float pv = exp2f(pt[i] * sl2 - lse2[i]);
-        if (!k_valid || (need_mask && (k_pos > p.q_pos0 + qrow + c0 + i))) pv = 0.f;
-        pt[i] = pv;
-        ds[i] = pv * (ds[i] - dd[i]);
+        for (int i = 0; i < 32; i += 4) {
+          const float4 nl = nl4[i >> 2], dd = dd4[i >> 2];
+          pt[i + 0] = ex2(fmaf(pt[i + 0], sl2, nl.x)); pt[i + 1] = ex2(fmaf(pt[i + 1], sl2, nl.y));
+          pt[i + 2] = ex2(fmaf(pt[i + 2], sl2, nl.z)); pt[i + 3] = ex2(fmaf(pt[i + 3], sl2, nl.w));
+          ds[i + 0] -= dd.x; ds[i + 1] -= dd.y; ds[i + 2] -= dd.z; ds[i + 3] -= dd.w;
+        }
+        // only steps that touch the diagonal, or a key block with rows past the end, need the mask
+        const bool need_mask = !k_valid || (p.causal && (p.q_pos0 + qrow < p.k_pos0 + k0 + 127));
+        if (need_mask) {
+          const int q_base = p.q_pos0 + qrow + c0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (!k_valid || (p.causal && k_pos > q_base + i)) pt[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ds[i] *= pt[i];
+      }
+      // the next step's statistics go to the other buffer: every thread is past its reads of that buffer (they
+      // all arrived on this step's stats barrier after finishing the previous step)
+      if (it + 1 < n_it) {
+        if (tid < 128) sStats[(st ^ 1) * 128 + tid] = stat_next;
+        mbar_arrive(&stats_full[st ^ 1]);
+        stat_next = load_stat();
       }
       if (it >= 2) {   // these buffers were last read by the dV / dK products of step it-2
         if (!mbar_wait_warp(&pds_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
@@ -719,21 +782,23 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             doslot = p.domap.slot(h, p.qpg);
 
   if (warp == 0) {
-    if (lane_id() == 0 && n_it > 0) {
-      mbar_expect_tx(qdo_full, 2 * DqSmem<HD>::kQ);
+    if (n_it > 0) {
+      // the whole warp walks the loop, one elected lane issues the copies (see producer_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
+      if (issuer) mbar_expect_tx(qdo_full, 2 * DqSmem<HD>::kQ);
 #pragma unroll
       for (int c = 0; c < HD / 64; ++c) {
-        tma_load_4d(sQ + c * 128 * 128, &tmQ, qdo_full, c * 64, qslot, q0, b);
-        tma_load_4d(sDO + c * 128 * 128, &tmDO, qdo_full, c * 64, doslot, q0, b);
+        if (issuer) tma_load_4d(sQ + c * 128 * 128, &tmQ, qdo_full, c * 64, qslot, q0, b);
+        if (issuer) tma_load_4d(sDO + c * 128 * 128, &tmDO, qdo_full, c * 64, doslot, q0, b);
       }
       for (int it = 0; it < n_it; ++it) {
         const int st = it & 1;
-        if (!mbar_wait(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
-        mbar_expect_tx(&kv_full[st], 2 * DqSmem<HD>::kKV);
+        if (!mbar_wait_warp(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&kv_full[st], 2 * DqSmem<HD>::kKV);
 #pragma unroll
         for (int c = 0; c < HD / 64; ++c) {
-          tma_load_4d(sK + st * DqSmem<HD>::kKV + c * 64 * 128, &tmK, &kv_full[st], c * 64, kslot, it * 64, b);
-          tma_load_4d(sV + st * DqSmem<HD>::kKV + c * 64 * 128, &tmV, &kv_full[st], c * 64, vslot, it * 64, b);
+          if (issuer) tma_load_4d(sK + st * DqSmem<HD>::kKV + c * 64 * 128, &tmK, &kv_full[st], c * 64, kslot, it * 64, b);
+          if (issuer) tma_load_4d(sV + st * DqSmem<HD>::kKV + c * 64 * 128, &tmV, &kv_full[st], c * 64, vslot, it * 64, b);
         }
       }
     }
@@ -798,6 +863,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       lse2 = p.LSE[idx] * kLog2e;
       dsum = p.D[idx];
     }
+    const float nlse2 = -lse2;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       const int st = it & 1;
@@ -819,11 +885,14 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         const int kbase = it * 64 + c0;
         const bool need_mask = (p.causal && (p.k_pos0 + kbase + 31 > p.q_pos0 + q0)) || (kbase + 32 > p.Skv);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float pv = exp2f(sv[i] * sl2 - lse2);
-          if (need_mask && ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos)))) pv = 0.f;
-          ds[i] = pv * (ds[i] - dsum);
+        for (int i = 0; i < 32; ++i) sv[i] = ex2(fmaf(sv[i], sl2, nlse2));
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos))) sv[i] = 0.f;
         }
+#pragma unroll
+        for (int i = 0; i < 32; ++i) ds[i] = sv[i] * (ds[i] - dsum);
       }
       if (it >= 2) {   // this buffer was last read by the dQ product of step it-2
         if (!mbar_wait_warp(&ds_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
@@ -892,8 +961,12 @@ template <int HD>
 struct Dq128Smem {
   static constexpr int kQ = 128 * HD * 2;      // resident Q or dO
   static constexpr int kKV = 128 * HD * 2;     // one stage of K or V
+  // K is read by the first and by the last product of a step (S = Q K^T, dQ += dS K), so a K slot is held for more
+  // than a step: three slots let the load of step i+2 start while step i is still being multiplied.  V is read by
+  // dP = dO V^T only, early in the step, so one slot suffices: its reload has the rest of the step to land.
+  static constexpr int kKStages = 3;
   static constexpr int kDS = 128 * 128 * 2;    // dS: two K-major slabs of [128 rows x 64 keys]
-  static constexpr int kTotal = 2 * kQ + 4 * kKV + kDS + 1024 + 256;
+  static constexpr int kTotal = 2 * kQ + (kKStages + 1) * kKV + kDS + 1024 + 256;
 };
 
 template <int HD>
@@ -906,18 +979,21 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = base;
   uint8_t* sDO = sQ + L::kQ;
-  uint8_t* sK = sDO + L::kQ;            // 2 stages
-  uint8_t* sV = sK + 2 * L::kKV;        // 2 stages
-  uint8_t* sDS = sV + 2 * L::kKV;
+  constexpr int NK = L::kKStages;
+  uint8_t* sK = sDO + L::kQ;            // NK stages
+  uint8_t* sV = sK + NK * L::kKV;       // 1 stage
+  uint8_t* sDS = sV + L::kKV;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + L::kDS);
   uint64_t* qdo_full = bars;       // 1
-  uint64_t* kv_full = bars + 1;    // 2
-  uint64_t* kv_empty = bars + 3;   // 2
-  uint64_t* s_full = bars + 5;     // 1
-  uint64_t* s_empty = bars + 6;    // 1
-  uint64_t* ds_full = bars + 7;    // 1
-  uint64_t* ds_empty = bars + 8;   // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* k_full = bars + 1;     // 3
+  uint64_t* k_empty = bars + 4;    // 3
+  uint64_t* v_full = bars + 7;     // 1
+  uint64_t* v_empty = bars + 8;    // 1
+  uint64_t* s_full = bars + 9;     // 1
+  uint64_t* s_empty = bars + 10;   // 1
+  uint64_t* ds_full = bars + 11;   // 1
+  uint64_t* ds_empty = bars + 12;  // 1
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -931,10 +1007,12 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   if (threadIdx.x == 0) {
     tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
     mbar_init(qdo_full, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&kv_full[i], 1);
-      mbar_init(&kv_empty[i], 1);
+    for (int i = 0; i < NK; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
     }
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
     mbar_init(s_empty, kBwdSoftmaxThreads);
     mbar_init(ds_full, kBwdSoftmaxThreads);
@@ -956,22 +1034,29 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             doslot = p.domap.slot(h, p.qpg);
 
   if (warp == 0) {
-    if (lane_id() == 0 && n_it > 0) {
-      mbar_expect_tx(qdo_full, 2 * L::kQ);
+    if (n_it > 0) {
+      // the whole warp walks the loop, one elected lane issues the copies (see producer_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
+      if (issuer) mbar_expect_tx(qdo_full, 2 * L::kQ);
 #pragma unroll
       for (int c = 0; c < HD / 64; ++c) {
-        tma_load_4d(sQ + c * 128 * 128, &tmQ, qdo_full, c * 64, qslot, q0, b);
-        tma_load_4d(sDO + c * 128 * 128, &tmDO, qdo_full, c * 64, doslot, q0, b);
+        if (issuer) tma_load_4d(sQ + c * 128 * 128, &tmQ, qdo_full, c * 64, qslot, q0, b);
+        if (issuer) tma_load_4d(sDO + c * 128 * 128, &tmDO, qdo_full, c * 64, doslot, q0, b);
       }
+      int ks = 0;
+      uint32_t kph = 0;
       for (int it = 0; it < n_it; ++it) {
-        const int st = it & 1;
-        if (!mbar_wait(&kv_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
-        mbar_expect_tx(&kv_full[st], 2 * L::kKV);
+        if (!mbar_wait_warp(&k_empty[ks], kph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&k_full[ks], L::kKV);
 #pragma unroll
-        for (int c = 0; c < HD / 64; ++c) {
-          tma_load_4d(sK + st * L::kKV + c * 128 * 128, &tmK, &kv_full[st], c * 64, kslot, it * 128, b);
-          tma_load_4d(sV + st * L::kKV + c * 128 * 128, &tmV, &kv_full[st], c * 64, vslot, it * 128, b);
-        }
+        for (int c = 0; c < HD / 64; ++c)
+          if (issuer) tma_load_4d(sK + ks * L::kKV + c * 128 * 128, &tmK, &k_full[ks], c * 64, kslot, it * 128, b);
+        if (!mbar_wait_warp(v_empty, (it & 1) ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(v_full, L::kKV);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          if (issuer) tma_load_4d(sV + c * 128 * 128, &tmV, v_full, c * 64, vslot, it * 128, b);
+        if (++ks == NK) { ks = 0; kph ^= 1; }
       }
     }
   } else if (warp == 1) {
@@ -982,39 +1067,48 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
       bool ok = mbar_wait_warp(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      int ks_s = 0, ks_d = 0;          // K slot of the next S issue and of the next dQ issue
+      uint32_t kph_s = 0;
+      const uint32_t aV = smem_u32(sV);
       auto issue_s = [&](int it) -> bool {
-        const int st = it & 1;
-        if (!mbar_wait_warp(&kv_full[st], (it >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        if (!mbar_wait_warp(&k_full[ks_s], kph_s, p.status, kTimeoutSmemFull, abort_flag)) return false;
         if (!mbar_wait_warp(s_empty, (it & 1) ^ 1, p.status, kTimeoutTmemEmpty, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t aK = smem_u32(sK + st * L::kKV), aV = smem_u32(sV + st * L::kKV);
+        const uint32_t aK = smem_u32(sK + ks_s * L::kKV);
         if (issuer) {
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk)
             umma_f16_ss(tS, kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 128, kk), idesc_s, kk != 0);
+        }
+        __syncwarp();
+        if (!mbar_wait_warp(v_full, it & 1, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        tc_fence_after();
+        if (issuer) {
 #pragma unroll
           for (int kk = 0; kk < HD / 16; ++kk)
             umma_f16_ss(tDP, kmajor_desc(aDO, 128, kk), kmajor_desc(aV, 128, kk), idesc_s, kk != 0);
+          umma_commit(v_empty);
           umma_commit(s_full);
         }
         __syncwarp();
+        if (++ks_s == NK) { ks_s = 0; kph_s ^= 1; }
         return true;
       };
       if (ok) ok = issue_s(0);
       for (int it = 0; ok && it < n_it; ++it) {
         if (it + 1 < n_it) { ok = issue_s(it + 1); if (!ok) break; }
-        const int st = it & 1;
         if (!mbar_wait_warp(ds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t aK = smem_u32(sK + st * L::kKV);
+        const uint32_t aK = smem_u32(sK + ks_d * L::kKV);
         if (issuer) {
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
             umma_f16_ss(tDQ, kmajor_desc(aDS, 128, kk), mnmajor_desc(aK, 128, kk), idesc_dq, (it | kk) != 0);
-          umma_commit(&kv_empty[st]);
+          umma_commit(&k_empty[ks_d]);
           umma_commit(ds_empty);
         }
         __syncwarp();
+        if (++ks_d == NK) ks_d = 0;
       }
       if (!ok) *abort_flag = 1;
     }
@@ -1033,6 +1127,7 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       lse2 = p.LSE[idx] * kLog2e;
       dsum = p.D[idx];
     }
+    const float nlse2 = -lse2;
     uint8_t* sDSh = sDS + half * (128 * 128);   // this warpgroup's slab
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
@@ -1055,11 +1150,14 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int kbase = it * 128 + c0;
         const bool need_mask = (p.causal && (p.k_pos0 + kbase + 63 > p.q_pos0 + q0)) || (kbase + 64 > p.Skv);
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
-          float pv = exp2f(sv[i] * sl2 - lse2);
-          if (need_mask && ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos)))) pv = 0.f;
-          ds[i] = pv * (ds[i] - dsum);
+        for (int i = 0; i < 64; ++i) sv[i] = ex2(fmaf(sv[i], sl2, nlse2));
+        if (need_mask) {
+#pragma unroll
+          for (int i = 0; i < 64; ++i)
+            if ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos))) sv[i] = 0.f;
         }
+#pragma unroll
+        for (int i = 0; i < 64; ++i) ds[i] = sv[i] * (ds[i] - dsum);
       }
       if (it > 0) {
         if (!mbar_wait_warp(ds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }

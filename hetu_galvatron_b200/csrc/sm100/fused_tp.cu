@@ -95,7 +95,7 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *s.tmem_base;
 
   if (warp == 0) {
-    if (lane_id() == 0) producer_loop<false, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);
+    producer_loop<false, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else if (warp == 1) {
     mma_loop<false, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else if (warp < 6) {
@@ -311,7 +311,7 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t tmem_base = *s.tmem_base;
 
   if (warp == 0) {
-    if (lane_id() == 0) producer_loop<false, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);
+    producer_loop<false, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else if (warp == 1) {
     mma_loop<false, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else if (warp < 6) {

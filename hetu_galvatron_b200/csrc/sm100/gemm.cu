@@ -28,7 +28,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = *s.tmem_base;
 
   if (warp == 0) {
-    if (lane_id() == 0) producer_loop<A_MN, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);
+    producer_loop<A_MN, B_MN>(&tmA, &tmB, p, s, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else if (warp == 1) {
     mma_loop<A_MN, B_MN>(p, s, tmem_base, blockIdx.x, gridDim.x, num_tiles);  // whole warp, one elected issuer
   } else {
@@ -98,16 +98,18 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
   };
 
   if (warp == 0) {
-    if (lane_id() == 0) {
-      uint32_t stage = 0, phase = 0;
-      bool ok = true;
-      for_each_tile([&](int g, int m0, int m_end, int n0) {
-        for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; return false; }
+    // the whole warp walks the tile list; one elected lane issues the copies (see producer_loop in gemm_core.cuh)
+    uint32_t stage = 0, phase = 0;
+    bool ok = true;
+    const bool issuer = elect_one() != 0;
+    for_each_tile([&](int g, int m0, int m_end, int n0) {
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait_warp(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; return false; }
+        uint8_t* sa = s.a + stage * A_STAGE_BYTES;
+        uint8_t* sb = s.b + stage * B_STAGE_BYTES;
+        const int k0 = kb * BK;
+        if (issuer) {
           mbar_expect_tx(&s.full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
-          uint8_t* sa = s.a + stage * A_STAGE_BYTES;
-          uint8_t* sb = s.b + stage * B_STAGE_BYTES;
-          const int k0 = kb * BK;
           tma_load_2d(sa, &tmA, &s.full[stage], k0, m0);
           if (B_MN) {
 #pragma unroll
@@ -116,12 +118,13 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
           } else {
             tma_load_2d(sb, &tmB, &s.full[stage], k0, g * gp.b_group_rows + n0);
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        return true;
-      });
-      if (!ok) *s.abort = 1;
-    }
+        __syncwarp();
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+      }
+      return true;
+    });
+    if (!ok) *s.abort = 1;
   } else if (warp == 1) {
     // the whole warp walks the tile list; one elected lane issues the MMAs (see mma_loop in gemm_core.cuh)
     constexpr uint32_t idesc = make_idesc_bf16(BM, BN, false, B_MN);

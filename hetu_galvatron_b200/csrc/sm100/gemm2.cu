@@ -5,7 +5,7 @@
 // from both, so a 128 x 256 slice of the output costs 32 KB of operand traffic per k-block per SM instead of 48 KB,
 // and six stages fit where four did.
 //
-// Roles per CTA (192 threads): warp 0 TMA producer (one lane), warp 1 TMEM allocator (+ UMMA issuer in the leader
+// Roles per CTA (192 threads): warp 0 TMA producer (the warp walks the loop, one elected lane issues), warp 1 TMEM allocator (+ UMMA issuer in the leader
 // CTA only: the warp walks the loop, one elected lane issues), warps 2-5 epilogue.  Barriers (same shared-memory offsets in both CTAs):
 //   full[s]        leader only; the leader's producer arrives with the byte count of BOTH CTAs' loads, every load
 //                  (from either CTA) completes its bytes on the leader's barrier
@@ -126,30 +126,34 @@ __device__ __forceinline__ void producer2(const CUtensorMap* tmA, const CUtensor
   for (int i = 0; i < STAGES2; ++i) { issued[i] = false; issued_parity[i] = 0; }
   const int num_kb = (p.K + BK - 1) / BK;
   bool ok = true;
+  const bool issuer = elect_one() != 0;   // the warp walks the loop together; only this lane issues the copies
   for (int tile = first; ok && tile < num_tiles; tile += step) {
     int tm, tn;
     tile_coords(p, tile, tm, tn);
     const int m0 = tm * CM + int(rank) * BM;
     const int n0 = tn * BN + int(rank) * HALF_N;
     for (int kb = 0; kb < num_kb; ++kb) {
-      if (!mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }
-      if (rank == 0) mbar_expect_tx(&s.full[stage], 2 * (A2_BYTES + B2_BYTES));
+      if (!mbar_wait_warp(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }
       const uint32_t bar = map_to_cta(smem_u32(&s.full[stage]), 0);
       uint8_t* sa = s.a + stage * A2_BYTES;
       uint8_t* sb = s.b + stage * B2_BYTES;
       const int k0 = kb * BK;
-      if (A_MN) {
+      if (issuer) {
+        if (rank == 0) mbar_expect_tx(&s.full[stage], 2 * (A2_BYTES + B2_BYTES));
+        if (A_MN) {
 #pragma unroll
-        for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * SLAB_BYTES, tmA, bar, m0 + j * 64, k0);
-      } else {
-        tma_load_2d_pair(sa, tmA, bar, k0, m0);
-      }
-      if (B_MN) {
+          for (int j = 0; j < BM / 64; ++j) tma_load_2d_pair(sa + j * SLAB_BYTES, tmA, bar, m0 + j * 64, k0);
+        } else {
+          tma_load_2d_pair(sa, tmA, bar, k0, m0);
+        }
+        if (B_MN) {
 #pragma unroll
-        for (int j = 0; j < HALF_N / 64; ++j) tma_load_2d_pair(sb + j * SLAB_BYTES, tmB, bar, n0 + j * 64, k0);
-      } else {
-        tma_load_2d_pair(sb, tmB, bar, k0, n0);
+          for (int j = 0; j < HALF_N / 64; ++j) tma_load_2d_pair(sb + j * SLAB_BYTES, tmB, bar, n0 + j * 64, k0);
+        } else {
+          tma_load_2d_pair(sb, tmB, bar, k0, n0);
+        }
       }
+      __syncwarp();
       issued[stage] = true;
       issued_parity[stage] = phase;
       if (++stage == STAGES2) { stage = 0; phase ^= 1; }
@@ -281,7 +285,7 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
   const uint32_t tmem_base = *s.tmem_base;
 
   if (warp == 0) {
-    if (lane_id() == 0) producer2<A_MN, B_MN>(&tmA, &tmB, p, s, rank, pair, pairs, num_tiles);
+    producer2<A_MN, B_MN>(&tmA, &tmB, p, s, rank, pair, pairs, num_tiles);
   } else if (warp == 1) {
     if (rank == 0) mma2<A_MN, B_MN>(p, s, tmem_base, pair, pairs, num_tiles);
   } else {

@@ -138,7 +138,10 @@ __device__ __forceinline__ SmemLayout carve(uint8_t* raw) {
   return s;
 }
 
-// ---- producer: one lane ----------------------------------------------------------------------
+// ---- producer: the whole warp walks the loop, one elected lane issues the copies ------------------------
+// (same reason as for the MMA issuer below: a lane that branched away from its warp pays on the order of a
+// hundred cycles per TMA instruction, which made the M/N-major layouts, with their four loads per stage,
+// producer-bound)
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ void producer_loop(const CUtensorMap* tmA, const CUtensorMap* tmB, const Params& p,
                                               const SmemLayout& s, int first_tile, int tile_step, int num_tiles) {
@@ -148,6 +151,7 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tmA, const CUte
 #pragma unroll
   for (int i = 0; i < STAGES; ++i) { issued[i] = false; issued_parity[i] = 0; }
   bool ok = true;
+  const bool issuer = elect_one() != 0;
   for (int tile = first_tile; ok && tile < num_tiles; tile += tile_step) {
     const TileInfo ti = tile_info(p, tile);
     const int m0 = ti.m0, n0 = ti.n0, num_kb = ti.num_kb;
@@ -155,39 +159,47 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tmA, const CUte
       // all rows of this tile must have landed: check the flags of its first and last row
       const int f0 = m0 / p.rows_per_flag;
       const int f1 = (min(m0 + BM, p.M) - 1) / p.rows_per_flag;
-      for (int f = f0; ok && f <= f1; ++f) {
-        const uint64_t t0 = globaltimer_ns();
-        while (ld_acquire_sys(p.ready + f) < p.ready_target) {
-          if (*s.abort || globaltimer_ns() - t0 > kWaitLimitNs) {
-            set_status(p.status, kTimeoutPeerFlag);
-            ok = false;
-            break;
+      int landed = 1;
+      if (lane_id() == 0) {  // one lane polls; the verdict is made warp-uniform below
+        for (int f = f0; landed && f <= f1; ++f) {
+          const uint64_t t0 = globaltimer_ns();
+          while (ld_acquire_sys(p.ready + f) < p.ready_target) {
+            if (*s.abort || globaltimer_ns() - t0 > kWaitLimitNs) {
+              set_status(p.status, kTimeoutPeerFlag);
+              landed = 0;
+              break;
+            }
+            __nanosleep(64);
           }
-          __nanosleep(64);
         }
       }
-      if (!ok) break;
+      landed = __shfl_sync(0xffffffffu, landed, 0);
+      __syncwarp();
+      if (!landed) { ok = false; break; }
       // the rows were written with ordinary stores (generic proxy); TMA reads through the async proxy
       asm volatile("fence.proxy.async.global;" ::: "memory");
     }
     for (int kb = 0; kb < num_kb; ++kb) {
-      if (!mbar_wait(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }
-      mbar_expect_tx(&s.full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+      if (!mbar_wait_warp(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }
       uint8_t* sa = s.a + stage * A_STAGE_BYTES;
       uint8_t* sb = s.b + stage * B_STAGE_BYTES;
       const int k0 = ti.k_start + kb * BK;
-      if (A_MN) {
+      if (issuer) {
+        mbar_expect_tx(&s.full[stage], A_STAGE_BYTES + B_STAGE_BYTES);
+        if (A_MN) {
 #pragma unroll
-        for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * SLAB_BYTES, tmA, &s.full[stage], m0 + j * 64, k0);
-      } else {
-        tma_load_2d(sa, tmA, &s.full[stage], k0, m0);
-      }
-      if (B_MN) {
+          for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * SLAB_BYTES, tmA, &s.full[stage], m0 + j * 64, k0);
+        } else {
+          tma_load_2d(sa, tmA, &s.full[stage], k0, m0);
+        }
+        if (B_MN) {
 #pragma unroll
-        for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * SLAB_BYTES, tmB, &s.full[stage], n0 + j * 64, k0);
-      } else {
-        tma_load_2d(sb, tmB, &s.full[stage], k0, n0);
+          for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * SLAB_BYTES, tmB, &s.full[stage], n0 + j * 64, k0);
+        } else {
+          tma_load_2d(sb, tmB, &s.full[stage], k0, n0);
+        }
       }
+      __syncwarp();
       issued[stage] = true;
       issued_parity[stage] = phase;
       if (++stage == STAGES) { stage = 0; phase ^= 1; }
