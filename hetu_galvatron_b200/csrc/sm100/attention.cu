@@ -575,20 +575,20 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       if (tid < 128 && ld_it < n_it) {
         const int q = ld_qs * 64 + (tid & 63);
         if (q >= p.Sq) {
-          v = (tid < 64) ? -INFINITY : 0.f;   // rows past the end: 2^-inf = 0
+          v = (tid < 64) ? INFINITY : 0.f;    // rows past the end: -inf after scaling, 2^-inf = 0
         } else {
           const float* src = (tid < 64) ? p.LSE : p.D;
-          v = src[(size_t(b) * p.nheads + ld_h) * p.Sq + q];
-          if (tid < 64) v *= -kLog2e;
-        }
+          v = src[(size_t(b) * p.nheads + ld_h) * p.Sq + q];   // raw; scaled by stat_scale when it is stored, so
+        }                                                        // that nothing waits for the load here
       }
       ++ld_it;
       if (++ld_qs == n_qs) { ld_qs = qs0; ++ld_h; }
       return v;
     };
+    const float stat_scale = (tid < 64) ? -kLog2e : 1.f;   // -LSE * log2 e for the first 64 threads, D as it is
     float stat_next = load_stat();
     if (n_it > 0) {
-      if (tid < 128) sStats[tid] = stat_next;
+      if (tid < 128) sStats[tid] = stat_next * stat_scale;
       mbar_arrive(&stats_full[0]);
       stat_next = load_stat();
     }
@@ -614,28 +614,38 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       {
         const float4* nl4 = reinterpret_cast<const float4*>(sStats + st * 128 + c0);   // -lse2
         const float4* dd4 = nl4 + 16;                                                  // D
-#pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          const float4 nl = nl4[i >> 2], dd = dd4[i >> 2];
-          pt[i + 0] = ex2(fmaf(pt[i + 0], sl2, nl.x)); pt[i + 1] = ex2(fmaf(pt[i + 1], sl2, nl.y));
-          pt[i + 2] = ex2(fmaf(pt[i + 2], sl2, nl.z)); pt[i + 3] = ex2(fmaf(pt[i + 3], sl2, nl.w));
-          ds[i + 0] -= dd.x; ds[i + 1] -= dd.y; ds[i + 2] -= dd.z; ds[i + 3] -= dd.w;
-        }
         // only steps that touch the diagonal, or a key block with rows past the end, need the mask
         const bool need_mask = !k_valid || (p.causal && (p.q_pos0 + qrow < p.k_pos0 + k0 + 127));
-        if (need_mask) {
-          const int q_base = p.q_pos0 + qrow + c0;
+        const int q_base = p.q_pos0 + qrow + c0;
+        if (!need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (!k_valid || (p.causal && k_pos > q_base + i)) pt[i] = 0.f;
+          for (int i = 0; i < 32; i += 4) {
+            const float4 nl = nl4[i >> 2], dd = dd4[i >> 2];
+            const float nlv[4] = {nl.x, nl.y, nl.z, nl.w}, ddv[4] = {dd.x, dd.y, dd.z, dd.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              pt[i + u] = ex2(fmaf(pt[i + u], sl2, nlv[u]));
+              ds[i + u] = pt[i + u] * (ds[i + u] - ddv[u]);   // in the same loop: these overlap with the exp2 unit
+            }
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 nl = nl4[i >> 2], dd = dd4[i >> 2];
+            const float nlv[4] = {nl.x, nl.y, nl.z, nl.w}, ddv[4] = {dd.x, dd.y, dd.z, dd.w};
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const bool dead = !k_valid || (p.causal && k_pos > q_base + i + u);
+              pt[i + u] = dead ? 0.f : ex2(fmaf(pt[i + u], sl2, nlv[u]));
+              ds[i + u] = pt[i + u] * (ds[i + u] - ddv[u]);
+            }
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) ds[i] *= pt[i];
       }
       // the next step's statistics go to the other buffer: every thread is past its reads of that buffer (they
       // all arrived on this step's stats barrier after finishing the previous step)
       if (it + 1 < n_it) {
-        if (tid < 128) sStats[(st ^ 1) * 128 + tid] = stat_next;
+        if (tid < 128) sStats[(st ^ 1) * 128 + tid] = stat_next * stat_scale;
         mbar_arrive(&stats_full[st ^ 1]);
         stat_next = load_stat();
       }
@@ -884,15 +894,16 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         mbar_arrive(&s_empty[st]);
         const int kbase = it * 64 + c0;
         const bool need_mask = (p.causal && (p.k_pos0 + kbase + 31 > p.q_pos0 + q0)) || (kbase + 32 > p.Skv);
+        if (!need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sv[i] = ex2(fmaf(sv[i], sl2, nlse2));
-        if (need_mask) {
+          for (int i = 0; i < 32; ++i) ds[i] = ex2(fmaf(sv[i], sl2, nlse2)) * (ds[i] - dsum);
+        } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos))) sv[i] = 0.f;
+          for (int i = 0; i < 32; ++i) {
+            const bool dead = (kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos));
+            ds[i] = dead ? 0.f : ex2(fmaf(sv[i], sl2, nlse2)) * (ds[i] - dsum);
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 32; ++i) ds[i] = sv[i] * (ds[i] - dsum);
       }
       if (it >= 2) {   // this buffer was last read by the dQ product of step it-2
         if (!mbar_wait_warp(&ds_empty[st], ((it >> 1) & 1) ^ 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
@@ -1149,15 +1160,16 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         mbar_arrive(s_empty);
         const int kbase = it * 128 + c0;
         const bool need_mask = (p.causal && (p.k_pos0 + kbase + 63 > p.q_pos0 + q0)) || (kbase + 64 > p.Skv);
+        if (!need_mask) {
 #pragma unroll
-        for (int i = 0; i < 64; ++i) sv[i] = ex2(fmaf(sv[i], sl2, nlse2));
-        if (need_mask) {
+          for (int i = 0; i < 64; ++i) ds[i] = ex2(fmaf(sv[i], sl2, nlse2)) * (ds[i] - dsum);
+        } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i)
-            if ((kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos))) sv[i] = 0.f;
+          for (int i = 0; i < 64; ++i) {
+            const bool dead = (kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos));
+            ds[i] = dead ? 0.f : ex2(fmaf(sv[i], sl2, nlse2)) * (ds[i] - dsum);
+          }
         }
-#pragma unroll
-        for (int i = 0; i < 64; ++i) ds[i] = sv[i] * (ds[i] - dsum);
       }
       if (it > 0) {
         if (!mbar_wait_warp(ds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
