@@ -27,7 +27,8 @@ constexpr int HALF_N = BN / 2;                // B rows staged by one CTA
 constexpr int STAGES2 = 6;
 constexpr int A2_BYTES = BM * BK * 2;         // 16 KB
 constexpr int B2_BYTES = HALF_N * BK * 2;     // 16 KB
-constexpr int SMEM2_BYTES = STAGES2 * (A2_BYTES + B2_BYTES) + 1024 + 256;
+constexpr int EPI_STAGE_FLOATS = 32 * 33;     // one 32 x 32 fp32 block per epilogue warp, rows padded to 33 words
+constexpr int SMEM2_BYTES = STAGES2 * (A2_BYTES + B2_BYTES) + 1024 + 256 + EPI_WARPS * EPI_STAGE_FLOATS * 4;
 constexpr uint16_t kPairMask = 0x3;
 
 struct Smem2 {
@@ -39,6 +40,7 @@ struct Smem2 {
   uint64_t* tmem_empty;
   uint32_t* tmem_base;
   volatile int* abort;
+  float* epi_stage;
 };
 
 __device__ __forceinline__ Smem2 carve2(uint8_t* raw) {
@@ -53,6 +55,7 @@ __device__ __forceinline__ Smem2 carve2(uint8_t* raw) {
   s.tmem_empty = bars + 2 * STAGES2 + 2;
   s.tmem_base = reinterpret_cast<uint32_t*>(bars + 2 * STAGES2 + 4);
   s.abort = reinterpret_cast<volatile int*>(s.tmem_base + 1);
+  s.epi_stage = reinterpret_cast<float*>(base + STAGES2 * (A2_BYTES + B2_BYTES) + 256);
   return s;
 }
 
@@ -214,15 +217,57 @@ __device__ __forceinline__ void mma2(const Params& p, const Smem2& s, uint32_t t
   if (!ok) *s.abort = 1;
 }
 
+// Epilogue: tcgen05.ld hands every thread one accumulator ROW (32 consecutive columns), but a row per thread is the
+// wrong shape for global memory: a warp's 16-byte accesses land in 32 different rows and fill only half of every
+// 32-byte sector (138 MB of L2 writes for a 67 MB result, and twice that again for the read-modify-write of the
+// fp32 accumulate mode).  Each warp therefore turns its 32 x 32 block through shared memory and touches global
+// memory one row at a time, 32 lanes on 32 consecutive columns: whole sectors only.
+__device__ __forceinline__ void store_block_rows(const Params& p, const float* stg, int row0, int col0) {
+  const int lane = int(lane_id());
+  const int col = col0 + lane;
+  if (col >= p.N) return;
+  const float bias = p.bias != nullptr ? __bfloat162float(p.bias[col]) : 0.f;
+  const int rows = min(32, p.M - row0);
+  if (p.out_mode == kOutBf16 || p.out_mode == kOutBf16Acc) {
+    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(row0) * p.ldc + col;
+    float old[32];
+    if (p.out_mode == kOutBf16Acc) {   // all 32 loads in flight before the first use
+#pragma unroll
+      for (int r = 0; r < 32; ++r) old[r] = r < rows ? __bfloat162float(c[size_t(r) * p.ldc]) : 0.f;
+    } else {
+#pragma unroll
+      for (int r = 0; r < 32; ++r) old[r] = 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < 32; ++r)
+      if (r < rows) c[size_t(r) * p.ldc] = __float2bfloat16(stg[r * 33 + lane] + bias + old[r]);
+  } else {
+    float* c = reinterpret_cast<float*>(p.C) + size_t(row0) * p.ldc + col;
+    float old[32];
+    if (p.out_mode == kOutF32Acc) {
+#pragma unroll
+      for (int r = 0; r < 32; ++r) old[r] = r < rows ? c[size_t(r) * p.ldc] : 0.f;
+    } else {
+#pragma unroll
+      for (int r = 0; r < 32; ++r) old[r] = 0.f;
+    }
+#pragma unroll
+    for (int r = 0; r < 32; ++r)
+      if (r < rows) c[size_t(r) * p.ldc] = stg[r * 33 + lane] + bias + old[r];
+  }
+}
+
 __device__ __forceinline__ void epilogue2(const Params& p, const Smem2& s, uint32_t tmem_base, uint32_t rank, int first,
                                           int step, int num_tiles) {
   const int wq = (threadIdx.x >> 5) & 3;
+  const int lane = int(lane_id());
   const uint32_t lane_off = uint32_t(wq * 32) << 16;
+  float* stg = s.epi_stage + wq * EPI_STAGE_FLOATS;
   uint32_t acc = 0, acc_phase = 0;
   for (int tile = first; tile < num_tiles; tile += step) {
     int tm, tn;
     tile_coords(p, tile, tm, tn);
-    const int row = tm * CM + int(rank) * BM + wq * 32 + lane_id();
+    const int row0 = tm * CM + int(rank) * BM + wq * 32;   // first of this warp's 32 rows
     const int n0 = tn * BN;
     if (!mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort)) {
       *s.abort = 1;
@@ -230,14 +275,16 @@ __device__ __forceinline__ void epilogue2(const Params& p, const Smem2& s, uint3
     }
     tc_fence_after();
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; c += 2) {
-      uint32_t r0[32], r1[32];
+    for (int c = 0; c < BN / 32; ++c) {
+      uint32_t r0[32];
       tmem_ld32(tmem_base + lane_off + acc * BN + c * 32, r0);
-      tmem_ld32(tmem_base + lane_off + acc * BN + (c + 1) * 32, r1);
       tmem_ld_wait();
-      if (row < p.M) {
-        if (n0 + c * 32 < p.N) store_row_chunk(p, row, n0 + c * 32, r0);
-        if (n0 + (c + 1) * 32 < p.N) store_row_chunk(p, row, n0 + (c + 1) * 32, r1);
+      if (row0 < p.M && n0 + c * 32 < p.N) {   // warp-uniform
+#pragma unroll
+        for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(r0[i]);   // bank (lane + i) % 32: no conflicts
+        __syncwarp();
+        store_block_rows(p, stg, row0, n0 + c * 32);
+        __syncwarp();
       }
     }
     tc_fence_before();

@@ -45,6 +45,47 @@ def timed(fn, iters, warmup, flush):
     return ts[len(ts) // 2]
 
 
+def sustained(fn, secs):
+    """Launch ``fn`` back to back for ``secs`` seconds; returns (ms per call, median SM MHz, median watts) of the
+    second half, when the 1 kW power cap has settled the clocks.  Clocks and power are read (never set) via NVML."""
+    import threading
+    import time
+
+    import pynvml
+
+    pynvml.nvmlInit()
+    h = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
+    samples, stop = [], []
+
+    def sample():
+        while not stop:
+            samples.append((pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM),
+                            pynvml.nvmlDeviceGetPowerUsage(h) / 1000.0))
+            time.sleep(0.05)
+
+    for _ in range(5):
+        fn()
+    torch.cuda.synchronize()
+    th = threading.Thread(target=sample)
+    th.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n, t0 = 0, time.time()
+    e0.record()
+    while time.time() - t0 < secs:
+        for _ in range(50):
+            fn()
+        n += 50
+        torch.cuda.synchronize()
+    e1.record()
+    torch.cuda.synchronize()
+    stop.append(1)
+    th.join()
+    half = samples[len(samples) // 2:] or [(0, 0.0)]
+    mhz = sorted(c for c, _ in half)[len(half) // 2]
+    watts = sorted(w for _, w in half)[len(half) // 2]
+    return e0.elapsed_time(e1) / n, mhz, watts
+
+
 def main(argv=None):
     from hetu_galvatron_b200 import ops
     from hetu_galvatron_b200.ops import _lib
@@ -67,6 +108,9 @@ def main(argv=None):
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--sustain", type=float, default=0.0,
+                    help="gemm only: also run back to back for this many seconds (ours and torch.matmul) and report "
+                         "the power-capped rate with the clocks and watts seen")
     a = ap.parse_args(argv)
     dev = "cuda"
     hbm, tf, tag = peaks()
@@ -84,6 +128,12 @@ def main(argv=None):
         ms = timed(fn, a.iters, a.warmup, flush)
         rate = 2.0 * M * N * K / ms / 1e9
         out.update(shape=[M, N, K], variant=a.variant, ms=ms, tflops=rate, frac=rate / tf, frac_of=tag)
+        if a.sustain > 0:
+            lib_fn = {"fwd": lambda: torch.matmul(x, w.t()), "dgrad": lambda: torch.matmul(dy, w),
+                      "wgrad": lambda: torch.matmul(dy.t(), x)}[a.variant]
+            for name, f in (("sustained", fn), ("sustained_cublas", lib_fn)):
+                ms_s, mhz, watts = sustained(f, a.sustain)
+                out[name] = {"tflops": 2.0 * M * N * K / ms_s / 1e9, "sm_mhz": mhz, "watts": watts}
     elif a.kernel == "attn":
         S, B, nh, ng, hd = a.s, a.b, a.heads, a.kv_heads, a.hd
         q = torch.randn(S, B, nh, hd, device=dev, dtype=bf, requires_grad=True)
