@@ -378,7 +378,9 @@ class GalvatronMoEMLP(nn.Module):
         k, E, ep, E_loc = s.topk, s.experts, c.ep_size, self.experts.E_loc
         if local_only:
             E, ep = E_loc, 1
-        if ep > 1 and getattr(c, "fused_comm", False):
+        # "flex" is the reference's fused dispatcher (DeepEP, moe/token_dispatcher.py:743-1037); here it selects the
+        # peer-memory pull kernels, which the fused-communication switch also turns on for "alltoall"
+        if ep > 1 and (getattr(c, "fused_comm", False) or s.dispatcher == "flex"):
             from ..parallel import fused_a2a as fa
 
             if fa.usable(x2d, c.ep):

@@ -182,6 +182,20 @@ def test_model_training_matches_nccl_path(name, cfg):
             assert abs(l0 - l1) / abs(l0) < 5e-3 and abs(n0 - n1) / n0 < 5e-2, (name, ref, got)
 
 
+def test_flex_dispatcher_selects_the_pull_kernels():
+    """``moe_token_dispatcher_type: flex`` runs the fused dispatcher without the global switch and trains like
+    the all-to-all dispatcher."""
+    _need(2)
+    ref = run_distributed(__file__, "train_moe", 2, {"parallel": {"global_ep_deg": 2}, "model": MOE, "fused": False},
+                          timeout=300, extra_env=ENV)
+    got = run_distributed(__file__, "train_moe", 2,
+                          {"parallel": {"global_ep_deg": 2}, "model": dict(MOE, moe_token_dispatcher_type="flex"),
+                           "fused": False}, timeout=300, extra_env=ENV)
+    for r in range(2):
+        for (l0, n0), (l1, n1) in zip(ref[r], got[r]):
+            assert abs(l0 - l1) / abs(l0) < 5e-3 and abs(n0 - n1) / n0 < 5e-2, (ref, got)
+
+
 if __name__ == "__main__":
     func, payload = sys.argv[2], json.loads(sys.argv[3])
     out = REGISTRY[func](payload)

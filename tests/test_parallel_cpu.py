@@ -143,6 +143,13 @@ def test_moe_allgather_dispatcher():
           key="moe", rtol=1e-3, norm_rtol=2e-2)
 
 
+def test_moe_flex_dispatcher_name_is_accepted():
+    # "flex" picks the peer-memory kernels on GPUs; on CPU ranks it takes the all-to-all path
+    base = {"chunks": 1, "model": MOE}
+    check(2, {"parallel": {"global_ep_deg": 2}, "model": dict(MOE, moe_token_dispatcher_type="flex")}, base,
+          key="moe", rtol=1e-3, norm_rtol=2e-2)
+
+
 def test_moe_expert_tensor_parallel():
     base = {"chunks": 1, "model": MOE}
     check(4, {"parallel": {"global_ep_deg": 2, "global_tp_of_ep_deg": 2}, "model": MOE}, base, key="moe", rtol=1e-3,
