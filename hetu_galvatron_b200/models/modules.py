@@ -131,6 +131,9 @@ class SelfAttention(nn.Module):
         rot = [g * (qpg + 2) + j for g in range(self.ng) for j in range(qpg + 1)]  # q heads and the k head
         self.register_buffer("rope_slots", torch.tensor(rot, dtype=torch.int32, device=device), persistent=False)
         self.rot_dim = int(self.hd * spec.rope_pct)
+        # set by models.inference.forward_step for the duration of a cached forward; None in training
+        self.inference_context = None
+        self.layer_number = ctx.layer_index
 
     def reset_parameters(self, seed: int, full_init: bool):
         s, c = self.spec, self.ctx
@@ -154,6 +157,9 @@ class SelfAttention(nn.Module):
         S_att, B = qkv.shape[0], qkv.shape[1]
         S_full = c.seq_len or S_att * c.cp_size * c.sp_size
         qkv2 = qkv.reshape(S_att * B, -1)
+        if self.inference_context is not None:
+            ctxv = self._cached_attention(qkv2, S_att, B)
+            return row_parallel_linear(ctxv, self.linear_proj.weight, self.linear_proj.bias, c)
         if s.pos == "rope":
             row0 = c.sp_rank * S_att if c.sp_size > 1 else 0
             pos, off = local_positions(c, S_full, S_att, row0, qkv.device)
@@ -180,6 +186,94 @@ class SelfAttention(nn.Module):
                 o = ring_attention(q, k, v, c.cp, S_full)
             ctxv = o.reshape(S_att, B, self.nh * self.hd)
         return row_parallel_linear(ctxv, self.linear_proj.weight, self.linear_proj.bias, c)
+
+
+    def _cached_attention(self, qkv2, S_new: int, B: int):
+        """Incremental forward with a key / value cache (static batching): the new keys and values are written
+        behind the ``sequence_len_offset`` tokens already cached for this layer and the new queries attend to
+        everything up to their own position.  Counterpart of ``_adjust_key_value_for_inference`` and the
+        cached branches of the reference's attention (transformer/attention.py:253-389, 398-513), which no entry
+        point of the reference reaches; here ``models.inference`` drives it."""
+        s, c, ic = self.spec, self.ctx, self.inference_context
+        if c.sp_size > 1 or c.cp_size > 1:
+            raise NotImplementedError("cached attention needs sp = cp = 1")
+        past = ic.sequence_len_offset
+        b0 = ic.batch_size_offset
+        if past + S_new > ic.max_sequence_length or b0 + B > ic.max_batch_size:
+            raise ValueError("inference context too small: %d + %d tokens of %d, batch %d + %d of %d" %
+                             (past, S_new, ic.max_sequence_length, b0, B, ic.max_batch_size))
+        if s.pos == "rope":
+            cos, sin = ops.rope_tables(ic.max_sequence_length, self.rot_dim, s.rope_base, str(qkv2.device),
+                                        s.rope_interp, s.rope_scaling_factor)
+            qkv2 = ops.rope_packed(qkv2, self.rope_slots, self.hd, cos, sin, B, None, past)
+        q, k, v = ops.attention.split_packed(qkv2, self.nh, self.ng, self.hd)
+        q = q.reshape(S_new, B, self.nh, self.hd)
+        k = k.reshape(S_new, B, self.ng, self.hd)
+        v = v.reshape(S_new, B, self.ng, self.hd)
+        key = self.layer_number
+        if key not in ic.key_value_memory_dict:
+            shape = (ic.max_sequence_length, ic.max_batch_size, self.ng, self.hd)
+            ic.key_value_memory_dict[key] = (torch.zeros(shape, dtype=k.dtype, device=k.device),
+                                             torch.zeros(shape, dtype=v.dtype, device=v.device))
+        kc, vc = ic.key_value_memory_dict[key]
+        kc[past:past + S_new, b0:b0 + B] = k
+        vc[past:past + S_new, b0:b0 + B] = v
+        o = ops.flash_attention(q, kc[:past + S_new, b0:b0 + B], vc[:past + S_new, b0:b0 + B], causal=True,
+                                q_pos0=past, k_pos0=0)
+        return o.reshape(S_new, B, self.nh * self.hd)
+
+
+class CrossAttention(nn.Module):
+    """Attention of the hidden states over another sequence: queries from ``x``, keys and values from
+    ``key_value_states`` (``linear_q`` and a fused ``linear_kv``, both column-parallel over the layer's tp group),
+    no mask, row-parallel output projection.  Same restriction as the reference's class
+    (transformer/attention.py:929-1017): no grouped-query attention."""
+
+    def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str):
+        super().__init__()
+        if spec.kv_heads != spec.heads:
+            raise ValueError("Group query attention is not currently supported in cross attention.")
+        if ctx.sp_size > 1 or ctx.cp_size > 1:
+            raise NotImplementedError("cross attention with Ulysses or context parallelism")
+        self.spec, self.ctx, self.name = spec, ctx, name
+        t = ctx.tp_size
+        if spec.heads % t:
+            raise ValueError("heads (%d) must be divisible by tp=%d" % (spec.heads, t))
+        self.nh, self.hd = spec.heads // t, spec.head_dim
+        self.linear_q = _Linear(self.nh * self.hd, spec.hidden, spec.bias, spec, device)
+        self.linear_kv = _Linear(2 * self.nh * self.hd, spec.hidden, spec.bias, spec, device)   # per head: [k | v]
+        self.linear_proj = _Linear(spec.hidden, self.nh * self.hd, spec.bias, spec, device)
+
+    def reset_parameters(self, seed: int, full_init: bool):
+        s, c = self.spec, self.ctx
+        full = s.heads * s.head_dim
+        init_normal_sharded_(self.linear_q.weight, s.init_std, (full, s.hidden), 0, c.tp_rank, c.tp_size, seed,
+                             self.name + ".linear_q.weight", full_init)
+        init_normal_sharded_(self.linear_kv.weight, s.init_std, (2 * full, s.hidden), 0, c.tp_rank, c.tp_size, seed,
+                             self.name + ".linear_kv.weight", full_init)
+        init_normal_sharded_(self.linear_proj.weight, s.init_std, (s.hidden, full), 1, c.tp_rank, c.tp_size, seed,
+                             self.name + ".linear_proj.weight", full_init)
+        for lin in (self.linear_q, self.linear_kv, self.linear_proj):
+            if lin.bias is not None:
+                nn.init.zeros_(lin.bias)
+        if self.linear_proj.bias is not None:
+            self.linear_proj.bias.tp_replicated = True
+
+    def forward(self, x, key_value_states):
+        """``x [Sq_local, B, H]``, ``key_value_states [Sk_local, B, H]`` -> ``[Sq_local, B, H]``."""
+        c = self.ctx
+        from ..parallel.tp_layers import column_parallel_linear, row_parallel_linear
+
+        q = column_parallel_linear(x, self.linear_q.weight, self.linear_q.bias, c)                       # [Sq, B, np*hn]
+        kv = column_parallel_linear(key_value_states, self.linear_kv.weight, self.linear_kv.bias, c)    # [Sk, B, np*2*hn]
+        Sq, B = q.shape[0], q.shape[1]
+        Sk = kv.shape[0]
+        q = q.reshape(Sq, B, self.nh, self.hd)
+        kv = kv.reshape(Sk, B, self.nh, 2 * self.hd)
+        k, v = kv[..., :self.hd], kv[..., self.hd:]
+        o = ops.flash_attention(q, k.contiguous(), v.contiguous(), causal=False)
+        return row_parallel_linear(o.reshape(Sq, B, self.nh * self.hd), self.linear_proj.weight,
+                                   self.linear_proj.bias, c)
 
 
 class GalvatronAttention(nn.Module):

@@ -203,6 +203,39 @@ def rope_packed(qkv: torch.Tensor, head_slots: torch.Tensor, hd: int, cos: torch
     return _RopeInplace.apply(qkv, head_off, cos, sin, batch, pos, pos_offset, rot_dim)
 
 
+def mrope_angles(position_ids: torch.Tensor, mrope_section, rot_dim: int, base: float = 10000.0,
+                 interp: float = 1.0) -> torch.Tensor:
+    """Multimodal RoPE angles.  ``position_ids [3, B, S]`` carries a temporal, a height and a width position per
+    token; the ``rot_dim / 2`` frequency channels are cut into ``mrope_section`` (e.g. ``[16, 24, 24]``) and section
+    ``i`` takes its angle from position row ``i % 3``.  Returns fp32 angles ``[S, B, rot_dim / 2]`` (the two halves of
+    the rotate-half layout share them).  Same channel assignment as the reference's ``MultimodalRotaryEmbedding``
+    (galvatron/core/runtime/transformer/rotary_pos_embedding.py:267-353) and as Qwen2-VL."""
+    if position_ids.dim() != 3 or position_ids.shape[0] != 3:
+        raise ValueError("position_ids must be [3, batch, seq]")
+    half = rot_dim // 2
+    if sum(mrope_section) != half:
+        raise ValueError("mrope_section %s must sum to rot_dim / 2 = %d" % (list(mrope_section), half))
+    inv = 1.0 / (base ** (torch.arange(0, rot_dim, 2, dtype=torch.float32, device=position_ids.device) / rot_dim))
+    ang = position_ids.to(torch.float32)[..., None] / interp * inv          # [3, B, S, half]
+    parts, lo = [], 0
+    for i, n in enumerate(mrope_section):
+        parts.append(ang[i % 3, :, :, lo:lo + n])
+        lo += n
+    return torch.cat(parts, dim=-1).transpose(0, 1).contiguous()           # [S, B, half]
+
+
+def apply_mrope(t: torch.Tensor, angles: torch.Tensor) -> torch.Tensor:
+    """Rotate-half RoPE of ``t [S, B, heads, hd]`` by per-token ``angles [S, B, rot_dim / 2]`` (from
+    :func:`mrope_angles`); channels past ``rot_dim`` pass through.  Differentiable (plain tensor ops: the vision
+    position rows change per sample, so there is no table to cache)."""
+    half = angles.shape[-1]
+    c = angles.cos()[:, :, None, :]
+    s = angles.sin()[:, :, None, :]
+    a, b = t[..., :half].float(), t[..., half:2 * half].float()
+    rot = torch.cat([a * c - b * s, b * c + a * s], dim=-1).to(t.dtype)
+    return torch.cat([rot, t[..., 2 * half:]], dim=-1) if t.shape[-1] > 2 * half else rot
+
+
 # --------------------------------------------------------------------------------------------
 # Gated activations
 # --------------------------------------------------------------------------------------------

@@ -80,8 +80,33 @@ class IndexedDatasetBuilder:
 
 
 class IndexedDataset:
-    def __init__(self, path_prefix: str, multimodal: bool = False, mmap: bool = True):
+    """``path_prefix`` may be an ``s3://bucket/key-prefix``: the index is then downloaded into
+    ``s3_config.path_to_idx_cache`` and the data file read by byte range (``runtime/datasets/s3.py``)."""
+
+    def __init__(self, path_prefix: str, multimodal: bool = False, mmap: bool = True, s3_config=None, s3_client=None):
         self.prefix, self.multimodal = path_prefix, multimodal
+        self._s3 = None
+        if path_prefix.startswith("s3://"):
+            from . import s3 as _s3
+
+            if s3_config is None:
+                raise ValueError("an S3 dataset needs an S3Config (where to cache the index, window size)")
+            local_idx = os.path.join(s3_config.path_to_idx_cache, os.path.basename(idx_path(path_prefix)))
+            _s3.maybe_download_file(idx_path(path_prefix), local_idx, s3_client)
+            self._s3 = _s3.S3BinReader(bin_path(path_prefix), s3_config.bin_chunk_nbytes, s3_client)
+            local_prefix, mmap = local_idx[:-len(".idx")], False
+        else:
+            local_prefix = path_prefix
+        self._open_index(local_prefix, multimodal)
+        if self._s3 is not None:
+            self._bin, self._file = None, None
+        elif mmap:
+            self._bin = np.memmap(bin_path(path_prefix), mode="r", order="C")
+            self._file = None
+        else:
+            self._bin, self._file = None, open(bin_path(path_prefix), "rb")
+
+    def _open_index(self, path_prefix: str, multimodal: bool):
         with open(idx_path(path_prefix), "rb") as f:
             if f.read(9) != MAGIC:
                 raise ValueError("%s is not an indexed-dataset index" % idx_path(path_prefix))
@@ -101,20 +126,22 @@ class IndexedDataset:
         self.sequence_modes = None
         if multimodal:
             self.sequence_modes = np.frombuffer(self._idx, dtype=np.int8, count=n, offset=offset + 12 * n + 8 * self.document_count)
-        if mmap:
-            self._bin = np.memmap(bin_path(path_prefix), mode="r", order="C")
-            self._file = None
-        else:
-            self._bin, self._file = None, open(bin_path(path_prefix), "rb")
 
     @staticmethod
-    def exists(prefix: str) -> bool:
+    def exists(prefix: str, s3_client=None) -> bool:
+        if prefix.startswith("s3://"):
+            from . import s3 as _s3
+
+            cl = s3_client if s3_client is not None else _s3.default_client()
+            return _s3.object_exists(cl, idx_path(prefix)) and _s3.object_exists(cl, bin_path(prefix))
         return os.path.exists(idx_path(prefix)) and os.path.exists(bin_path(prefix))
 
     def __len__(self):
         return self.sequence_count
 
     def _read(self, pointer: int, count: int):
+        if self._s3 is not None:
+            return self._s3.read(self.dtype, count, pointer)
         if self._bin is not None:
             return np.frombuffer(self._bin, dtype=self.dtype, count=count, offset=pointer)
         self._file.seek(pointer)
