@@ -65,6 +65,36 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const int* __restri
   }
 }
 
+// RoPE, interleaved form: channel pairs (2i, 2i+1) rotate by angle i.
+//   out[2i]   = x[2i]*cos[i] - x[2i+1]*sin[i]
+//   out[2i+1] = x[2i+1]*cos[i] + x[2i]*sin[i]
+// One thread takes 8 consecutive channels (4 pairs) of one head of one token.
+__global__ void rope_interleaved_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ head_off, int nheads,
+                                        int row_pitch, int tokens, int batch, const int* __restrict__ pos,
+                                        int pos_offset, const float* __restrict__ cos_t,
+                                        const float* __restrict__ sin_t, int half, float sign) {
+  const int vec_per_head = half >> 2;  // uint4 chunks over the 2*half rotated channels
+  const int64_t total = int64_t(tokens) * nheads * vec_per_head;
+  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
+    const int c = int(i % vec_per_head);
+    const int h = int((i / vec_per_head) % nheads);
+    const int t = int(i / (int64_t(vec_per_head) * nheads));
+    const int p = pos ? pos[t] : (t / batch + pos_offset);
+    __nv_bfloat16* base = buf + size_t(t) * row_pitch + head_off[h] + c * 8;
+    float x[8], o[8];
+    unpack8(*reinterpret_cast<const uint4*>(base), x);
+    const float4 cs = *reinterpret_cast<const float4*>(cos_t + size_t(p) * half + c * 4);
+    const float4 sn = *reinterpret_cast<const float4*>(sin_t + size_t(p) * half + c * 4);
+    const float cv[4] = {cs.x, cs.y, cs.z, cs.w}, sv[4] = {sn.x * sign, sn.y * sign, sn.z * sign, sn.w * sign};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      o[2 * j] = x[2 * j] * cv[j] - x[2 * j + 1] * sv[j];
+      o[2 * j + 1] = x[2 * j + 1] * cv[j] + x[2 * j] * sv[j];
+    }
+    *reinterpret_cast<uint4*>(base) = pack8(o);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // Gated activations on y = [y1 | y2] (each F wide, row pitch 2F):  out = act(y1) * y2
 //   kind 0: SwiGLU (silu), kind 1: GeGLU (tanh GELU).  Non-gated kind 2: out = gelu_tanh(y) (pitch F).
@@ -229,14 +259,23 @@ inline int grid_for(int64_t work, int threads) {
 extern "C" {
 
 int hg_rope(void* buf, const void* head_off, int nheads, int row_pitch, int tokens, int batch, const void* pos,
-            int pos_offset, const void* cos_t, const void* sin_t, int rot_dim, int backward, void* stream) {
+            int pos_offset, const void* cos_t, const void* sin_t, int rot_dim, int flags, void* stream) {
+  // flags: bit 0 = backward (rotate by the negative angle), bit 1 = interleaved channel pairs
   if (tokens <= 0 || nheads <= 0) return 0;
   const int half = rot_dim / 2;
   if ((half & 7) || (row_pitch & 7)) return -1;
-  const int64_t work = int64_t(tokens) * nheads * (half >> 3);
-  rope_kernel<<<grid_for(work, 256), 256, 0, (cudaStream_t)stream>>>(
-      (__nv_bfloat16*)buf, (const int*)head_off, nheads, row_pitch, tokens, batch, (const int*)pos, pos_offset,
-      (const float*)cos_t, (const float*)sin_t, half, backward ? -1.f : 1.f);
+  const float sign = (flags & 1) ? -1.f : 1.f;
+  if (flags & 2) {
+    const int64_t work = int64_t(tokens) * nheads * (half >> 2);
+    rope_interleaved_kernel<<<grid_for(work, 256), 256, 0, (cudaStream_t)stream>>>(
+        (__nv_bfloat16*)buf, (const int*)head_off, nheads, row_pitch, tokens, batch, (const int*)pos, pos_offset,
+        (const float*)cos_t, (const float*)sin_t, half, sign);
+  } else {
+    const int64_t work = int64_t(tokens) * nheads * (half >> 3);
+    rope_kernel<<<grid_for(work, 256), 256, 0, (cudaStream_t)stream>>>(
+        (__nv_bfloat16*)buf, (const int*)head_off, nheads, row_pitch, tokens, batch, (const int*)pos, pos_offset,
+        (const float*)cos_t, (const float*)sin_t, half, sign);
+  }
   return int(cudaGetLastError());
 }
 

@@ -167,7 +167,7 @@ class SelfAttention(nn.Module):
                 pos = pos.repeat_interleave(B)
             cos, sin = ops.rope_tables(max(S_full, 1), self.rot_dim, s.rope_base, str(qkv.device), s.rope_interp,
                                         s.rope_scaling_factor)
-            qkv2 = ops.rope_packed(qkv2, self.rope_slots, self.hd, cos, sin, B, pos, off)
+            qkv2 = ops.rope_packed(qkv2, self.rope_slots, self.hd, cos, sin, B, pos, off, s.rope_interleaved)
         if c.sp_size == 1 and c.cp_size == 1:
             ctxv = ops.flash_attention_packed(qkv2, S_att, B, self.nh, self.ng, self.hd, causal=True)
             ctxv = ctxv.view(S_att, B, self.nh * self.hd)
@@ -205,7 +205,7 @@ class SelfAttention(nn.Module):
         if s.pos == "rope":
             cos, sin = ops.rope_tables(ic.max_sequence_length, self.rot_dim, s.rope_base, str(qkv2.device),
                                         s.rope_interp, s.rope_scaling_factor)
-            qkv2 = ops.rope_packed(qkv2, self.rope_slots, self.hd, cos, sin, B, None, past)
+            qkv2 = ops.rope_packed(qkv2, self.rope_slots, self.hd, cos, sin, B, None, past, s.rope_interleaved)
         q, k, v = ops.attention.split_packed(qkv2, self.nh, self.ng, self.hd)
         q = q.reshape(S_new, B, self.nh, self.hd)
         k = k.reshape(S_new, B, self.ng, self.hd)

@@ -33,6 +33,7 @@ class ModelSpec:
     rope_pct: float = 1.0
     rope_interp: float = 1.0
     rope_scaling_factor: float = 0.0  # > 0: Llama-3.x frequency scaling with this factor
+    rope_interleaved: bool = False   # rotate channel pairs (2i, 2i+1) instead of the two halves
     bias: bool = False               # bias on every linear
     qkv_bias: bool = False
     tied: bool = False               # embedding and LM head share one weight
@@ -130,6 +131,7 @@ def spec_from_args(args) -> ModelSpec:
         rope_scaling_factor=(float(getattr(m, "rope_scaling_factor", 8.0) or 8.0)
                              if getattr(m, "use_rope_scaling", False) else 0.0),
         hidden_dropout=float(getattr(m, "hidden_dropout", 0.0) or 0.0),
+        rope_interleaved=bool(getattr(m, "rotary_interleaved", False)),
         experts=m.num_moe_experts or 0, moe_ffn=m.moe_ffn_hidden_size or m.ffn_hidden_size or 0,
         topk=m.moe_router_topk, router_score=m.moe_router_score_function, router_pre_softmax=m.moe_router_pre_softmax,
         router_scaling=m.moe_router_topk_scaling_factor, router_groups=m.moe_router_num_groups,

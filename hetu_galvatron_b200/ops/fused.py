@@ -139,13 +139,18 @@ def rope_tables(max_pos: int, rot_dim: int, base: float, device: str, interp: fl
     return out
 
 
-def _rope_ref(t, cos, sin, pos, sign=1.0):
-    # t: [tokens, heads, hd]; rotate-half on the first 2*half channels
+def _rope_ref(t, cos, sin, pos, sign=1.0, interleaved=False):
+    # t: [tokens, heads, hd]; rotate-half (or interleaved pairs) on the first 2*half channels
     half = cos.shape[1]
     c = cos[pos][:, None, :]
     s = sin[pos][:, None, :] * sign
-    a, b = t[..., :half].float(), t[..., half:2 * half].float()
     out = t.clone()
+    if interleaved:
+        a, b = t[..., 0:2 * half:2].float(), t[..., 1:2 * half:2].float()
+        out[..., 0:2 * half:2] = (a * c - b * s).to(t.dtype)
+        out[..., 1:2 * half:2] = (b * c + a * s).to(t.dtype)
+        return out
+    a, b = t[..., :half].float(), t[..., half:2 * half].float()
     out[..., :half] = (a * c - b * s).to(t.dtype)
     out[..., half:2 * half] = (b * c + a * s).to(t.dtype)
     return out
@@ -155,36 +160,38 @@ class _RopeInplace(torch.autograd.Function):
     """Rotates the listed head slots of a ``[tokens, slots*hd]`` buffer in place."""
 
     @staticmethod
-    def forward(ctx, buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim):
-        ctx.args = (head_off, cos, sin, batch, pos, pos_offset, rot_dim)
-        _rope_launch(buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim, False)
+    def forward(ctx, buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim, interleaved=False):
+        ctx.args = (head_off, cos, sin, batch, pos, pos_offset, rot_dim, interleaved)
+        _rope_launch(buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim, False, interleaved)
         ctx.mark_dirty(buf)
         return buf
 
     @staticmethod
     def backward(ctx, g):
-        head_off, cos, sin, batch, pos, pos_offset, rot_dim = ctx.args
+        head_off, cos, sin, batch, pos, pos_offset, rot_dim, interleaved = ctx.args
         # the incoming gradient buffer is produced by the attention backward for this op alone, so it is
         # rotated back in place
         if not g.is_contiguous():
             g = g.contiguous()
-        _rope_launch(g, head_off, cos, sin, batch, pos, pos_offset, rot_dim, True)
-        return g, None, None, None, None, None, None, None
+        _rope_launch(g, head_off, cos, sin, batch, pos, pos_offset, rot_dim, True, interleaved)
+        return g, None, None, None, None, None, None, None, None
 
 
-def _rope_launch(buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim, backward):
+def _rope_launch(buf, head_off, cos, sin, batch, pos, pos_offset, rot_dim, backward, interleaved=False):
     lib = _lib.load()
     tokens, pitch = buf.shape
     rc = lib.hg_rope(buf.data_ptr(), head_off.data_ptr(), head_off.numel(), pitch, tokens, batch, _lib.ptr(pos),
-                     pos_offset, cos.data_ptr(), sin.data_ptr(), rot_dim, int(backward), _lib.stream())
+                     pos_offset, cos.data_ptr(), sin.data_ptr(), rot_dim, int(backward) | (2 if interleaved else 0), _lib.stream())
     _lib.check(rc, "hg_rope")
     _lib.count_launch()
 
 
 def rope_packed(qkv: torch.Tensor, head_slots: torch.Tensor, hd: int, cos: torch.Tensor, sin: torch.Tensor,
-                batch: int, pos: torch.Tensor | None = None, pos_offset: int = 0) -> torch.Tensor:
-    """Apply rotate-half RoPE to the head slots ``head_slots`` (int32 slot indices) of ``qkv``
-    ``[tokens, slots*hd]`` (token t = s*batch + b has position ``pos[t]`` or ``s + pos_offset``)."""
+                batch: int, pos: torch.Tensor | None = None, pos_offset: int = 0,
+                interleaved: bool = False) -> torch.Tensor:
+    """Apply RoPE to the head slots ``head_slots`` (int32 slot indices) of ``qkv`` ``[tokens, slots*hd]`` (token
+    t = s*batch + b has position ``pos[t]`` or ``s + pos_offset``): rotate-half, or with ``interleaved`` the
+    channel pairs ``(2i, 2i+1)`` (the reference's ``rotary_interleaved``, rope_utils.py:67-83)."""
     rot_dim = 2 * cos.shape[1]
     if not qkv.is_cuda:
         tokens = qkv.shape[0]
@@ -195,12 +202,12 @@ def rope_packed(qkv: torch.Tensor, head_slots: torch.Tensor, hd: int, cos: torch
             p = pos.long()
         out = t3.clone()
         idx = head_slots.long()
-        out[:, idx] = _rope_ref(t3[:, idx], cos, sin, p)
+        out[:, idx] = _rope_ref(t3[:, idx], cos, sin, p, interleaved=interleaved)
         return out.view_as(qkv)
     head_off = (head_slots.to(torch.int32) * hd).contiguous()
     if pos is not None:
         pos = pos.to(torch.int32).contiguous()
-    return _RopeInplace.apply(qkv, head_off, cos, sin, batch, pos, pos_offset, rot_dim)
+    return _RopeInplace.apply(qkv, head_off, cos, sin, batch, pos, pos_offset, rot_dim, interleaved)
 
 
 def mrope_angles(position_ids: torch.Tensor, mrope_section, rot_dim: int, base: float = 10000.0,

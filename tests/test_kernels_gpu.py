@@ -130,7 +130,8 @@ def test_norm(rms, H):
         assert rel_err(b.grad, br.grad) < 2e-2
 
 
-def test_rope_packed():
+@pytest.mark.parametrize("interleaved", [False, True])
+def test_rope_packed(interleaved):
     torch.manual_seed(5)
     S, B, nh, ng, hd = 96, 2, 8, 2, 128
     slots = nh + 2 * ng
@@ -139,14 +140,14 @@ def test_rope_packed():
     qpg = nh // ng
     rot = torch.tensor([g * (qpg + 2) + j for g in range(ng) for j in range(qpg + 1)], dtype=torch.int32, device=DEV)
     ref_in = qkv.clone().cpu()
-    ref = ops.rope_packed(ref_in, rot.cpu(), hd, cos.cpu(), sin.cpu(), B)
+    ref = ops.rope_packed(ref_in, rot.cpu(), hd, cos.cpu(), sin.cpu(), B, interleaved=interleaved)
     x = qkv.clone().requires_grad_()
-    out = ops.rope_packed(x * 1.0, rot, hd, cos, sin, B)
+    out = ops.rope_packed(x * 1.0, rot, hd, cos, sin, B, interleaved=interleaved)
     assert rel_err(out.cpu(), ref) < 1e-2
     g = torch.randn_like(out)
     out.backward(g.clone())
     xr = ref_in.float().requires_grad_()
-    ops.rope_packed(xr, rot.cpu(), hd, cos.cpu(), sin.cpu(), B).backward(g.cpu().float())
+    ops.rope_packed(xr, rot.cpu(), hd, cos.cpu(), sin.cpu(), B, interleaved=interleaved).backward(g.cpu().float())
     assert rel_err(x.grad.cpu(), xr.grad) < 1e-2
 
 

@@ -185,3 +185,33 @@ def test_indexed_dataset_from_s3_reads_what_the_local_reader_reads(tmp_path):
     assert remote._s3.requests < 20 and all(lo % 4096 == 0 for lo, _ in fake.ranges)
     with pytest.raises(ValueError):
         IndexedDataset("s3://bkt/data/corpus")          # no S3Config
+
+
+# ---- interleaved RoPE -------------------------------------------------------------------------------------------
+def test_interleaved_rope_rotates_channel_pairs():
+    torch.manual_seed(4)
+    S, B, slots, hd = 6, 2, 3, 16
+    qkv = torch.randn(S * B, slots * hd)
+    cos, sin = ops.rope_tables(32, hd, 10000.0, "cpu")
+    out = ops.rope_packed(qkv.clone(), torch.tensor([0, 2], dtype=torch.int32), hd, cos, sin, B, None, 3,
+                          interleaved=True).view(S * B, slots, hd)
+    x = qkv.view(S * B, slots, hd)
+    pos = torch.arange(S * B) // B + 3
+    # complex form: (x[2i] + j x[2i+1]) * exp(j * angle_i)
+    ang = torch.outer(pos.float(), 1.0 / (10000.0 ** (torch.arange(0, hd, 2).float() / hd)))
+    rot = torch.polar(torch.ones_like(ang), ang)[:, None, :]
+    for h in (0, 2):
+        z = torch.view_as_complex(x[:, h].reshape(S * B, hd // 2, 2).contiguous()) * rot[:, 0]
+        assert torch.allclose(out[:, h], torch.view_as_real(z).reshape(S * B, hd), atol=1e-5)
+    assert torch.equal(out[:, 1], x[:, 1])                       # the slot that is not listed stays as it is
+
+
+def test_rotary_interleaved_reaches_the_model_spec():
+    from hetu_galvatron_b200.models.spec import spec_from_args
+
+    args = GalvatronRuntimeArgs(
+        parallel=dict(mixed_precision="fp32"),
+        model=dict(model_size="llama-test", hidden_size=64, num_layers=1, num_attention_heads=4, ffn_hidden_size=96,
+                   vocab_size=128, rotary_interleaved=True),
+        train=dict(seq_length=32, global_batch_size=2, chunks=1))
+    assert spec_from_args(args).rope_interleaved is True
