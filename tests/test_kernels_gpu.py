@@ -327,3 +327,74 @@ def test_gemm_cta_pair_variants(M, N, K, a_mn, b_mn):
     want = acc + ref
     ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=acc, out_mode=OUT_F32_ACC, pair=True)
     assert rel_err(acc, want) < 1e-3
+
+
+# ---- determinism: the same inputs give the same bits (no atomics, fixed tile order and reduction order) ------------
+def _twice(fn):
+    a = fn()
+    b = fn()
+    a = a if isinstance(a, (list, tuple)) else [a]
+    b = b if isinstance(b, (list, tuple)) else [b]
+    return all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+@pytest.mark.parametrize("pair", [False, True])
+def test_gemm_is_bitwise_reproducible(pair):
+    torch.manual_seed(21)
+    M, N, K = 1024, 768, 512
+    a = torch.randn(M, K, device=DEV, dtype=torch.bfloat16)
+    b = torch.randn(N, K, device=DEV, dtype=torch.bfloat16)
+    dy = torch.randn(M, N, device=DEV, dtype=torch.bfloat16)
+    assert _twice(lambda: ops.gemm(a, b, pair=pair))
+    assert _twice(lambda: ops.gemm(dy, b, b_mn=True, pair=pair))
+
+    def wgrad():
+        acc = torch.ones(N, K, device=DEV, dtype=torch.float32)
+        ops.gemm(dy, a, a_mn=True, b_mn=True, out=acc, out_mode=OUT_F32_ACC, pair=pair)
+        return acc
+
+    assert _twice(wgrad)
+
+
+def test_attention_is_bitwise_reproducible():
+    torch.manual_seed(22)
+    S, B, nh, ng, hd = 512, 2, 4, 2, 128
+    q = torch.randn(S, B, nh, hd, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(S, B, ng, hd, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(S, B, ng, hd, device=DEV, dtype=torch.bfloat16)
+    g = torch.randn(S, B, nh, hd, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
+        o = ops.flash_attention(qq, kk, vv, causal=True)
+        o.backward(g)
+        return [o.detach(), qq.grad, kk.grad, vv.grad]
+
+    assert _twice(run)
+
+
+def test_norm_and_loss_are_bitwise_reproducible():
+    torch.manual_seed(23)
+    T, H, V = 300, 1024, 4096
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+    w = torch.ones(H, device=DEV, dtype=torch.bfloat16)
+    gy = torch.randn(T, H, device=DEV, dtype=torch.bfloat16)
+
+    def norm():
+        xx, ww = x.clone().requires_grad_(), w.clone().requires_grad_()
+        y, _ = ops.norm(xx, ww, None, 1e-5, True)
+        y.backward(gy)
+        return [y.detach(), xx.grad, ww.grad]
+
+    assert _twice(norm)
+    lg = torch.randn(T, V, device=DEV, dtype=torch.bfloat16)
+    tg = torch.randint(0, V, (T,), device=DEV)
+
+    def xent():
+        ll = lg.clone().requires_grad_()
+        loss = ops.cross_entropy(ll, tg)
+        loss.sum().backward()
+        return [loss.detach(), ll.grad]
+
+    assert _twice(xent)
+    _lib.assert_healthy()
