@@ -73,22 +73,32 @@ def forward_step(model, tokens: torch.Tensor, ctx: StaticInferenceContext) -> to
 
 
 @torch.no_grad()
-def greedy_generate(model, prompt: torch.Tensor, max_new_tokens: int, vocab_group=None) -> torch.Tensor:
+def greedy_generate(model, prompt: torch.Tensor, max_new_tokens: int, vocab_group=None,
+                    new_tokens_per_step: int = 1) -> torch.Tensor:
     """Greedy continuation of ``prompt [B, S]``: prefill once, then one token per step.  With a vocab-parallel head
     pass its group (a ``parallel.groups.CommGroup``, e.g. ``model.vocab_ctx.tp``) so that the arg-max runs over the
-    gathered vocabulary."""
+    gathered vocabulary.
+
+    Tensor-parallel layers keep sequence-parallel activations, so every call must feed a multiple of the tp degree:
+    with ``new_tokens_per_step = t`` each step re-feeds the last ``t - 1`` cached tokens together with the new one
+    (the cache offset is moved back accordingly), which costs ``t`` rows per step instead of one."""
     import torch.distributed as dist
 
     B, S = prompt.shape
+    t = max(1, int(new_tokens_per_step))
+    if S % t:
+        raise ValueError("the prompt length (%d) must be divisible by new_tokens_per_step (%d)" % (S, t))
     ctx = StaticInferenceContext(B, S + max_new_tokens)
-    out = [prompt]
-    tokens = prompt
+    seq = prompt
+    feed = prompt
     for _ in range(max_new_tokens):
-        logits = forward_step(model, tokens, ctx)[-1]                 # [B, V / t]
+        logits = forward_step(model, feed, ctx)[-1]                   # [B, V / tp]
         if vocab_group is not None and vocab_group.size > 1:
             parts = [torch.empty_like(logits) for _ in range(vocab_group.size)]
             dist.all_gather(parts, logits.contiguous(), group=vocab_group.group)
             logits = torch.cat(parts, dim=-1)
-        tokens = logits.float().argmax(dim=-1, keepdim=True).to(prompt.dtype)
-        out.append(tokens)
-    return torch.cat(out, dim=1)
+        nxt = logits.float().argmax(dim=-1, keepdim=True).to(prompt.dtype)
+        seq = torch.cat([seq, nxt], dim=1)
+        feed = seq[:, -t:]                                            # the new token and the t - 1 before it
+        ctx.sequence_len_offset = seq.shape[1] - t                    # their keys / values are simply rewritten
+    return seq

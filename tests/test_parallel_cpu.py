@@ -57,7 +57,28 @@ def train(cfg):
     return out
 
 
-REGISTRY = {"train": train}
+def generate(cfg):
+    """Greedy continuation through the key / value cache on this strategy; returns the generated tokens."""
+    import torch
+
+    from hetu_galvatron_b200.models.inference import StaticInferenceContext, forward_step, greedy_generate
+    from hetu_galvatron_b200.runtime.engine import build_model
+
+    torch.manual_seed(0)
+    args = make_args(cfg)
+    model = build_model(args, device=torch.device("cpu"), full_init=True)
+    g = torch.Generator().manual_seed(11)
+    prompt = torch.randint(0, VOCAB, (2, 16), generator=g)
+    out = greedy_generate(model, prompt, 4, vocab_group=model.vocab_ctx.tp, new_tokens_per_step=cfg.get("per_step", 1))
+    # the cached logits of the prompt equal the plain forward's
+    ctx = StaticInferenceContext(2, 32)
+    cached = forward_step(model, prompt, ctx)
+    with torch.no_grad():
+        plain = model.model(prompt, None)
+    return {"tokens": out.tolist(), "diff": float((cached - plain).abs().max())}
+
+
+REGISTRY = {"train": train, "generate": generate}
 
 _baselines = {}
 
@@ -124,6 +145,15 @@ def test_layerwise_heterogeneous_strategy():
                 "use_sp": "0,0,0,1", "checkpoint": "0,1,0,0", "global_bsz": GBSZ, "chunks": 2, "pp_division": "4",
                 "pipeline_type": "gpipe", "default_dp_type": "zero2", "vtp": 2, "vsp": 0, "embed_sdp": 1}
     check(4, {"parallel": {"galvatron_config_path": strategy}})
+
+
+def test_cached_generation_under_tensor_parallelism():
+    """Vocab- and tensor-parallel ranks generate the same tokens as one process (two tokens per step keep the
+    sequence-parallel activations divisible by the tp degree)."""
+    one = run_distributed(__file__, "generate", 1, {"per_step": 2})
+    two = run_distributed(__file__, "generate", 2, {"per_step": 2, "parallel": {"global_tp_deg": 2, "vocab_tp": 2}})
+    assert one[0]["diff"] < 1e-5 and all(r["diff"] < 1e-5 for r in two)
+    assert two[0]["tokens"] == two[1]["tokens"] == one[0]["tokens"]
 
 
 def test_moe_expert_parallel():
