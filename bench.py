@@ -129,7 +129,7 @@ def run_ours(a):
         train=dict(seq_length=a.seq, global_batch_size=gbsz, chunks=chunks, lr=1e-4, adam_beta1=0.9, adam_beta2=0.95,
                    weight_decay=0.1, clip_grad=1.0, seed=1234),
         rank=rank, world_size=n, local_rank=local_rank)
-    os.environ.setdefault("HG_QUIET", "1" if rank else "0")
+    os.environ.setdefault("HG_QUIET", "1")   # stdout carries the one JSON line only; the plan is in its "config"
     model = build_model(args, device=dev)
     opt = ShardedAdamW(model.sharded_units, lr=1e-4, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1, clip_grad=1.0,
                        device=dev)
