@@ -109,6 +109,15 @@ def test_data_parallel_and_zero(dp_type, async_reduce, chunks):
                                              "async_grad_reduce": async_reduce}})
 
 
+@pytest.mark.parametrize("mp", ["bf16", "fp16"])
+def test_mixed_precision_data_parallel(mp):
+    """16-bit parameters and activations with fp32 master weights and fp32 gradient reduction: two ZeRO-2 ranks
+    against one process at the same precision (the counterpart of the reference's tests/core/test_mixed_precision.py)."""
+    base = {"chunks": 1, "parallel": {"mixed_precision": mp}}
+    check(2, {"chunks": 2, "parallel": {"mixed_precision": mp, "default_dp_type": "zero2"}}, base, key="mp_" + mp,
+          rtol=2e-3, norm_rtol=2e-2)
+
+
 def test_tensor_parallel_with_sequence_parallel_and_vocab_tp():
     check(2, {"parallel": {"global_tp_deg": 2, "vocab_tp": 2}})
 
