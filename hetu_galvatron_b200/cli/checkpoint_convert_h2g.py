@@ -2,7 +2,8 @@
 
     python -m hetu_galvatron_b200.cli.checkpoint_convert_h2g --model_type llama --input_checkpoint <hf dir> --output_dir <dir>
 
-``model_type``: ``llama`` (also qwen / mistral dense), ``gpt``, ``mixtral``.  Output layout: one ``.pt`` per module
+``model_type``: ``llama`` (also qwen / mistral dense), ``gpt``, ``mixtral``, ``bert-mlm`` (key regrouping only, as in the
+reference: no BERT model is built from it).  Output layout: one ``.pt`` per module
 (``model_embed_tokens.pt``, ``model_layers_{i}.pt``, ``model_norm.pt``, ``lm_head.pt``) with the HF key names minus the
 module prefix.  Same tool as galvatron/tools/checkpoint_convert_h2g.py:140-159.
 """
@@ -15,7 +16,7 @@ from ..runtime.checkpoint import convert_hf_to_split, read_hf_checkpoint
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("--model_type", required=True, choices=["llama", "gpt", "mixtral", "qwen", "mistral"])
+    ap.add_argument("--model_type", required=True, choices=["llama", "gpt", "mixtral", "qwen", "mistral", "bert-mlm"])
     ap.add_argument("--input_checkpoint", required=True)
     ap.add_argument("--output_dir", required=True)
     a = ap.parse_args(argv)

@@ -60,13 +60,16 @@ def convert_hf_to_split(state_dict: Dict[str, torch.Tensor], model_type: str, ou
                 fname, sub = "transformer_embedding", ".".join(parts[1:])
             else:
                 fname, sub = "transformer_%s" % parts[1], ".".join(parts[2:])
-        elif model_type == "bert":
+        elif model_type in ("bert", "bert-mlm"):
+            # same grouping as the reference's convert_checkpoints_bert_mlm (tools/checkpoint_convert_h2g.py:93-138)
             if parts[0] == "bert" and parts[1] == "encoder":
                 fname, sub = "bert_encoder_layer_%s" % parts[3], ".".join(parts[4:])
-            elif parts[0] == "bert":
+            elif parts[0] == "bert" and parts[1] in ("embeddings", "pooler"):
                 fname, sub = "bert_%s" % parts[1], ".".join(parts[2:])
+            elif parts[0] == "cls" and parts[1] == "predictions":
+                fname, sub = "cls_predictions", ".".join(parts[2:])
             else:
-                fname, sub = parts[0], ".".join(parts[1:])
+                continue
         else:
             raise ValueError("unknown model type %r" % model_type)
         groups.setdefault(fname, {})[sub] = val.detach().clone()

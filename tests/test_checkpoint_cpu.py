@@ -226,3 +226,24 @@ def test_export_back_to_hf_names(split_dir, tmp_path):
 
 if __name__ == "__main__":
     worker_main(REGISTRY)
+
+
+def test_bert_mlm_checkpoint_is_regrouped_like_the_reference_tool(tmp_path):
+    """Key layout of the reference's tests/models/test_checkpoint_convert.py."""
+    import torch
+
+    from hetu_galvatron_b200.cli import checkpoint_convert_h2g as h2g
+
+    src, dst = tmp_path / "hf", tmp_path / "split"
+    src.mkdir()
+    keys = ["bert.embeddings.word_embeddings.weight", "bert.embeddings.LayerNorm.bias",
+            "bert.encoder.layer.0.attention.self.query.weight", "bert.encoder.layer.0.output.LayerNorm.bias",
+            "bert.encoder.layer.1.intermediate.dense.weight", "bert.pooler.dense.weight",
+            "cls.predictions.transform.dense.weight", "cls.predictions.decoder.weight", "cls.predictions.bias"]
+    torch.save({k: torch.randn(3, 2) for k in keys}, src / "bert_model.bin")
+    files = h2g.main(["--model_type", "bert-mlm", "--input_checkpoint", str(src), "--output_dir", str(dst)])
+    assert files == ["bert_embeddings.pt", "bert_encoder_layer_0.pt", "bert_encoder_layer_1.pt", "bert_pooler.pt",
+                     "cls_predictions.pt"]
+    assert set(torch.load(dst / "bert_embeddings.pt")) == {"word_embeddings.weight", "LayerNorm.bias"}
+    assert set(torch.load(dst / "bert_encoder_layer_0.pt")) == {"attention.self.query.weight", "output.LayerNorm.bias"}
+    assert set(torch.load(dst / "cls_predictions.pt")) == {"transform.dense.weight", "decoder.weight", "bias"}
