@@ -184,9 +184,14 @@ def pp_division_memory_balanced(model_args_list, train_args_list, parallel_args_
     return balance_stages(layers, other, pp_deg)
 
 
+def ensure_log_dir(log_dir: str) -> str:
+    """Create the directory of the per-task search logs (galvatron/core/search_engine/utils.py:33-40)."""
+    os.makedirs(log_dir, exist_ok=True)
+    return log_dir
+
+
 def _task_logger(log_dir: str, gbsz, chunks, pp, buffer_tp, mode) -> logging.Logger:
-    d = os.path.join(log_dir, "search_gbsz%d_chunks%d" % (gbsz, chunks))
-    os.makedirs(d, exist_ok=True)
+    d = ensure_log_dir(os.path.join(log_dir, "search_gbsz%d_chunks%d" % (gbsz, chunks)))
     name = "hg.search.%s.%d.%d.%d.%s.%d.%d" % (log_dir, gbsz, chunks, pp, mode, buffer_tp, threading.get_ident())
     logger = logging.getLogger(name)
     logger.setLevel(logging.INFO)
