@@ -85,10 +85,9 @@ def _one_prefix(prefix: str, bounds, num_samples, cfg: GPTDatasetConfig, mmap: b
 def build_train_valid_test_datasets(args):
     t, d = args.train, args.data
     cfg = _gpt_config(args)
-    gbsz = t.global_batch_size
-    train_n = (t.train_iters or 0) * gbsz if t.train_iters else t.train_samples
-    eval_n = ((t.train_iters or 0) // max(1, t.eval_interval or 1) + 1) * (t.eval_iters or 0) * gbsz
-    test_n = (t.eval_iters or 0) * gbsz
+    from ..data import get_train_valid_test_num_samples
+
+    train_n, eval_n, test_n = get_train_valid_test_num_samples(args)
     targets = [train_n or None, eval_n or None, test_n or None]
     per_split = [d.train_data_path, d.valid_data_path, d.test_data_path]
     results = []

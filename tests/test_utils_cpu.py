@@ -112,3 +112,21 @@ def test_ensure_log_dir(tmp_path):
 
     d = ensure_log_dir(str(tmp_path / "a" / "b"))
     assert (tmp_path / "a" / "b").is_dir() and d.endswith("b")
+
+
+def test_random_seed_dataset_is_reproducible_per_item_and_epoch():
+    from hetu_galvatron_b200.runtime.data import RandomSeedDataset
+
+    class Noisy(torch.utils.data.Dataset):
+        def __len__(self):
+            return 8
+
+        def __getitem__(self, i):
+            return torch.rand(3)
+
+    ds = RandomSeedDataset(Noisy(), seed=7)
+    a, b = ds[2], ds[5]
+    assert torch.equal(ds[2], a) and not torch.equal(a, b)      # same item, same numbers, whatever was drawn between
+    ds.set_epoch(1)
+    assert not torch.equal(ds[2], a) and torch.equal(ds[1], a) and torch.equal(ds[4], b)  # seed = base + epoch + index
+    assert len(ds) == 8
