@@ -133,3 +133,23 @@ def test_memory_balanced_stage_division():
     # more stages than a greedy fill would populate: every stage still gets a layer
     div, _ = balance_stages([5.0, 1.0, 1.0, 1.0], [0.0, 0.0, 0.0, 0.0], 4)
     assert div == [1, 1, 1, 1]
+
+
+def test_shipped_b200_profiles_reproduce_the_shipped_plan(tmp_path, monkeypatch):
+    """The B200 hardware profile, model profiles and refit under ``cli/`` give the strategy file that ships beside them
+    (search space cut to the data-parallel strategies, which contain the optimum, to keep the test short)."""
+    import hetu_galvatron_b200.cli as cli_pkg
+    from hetu_galvatron_b200.cli import search_dist
+
+    cli = os.path.dirname(cli_pkg.__file__)
+    monkeypatch.setenv("HG_PROFILE_DIR", cli)
+    thr = search_dist.main([os.path.join(cli, "configs", "search_dist.yaml"),
+                            "search_engine.search_space_info.max_pp_deg=1", "search_engine.search_space_info.max_tp_deg=1",
+                            "search_engine.search_space_info.max_sp_deg=1",
+                            "search_engine.options_info.output_config_path=%s" % tmp_path,
+                            "search_engine.options_info.log_dir=%s" % tmp_path])
+    assert 1.4 < 64 / thr < 1.8                                   # seconds per iteration of 64 sequences on 8 GPUs
+    name = "galvatron_config_llama2-7b_1nodes_8gpus_per_node_160GB_bf16.json"
+    got = json.load(open(tmp_path / name))
+    shipped = json.load(open(os.path.join(cli, "configs", name)))
+    assert got == shipped
