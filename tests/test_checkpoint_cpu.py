@@ -247,3 +247,71 @@ def test_bert_mlm_checkpoint_is_regrouped_like_the_reference_tool(tmp_path):
     assert set(torch.load(dst / "bert_embeddings.pt")) == {"word_embeddings.weight", "LayerNorm.bias"}
     assert set(torch.load(dst / "bert_encoder_layer_0.pt")) == {"attention.self.query.weight", "output.LayerNorm.bias"}
     assert set(torch.load(dst / "cls_predictions.pt")) == {"transform.dense.weight", "decoder.weight", "bias"}
+
+
+def _family_loss(model_type, model_kw, state_dict, tmp):
+    """Split an HF state dict, load it into our model of the same shape, return the loss on the fixed batch."""
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+    from hetu_galvatron_b200.runtime import checkpoint as ck
+    from hetu_galvatron_b200.runtime.engine import build_model
+
+    ck.convert_hf_to_split(state_dict, model_type, str(tmp))
+    args = GalvatronRuntimeArgs(parallel=dict(mixed_precision="fp32"), data=dict(use_random_dataset=True),
+                                train=dict(seq_length=SEQ, global_batch_size=GB, chunks=1, lr=1e-3, seed=3),
+                                model=model_kw)
+    m = build_model(args, device=torch.device("cpu"))
+    ck.load_hf_split(m, str(tmp))
+    tok = batch()
+    return float(m.forward_backward(tok[:, :-1], 0, labels=tok[:, 1:], forward_only=True))
+
+
+def _hf_loss(m):
+    tok = batch()
+    with torch.no_grad():
+        lg = m(input_ids=tok[:, :-1]).logits.float()
+    return torch.nn.functional.cross_entropy(lg.reshape(-1, lg.shape[-1]), tok[:, 1:].reshape(-1)).item()
+
+
+def test_gpt2_hf_weights_give_hf_loss(tmp_path):
+    """GPT-2 family: learned positions, LayerNorm, biases, tanh-GELU, tied embeddings, HF's transposed Conv1D weights."""
+    from transformers import GPT2Config, GPT2LMHeadModel
+
+    torch.manual_seed(31)
+    hf = GPT2LMHeadModel(GPT2Config(n_embd=H, n_layer=L, n_head=NH, n_inner=4 * H, vocab_size=V, n_positions=SEQ,
+                                    resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0,
+                                    activation_function="gelu_new")).eval()
+    with torch.no_grad():                      # biases and norm weights away from their 0 / 1 initial values
+        for p in hf.parameters():
+            if p.dim() == 1:
+                p.add_(0.05 * torch.randn_like(p))
+    ours = _family_loss("gpt", dict(model_size="gpt-test", hidden_size=H, num_layers=L, num_attention_heads=NH,
+                                    ffn_hidden_size=4 * H, vocab_size=V, normalization="LayerNorm",
+                                    activation_func="torch.nn.functional.gelu", gated_linear_unit=False,
+                                    position_embedding_type="learned_absolute", add_bias_linear=True,
+                                    add_qkv_bias=True, make_vocab_size_divisible_by=8, norm_epsilon=1e-5),
+                        hf.state_dict(), tmp_path)
+    ref = _hf_loss(hf)
+    assert abs(ours - ref) / ref < 1e-4, (ours, ref)
+
+
+def test_qwen2_hf_weights_give_hf_loss(tmp_path):
+    """Qwen-2 family: Llama-style layers with biases on q / k / v only, GQA, rope base 1e6."""
+    from transformers import Qwen2Config, Qwen2ForCausalLM
+
+    torch.manual_seed(32)
+    hf = Qwen2ForCausalLM(Qwen2Config(hidden_size=H, num_hidden_layers=L, num_attention_heads=NH,
+                                      num_key_value_heads=NKV, intermediate_size=FFN, vocab_size=V, rms_norm_eps=1e-6,
+                                      max_position_embeddings=SEQ, tie_word_embeddings=False, rope_theta=1000000.0,
+                                      use_sliding_window=False)).eval()
+    with torch.no_grad():
+        for n, p in hf.named_parameters():
+            if n.endswith("bias"):
+                p.copy_(0.1 * torch.randn_like(p))
+    ours = _family_loss("qwen", dict(model_size="qwen-test", hidden_size=H, num_layers=L, num_attention_heads=NH,
+                                     num_query_groups=NKV, ffn_hidden_size=FFN, vocab_size=V, normalization="RMSNorm",
+                                     gated_linear_unit=True, activation_func="torch.nn.functional.silu",
+                                     untie_embeddings_and_output_weights=True, make_vocab_size_divisible_by=8,
+                                     norm_epsilon=1e-6, add_qkv_bias=True, rotary_base=1000000),
+                        hf.state_dict(), tmp_path)
+    ref = _hf_loss(hf)
+    assert abs(ours - ref) / ref < 1e-4, (ours, ref)
