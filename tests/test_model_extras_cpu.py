@@ -215,3 +215,29 @@ def test_rotary_interleaved_reaches_the_model_spec():
                    vocab_size=128, rotary_interleaved=True),
         train=dict(seq_length=32, global_batch_size=2, chunks=1))
     assert spec_from_args(args).rope_interleaved is True
+
+
+def test_cached_forward_of_a_moe_model_and_beam_reorder():
+    torch.manual_seed(0)
+    args = GalvatronRuntimeArgs(
+        parallel=dict(mixed_precision="fp32"),
+        model=dict(model_size="mixtral-test", hidden_size=64, num_layers=2, num_attention_heads=4, num_query_groups=2,
+                   vocab_size=128, make_vocab_size_divisible_by=8, normalization="RMSNorm",
+                   activation_func="torch.nn.functional.silu", gated_linear_unit=True, is_moe_model=True,
+                   num_moe_experts=4, moe_router_topk=2, moe_ffn_hidden_size=96),
+        train=dict(seq_length=32, global_batch_size=2, chunks=1))
+    m = build_model(args, device=torch.device("cpu"), full_init=True)
+    tok = torch.randint(0, 128, (2, 20))
+    with torch.no_grad():
+        full = m.model(tok, None)
+    ctx = StaticInferenceContext(2, 32)
+    parts = [forward_step(m, tok[:, :12], ctx)] + [forward_step(m, tok[:, i:i + 1], ctx) for i in range(12, 20)]
+    assert torch.allclose(torch.cat(parts, 0), full, atol=1e-5, rtol=1e-5)
+    # swapping the two cached sequences and feeding the swapped next tokens gives the swapped logits
+    nxt = torch.randint(0, 128, (2, 1))
+    ref = StaticInferenceContext(2, 32)
+    forward_step(m, tok, ref)
+    a = forward_step(m, nxt, ref)
+    ctx.swap_key_value_dict(torch.tensor([1, 0]))
+    b = forward_step(m, nxt.flip(0), ctx)
+    assert torch.allclose(b, a.flip(1), atol=1e-5, rtol=1e-5)
