@@ -79,6 +79,67 @@ zero_reduce_scatter_kernel(PeerPtrs grads, int me, long long shard_floats, long 
   }
 }
 
+
+// bf16-on-the-wire variant (the reference's default, reduce_in_fp32 = false): every rank first rounds its fp32
+// gradient buffer into a bf16 staging buffer (symmetric memory); this kernel then sums, in fp32 and in rank order,
+// the peers' bf16 slices (16-byte loads of 8 values: half the NVLink bytes of the fp32 kernel) and this rank's own
+// slice taken from the fp32 buffer, unrounded.  n8 = number of 8-element groups of the shard.  With `accumulate` the
+// result is added to `out` (running shard of the per-micro-batch reduction mode).
+template <int T, bool kAcc>
+__global__ void __launch_bounds__(kThreads)
+zero_reduce_scatter_bf16wire_kernel(PeerPtrs staged, const float* __restrict__ own, int me, long long shard_elems,
+                                    long long n8, float4* __restrict__ out) {
+  const uint4* src[T];
+#pragma unroll
+  for (int r = 0; r < T; ++r) {
+    src[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(staged.p[r]) + me * shard_elems);
+  }
+  const float4* mine = reinterpret_cast<const float4*>(own + me * shard_elems);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += stride) {
+    uint4 a[T];
+#pragma unroll
+    for (int r = 0; r < T; ++r) {
+      if (r != me) a[r] = __ldcs(src[r] + i);
+    }
+    const float4 m0 = __ldcs(mine + 2 * i), m1 = __ldcs(mine + 2 * i + 1);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int r = 0; r < T; ++r) {
+      if (r == me) {
+        acc[0] += m0.x; acc[1] += m0.y; acc[2] += m0.z; acc[3] += m0.w;
+        acc[4] += m1.x; acc[5] += m1.y; acc[6] += m1.z; acc[7] += m1.w;
+      } else {
+        const uint32_t w[4] = {a[r].x, a[r].y, a[r].z, a[r].w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          acc[2 * k] += __uint_as_float(w[k] << 16);
+          acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+        }
+      }
+    }
+    float4 o0 = make_float4(acc[0], acc[1], acc[2], acc[3]), o1 = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    if (kAcc) {
+      const float4 p0 = out[2 * i], p1 = out[2 * i + 1];
+      o0.x += p0.x; o0.y += p0.y; o0.z += p0.z; o0.w += p0.w;
+      o1.x += p1.x; o1.y += p1.y; o1.z += p1.z; o1.w += p1.w;
+    }
+    out[2 * i] = o0;
+    out[2 * i + 1] = o1;
+  }
+}
+
+// out[i] += x[i] on float4 groups (running shard of the per-micro-batch reduction mode, fp32 wire).
+__global__ void __launch_bounds__(kThreads) add_inplace_kernel(float4* __restrict__ out, const float4* __restrict__ x, long long n4) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4; i += stride) {
+    float4 a = out[i];
+    const float4 b = __ldcs(x + i);
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    out[i] = a;
+  }
+}
+
 __device__ __forceinline__ float adam_one(float& p, float g, float& m, float& v, const AdamHyper& a, float step,
                                           float inv_b2) {
   m = a.beta1 * m + (1.f - a.beta1) * g;
@@ -143,13 +204,21 @@ extern "C" {
 
 // grads[r]: rank r's fp32 gradient buffer (t * shard_floats elements, peer-mapped).  out: this rank's reduced shard.
 // shard_floats must be a multiple of 4 and every buffer 16-byte aligned.
+int hg_zero_reduce_scatter_capped(void* const* grads, int t, int me, long long shard_floats, void* out, int max_ctas,
+                                  void* stream);
 int hg_zero_reduce_scatter(void* const* grads, int t, int me, long long shard_floats, void* out, void* stream) {
+  return hg_zero_reduce_scatter_capped(grads, t, me, shard_floats, out, 0, stream);
+}
+// As above with the grid capped at max_ctas blocks (0 = no cap), for a reduction that overlaps the backward GEMMs.
+int hg_zero_reduce_scatter_capped(void* const* grads, int t, int me, long long shard_floats, void* out, int max_ctas,
+                                  void* stream) {
   if (t < 1 || t > kMaxPeers || me < 0 || me >= t || shard_floats <= 0 || (shard_floats & 3)) return -1;
   PeerPtrs pp{};
   for (int r = 0; r < t; ++r) pp.p[r] = grads[r];
   const long long n4 = shard_floats / 4;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  const int grid = grid_for((n4 + 1) / 2);
+  int grid = grid_for((n4 + 1) / 2);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
 #define HG_RS(T_) zero_reduce_scatter_kernel<T_><<<grid, kThreads, 0, st>>>(pp, me, shard_floats, n4, (float4*)out)
   switch (t) {
     case 1: HG_RS(1); break;
@@ -162,6 +231,44 @@ int hg_zero_reduce_scatter(void* const* grads, int t, int me, long long shard_fl
     default: HG_RS(8); break;
   }
 #undef HG_RS
+  return int(cudaGetLastError());
+}
+
+
+// bf16 wire: staged[r] = rank r's bf16 staging buffer (t * shard elements, peer-mapped); own = this rank's fp32
+// gradient buffer (local).  shard a multiple of 8.  max_ctas > 0 caps the grid (a reduction that runs beside the
+// backward GEMMs should not take every SM).  accumulate != 0: out += sum.
+int hg_zero_reduce_scatter_bf16wire(void* const* staged, const void* own, int t, int me, long long shard, void* out,
+                                    int accumulate, int max_ctas, void* stream) {
+  if (t < 1 || t > kMaxPeers || me < 0 || me >= t || shard <= 0 || (shard & 7) || own == nullptr) return -1;
+  PeerPtrs pp{};
+  for (int r = 0; r < t; ++r) pp.p[r] = staged[r];
+  const long long n8 = shard / 8;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int grid = grid_for(n8);
+  if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
+#define HG_RSB(T_)                                                                                                  \
+  if (accumulate) zero_reduce_scatter_bf16wire_kernel<T_, true><<<grid, kThreads, 0, st>>>(pp, (const float*)own, me, shard, n8, (float4*)out); \
+  else zero_reduce_scatter_bf16wire_kernel<T_, false><<<grid, kThreads, 0, st>>>(pp, (const float*)own, me, shard, n8, (float4*)out)
+  switch (t) {
+    case 1: HG_RSB(1); break;
+    case 2: HG_RSB(2); break;
+    case 3: HG_RSB(3); break;
+    case 4: HG_RSB(4); break;
+    case 5: HG_RSB(5); break;
+    case 6: HG_RSB(6); break;
+    case 7: HG_RSB(7); break;
+    default: HG_RSB(8); break;
+  }
+#undef HG_RSB
+  return int(cudaGetLastError());
+}
+
+// out[0:n] += x[0:n] (fp32, n a multiple of 4, both 16-byte aligned).
+int hg_add_inplace_f32(void* out, const void* x, long long n, void* stream) {
+  if (n <= 0) return 0;
+  if (n & 3) return -1;
+  add_inplace_kernel<<<grid_for(n / 4), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>((float4*)out, (const float4*)x, n / 4);
   return int(cudaGetLastError());
 }
 

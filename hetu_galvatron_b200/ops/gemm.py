@@ -202,8 +202,3 @@ def grouped_wgrad(dy: torch.Tensor, x: torch.Tensor, row_start: torch.Tensor, ou
     return out
 
 
-def grouped_gemm_is_available() -> bool:
-    """The reference guards an optional ``grouped_gemm`` package (moe/grouped_gemm_util.py:6-22); the grouped expert
-    GEMM here is part of the kernel library, so it is available whenever that library is built (on CPU the experts
-    fall back to a per-expert loop)."""
-    return _lib.available()

@@ -97,11 +97,6 @@ class PipelineEngine:
             return self._run_gpipe(tokens, labels, loss_fns, mb_sizes, scale, forward_only)
         return self._run_1f1b(tokens, labels, loss_fns, mb_sizes, scale)
 
-    def _set_sync(self, is_last_mb: bool):
-        for u in self.model.units:
-            for w in getattr(u, "wrappers", [u]):
-                w.sync_this_backward = True
-
     def _finish_backward(self):
         for u in self.model.units:
             for w in getattr(u, "wrappers", [u]):

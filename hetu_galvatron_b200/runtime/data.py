@@ -41,33 +41,6 @@ class FakeCausalLMDataset(RandomTokenDataset):
     """Alias kept for the profiling paths (a fake dataset whose length covers the requested iterations)."""
 
 
-class RandomSeedDataset(Dataset):
-    """Wraps a dataset whose items draw random numbers (augmentation, masking): item ``i`` of epoch ``e`` is produced
-    under the seed ``base_seed + e + i`` for the ``torch``, ``random`` and ``numpy`` generators, whatever worker or rank
-    fetches it (galvatron/core/runtime/dataloader.py:162-181)."""
-
-    def __init__(self, dataset: Dataset, seed: int = 1234):
-        self.base_seed = self.curr_seed = int(seed)
-        self.dataset = dataset
-
-    def __len__(self):
-        return len(self.dataset)
-
-    def set_epoch(self, epoch: int):
-        self.curr_seed = self.base_seed + int(epoch)
-
-    def __getitem__(self, idx):
-        import random
-
-        import numpy as np
-
-        seed = int(idx) + self.curr_seed
-        torch.manual_seed(seed)
-        random.seed(seed)
-        np.random.seed(seed % (2 ** 32))
-        return self.dataset[idx]
-
-
 def get_train_valid_test_num_samples(args):
     """Samples each split must provide: ``(train, valid, test)`` from the iteration counts and the global batch
     (dataloader.py:299-318)."""

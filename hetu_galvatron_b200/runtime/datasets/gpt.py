@@ -100,11 +100,34 @@ class GPTDataset(torch.utils.data.Dataset):
         return hashlib.md5(json.dumps(desc, sort_keys=True).encode()).hexdigest()
 
     def _build_or_load(self):
+        """The three index arrays of this split.  With ``torch.distributed`` initialised, global rank 0 builds and
+        writes them (to temporary names, moved into place with ``os.replace`` so a reader never sees a partial file),
+        all ranks meet at a barrier, and the others then memory-map the finished files (the reference builds on rank 0
+        first as well: gpt_dataset.py:354, blended_megatron_dataset_builder.py:417)."""
+        import torch.distributed as dist
+
         cache = self.config.path_to_cache or os.path.join(os.path.dirname(self.prefix) or ".", "cache", "GPTDataset_indices")
         base = os.path.join(cache, self._key())
         paths = [base + "-%s.npy" % n for n in ("document_index", "sample_index", "shuffle_index")]
-        if all(os.path.exists(p) for p in paths):
+
+        def load():
             return tuple(np.load(p, allow_pickle=False, mmap_mode="r") for p in paths)
+
+        multi = dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1
+        builder = (not multi) or dist.get_rank() == 0
+        built = None
+        if builder and not all(os.path.exists(p) for p in paths):
+            built = self._build_indices()
+            os.makedirs(cache, exist_ok=True)
+            for p, a in zip(paths, built):
+                tmp = "%s.tmp.%d.npy" % (p[:-4], os.getpid())   # np.save appends ".npy" to other suffixes
+                np.save(tmp, a, allow_pickle=False)
+                os.replace(tmp, p)
+        if multi:
+            dist.barrier()
+        return built if built is not None else load()
+
+    def _build_indices(self):
         cfg = self.config
         extra = 1 if cfg.add_extra_token_to_sequence else 0
         sizes = self.indexed.sequence_lengths
@@ -121,9 +144,6 @@ class GPTDataset(torch.utils.data.Dataset):
         n = sample_index.shape[0] - 1
         shuffle_index = np.arange(n, dtype=np.uint32 if n < 2 ** 32 - 1 else np.int64)
         rng.shuffle(shuffle_index)
-        os.makedirs(cache, exist_ok=True)
-        for p, a in zip(paths, (doc_index, sample_index, shuffle_index)):
-            np.save(p, a, allow_pickle=False)
         return doc_index, sample_index, shuffle_index
 
     # ---- samples -------------------------------------------------------------------------------------------

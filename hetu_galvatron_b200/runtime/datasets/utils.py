@@ -18,13 +18,3 @@ def normalize(weights: Sequence[float]) -> List[float]:
     return _n(weights)
 
 
-def compile_helpers() -> str:
-    """Build (if stale) and return the path of the native dataset helpers (``csrc/host/dataset_helpers.cpp``).  The
-    reference shells out to ``make`` in its source tree; here the package's own build step does it."""
-    from ...csrc import build as _build
-
-    built = _build.build_host()
-    for path in built:
-        if "dataset_helpers" in str(path):
-            return str(path)
-    raise RuntimeError("the dataset helpers were not built: %s" % (built,))

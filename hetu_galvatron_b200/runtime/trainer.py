@@ -51,6 +51,35 @@ def _update_expert_bias(model, args):
             router.inner.update_expert_bias(rate, grp)
 
 
+def _device_status_code(device) -> int:
+    """The device status word of this process (0 = healthy; always 0 without a GPU).  Reading it clears it."""
+    if getattr(device, "type", "cpu") != "cuda":
+        return 0
+    from ..ops import _lib
+
+    return _lib.read_status(clear=True)
+
+
+def check_device_status(device) -> None:
+    """Raise ``KernelError`` on every rank if any kernel of any rank recorded a failure since the last check.
+
+    Every wait inside the kernels (mbarrier, tensor memory, peer flag) gives up after a bounded time, records a code
+    in a device status word and lets the kernel unwind with incomplete output.  The loop reads that word once per
+    iteration, right after the loss has been read (the device is idle then), and takes the maximum over the ranks,
+    so that a step computed from incomplete tiles is rejected everywhere before its parameters are kept or
+    checkpointed, and no rank is left waiting in a collective for one that raised."""
+    code = _device_status_code(device)
+    if dist.is_initialized() and dist.get_world_size() > 1:
+        t = torch.tensor([code], dtype=torch.int32, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        code = int(t.item())
+    if code != 0:
+        from ..ops import _lib
+
+        raise _lib.KernelError("device status word = %d (%s): the step used incomplete kernel output and is rejected"
+                               % (code, _lib._STATUS_NAMES.get(code, "?")))
+
+
 def get_optimizer_and_param_scheduler(model, args):
     t = args.train
     opt = ShardedAdamW(model.sharded_units, lr=t.lr, betas=(t.adam_beta1, t.adam_beta2), eps=t.adam_eps,
@@ -128,6 +157,7 @@ def train(args, max_iters: Optional[int] = None, profile_window=None):
         profiler.profile_memory(it, "After optimizer_step")
         lr = optimizer.param_groups[0]["lr"]
         loss_val = float(loss) if loss is not None else None
+        check_device_status(model.device)
         losses.append(loss_val)
         if loss_val is not None:
             from ..parallel import state as _state

@@ -4,18 +4,6 @@ from __future__ import annotations
 import os
 
 
-class ColorSet:
-    """ANSI colour codes for console messages (galvatron/utils/print_utils.py:6-12)."""
-
-    RED = "\033[31m"
-    GREEN = "\033[32m"
-    YELLOW = "\033[33m"
-    BLUE = "\033[34m"
-    MAGENTA = "\033[35m"
-    CYAN = "\033[36m"
-    RESET = "\033[0m"
-
-
 def is_rank0() -> bool:
     return int(os.environ.get("RANK", "0")) == 0
 

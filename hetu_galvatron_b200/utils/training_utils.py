@@ -60,23 +60,6 @@ def divide(numerator: int, denominator: int) -> int:
     return numerator // denominator
 
 
-def split_tensor_along_last_dim(tensor, num_partitions: int, contiguous_split_chunks: bool = False):
-    """Equal chunks of the last dimension (galvatron/core/runtime/tensor_parallel/utils.py:14-30)."""
-    chunks = tensor.split(divide(tensor.size(-1), num_partitions), dim=-1)
-    return tuple(c.contiguous() for c in chunks) if contiguous_split_chunks else chunks
-
-
-def init_method_normal(sigma: float):
-    """``N(0, sigma)`` initialiser (tensor_parallel/utils.py; the modules of this framework initialise through
-    ``models.modules.init_normal_sharded_``, which also makes shards independent of the parallel layout)."""
-    import torch
-
-    def init_(tensor):
-        return torch.nn.init.normal_(tensor, mean=0.0, std=sigma)
-
-    return init_
-
-
 class VocabUtility:
     """Vocabulary range ``[first, last)`` owned by a rank of a vocab-parallel group
     (galvatron/core/runtime/tensor_parallel/utils.py:32-82)."""

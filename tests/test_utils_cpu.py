@@ -88,23 +88,13 @@ def test_loss_average_without_process_group():
     assert torch.equal(out, torch.tensor([1.0, 3.0]))
 
 
-def test_small_helpers_of_the_reference_inventory():
-    from hetu_galvatron_b200.ops.gemm import grouped_gemm_is_available
-    from hetu_galvatron_b200.runtime.datasets.utils import Split, compile_helpers, normalize
-    from hetu_galvatron_b200.search.engine import ensure_log_dir
-    from hetu_galvatron_b200.utils.print_utils import ColorSet
-    from hetu_galvatron_b200.utils.training_utils import VocabUtility, divide, init_method_normal, split_tensor_along_last_dim
+def test_small_helpers():
+    from hetu_galvatron_b200.runtime.datasets.utils import Split, normalize
+    from hetu_galvatron_b200.utils.training_utils import VocabUtility, divide
 
-    a, b = split_tensor_along_last_dim(torch.arange(12).view(2, 6), 2, contiguous_split_chunks=True)
-    assert a.tolist() == [[0, 1, 2], [6, 7, 8]] and b.is_contiguous()
     assert divide(12, 4) == 3
     assert VocabUtility.vocab_range_from_global_vocab_size(128, 1, 4) == (32, 64)
-    w = init_method_normal(0.02)(torch.empty(256, 256))
-    assert abs(float(w.std()) - 0.02) < 2e-3
     assert [s.name for s in Split] == ["train", "valid", "test"] and normalize([1, 3]) == [0.25, 0.75]
-    assert compile_helpers().endswith(".so")
-    assert isinstance(grouped_gemm_is_available(), bool)
-    assert ColorSet.RED.startswith("\033[") and ColorSet.RESET == "\033[0m"
 
 
 def test_ensure_log_dir(tmp_path):
@@ -112,21 +102,3 @@ def test_ensure_log_dir(tmp_path):
 
     d = ensure_log_dir(str(tmp_path / "a" / "b"))
     assert (tmp_path / "a" / "b").is_dir() and d.endswith("b")
-
-
-def test_random_seed_dataset_is_reproducible_per_item_and_epoch():
-    from hetu_galvatron_b200.runtime.data import RandomSeedDataset
-
-    class Noisy(torch.utils.data.Dataset):
-        def __len__(self):
-            return 8
-
-        def __getitem__(self, i):
-            return torch.rand(3)
-
-    ds = RandomSeedDataset(Noisy(), seed=7)
-    a, b = ds[2], ds[5]
-    assert torch.equal(ds[2], a) and not torch.equal(a, b)      # same item, same numbers, whatever was drawn between
-    ds.set_epoch(1)
-    assert not torch.equal(ds[2], a) and torch.equal(ds[1], a) and torch.equal(ds[4], b)  # seed = base + epoch + index
-    assert len(ds) == 8
