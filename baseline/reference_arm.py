@@ -58,9 +58,11 @@ def _write_tokenizer(path: str, vocab_size: int) -> None:
 
 def overrides_for(a, world: int, tokenizer_dir: str):
     """Dotted overrides that turn the reference's ``scripts/train_dist.yaml`` into the benchmark's configuration."""
-    mbs = getattr(a, "micro_batch", 2)
-    chunks = max(1, PER_GPU_BATCH // mbs)
-    dp_type = getattr(a, "dp_type", "zero2") if world > 1 else "ddp"
+    # same micro-batching and data-parallel type as the other arm (bench.plan_knobs: the searched strategy's values)
+    sys.path.insert(0, os.path.dirname(HERE))
+    from bench import plan_knobs
+
+    _, _, chunks, dp_type = plan_knobs(world, a)
     layers = getattr(a, "layers", 0) or 32
     iters = a.warmup + a.steps + 1
     return [
@@ -209,6 +211,9 @@ def _train(a):
                 "h2d_bytes_per_step": int(B * (S + 1) * 8), "d2h_bytes_per_step": 4 * max(1, args.train.chunks)},
         "gpu_launches": 0,
         "peak_mem_gib": torch.cuda.max_memory_allocated() / 2 ** 30,
+        "peak_reserved_gib": torch.cuda.max_memory_reserved() / 2 ** 30,
+        # cudaMalloc failures that made the caching allocator free its cache and retry (each one stalls the device)
+        "alloc_retries": int(torch.cuda.memory_stats().get("num_alloc_retries", 0)),
         "final_loss": float(loss) if loss is not None else None,
     }
     if world > 1:

@@ -4,8 +4,12 @@
     python bench.py --impl reference ...                      (the unmodified reference, when installable)
 
 Weak scaling: 8 sequences per GPU (global batch 8*N -- 64 at N = 8, the configuration the baseline names).
-Synthetic uniform-random token ids, random-init N(0, 0.02) weights.  Per step: forward + backward of all
-micro-batches, gradient reduction, global-norm clipping, AdamW.  Two timed regions of K steps each:
+Synthetic uniform-random token ids (a fresh batch every step), random-init N(0, 0.02) weights.  The parallel plan is
+the one the strategy search wrote for N GPUs from the shipped B200 profiles
+(``hetu_galvatron_b200/cli/configs/galvatron_config_llama2-7b_1nodes_<N>gpus_per_node_160GB_bf16.json``, produced by
+``python -m hetu_galvatron_b200.cli.search_dist``); its predicted iteration time is printed beside the measured one.
+Per step: forward + backward of all micro-batches, gradient reduction, global-norm clipping, AdamW.  Two timed
+regions of K steps each:
 
   * ``value``      device-timed with CUDA events (inputs resident on the device), max over ranks;
   * ``e2e.value``  the same step through the public API with the step's inputs copied host->device from
@@ -89,6 +93,33 @@ class ClockSampler:
         return out
 
 
+def searched_strategy(n: int, a):
+    """The strategy JSON the search engine wrote for ``n`` GPUs (``--strategy PATH`` overrides, ``--strategy none``
+    falls back to plain flags).  Returns ``(dict or None, path or None)``."""
+    if a.strategy == "none":
+        return None, None
+    path = a.strategy or os.path.join(ROOT, "hetu_galvatron_b200", "cli", "configs",
+                                      "galvatron_config_llama2-7b_1nodes_%dgpus_per_node_160GB_bf16.json" % n)
+    if not os.path.exists(path):
+        return None, None
+    with open(path) as f:
+        return json.load(f), path
+
+
+def plan_knobs(n: int, a):
+    """``(strategy dict or None, path, chunks, dp_type)`` used by both arms, so that they run the same plan."""
+    cfg, path = searched_strategy(n, a)
+    if cfg is not None and a.micro_batch is None:
+        chunks = int(cfg["chunks"])
+        dp_type = cfg.get("default_dp_type", a.dp_type)
+    else:
+        chunks = PER_GPU_BATCH // (a.micro_batch or 2)
+        dp_type = a.dp_type
+    if a.layers or a.micro_batch is not None or a.checkpoint or (cfg is not None and cfg.get("global_bsz") != PER_GPU_BATCH * n):
+        cfg = None      # debugging overrides: plain flags with the strategy's micro-batching
+    return cfg, path, max(1, chunks), (dp_type if n > 1 else "ddp")
+
+
 def run_reference(a):
     """The unmodified reference through its own public path, when it can be imported on this image."""
     from baseline import reference_arm
@@ -116,15 +147,16 @@ def run_ours(a):
         print("warning: --gpus %d but WORLD_SIZE=%d" % (a.gpus, world), file=sys.stderr)
     n = world
     gbsz = PER_GPU_BATCH * n
-    mbs = a.micro_batch
-    chunks = PER_GPU_BATCH // mbs
-    dp_type = a.dp_type if n > 1 else "ddp"
+    strategy, strategy_path, chunks, dp_type = plan_knobs(n, a)
     model_cfg = dict(MODEL)
     if a.layers:
         model_cfg["num_layers"] = a.layers
+    parallel = dict(pp_deg=1, global_tp_deg=1, default_dp_type=dp_type, sdp=1 if dp_type == "zero3" else 0,
+                    mixed_precision="bf16", async_grad_reduce=True, global_checkpoint=int(a.checkpoint))
+    if strategy is not None:
+        parallel["galvatron_config_path"] = strategy      # JSON mode: the per-layer plan comes from the search
     args = GalvatronRuntimeArgs(
-        parallel=dict(pp_deg=1, global_tp_deg=1, default_dp_type=dp_type, sdp=1 if dp_type == "zero3" else 0,
-                      mixed_precision="bf16", async_grad_reduce=True, global_checkpoint=int(a.checkpoint)),
+        parallel=parallel,
         model=model_cfg,
         train=dict(seq_length=a.seq, global_batch_size=gbsz, chunks=chunks, lr=1e-4, adam_beta1=0.9, adam_beta2=0.95,
                    weight_decay=0.1, clip_grad=1.0, seed=1234),
@@ -135,20 +167,25 @@ def run_ours(a):
                        device=dev)
     B = model.local_batch_size()
     S = a.seq
+    chunks = model.plan.chunks
+    mbs = max(1, B // chunks)
     g = torch.Generator().manual_seed(1234 + rank)
-    n_host = 4
+    # a fresh batch of uniform-random tokens for every step of the run (warm-up, device-timed, end-to-end)
+    n_host = a.warmup + 2 * a.steps
     host = [torch.randint(0, MODEL["vocab_size"], (B, S + 1), generator=g).pin_memory() for _ in range(n_host)]
-    dev_batches = [h.to(dev) for h in host]
+    dev_batches = [h.to(dev) for h in host[:a.warmup + a.steps]]
+    cursor = [0]
 
     def step_device(i):
-        t = dev_batches[i % n_host]
+        t = dev_batches[cursor[0]]
+        cursor[0] += 1
         opt.zero_grad()
         loss = model.forward_backward(t[:, :-1], i, labels=t[:, 1:])
         opt.step()
         return loss
 
     def step_e2e(i):
-        t = host[i % n_host].to(dev, non_blocking=True)
+        t = host[a.warmup + a.steps + i].to(dev, non_blocking=True)
         opt.zero_grad()
         loss = model.forward_backward(t[:, :-1], i, labels=t[:, 1:])
         opt.step()
@@ -206,8 +243,9 @@ def run_ours(a):
         "impl": "ours",
         "config": {"model": "llama2-7b (32L h4096 32 heads ffn 11008 vocab 32000)" if not a.layers else
                    "llama2-7b-shaped, %d layers" % a.layers,
-                   "global_batch": gbsz, "seq_len": S, "micro_batch": mbs,
-                   "parallelism": "dp%d%s" % (n, "" if n == 1 else "-" + dp_type) + ("-ckpt" if a.checkpoint else ""),
+                   "global_batch": gbsz, "seq_len": S, "micro_batch": mbs, "chunks": chunks,
+                   "parallelism": model.plan.short_name() + ("-ckpt" if a.checkpoint else ""),
+                   "strategy": ("searched: " + os.path.relpath(strategy_path, ROOT)) if strategy is not None else "flags",
                    "l2": "working set (13.5 GB of bf16 weights + activations per step) is far larger than the 126 MB L2",
                    "optimizer": "AdamW fp32 master + global-norm clip inside the timed region"},
         "clocks": clocks,
@@ -216,8 +254,13 @@ def run_ours(a):
         "gpu_launches": launches,
         "model_tflops_per_gpu": flops / (ms / 1000.0) / 1e12 / n,
         "peak_mem_gib": peak_mem,
+        "peak_reserved_gib": torch.cuda.max_memory_reserved() / 2 ** 30,
+        "alloc_retries": int(torch.cuda.memory_stats().get("num_alloc_retries", 0)),
         "final_loss": loss_val,
     }
+    if strategy is not None and strategy.get("predicted_time_cost"):
+        pred = float(strategy["predicted_time_cost"]) * 1000.0
+        out.update(predicted_ms=pred, measured_ms=ms, pred_error=(pred - ms) / ms)
     if rank == 0:
         print(json.dumps(out))
     if n > 1:
@@ -232,7 +275,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq", type=int, default=SEQ)
-    ap.add_argument("--micro-batch", type=int, default=int(os.environ.get("HG_BENCH_MBS", "2")))
+    ap.add_argument("--micro-batch", type=int, default=(int(os.environ["HG_BENCH_MBS"]) if "HG_BENCH_MBS" in os.environ else None),
+                    help="sequences per micro-batch (default: what the searched strategy says)")
+    ap.add_argument("--strategy", default=os.environ.get("HG_BENCH_STRATEGY"),
+                    help="strategy JSON to run (default: the shipped searched plan for N GPUs; 'none' = plain flags)")
     ap.add_argument("--dp-type", default=os.environ.get("HG_BENCH_DP", "zero2"))
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result is not a headline number)")
     ap.add_argument("--checkpoint", type=int, default=0)

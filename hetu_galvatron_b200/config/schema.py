@@ -83,6 +83,11 @@ GalvatronParallelArgs = _build("GalvatronParallelArgs", {
     "use_ulysses": (bool, False),
     "reduce_in_fp32": (bool, False),
     "entropy_in_fp32": (bool, False),
+    # this framework's own kernels over NVLink peer memory in place of NCCL (null = on wherever they apply):
+    # fused_comm: all-gather->GEMM / GEMM->reduce-scatter, Ulysses and MoE all-to-all, resharding; fused_zero: ZeRO
+    # gradient reduce-scatter and AdamW + parameter all-gather.  A strategy JSON may carry both keys.
+    "fused_comm": (O[bool], None),
+    "fused_zero": (O[bool], None),
 }, doc="Parallelism and strategy (GLOBAL mode flags, or a searched strategy JSON).")
 
 GalvatronModelArgs = _build("GalvatronModelArgs", {

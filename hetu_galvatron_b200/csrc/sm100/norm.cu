@@ -278,7 +278,7 @@ int hg_norm_bwd(const void* dy, const void* h, const void* w, const void* rstd, 
 
 namespace {
 
-constexpr int kNoAllocMaxDevices = 64;
+constexpr int kNoAllocMaxDevices = HG_NORM_NOALLOC_MAX_DEVICES;
 constexpr size_t kNoAllocFloats = size_t(2) * HG_NORM_NOALLOC_PARTS * HG_NORM_NOALLOC_MAX_H;
 
 // Per-CTA partial sums: rows [0, PARTS) for the weight gradient, rows [PARTS, 2*PARTS) for LayerNorm's bias
@@ -294,7 +294,7 @@ int noalloc_scratch(float** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return -(1000 + int(e));
-  if (dev < 0 || dev >= kNoAllocMaxDevices) return -1;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) return HG_NORM_NOALLOC_BAD_DEVICE;
   std::lock_guard<std::mutex> lock(g_scratch_mu);
   if (g_scratch_addr[dev] == nullptr) {
     float* p = nullptr;
@@ -314,6 +314,8 @@ extern "C" int hg_norm_bwd_noalloc(const void* dy, const void* h, const void* w,
   if (rows <= 0) return 0;
   if ((H & 7) || H <= 0) return -1;
   if (H > HG_NORM_NOALLOC_MAX_H) return HG_NORM_NOALLOC_TOO_WIDE;
+  // a null required pointer would be dereferenced on the device: refuse before anything is launched
+  if (!dy || !h || !w || !rstd || !dx || !dw || (!rms && !mean)) return HG_NORM_NOALLOC_NULL_ARG;
   float* P = nullptr;
   if (int rc = noalloc_scratch(&P)) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);

@@ -27,13 +27,22 @@
 //   * Arguments other than the scratch are those of hg_norm_bwd: bf16 dy / h / w / dres / dx, fp32 rstd / mean /
 //     dw / db; `mean` and `db` are null for RMSNorm; `dres` may be null; `accumulate` != 0 adds into dw / db.
 //
-// Returns 0 on success, -1 for a bad shape, HG_NORM_NOALLOC_TOO_WIDE for H beyond the maximum,
-// -(1000 + cudaError) when the address lookup fails, else the cudaError of the launches.
+//   * dy, h, w, rstd, dx and dw must not be null, nor `mean` for LayerNorm (rms == 0): a null one is rejected with
+//     HG_NORM_NOALLOC_NULL_ARG before anything is launched (the kernel would read or write through it).
+//   * The per-device address cache has HG_NORM_NOALLOC_MAX_DEVICES entries: a call made with a current device
+//     index at or beyond that is rejected with HG_NORM_NOALLOC_BAD_DEVICE.
+//
+// Returns 0 on success, -1 for a bad shape (H not a positive multiple of 8), HG_NORM_NOALLOC_TOO_WIDE for H beyond
+// the maximum, HG_NORM_NOALLOC_NULL_ARG, HG_NORM_NOALLOC_BAD_DEVICE, -(1000 + cudaError) when the address lookup
+// fails, else the cudaError of the launches.
 #pragma once
 
 #define HG_NORM_NOALLOC_MAX_H 8192
 #define HG_NORM_NOALLOC_PARTS 148
 #define HG_NORM_NOALLOC_TOO_WIDE (-2)
+#define HG_NORM_NOALLOC_NULL_ARG (-3)
+#define HG_NORM_NOALLOC_BAD_DEVICE (-4)
+#define HG_NORM_NOALLOC_MAX_DEVICES 64
 
 #ifdef __cplusplus
 extern "C" {

@@ -134,8 +134,12 @@ def build_stage(spec: ModelSpec, plan: HybridPlan, groups: ModelGroups, device, 
 
                 unit = wrap_moe_units(mod, lp, ctx, plan, reduce_in_fp32, fused_zero)
             else:
+                tied_over_pp = spec.tied and plan.pp_deg > 1 and lp.kind in ("embedding", "lm_head")
+                # a weight tied across stages is summed over the two stages first (engine.sync_tied_embedding_grads):
+                # its unit accumulates the whole step in main_grad whatever the reduction mode of the other units
                 su = ShardedUnit(mod, lp.name, ctx.sdp, dp_size, lp.dp_type, reduce_in_fp32, tp=ctx.tp,
-                                 defer_sync=plan.async_grad_reduce, fused_zero=fused_zero)
+                                 defer_sync=plan.async_grad_reduce or tied_over_pp, fused_zero=fused_zero)
+                su.reduce_at_step_only = tied_over_pp
                 if lp.kind == "lm_head" and spec.tied and plan.pp_deg > 1:
                     su.count_in_norm = False  # the first stage's copy of the tied weight carries the norm
                 stage.sharded.append(su)

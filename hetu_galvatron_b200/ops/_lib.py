@@ -37,6 +37,9 @@ _SIGNATURES = {
     "hg_router_topk_fwd": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 5,
     "hg_router_topk_bwd": [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "hg_zero_reduce_scatter": [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p],
+    "hg_zero_reduce_scatter_capped": [c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_void_p],
+    "hg_zero_reduce_scatter_bf16wire": [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_void_p],
+    "hg_add_inplace_f32": [c_void_p, c_void_p, c_ll, c_void_p],
     "hg_zero_adamw_allgather": [c_void_p] * 5 + [c_int, c_ll, c_ll] + [ctypes.c_float] * 5 + [c_int, c_void_p, c_void_p, c_void_p],
     "hg_rope": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                 c_void_p],

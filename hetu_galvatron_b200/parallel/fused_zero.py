@@ -4,8 +4,10 @@
 A wrap unit that uses this path keeps its flat fp32 gradient buffer and its flat bf16 parameter buffer in symmetric
 memory (same size on every rank of the sharding group, mapped into every peer).  Per optimizer step:
 
-1. ``peer_barrier``          one-element all-reduce: every rank's backward has finished writing its gradients;
-2. ``reduce_scatter_peer``   this rank's shard = sum over ranks of their gradient buffers' slice (peer loads);
+1. ``peer_barrier``          one-element all-reduce: every rank's backward has finished writing its gradients
+                             (bf16 wire: has finished rounding them into the staging buffer);
+2. ``reduce_scatter_peer`` / ``reduce_scatter_staged``
+                             this rank's shard = sum over ranks of their buffers' slice (peer loads, fp32 or bf16);
 3. (global gradient norm -- a scalar all-reduce over all ranks, which also orders step 2 on every rank before 4)
 4. ``adamw_allgather_peer``  AdamW on the shard; bf16 results stored into every rank's parameter buffer;
 5. ``peer_barrier``          every rank's stores have landed before anyone's next forward.
@@ -66,10 +68,68 @@ def peer_barrier(pg, device):
     dist.all_reduce(t, group=pg)
 
 
-def reduce_scatter_peer(grads: SymmetricBuffer, me: int, shard_numel: int, out: torch.Tensor):
+def reduce_scatter_peer(grads: SymmetricBuffer, me: int, shard_numel: int, out: torch.Tensor, max_ctas: int = 0):
+    """fp32 on the wire: ``out = sum_r grads_r[me*S:(me+1)*S]`` by peer loads.  ``max_ctas`` caps the grid (0 = none)."""
     lib = _lib.load()
-    rc = lib.hg_zero_reduce_scatter(grads.ptr_array(), grads.t, me, shard_numel, out.data_ptr(), _lib.stream())
+    rc = lib.hg_zero_reduce_scatter_capped(grads.ptr_array(), grads.t, me, shard_numel, out.data_ptr(), int(max_ctas),
+                                           _lib.stream())
     _lib.check(rc, "hg_zero_reduce_scatter")
+    _lib.count_launch()
+    return out
+
+
+class StagingPair:
+    """Two symmetric buffers of the wire dtype, used alternately by consecutive reductions."""
+
+    def __init__(self, numel: int, dtype, device, pg):
+        self.bufs = [SymmetricBuffer(numel, dtype, device, pg) for _ in range(2)]
+        self.turn = 0
+
+    def next(self) -> SymmetricBuffer:
+        b = self.bufs[self.turn]
+        self.turn ^= 1
+        return b
+
+
+_STAGING: Dict[tuple, StagingPair] = {}
+
+
+def staging_buffers(numel: int, dtype, device, pg) -> StagingPair:
+    """The staging pair for units of ``numel`` elements over ``pg`` (one pair per size and group, shared by every unit
+    of that size): a unit rounds its gradient into the pair's next buffer right before its reduce-scatter
+    (``ShardedUnit._reduce_into`` explains why alternating needs no extra rendezvous)."""
+    key = (numel, dtype, str(device), id(pg))
+    pair = _STAGING.get(key)
+    if pair is None:
+        pair = _STAGING[key] = StagingPair(numel, dtype, device, pg)
+    return pair
+
+
+def round_into_staging(grad32: torch.Tensor, staging: SymmetricBuffer, me: int, shard_numel: int):
+    """bf16 copy of every slice of the fp32 gradient buffer except this rank's own (which nobody reads remotely)."""
+    from ..ops.optim import cast_bf16
+
+    lo, hi = me * shard_numel, (me + 1) * shard_numel
+    if lo > 0:
+        cast_bf16(grad32[:lo], staging.tensor[:lo])
+    if hi < grad32.numel():
+        cast_bf16(grad32[hi:], staging.tensor[hi:])
+
+
+def reduce_scatter_staged(staging: SymmetricBuffer, own32: torch.Tensor, me: int, shard_numel: int, out: torch.Tensor,
+                          accumulate: bool = False, max_ctas: int = 0):
+    """bf16 on the wire: ``out (+)= own32[slice] + sum_{r != me} staging_r[slice]`` (fp32 sum in rank order)."""
+    lib = _lib.load()
+    rc = lib.hg_zero_reduce_scatter_bf16wire(staging.ptr_array(), own32.data_ptr(), staging.t, me, shard_numel,
+                                             out.data_ptr(), int(bool(accumulate)), int(max_ctas), _lib.stream())
+    _lib.check(rc, "hg_zero_reduce_scatter_bf16wire")
+    _lib.count_launch()
+    return out
+
+
+def add_inplace(out: torch.Tensor, x: torch.Tensor):
+    lib = _lib.load()
+    _lib.check(lib.hg_add_inplace_f32(out.data_ptr(), x.data_ptr(), out.numel(), _lib.stream()), "hg_add_inplace_f32")
     _lib.count_launch()
     return out
 

@@ -17,6 +17,8 @@ from typing import Callable, List, Optional, Sequence
 import torch
 import torch.distributed as dist
 
+from .zero import set_last_microbatch
+
 
 def chunk_batch(t: Optional[torch.Tensor], chunks: int) -> List[Optional[torch.Tensor]]:
     """Split along the batch dimension into at most ``chunks`` micro-batches (the last may be smaller)."""
@@ -110,6 +112,7 @@ class PipelineEngine:
             if i == 0 and self.after_forward is not None:
                 self.after_forward()
             if not forward_only:
+                set_last_microbatch(i == len(tokens) - 1)   # deferred units launch their reduction in this backward
                 loss.backward()
                 self._finish_backward()
             losses.append(loss.detach())
@@ -141,6 +144,7 @@ class PipelineEngine:
             self.p2p.drain()
             return losses
         for i in range(chunks):
+            set_last_microbatch(i == chunks - 1)
             self._backward_step(inputs[i], outputs[i], mb_sizes[i])
             inputs[i] = outputs[i] = None
         self.p2p.drain()
@@ -179,8 +183,12 @@ class PipelineEngine:
             inputs.append(x)
             outputs.append(out)
 
+        done = [0]
+
         def bwd():
             x, out = inputs.pop(0), outputs.pop(0)
+            done[0] += 1
+            set_last_microbatch(done[0] == chunks)
             self._backward_step(x, out, None)
 
         for i in range(warm):

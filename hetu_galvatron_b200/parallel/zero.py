@@ -20,9 +20,18 @@ zero3      sharded; all-gathered before the        reduce-scatter -> shard
            backward, storage released in between
 =========  =====================================  ==========================================
 
-With ``defer_sync`` (the reference's ``async_grad_reduce=True``) the reduction runs once, after the last
-micro-batch; otherwise after every micro-batch's backward of the unit.  Gradients are *summed* over the
+With ``defer_sync`` (the reference's ``async_grad_reduce=True``) the reduction runs once per step: it is launched
+from the unit's post-backward hook of the *last* micro-batch, on a side stream, so that it overlaps the backward
+of the layers below (the reference does the same through FSDP's post-backward hook:
+pipeline/sp_grad_reduce.py:48-132).  Otherwise it runs after every micro-batch's backward of the unit, also on the
+side stream, and the unit's unsharded fp32 gradient buffer is *transient*: it comes from a small pool
+(:class:`GradPool`) shared by all units of the same size and goes back once its reduce-scatter has run, so a rank
+holds ``pool x layer`` unsharded gradients plus its own shards instead of a whole model's worth (FSDP's
+``SHARD_GRAD_OP`` / ``FULL_SHARD`` memory behaviour, parallel.py:119-152).  Gradients are *summed* over the
 sequence/context-parallel part of the group and *averaged* over the data-parallel replicas.
+
+On the wire the gradients travel in the working precision (bf16) unless ``reduce_in_fp32`` is set, as in the
+reference (parallel.py:128-131); they are accumulated over micro-batches and summed over ranks in fp32 either way.
 
 This replaces torch FSDP as used by the reference (galvatron/core/runtime/parallel.py:100-210,
 pipeline/grad_reduce.py:48-149, pipeline/sp_grad_reduce.py:48-132) so that the collectives can be fused
@@ -30,6 +39,7 @@ with our own kernels.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import torch
@@ -41,6 +51,86 @@ from .. import ops
 from . import mappings as mp
 
 ALIGN = 64  # elements; keeps every parameter 128-byte aligned inside the flat buffers
+POOL_BUFFERS = 3  # unsharded gradient buffers per (size, group) in the per-micro-batch reduction mode
+
+
+class _ReduceState:
+    """Process-wide state of the overlapped gradient reduction."""
+
+    def __init__(self):
+        self.last_microbatch = True       # set by the pipeline engine before each backward
+        self.overlap = os.environ.get("HG_OVERLAP_REDUCE", "1") == "1"
+        self.max_ctas = int(os.environ.get("HG_REDUCE_CTAS", "32"))   # grid cap of a reduction that runs beside GEMMs
+        self._streams: Dict[int, "torch.cuda.Stream"] = {}
+        self.used = False                 # something was queued on a side stream since the last join
+
+    def stream(self, device):
+        if device.type != "cuda" or not self.overlap:
+            return None
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        st = self._streams.get(idx)
+        if st is None:
+            st = self._streams[idx] = torch.cuda.Stream(device=device)
+        return st
+
+    def join(self, device):
+        """The current stream waits for everything queued on the reduction stream."""
+        if device.type == "cuda" and self.used:
+            idx = device.index if device.index is not None else torch.cuda.current_device()
+            st = self._streams.get(idx)
+            if st is not None:
+                torch.cuda.current_stream(device).wait_stream(st)
+            self.used = False
+
+
+REDUCE = _ReduceState()
+_WIRE_SCRATCH: Dict[tuple, torch.Tensor] = {}
+
+
+def set_last_microbatch(flag: bool):
+    """Called by the schedule before a micro-batch's backward: deferred units reduce during the last one."""
+    REDUCE.last_microbatch = bool(flag)
+
+
+class GradPool:
+    """Unsharded fp32 gradient buffers shared by the units of one size and sharding group.
+
+    A unit takes the next buffer (round-robin) when its backward starts and hands it back when its reduce-scatter
+    has been queued; ``free[k]`` is the event after which buffer ``k`` may be overwritten (on the fused fp32-wire
+    path that is after a rendezvous of the group, because peers read the buffer)."""
+
+    _pools: Dict[tuple, "GradPool"] = {}
+
+    def __init__(self, numel: int, device, pg, symmetric: bool):
+        self.bufs, self.sym = [], []
+        for _ in range(POOL_BUFFERS):
+            if symmetric:
+                from . import fused_zero as fz
+
+                sb = fz.SymmetricBuffer(numel, torch.float32, device, pg)
+                self.sym.append(sb)
+                self.bufs.append(sb.tensor)
+            else:
+                self.sym.append(None)
+                self.bufs.append(torch.zeros(numel, dtype=torch.float32, device=device))
+        self.free: List[Optional[object]] = [None] * POOL_BUFFERS
+        self.next = 0
+
+    @classmethod
+    def get(cls, numel: int, device, pg, symmetric: bool) -> "GradPool":
+        key = (numel, str(device), id(pg), symmetric)
+        if key not in cls._pools:
+            cls._pools[key] = GradPool(numel, device, pg, symmetric)
+        return cls._pools[key]
+
+    def acquire(self) -> int:
+        k = self.next
+        self.next = (k + 1) % len(self.bufs)
+        ev = self.free[k]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            self.free[k] = None
+        return k
 
 
 def _group_info(g):
@@ -51,7 +141,7 @@ def _group_info(g):
 
 class ShardedUnit:
     def __init__(self, module: nn.Module, name: str, sdp, dp_size: int, dp_type: str = "ddp",
-                 reduce_in_fp32: bool = True, tp=None, defer_sync: bool = True, grad_sum_group=None,
+                 reduce_in_fp32: bool = False, tp=None, defer_sync: bool = True, grad_sum_group=None,
                  fused_zero: bool = False):
         self.module, self.name = module, name
         self.pg, self.n, self.rank = _group_info(sdp)
@@ -82,19 +172,27 @@ class ShardedUnit:
         self.shard_numel = self.numel // self.n
         self.device = params[0].device if params else torch.device("cpu")
         self.dtype = params[0].dtype if params else torch.float32
+        # dtype in which gradients cross the links; accumulation and the sum over ranks are fp32 regardless
+        self.wire_dtype = torch.float32 if (reduce_in_fp32 or self.dtype == torch.float32) else self.dtype
         self.flat: Optional[torch.Tensor] = None
         self.main_grad: Optional[torch.Tensor] = None
         self.gathered = True
         self.step_count = 0
         self._reduced = False
         self._bwd_pending = False
+        self._acc_used = False
         self.count_in_norm = True  # False for the second copy of a weight tied across pipeline stages
+        # a weight tied across pipeline stages is summed over the two stages before the sharding group reduces it:
+        # its unit keeps the whole-step gradient and reduces at the optimizer step
+        self.reduce_at_step_only = False
         # own reduce-scatter / AdamW+all-gather kernels over peer memory instead of NCCL (parallel/fused_zero.py)
         self.fused = False
-        if fused_zero and params and self.dp_type in ("zero2", "zero3"):
+        if fused_zero and params and self.dp_type in ("zero2", "zero3") and self.dtype == torch.bfloat16:
             from . import fused_zero as fz
 
             self.fused = fz.available(self.device, self.n)
+        # per-micro-batch reduction of a sharded unit: the unsharded gradient buffer is borrowed from a pool
+        self.pooled = bool(params) and not defer_sync and self.dp_type in ("zero2", "zero3")
         if params:
             self._materialise()
 
@@ -102,30 +200,45 @@ class ShardedUnit:
     def _materialise(self):
         dev = self.device
         self._sym_grad = self._sym_flat = None
+        self._pool: Optional[GradPool] = None
+        self._pool_slot = -1
+        self._staging = None            # bf16 wire: buffer pair the gradient is rounded into before it is reduced
+        peers_read_fp32 = self.fused and self.wire_dtype == torch.float32
         if self.fused:
             from . import fused_zero as fz
 
-            # peers read the gradient buffer and (ZeRO-2) write the parameter buffer: both symmetric
-            self._sym_grad = fz.SymmetricBuffer(self.numel, torch.float32, dev, self.pg)
-            if self.dp_type == "zero2" and self.dtype == torch.bfloat16:
-                self._sym_flat = fz.SymmetricBuffer(self.numel, self.dtype, dev, self.pg)
+            if self.dp_type == "zero2":
+                self._sym_flat = fz.SymmetricBuffer(self.numel, self.dtype, dev, self.pg)   # peers write parameters
+            if self.wire_dtype != torch.float32:
+                self._staging = fz.staging_buffers(self.numel, self.wire_dtype, dev, self.pg)
         self.flat = self._sym_flat.tensor if self._sym_flat is not None else torch.zeros(self.numel, dtype=self.dtype, device=dev)
         for p, o in zip(self.params, self.offsets):
             self.flat[o:o + p.numel()].copy_(p.data.reshape(-1))
         self._bind_params()
-        self.main_grad = self._sym_grad.tensor if self._sym_grad is not None else \
-            torch.zeros(self.numel, dtype=torch.float32, device=dev)
-        for p, o in zip(self.params, self.offsets):
-            p.main_grad = self.main_grad[o:o + p.numel()].view(p.shape)
-            p.mg_fresh = True
+        if self.pooled:
+            self._pool = GradPool.get(self.numel, dev, self.pg, peers_read_fp32)
+            self._bind_grads(self._pool.bufs[0])       # placeholder views until the first backward borrows a buffer
+            self.main_grad = None
+        else:
+            if peers_read_fp32:
+                from . import fused_zero as fz
+
+                self._sym_grad = fz.SymmetricBuffer(self.numel, torch.float32, dev, self.pg)   # peers read gradients
+                self.main_grad = self._sym_grad.tensor
+            else:
+                self.main_grad = torch.zeros(self.numel, dtype=torch.float32, device=dev)
+            self._bind_grads(self.main_grad)
         lo, hi = self.shard_range()
         self.master = self.flat[lo:hi].float().clone()
         self.exp_avg = torch.zeros_like(self.master)
         self.exp_avg_sq = torch.zeros_like(self.master)
-        self.grad_shard = None  # fp32 view / buffer holding this rank's reduced gradient
+        # this rank's reduced gradient of the step (fp32): the whole buffer for ddp, the shard otherwise
+        self.grad_shard = None
+        self._red_buf = None if self.dp_type == "ddp" and self.defer_sync else \
+            torch.zeros(hi - lo, dtype=torch.float32, device=dev)
         self._sym_shard = None
         if self.dp_type == "zero3":
-            if self.fused and self.dtype == torch.bfloat16:
+            if self.fused:
                 # the bf16 shard is what peers pull from when they re-assemble the unit's parameters: it changes only
                 # in the optimizer step, which ends with a rendezvous, so gathers need no synchronisation of their own
                 from . import fused_zero as fz
@@ -144,23 +257,15 @@ class ShardedUnit:
         for p, o in zip(self.params, self.offsets):
             p.data = self.flat[o:o + p.numel()].view(p.shape)
 
+    def _bind_grads(self, buf: torch.Tensor):
+        for p, o in zip(self.params, self.offsets):
+            p.main_grad = buf[o:o + p.numel()].view(p.shape)
+            p.mg_fresh = True
+
     def shard_range(self):
         if self.dp_type == "ddp":
             return 0, self.numel
         return self.rank * self.shard_numel, (self.rank + 1) * self.shard_numel
-
-    def sync_params_from(self, src_rank_in_group: int = 0):
-        """Broadcast the working parameters from one rank of the sdp group (after a non-deterministic
-        initialisation) and rebuild the master copy."""
-        if self.n > 1:
-            was = self.gathered
-            if self.dp_type == "zero3" and not was:
-                self.flat.untyped_storage().resize_(self.numel * self.flat.element_size())
-            if self.dp_type != "zero3" or was:
-                src = dist.get_global_rank(self.pg, src_rank_in_group)
-                dist.broadcast(self.flat, src=src, group=self.pg)
-                lo, hi = self.shard_range()
-                self.master.copy_(self.flat[lo:hi])
 
     def reload_master(self):
         """Re-derive master weights / bf16 shard from ``flat`` (after a checkpoint load into the params)."""
@@ -209,9 +314,15 @@ class ShardedUnit:
         self._reduced = False
         self._acc_used = False
 
+    def begin_backward(self):
+        """Before the unit's backward of a micro-batch: a pooled unit borrows its gradient buffer."""
+        if self.pooled and self.main_grad is None:
+            self._pool_slot = self._pool.acquire()
+            self.main_grad = self._pool.bufs[self._pool_slot]
+            self._bind_grads(self.main_grad)
+
     def _finish_accumulation(self):
-        """Fold stray ``.grad`` tensors (bias / generic autograd paths) into ``main_grad`` and zero what
-        received nothing."""
+        """Fold stray ``.grad`` tensors (bias / generic autograd paths) into ``main_grad``."""
         for p in self.params:
             if p.grad is not None:
                 if getattr(p, "mg_fresh", False):
@@ -224,6 +335,7 @@ class ShardedUnit:
     def prepare_grads(self):
         """Make ``main_grad`` complete for the micro-batches seen so far: fold autograd ``.grad`` tensors in
         and zero the parameters that received nothing."""
+        self.begin_backward()
         self._finish_accumulation()
         for p in self.params:
             if getattr(p, "mg_fresh", False):  # received nothing since the last reset
@@ -237,65 +349,122 @@ class ShardedUnit:
 
             fz.peer_barrier(self.pg, self.device)
 
-    def _reduce_now(self, presynced: bool = False) -> torch.Tensor:
-        """Sum the current ``main_grad`` over the sdp group; returns the buffer holding this rank's part."""
-        self.prepare_grads()
+    def _wire_scratch(self, numel: int) -> torch.Tensor:
+        """A reusable buffer of the wire dtype (NCCL / gloo path; all its uses are ordered on one stream)."""
+        key = (numel, self.wire_dtype, str(self.device))
+        buf = _WIRE_SCRATCH.get(key)
+        if buf is None:
+            buf = _WIRE_SCRATCH[key] = torch.empty(numel, dtype=self.wire_dtype, device=self.device)
+        return buf
+
+    def _reduce_into(self, out: torch.Tensor, accumulate: bool, presynced: bool = False, capped: bool = False):
+        """``out (+)= sum over the sharding group of main_grad`` (this rank's slice for zero2 / zero3).  Runs on the
+        current stream; ``main_grad`` must be complete (``prepare_grads``)."""
+        mg = self.main_grad
         if self.tp_n > 1 and self.replicated_numel > 0:
             # norm weights / replicated biases saw only this rank's S/t tokens: sum over the tp group
-            dist.all_reduce(self.main_grad[: self.replicated_numel], group=self.tp_pg)
+            dist.all_reduce(mg[: self.replicated_numel], group=self.tp_pg)
         if self.n == 1:
-            return self.main_grad
+            if out is not mg:
+                out.add_(mg) if accumulate else out.copy_(mg)
+            return
+        lowp = self.wire_dtype != torch.float32
+        max_ctas = REDUCE.max_ctas if capped else 0
         if self.dp_type == "ddp":
-            dist.all_reduce(self.main_grad, group=self.pg)
-            return self.main_grad
-        if getattr(self, "_rs_out", None) is None:
-            self._rs_out = torch.empty(self.shard_numel, dtype=torch.float32, device=self.device)
+            if lowp:
+                w = self._wire_scratch(self.numel)
+                w.copy_(mg)
+                dist.all_reduce(w, group=self.pg)
+                red = w
+            else:
+                dist.all_reduce(mg, group=self.pg)
+                red = mg
+            if out is not red:
+                out.add_(red) if accumulate else out.copy_(red)
+            return
+        lo, hi = self.shard_range()
         if self.fused:
             from . import fused_zero as fz
 
-            if not presynced:
-                self.sync_peers()        # every rank's gradients are complete
-            fz.reduce_scatter_peer(self._sym_grad, self.rank, self.shard_numel, self._rs_out)
-            if not self.defer_sync:
-                self.sync_peers()        # main_grad is reused by the next micro-batch right away
-            return self._rs_out
-        if self.main_grad.device.type == "cpu":
-            tmp = self.main_grad.clone()
+            if lowp:
+                st = self._staging.next()
+                fz.round_into_staging(mg, st, self.rank, self.shard_numel)
+                self.sync_peers()        # every rank's staged gradients are complete
+                fz.reduce_scatter_staged(st, mg, self.rank, self.shard_numel, out, accumulate, max_ctas)
+                # no rendezvous afterwards: the staging buffers alternate, and a rank rounds into a buffer again only
+                # after the rendezvous of the unit in between, which every peer enters after its reads of this one
+            else:
+                if not presynced:
+                    self.sync_peers()    # every rank's gradients are complete
+                src = self._sym_grad if self._pool is None else self._pool.sym[self._pool_slot]
+                if accumulate:
+                    tmp = self._wire_scratch(self.shard_numel)
+                    fz.reduce_scatter_peer(src, self.rank, self.shard_numel, tmp, max_ctas)
+                    fz.add_inplace(out, tmp)
+                else:
+                    fz.reduce_scatter_peer(src, self.rank, self.shard_numel, out, max_ctas)
+                if not self.defer_sync:
+                    self.sync_peers()    # peers have finished reading before the buffer is written again
+            return
+        if mg.device.type == "cpu":
+            tmp = mg.to(self.wire_dtype) if lowp else mg.clone()
             dist.all_reduce(tmp, group=self.pg)
-            self._rs_out.copy_(tmp[self.rank * self.shard_numel:(self.rank + 1) * self.shard_numel])
+            red = tmp[lo:hi]
         else:
-            dist.reduce_scatter_tensor(self._rs_out, self.main_grad, group=self.pg)
-        return self._rs_out
+            src = mg
+            if lowp:
+                src = self._wire_scratch(self.numel)
+                src.copy_(mg)
+            red = self._wire_scratch(self.shard_numel) if (accumulate or lowp) else out
+            dist.reduce_scatter_tensor(red, src, group=self.pg)
+        if red is not out:
+            out.add_(red) if accumulate else out.copy_(red)
+
+    def _target(self) -> torch.Tensor:
+        return self.main_grad if self._red_buf is None else self._red_buf
+
+    def _launch_reduce(self, accumulate: bool, presynced: bool = False, overlap: bool = True):
+        """Queue the reduction of the current ``main_grad``: on the side stream (ordered after everything queued so
+        far on the current one) when overlap is on, else in place.  A pooled unit hands its buffer back."""
+        self.prepare_grads()          # on the current stream: autograd's tensors live there
+        has_comm = self.n > 1 or (self.tp_n > 1 and self.replicated_numel > 0)
+        side = REDUCE.stream(self.device) if (overlap and has_comm) else None
+        out = self._target()
+        if side is None:
+            self._reduce_into(out, accumulate, presynced)
+            if self.pooled:
+                self.main_grad = None
+            return
+        side.wait_stream(torch.cuda.current_stream(self.device))
+        with torch.cuda.stream(side):
+            self._reduce_into(out, accumulate, presynced, capped=True)
+            if self.pooled:
+                ev = torch.cuda.Event()
+                ev.record(side)
+                self._pool.free[self._pool_slot] = ev
+                self.main_grad = None
+        REDUCE.used = True
+
+    def on_backward_done(self):
+        """Post-backward hook of one micro-batch of this unit."""
+        if self._reduced or self.reduce_at_step_only:
+            return
+        if not self.defer_sync:
+            self._launch_reduce(accumulate=self._acc_used)
+            self._acc_used = True
+        elif REDUCE.last_microbatch and REDUCE.overlap and self.device.type == "cuda":
+            self._launch_reduce(accumulate=False)
+            self.grad_shard = self._target()
+            self._reduced = True
 
     def reduce_grads(self, final: bool = True, presynced: bool = False):
-        """Gradient synchronisation.  Deferred mode: one reduction at the end of the step.  Immediate mode:
-        every micro-batch's gradient is reduced right after the unit's backward and added to the running
-        shard, and ``main_grad`` starts fresh for the next micro-batch."""
-        if self._reduced:
+        """Whatever of the step's gradient synchronisation has not been launched from the backward hooks."""
+        if self._reduced or not final:
             return
-        if self.defer_sync:
-            if final:
-                self.grad_shard = self._reduce_now(presynced)
-                self._reduced = True
-            return
-        if not final:
-            red = self._reduce_now()
-            if getattr(self, "_acc", None) is None:
-                self._acc = torch.zeros_like(red)
-                self._acc_used = False
-            if self._acc_used:
-                self._acc.add_(red)
-            else:
-                self._acc.copy_(red)
-                self._acc_used = True
-            for p in self.params:
-                p.mg_fresh = True
-        else:
-            if getattr(self, "_acc", None) is None or not self._acc_used:
-                self.grad_shard = self._reduce_now()
-            else:
-                self.grad_shard = self._acc
-            self._reduced = True
+        if self.defer_sync or not self._acc_used:
+            self._launch_reduce(accumulate=False, presynced=presynced, overlap=False)
+        self.grad_shard = self._target()
+        self._reduced = True
 
     def grad_sumsq(self, out: torch.Tensor):
         """Add this rank's share of the squared gradient norm to ``out[0]`` so that a SUM over all ranks
@@ -394,13 +563,14 @@ class UnitWrapper(nn.Module):
     def __init__(self, inner: nn.Module, unit: ShardedUnit, checkpoint: bool = False):
         super().__init__()
         self.inner, self.unit, self.checkpoint = inner, unit, checkpoint
-        self.sync_this_backward = True
         self.extra_units: List[ShardedUnit] = []  # units owning parameters this module borrows (tied weights)
 
     def _pre_backward(self):
         self.unit.gather()
         for e in self.extra_units:
             e.gather()
+        if not self.unit._bwd_pending:
+            self.unit.begin_backward()
         self.unit._bwd_pending = True
 
     def _post_backward(self):
@@ -411,8 +581,7 @@ class UnitWrapper(nn.Module):
         u.release()
         for e in self.extra_units:
             e.release()
-        if self.sync_this_backward and not u.defer_sync:
-            u.reduce_grads(final=False)
+        u.on_backward_done()
 
     def finish_backward(self):
         """Called by the engine after the whole backward: covers units whose inputs carry no gradient."""

@@ -136,6 +136,8 @@ class GalvatronModel:
         for lp, u in zip(self.model.plans, self.model.units):
             if lp.kind in ("embedding", "lm_head"):
                 w = u.inner.embed_tokens.weight if lp.kind == "embedding" else u.inner.lm_head.weight
+                # these units keep the whole step's gradient in main_grad and reduce over their sharding group only
+                # in optimizer.step() (ShardedUnit.reduce_at_step_only), i.e. after this sum over the two stages
                 w._hg_unit.prepare_grads()
                 dist.all_reduce(w.main_grad, group=g.group)
 
@@ -167,12 +169,19 @@ def build_model(args, device=None, full_init: bool = False, fused_comm: Optional
     shard_groups = [(c.tp if c.tp_size >= c.sp_size else c.sp) for c in ctxs]
     set_seed_with_group([g for g in shard_groups if g is not None and g.size > 1], None, args.train.seed or 1234,
                         cuda=device.type == "cuda")
+    # own kernels over peer memory instead of NCCL: argument > configuration field > environment > on (CUDA only)
     if fused_comm is None:
-        fused_comm = bool(int(os.environ.get("HG_FUSED_COMM", "0"))) and device.type == "cuda"
+        fused_comm = getattr(args.parallel, "fused_comm", None)
+    if fused_comm is None:
+        fused_comm = bool(int(os.environ.get("HG_FUSED_COMM", "1")))
     if fused_zero is None:
-        fused_zero = bool(int(os.environ.get("HG_FUSED_ZERO", "1"))) and device.type == "cuda"
+        fused_zero = getattr(args.parallel, "fused_zero", None)
+    if fused_zero is None:
+        fused_zero = bool(int(os.environ.get("HG_FUSED_ZERO", "1")))
+    fused_comm = bool(fused_comm) and device.type == "cuda" and spec.dtype == torch.bfloat16
+    fused_zero = bool(fused_zero) and device.type == "cuda"
     stage = build_stage(spec, plan, groups, device, seed=args.train.seed or 1234, full_init=full_init,
-                        fused_comm=fused_comm, reduce_in_fp32=args.parallel.reduce_in_fp32 or True,
+                        fused_comm=fused_comm, reduce_in_fp32=bool(args.parallel.reduce_in_fp32),
                         fused_zero=fused_zero)
     if rank == 0 and os.environ.get("HG_QUIET", "0") != "1":
         print("================ hybrid-parallel plan (%s) ================" % plan.source)

@@ -47,9 +47,21 @@ class ShardedAdamW:
                 u.sync_peers()
 
     def reduce_gradients(self):
-        self._sync_fused_groups()          # every rank's backward has written its gradients
-        for u in self.units:
-            u.reduce_grads(final=True, presynced=True)
+        """Finish the step's gradient synchronisation: units whose reduction was launched from their backward hook
+        (the usual case) only need the reduction stream joined; the rest (forward-only units, weights tied across
+        stages, CPU runs) reduce here."""
+        from ..parallel.zero import REDUCE
+
+        pending = [u for u in self.units if not u._reduced]
+        if any(getattr(u, "fused", False) and u.defer_sync and u.wire_dtype == torch.float32 for u in pending):
+            self._sync_fused_groups()      # every rank's backward has written its gradients
+            presynced = True
+        else:
+            presynced = False
+        for u in pending:
+            u.reduce_grads(final=True, presynced=presynced)
+        if self.units:
+            REDUCE.join(self.units[0].device)
 
     def compute_grad_norm(self):
         self._sumsq.zero_()
@@ -77,6 +89,12 @@ class ShardedAdamW:
 
     def load_state_dict(self, sd: Dict):
         self.param_groups[0].update({k: v for k, v in sd["param_groups"][0].items()})
+        missing = [u.name for u in self.units if u.name not in sd["state"]]
         for u in self.units:
             if u.name in sd["state"]:
                 u.load_optimizer_state(sd["state"][u.name])
+        if missing:
+            import warnings
+
+            warnings.warn("optimizer state has no entry for %d unit(s) (%s%s): they keep freshly initialised moments"
+                          % (len(missing), ", ".join(missing[:4]), ", ..." if len(missing) > 4 else ""))

@@ -90,6 +90,33 @@ class HybridPlan:
             "global_batch_size": self.global_batch_size,
         }
 
+    def short_name(self) -> str:
+        """One-line name of the plan, e.g. ``dp8-zero2``, ``pp2-tp2-dp2-zero3-ckpt16`` (decoder layers only; a
+        mixed plan lists each distinct layer strategy with its layer count)."""
+        kinds: Dict[str, int] = {}
+        for l in self.layers:
+            if l.kind not in ("decoder", "moe_decoder"):
+                continue
+            parts = []
+            if l.tp > 1:
+                parts.append("tp%d" % l.tp)
+            if l.sp > 1:
+                parts.append("sp%d" % l.sp)
+            if l.cp > 1:
+                parts.append("cp%d" % l.cp)
+            if l.kind == "moe_decoder" and l.ep > 1:
+                parts.append("ep%d" % l.ep)
+            d = self.dp_size(l)
+            parts.append("dp%d" % d)
+            if d > 1 or l.dp_type != "ddp":
+                parts.append(l.dp_type if d > 1 else "ddp")
+            if l.checkpoint:
+                parts.append("ckpt")
+            key = "-".join(p for p in parts if p != "ddp")
+            kinds[key] = kinds.get(key, 0) + 1
+        body = "+".join(k if len(kinds) == 1 else "%sx%d" % (k, c) for k, c in kinds.items())
+        return ("pp%d-" % self.pp_deg if self.pp_deg > 1 else "") + body
+
     def describe(self) -> str:
         lines = ["pp=%d  gbsz=%d  chunks=%d  pipeline=%s  default_dp=%s  vocab(tp=%d sp=%d cp=%d sdp=%d)" % (
             self.pp_deg, self.global_batch_size, self.chunks, self.pipeline_type, self.default_dp_type, self.vocab_tp,
@@ -149,6 +176,9 @@ def build_plan(args, world_size: int) -> HybridPlan:
         par.vocab_sdp = vocab_sdp
         train.global_batch_size, train.chunks = gbsz, chunks
         par.pp_deg, par.vocab_tp, par.vocab_sp, par.vocab_cp = pp, vtp, vsp, vcp
+        for key in ("fused_comm", "fused_zero", "async_grad_reduce", "reduce_in_fp32"):   # optional runtime switches
+            if key in cfg and cfg[key] is not None:
+                setattr(par, key, bool(cfg[key]))
     if division is None:
         division = pp_division_even(L, pp)
     if sum(division) != L or len(division) != pp:

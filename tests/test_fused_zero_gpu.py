@@ -48,6 +48,20 @@ def kernels_vs_nccl(cfg):
         fz.reduce_scatter_peer(grads, rank, S, got)
         fz.peer_barrier(dist.group.WORLD, dev)
         out["rs_%d" % rep] = float((got - ref).abs().max() / ref.abs().max())
+        # bf16 on the wire: peers' slices rounded to bf16, own slice exact, fp32 sum; then the accumulating form
+        pair = fz.staging_buffers(n, torch.bfloat16, dev, dist.group.WORLD)
+        st = pair.next()
+        fz.round_into_staging(grads.tensor, st, rank, S)
+        fz.peer_barrier(dist.group.WORLD, dev)
+        got16 = torch.empty(S, device=dev)
+        fz.reduce_scatter_staged(st, grads.tensor, rank, S, got16, accumulate=False, max_ctas=8 if rep else 0)
+        fz.reduce_scatter_staged(st, grads.tensor, rank, S, got16, accumulate=True)
+        fz.peer_barrier(dist.group.WORLD, dev)
+        rounded = [torch.empty(n, device=dev) for _ in range(t)]
+        dist.all_gather(rounded, grads.tensor.clone())
+        lo, hi = rank * S, (rank + 1) * S
+        want = sum((x[lo:hi] if r == rank else x[lo:hi].bfloat16().float()) for r, x in enumerate(rounded))
+        out["rs16_%d" % rep] = float((got16 - 2 * want).abs().max() / want.abs().max())
         # AdamW + all-gather against the plain kernel + NCCL all-gather
         master = torch.randn(S, device=dev, generator=g)
         m0, v0 = torch.randn(S, device=dev, generator=g) * 0.1, torch.rand(S, device=dev, generator=g) * 0.01
@@ -78,13 +92,14 @@ def train(cfg):
     dev = torch.device("cuda", rank)
     args = GalvatronRuntimeArgs(
         parallel=dict(mixed_precision="bf16", default_dp_type=cfg["dp_type"], sdp=1 if cfg["dp_type"] == "zero3" else 0,
-                      async_grad_reduce=cfg.get("defer", True)),
+                      async_grad_reduce=cfg.get("defer", True), reduce_in_fp32=cfg.get("fp32_wire", False)),
         model=dict(model_size="llama-test", hidden_size=256, num_layers=3, num_attention_heads=4, ffn_hidden_size=768,
                    vocab_size=1024, make_vocab_size_divisible_by=8, normalization="RMSNorm",
                    activation_func="torch.nn.functional.silu", gated_linear_unit=True, num_query_groups=2),
         train=dict(seq_length=256, global_batch_size=8, chunks=2, lr=1e-3))
     model = build_model(args, device=dev, full_init=True, fused_zero=cfg["fused"])
     assert all(u.fused == cfg["fused"] for u in model.sharded_units if u.params)
+    assert all(u.pooled == (not cfg.get("defer", True)) for u in model.sharded_units if u.params)
     opt = ShardedAdamW(model.sharded_units, lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01, clip_grad=1.0, device=dev)
     tok = torch.randint(0, 1024, (8, 257), generator=torch.Generator().manual_seed(3))
     mine = tok[rank * 4:(rank + 1) * 4].to(dev)
@@ -114,13 +129,18 @@ def test_peer_kernels_match_nccl(shard):
         assert r["status"] == 0, r
         for rep in range(2):
             assert r["rs_%d" % rep] < 1e-6 and r["adam_state_%d" % rep] < 1e-5 and r["gathered_%d" % rep] < 0.04, r
+            assert r["rs16_%d" % rep] < 1e-6, r
 
 
-@pytest.mark.parametrize("dp_type,defer", [("zero2", True), ("zero3", True), ("zero2", False)])
-def test_training_matches_nccl_path(dp_type, defer):
+@pytest.mark.parametrize("dp_type,defer,fp32_wire", [("zero2", True, False), ("zero2", True, True), ("zero3", True, False),
+                                                     ("zero2", False, False), ("zero3", False, True)])
+def test_training_matches_nccl_path(dp_type, defer, fp32_wire):
+    """Peer-memory reduce-scatter / AdamW + all-gather against the NCCL path of the same step, for both wire dtypes,
+    with the reduction launched from the last backward (deferred) or after every micro-batch from pooled buffers."""
     _need(2)
-    ref = run_distributed(__file__, "train", 2, {"dp_type": dp_type, "fused": False, "defer": defer}, timeout=300, extra_env=ENV)
-    got = run_distributed(__file__, "train", 2, {"dp_type": dp_type, "fused": True, "defer": defer}, timeout=300, extra_env=ENV)
+    cfg = {"dp_type": dp_type, "defer": defer, "fp32_wire": fp32_wire}
+    ref = run_distributed(__file__, "train", 2, dict(cfg, fused=False), timeout=300, extra_env=ENV)
+    got = run_distributed(__file__, "train", 2, dict(cfg, fused=True), timeout=300, extra_env=ENV)
     for r in range(2):
         for (l0, n0), (l1, n1) in zip(ref[r], got[r]):
             assert abs(l0 - l1) / abs(l0) < 2e-3 and abs(n0 - n1) / n0 < 2e-2, (ref, got)

@@ -143,6 +143,27 @@ def test_pipeline(ptype, chunks):
     check(2, {"chunks": chunks, "parallel": {"pp_deg": 2, "pipeline_type": ptype}})
 
 
+def test_reduce_in_fp32_and_low_precision_wire():
+    """bf16 parameters: gradients cross the links in bf16 by default and in fp32 with ``reduce_in_fp32``; both match
+    one process at the same precision."""
+    base = {"chunks": 1, "parallel": {"mixed_precision": "bf16"}}
+    for fp32 in (False, True):
+        for dp_type, defer in (("zero3", False), ("ddp", True)):
+            check(2, {"chunks": 2, "parallel": {"mixed_precision": "bf16", "default_dp_type": dp_type,
+                                                "sdp": 1 if dp_type == "zero3" else 0, "reduce_in_fp32": fp32,
+                                                "async_grad_reduce": defer}},
+                  base, key="mp_bf16", rtol=2e-3, norm_rtol=2e-2)
+
+
+def test_pipeline_tied_embeddings_immediate_reduction():
+    """Tied embedding / LM-head copies on two stages exchange their gradients also when every other unit reduces
+    after each micro-batch (``async_grad_reduce=False``)."""
+    model = {"untie_embeddings_and_output_weights": False}
+    check(4, {"chunks": 2, "parallel": {"pp_deg": 2, "pipeline_type": "gpipe", "default_dp_type": "zero2",
+                                        "async_grad_reduce": False}, "model": model},
+          {"chunks": 1, "model": model}, key="tied")
+
+
 def test_pipeline_tied_embeddings_tp():
     model = {"untie_embeddings_and_output_weights": False}
     check(4, {"chunks": 2, "parallel": {"pp_deg": 2, "pipeline_type": "pipedream_flush", "global_tp_deg": 2,

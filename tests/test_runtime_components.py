@@ -241,6 +241,57 @@ def test_gpt_dataset_samples_are_contiguous_token_windows(tmp_path):
     assert len(os.listdir(str(tmp_path / "cache"))) == 3
 
 
+def _cold_cache_worker(payload):
+    """One gloo rank: build the GPT dataset over a corpus whose index cache does not exist yet."""
+    import torch.distributed as dist
+
+    from hetu_galvatron_b200.runtime.datasets.gpt import GPTDataset, GPTDatasetConfig
+    from hetu_galvatron_b200.runtime.datasets.indexed import IndexedDataset
+
+    prefix, cache = payload["prefix"], payload["cache"]
+    cfg = GPTDatasetConfig(sequence_length=32, random_seed=11, path_to_cache=cache)
+    ds = GPTDataset(IndexedDataset(prefix), prefix, np.arange(80, dtype=np.int32), 400, "train", cfg)
+    return {"rank": dist.get_rank(), "len": len(ds), "sample": ds[7]["tokens"].tolist(),
+            "files": sorted(os.listdir(cache))}
+
+
+def test_dataset_index_cache_is_built_once_by_rank_zero(tmp_path):
+    """Four ranks start with a cold cache: rank 0 builds and publishes the index files atomically, the others wait at
+    the barrier and map the finished files; everybody sees the same samples and no temporary file is left."""
+    from tests.dist_utils import run_distributed
+
+    prefix = str(tmp_path / "c")
+    _write_corpus(prefix, _docs(80, seed=5))
+    cache = str(tmp_path / "cache")
+    res = run_distributed(__file__, "cold_cache", 4, {"prefix": prefix, "cache": cache}, timeout=120)
+    assert len({r["len"] for r in res}) == 1 and all(r["sample"] == res[0]["sample"] for r in res)
+    assert all(len(r["files"]) == 3 and not any(".tmp." in f for f in r["files"]) for r in res)
+
+
+def test_nonzero_device_status_rejects_the_step(monkeypatch):
+    """A kernel whose bounded wait ran out leaves a code in the device status word; the training loop reads it once
+    per iteration and raises instead of keeping the step."""
+    from hetu_galvatron_b200.ops._lib import KernelError
+    from hetu_galvatron_b200.runtime import trainer
+
+    trainer.check_device_status(torch.device("cpu"))          # healthy: no error
+    monkeypatch.setattr(trainer, "_device_status_code", lambda device: 5)
+    with pytest.raises(KernelError, match="peer flag"):
+        trainer.check_device_status(torch.device("cpu"))
+    # and the loop calls it: a one-layer model, first iteration
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+
+    args = GalvatronRuntimeArgs(
+        parallel=dict(mixed_precision="fp32"),
+        model=dict(model_size="llama-test", hidden_size=64, num_layers=1, num_attention_heads=2, ffn_hidden_size=128,
+                   vocab_size=128, make_vocab_size_divisible_by=8, normalization="RMSNorm",
+                   activation_func="torch.nn.functional.silu", gated_linear_unit=True),
+        train=dict(seq_length=16, global_batch_size=2, chunks=1, lr=1e-3, train_iters=2),
+        data=dict(use_random_dataset=True))
+    with pytest.raises(KernelError):
+        trainer.train(args, max_iters=2)
+
+
 def test_blended_dataset_follows_weights():
     from hetu_galvatron_b200.runtime.datasets.blended import BlendedDataset
 
@@ -445,3 +496,9 @@ def test_expert_bias_update_moves_towards_balance():
     r.update_expert_bias(0.1)
     assert torch.allclose(r.router.expert_bias, torch.tensor([-0.1, 0.1, 0.1, 0.1]))
     assert float(r.router.local_tokens_per_expert.sum()) == 0.0
+
+
+if __name__ == "__main__":
+    from tests.dist_utils import worker_main
+
+    worker_main({"cold_cache": _cold_cache_worker})

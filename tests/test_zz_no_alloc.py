@@ -11,7 +11,7 @@ import torch
 from hetu_galvatron_b200.ops import _lib
 
 pytestmark = pytest.mark.gpu
-MAX_H, PARTS, TOO_WIDE = 8192, 148, -2
+MAX_H, PARTS, TOO_WIDE, NULL_ARG = 8192, 148, -2, -3
 
 
 def _symbol():
@@ -49,17 +49,23 @@ def _run_regular(lib, t, rows, H, rms):
     return dx, dw, db
 
 
-def _run_noalloc(fn, t, rows, H, rms):
+def _run_noalloc(fn, t, rows, H, rms, check_driver_memory=False):
     dy, h, w, rstd, mean, dres = t
     dx = torch.empty_like(h)
     dw = torch.empty(H, dtype=torch.float32, device="cuda")
     db = None if rms else torch.zeros(H, dtype=torch.float32, device="cuda")
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before = torch.cuda.mem_get_info()[0]
     rc = fn(dy.data_ptr(), h.data_ptr(), w.data_ptr(), rstd.data_ptr(), _lib.ptr(mean), dres.data_ptr(),
             dx.data_ptr(), dw.data_ptr(), _lib.ptr(db), rows, H, int(rms), 0, _lib.stream())
     assert rc == 0
+    torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    if check_driver_memory:
+        # the driver's own count of free device memory also sees a raw cudaMalloc, which torch's counter does not
+        # (the first call on a device may still load the kernels' module, so only later calls are held to this)
+        assert torch.cuda.mem_get_info()[0] >= free_before
     return dx, dw, db
 
 
@@ -71,10 +77,11 @@ def _close(a, b, tol=1e-5):
 def test_noalloc_matches_regular_on_two_calls_in_a_row(rms):
     lib, fn = _symbol()
     # second call: fewer rows than scratch rows and a different width, on top of the first call's leftovers
-    for rows, H, seed in ((1000, 4096, 1), (90, 2048, 2)):
+    # then the widest supported row and a width between the two kernel instantiations
+    for call, (rows, H, seed) in enumerate(((1000, 4096, 1), (90, 2048, 2), (300, 8192, 3), (257, 5120, 4))):
         t = _inputs(rows, H, rms, seed)
         want = _run_regular(lib, t, rows, H, rms)
-        got = _run_noalloc(fn, t, rows, H, rms)
+        got = _run_noalloc(fn, t, rows, H, rms, check_driver_memory=call > 0)
         torch.cuda.synchronize()
         for g, w_ in zip(got, want):
             if w_ is not None:
@@ -88,3 +95,16 @@ def test_noalloc_rejects_widths_beyond_the_static_array():
     p = x.data_ptr()
     assert fn(p, p, p, p, 0, 0, p, p, 0, 4, 2 * MAX_H, 1, 0, _lib.stream()) == TOO_WIDE
     assert fn(p, p, p, p, 0, 0, p, p, 0, 4, 100, 1, 0, _lib.stream()) == -1
+
+
+def test_noalloc_rejects_null_pointers_before_launching():
+    _, fn = _symbol()
+    x = torch.zeros(8, device="cuda")
+    p = x.data_ptr()
+    st = _lib.stream()
+    assert fn(0, p, p, p, 0, 0, p, p, 0, 1, 8, 1, 0, st) == NULL_ARG        # dy
+    assert fn(p, p, p, p, 0, 0, 0, p, 0, 1, 8, 1, 0, st) == NULL_ARG        # dx
+    assert fn(p, p, p, p, 0, 0, p, 0, 0, 1, 8, 1, 0, st) == NULL_ARG        # dw
+    assert fn(p, p, p, p, 0, 0, p, p, 0, 1, 8, 0, 0, st) == NULL_ARG        # LayerNorm without mean
+    torch.cuda.synchronize()
+    _lib.assert_healthy()
