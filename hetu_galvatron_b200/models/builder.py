@@ -71,7 +71,9 @@ class ModelGroups:
             self.per_layer.append(self._cache[key])
         base = dense_layout(plan.world_size, plan.pp_deg)
         self.pp = factory.make(base.groups(("pp",)))
-        self.embedding = factory.make(embedding_group_ranks(base))
+        # gradients travel on a communicator of their own, so that each of the two is a one-way FIFO
+        self.pp_bwd = factory.make(base.groups(("pp",)), tag="pp_bwd") if plan.pp_deg > 1 else self.pp
+        self.embedding = factory.make(embedding_group_ranks(base), allow_absent=True)
         self.stage = base.coord(rank, "pp")
         self.stage_ranks = plan.world_size // plan.pp_deg
         self.layout = base

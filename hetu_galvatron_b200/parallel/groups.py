@@ -154,24 +154,28 @@ class GroupFactory:
 
     def __init__(self, rank: int, world: int, backend: Optional[str] = None):
         self.rank, self.world, self.backend = rank, world, backend
-        self._cache: Dict[Tuple[int, ...], object] = {}
+        self._cache: Dict[tuple, object] = {}
 
-    def make(self, all_groups: List[List[int]]) -> CommGroup:
+    def make(self, all_groups: List[List[int]], tag: str = "", allow_absent: bool = False) -> CommGroup:
+        """``tag`` asks for a communicator of its own over a rank set that may already have one (a second,
+        independent channel between the same ranks, e.g. the backward direction of the pipeline)."""
         import torch.distributed as dist
 
         mine = None
         for ranks in all_groups:
-            key = tuple(ranks)
+            key = tuple(ranks) if not tag else (tag,) + tuple(ranks)
             if key not in self._cache:
                 if len(ranks) == 1 or not dist.is_initialized():
                     self._cache[key] = None
-                elif len(ranks) == self.world and ranks == list(range(self.world)):
+                elif len(ranks) == self.world and ranks == list(range(self.world)) and not tag:
                     self._cache[key] = dist.group.WORLD
                 else:
                     self._cache[key] = dist.new_group(ranks, backend=self.backend)
             if self.rank in ranks:
                 mine = CommGroup(list(ranks), self._cache[key], ranks.index(self.rank))
         if mine is None:
+            if allow_absent:     # e.g. a middle pipeline stage and the first/last-stage embedding groups
+                return CommGroup([self.rank], None, 0)
             raise RuntimeError("rank %d is in none of the groups" % self.rank)
         return mine
 

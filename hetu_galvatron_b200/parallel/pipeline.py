@@ -2,9 +2,17 @@
 
 A stage runs ``StageModel`` on micro-batches; activations cross a stage boundary in the *sender's*
 layout ``[S/g, mb/d, H]`` between ranks with the same index inside their stage, and the receiver
-re-lays them out for its first layer.  Sends are asynchronous (``isend``) and are only waited for when
-their buffer is about to be reused, receives are posted before the compute they feed; nothing calls a
-device-wide synchronise.
+re-lays them out for its first layer.
+
+Communication.  A schedule is a list of steps ``("F", i)`` / ``("B", i)``.  Activations travel on one
+communicator, gradients on a second one over the same ranks, so each is a one-way FIFO between neighbours:
+a stage can post the receive of step ``k+1`` *before* it computes step ``k`` (the transfer then runs under
+the compute) and send its result with a plain ``isend`` right after the compute, and no ordering of those
+calls can make two neighbours wait on each other.  (With one communicator for both directions the
+steady state of 1F1B, where both neighbours send first, needs the send and the receive fused into one
+``batch_isend_irecv`` group, as the reference does in pipeline.py:1108-1139, and that rules out the early
+receive.)  Sends are only waited for when their buffer is dropped at the end of the step; nothing calls
+a device-wide synchronise.
 
 Capability parity: galvatron/core/runtime/pipeline/pipeline.py:307-385 (no pipeline), :387-713
 (1F1B-flush: warm-up / steady / cool-down), :730-895 (GPipe), :907-981 (forward / backward step),
@@ -29,23 +37,32 @@ def chunk_batch(t: Optional[torch.Tensor], chunks: int) -> List[Optional[torch.T
 
 
 class P2P:
-    """Point-to-point activations / gradients between neighbouring stages."""
+    """Point-to-point activations (forward channel) and gradients (backward channel) between neighbouring stages."""
 
-    def __init__(self, pp_group, stage: int, num_stages: int):
+    def __init__(self, pp_group, stage: int, num_stages: int, bwd_group=None):
         self.stage, self.n = stage, num_stages
         ranks = pp_group.ranks
         self.prev = ranks[stage - 1] if stage > 0 else None
         self.next = ranks[stage + 1] if stage < num_stages - 1 else None
+        self.fwd = pp_group.group
+        self.bwd = bwd_group.group if bwd_group is not None else pp_group.group
         self._pending: List = []
 
-    def recv(self, shape, dtype, device, src) -> (torch.Tensor, object):
+    def recv_activation(self, shape, dtype, device):
         buf = torch.empty(shape, dtype=dtype, device=device)
-        return buf, dist.irecv(buf, src=src)
+        return buf, dist.irecv(buf, src=self.prev, group=self.fwd)
 
-    def send(self, t: torch.Tensor, dst):
+    def recv_gradient(self, shape, dtype, device):
+        buf = torch.empty(shape, dtype=dtype, device=device)
+        return buf, dist.irecv(buf, src=self.next, group=self.bwd)
+
+    def send_activation(self, t: torch.Tensor):
         t = t.contiguous()
-        work = dist.isend(t, dst=dst)
-        self._pending.append((work, t))  # keep the buffer alive until the send completed
+        self._pending.append((dist.isend(t, dst=self.next, group=self.fwd), t))  # keeps the buffer alive
+
+    def send_gradient(self, t: torch.Tensor):
+        t = t.contiguous()
+        self._pending.append((dist.isend(t, dst=self.prev, group=self.bwd), t))
 
     def drain(self):
         for work, _ in self._pending:
@@ -59,7 +76,7 @@ class PipelineEngine:
     def __init__(self, stage_model, groups, plan, spec, device):
         self.model, self.groups, self.plan, self.spec, self.device = stage_model, groups, plan, spec, device
         self.stage, self.n = groups.stage, plan.pp_deg
-        self.p2p = P2P(groups.pp, self.stage, self.n) if self.n > 1 else None
+        self.p2p = P2P(groups.pp, self.stage, self.n, getattr(groups, "pp_bwd", None)) if self.n > 1 else None
         self.first, self.last = self.stage == 0, self.stage == self.n - 1
         self.after_forward = None  # optional hook (memory profiling): after the first forward / after all GPipe forwards
 
@@ -96,8 +113,10 @@ class PipelineEngine:
         if self.n == 1:
             return self._run_no_pp(tokens, labels, loss_fns, scale, forward_only)
         if self.plan.pipeline_type == "gpipe" or forward_only:
-            return self._run_gpipe(tokens, labels, loss_fns, mb_sizes, scale, forward_only)
-        return self._run_1f1b(tokens, labels, loss_fns, mb_sizes, scale)
+            steps = [("F", i) for i in range(chunks)] + ([] if forward_only else [("B", i) for i in range(chunks)])
+        else:
+            steps = one_f_one_b_steps(self.stage, self.n, chunks)
+        return self._run_steps(steps, tokens, labels, loss_fns, mb_sizes, scale, forward_only)
 
     def _finish_backward(self):
         for u in self.model.units:
@@ -118,85 +137,70 @@ class PipelineEngine:
             losses.append(loss.detach())
         return losses
 
-    # ---- GPipe ---------------------------------------------------------------------------------------------
-    def _run_gpipe(self, tokens, labels, loss_fns, mb_sizes, scale, forward_only):
-        chunks = len(mb_sizes)
-        dtype = self.spec.dtype
-        inputs, outputs, losses = [], [], []
-        for i in range(chunks):
+    # ---- pipelined schedules ------------------------------------------------------------------------------
+    def _post_recv(self, step, mb_sizes):
+        """Post the receive a step needs (``None`` when its input is local)."""
+        kind, i = step
+        if kind == "F":
             if self.first:
-                x = tokens[i]
-            else:
-                x, w = self.p2p.recv(self._recv_shape(mb_sizes[i]), dtype, self.device, self.p2p.prev)
-                w.wait()
-                x.requires_grad_(not forward_only)
-            with torch.set_grad_enabled(not forward_only):
-                out = self._forward(x, labels[i], loss_fns[i], scale)
-            if not self.last:
-                self.p2p.send(out.detach(), self.p2p.next)
-            else:
-                losses.append(out.detach())
-            inputs.append(x)
-            outputs.append(out)
-        if self.after_forward is not None:
-            self.after_forward()
-        if forward_only:
-            self.p2p.drain()
-            return losses
-        for i in range(chunks):
-            set_last_microbatch(i == chunks - 1)
-            self._backward_step(inputs[i], outputs[i], mb_sizes[i])
-            inputs[i] = outputs[i] = None
-        self.p2p.drain()
-        return losses
-
-    def _backward_step(self, x, out, mb):
+                return None
+            return self.p2p.recv_activation(self._recv_shape(mb_sizes[i]), self.spec.dtype, self.device)
         if self.last:
-            out.backward()
-        else:
-            g, w = self.p2p.recv(tuple(out.shape), out.dtype, self.device, self.p2p.next)
-            w.wait()
-            torch.autograd.backward(out, grad_tensors=g)
-        self._finish_backward()
-        if not self.first:
-            self.p2p.send(x.grad, self.p2p.prev)
+            return None
+        return self.p2p.recv_gradient(self._send_shape(mb_sizes[i]), self.spec.dtype, self.device)
 
-    # ---- 1F1B with flush ---------------------------------------------------------------------------------
-    def _run_1f1b(self, tokens, labels, loss_fns, mb_sizes, scale):
+    def _run_steps(self, steps, tokens, labels, loss_fns, mb_sizes, scale, forward_only):
         chunks = len(mb_sizes)
-        dtype = self.spec.dtype
-        warm = min(self.n - self.stage - 1, chunks)
-        inputs, outputs, losses = [], [], []
-
-        def fwd(i):
-            if self.first:
-                x = tokens[i]
+        inputs, outputs, losses = {}, {}, []
+        n_bwd = sum(1 for k, _ in steps if k == "B")
+        done_bwd = 0
+        first_fwd_hook = self.after_forward
+        nxt = self._post_recv(steps[0], mb_sizes) if steps else None
+        for k, (kind, i) in enumerate(steps):
+            cur = nxt
+            # the next step's input starts travelling while this step computes
+            nxt = self._post_recv(steps[k + 1], mb_sizes) if k + 1 < len(steps) else None
+            if kind == "F":
+                if cur is None:
+                    x = tokens[i]
+                else:
+                    x, work = cur
+                    work.wait()
+                    x.requires_grad_(not forward_only)
+                with torch.set_grad_enabled(not forward_only):
+                    out = self._forward(x, labels[i], loss_fns[i], scale)
+                if not self.last:
+                    self.p2p.send_activation(out.detach())
+                else:
+                    losses.append(out.detach())
+                inputs[i], outputs[i] = x, out
+                last_fwd = k + 1 == len(steps) or all(kk != "F" for kk, _ in steps[k + 1:])
+                if first_fwd_hook is not None and (last_fwd if self.plan.pipeline_type == "gpipe" else i == 0):
+                    first_fwd_hook()
+                    first_fwd_hook = None
             else:
-                x, w = self.p2p.recv(self._recv_shape(mb_sizes[i]), dtype, self.device, self.p2p.prev)
-                w.wait()
-                x.requires_grad_(True)
-            out = self._forward(x, labels[i], loss_fns[i], scale)
-            if not self.last:
-                self.p2p.send(out.detach(), self.p2p.next)
-            else:
-                losses.append(out.detach())
-            inputs.append(x)
-            outputs.append(out)
-
-        done = [0]
-
-        def bwd():
-            x, out = inputs.pop(0), outputs.pop(0)
-            done[0] += 1
-            set_last_microbatch(done[0] == chunks)
-            self._backward_step(x, out, None)
-
-        for i in range(warm):
-            fwd(i)
-        for i in range(warm, chunks):
-            fwd(i)
-            bwd()
-        for _ in range(warm):
-            bwd()
+                x, out = inputs.pop(i), outputs.pop(i)
+                done_bwd += 1
+                set_last_microbatch(done_bwd == n_bwd)
+                if cur is None:
+                    out.backward()
+                else:
+                    g, work = cur
+                    work.wait()
+                    torch.autograd.backward(out, grad_tensors=g)
+                self._finish_backward()
+                if not self.first:
+                    self.p2p.send_gradient(x.grad)
         self.p2p.drain()
         return losses
+
+
+def one_f_one_b_steps(stage: int, num_stages: int, chunks: int):
+    """1F1B with flush for one stage: ``num_stages - stage - 1`` warm-up forwards, then forward / backward pairs,
+    then the remaining backwards."""
+    warm = min(num_stages - stage - 1, chunks)
+    steps = [("F", i) for i in range(warm)]
+    for i in range(warm, chunks):
+        steps += [("F", i), ("B", i - warm)]
+    steps += [("B", i) for i in range(chunks - warm, chunks)]
+    return steps

@@ -143,6 +143,24 @@ def test_pipeline(ptype, chunks):
     check(2, {"chunks": chunks, "parallel": {"pp_deg": 2, "pipeline_type": ptype}})
 
 
+def test_pipeline_four_stages():
+    """Four stages (middle stages belong to no embedding group): 1F1B-flush and GPipe, receives posted one step
+    ahead on direction-separated communicators."""
+    check(4, {"chunks": 4, "parallel": {"pp_deg": 4, "pipeline_type": "pipedream_flush"}})
+    check(4, {"chunks": 2, "parallel": {"pp_deg": 4, "pipeline_type": "gpipe"}})
+
+
+def test_one_f_one_b_step_lists():
+    from hetu_galvatron_b200.parallel.pipeline import one_f_one_b_steps
+
+    assert one_f_one_b_steps(0, 2, 3) == [("F", 0), ("F", 1), ("B", 0), ("F", 2), ("B", 1), ("B", 2)]
+    assert one_f_one_b_steps(1, 2, 3) == [("F", 0), ("B", 0), ("F", 1), ("B", 1), ("F", 2), ("B", 2)]
+    for stage in range(4):     # every micro-batch once forward, once backward, backward after its forward
+        st = one_f_one_b_steps(stage, 4, 2)
+        assert sorted(st) == sorted([("F", 0), ("F", 1), ("B", 0), ("B", 1)])
+        assert all(st.index(("F", i)) < st.index(("B", i)) for i in range(2))
+
+
 def test_reduce_in_fp32_and_low_precision_wire():
     """bf16 parameters: gradients cross the links in bf16 by default and in fp32 with ``reduce_in_fp32``; both match
     one process at the same precision."""
