@@ -248,6 +248,48 @@ __global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_
   }
 }
 
+
+// Log-sum-exp merge of two partial attention results over disjoint key sets (ring / context-parallel attention):
+//   l = log(exp(lse_acc) + exp(lse_new));  out_acc = exp(lse_acc - l) * out_acc + exp(lse_new - l) * out_new;  lse_acc = l
+// out_acc fp32 [S, B*h, d] contiguous, out_new bf16 same shape, lse_new fp32 [B*h, S] contiguous, lse_acc fp32 with
+// row pitch `lse_pitch` (a slice of a longer sequence).  LPR = d / 8 lanes share a row; they all read the old lse
+// before lane 0 replaces it.
+template <int LPR>
+__global__ void attn_merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse_acc, long long lse_pitch,
+                                  const __nv_bfloat16* __restrict__ out_new, const float* __restrict__ lse_new, int S,
+                                  int BH) {
+  const int64_t rows = int64_t(S) * BH;
+  const int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+  const int64_t row = t / LPR;
+  const int lane = int(t % LPR);
+  const bool live = row < rows;
+  float wa = 0.f, wb = 0.f, l = 0.f;
+  float* lp = nullptr;
+  if (live) {
+    const int s = int(row / BH), bh = int(row % BH);
+    lp = lse_acc + int64_t(bh) * lse_pitch + s;
+    const float la = *lp, ln = lse_new[int64_t(bh) * S + s];
+    const float m = fmaxf(la, ln);
+    if (m == -INFINITY) {   // neither side has seen a key yet
+      l = -INFINITY;
+    } else {
+      l = m + __logf(__expf(la - m) + __expf(ln - m));
+      wa = __expf(la - l);
+      wb = __expf(ln - l);
+    }
+    float4* acc = reinterpret_cast<float4*>(out_acc + (row * LPR + lane) * 8);
+    float x[8];
+    unpack8(reinterpret_cast<const uint4*>(out_new)[row * LPR + lane], x);
+    float4 a0 = acc[0], a1 = acc[1];
+    a0.x = wa * a0.x + wb * x[0]; a0.y = wa * a0.y + wb * x[1]; a0.z = wa * a0.z + wb * x[2]; a0.w = wa * a0.w + wb * x[3];
+    a1.x = wa * a1.x + wb * x[4]; a1.y = wa * a1.y + wb * x[5]; a1.z = wa * a1.z + wb * x[6]; a1.w = wa * a1.w + wb * x[7];
+    acc[0] = a0;
+    acc[1] = a1;
+  }
+  __syncwarp();
+  if (live && lane == 0) *lp = l;
+}
+
 inline int grid_for(int64_t work, int threads) {
   int64_t g = (work + threads - 1) / threads;
   const int64_t cap = 148 * 16;
@@ -332,6 +374,24 @@ int hg_add_bf16(const void* a, const void* b, void* out, long long n, void* stre
   if (n <= 0) return 0;
   add_bf16_kernel<<<grid_for(n >> 3, 256), 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, n);
+  return int(cudaGetLastError());
+}
+
+// See attn_merge_kernel.  d must be 64 or 128; S * BH rows.
+int hg_attn_merge(void* out_acc, void* lse_acc, long long lse_pitch, const void* out_new, const void* lse_new, int S,
+                  int BH, int d, void* stream) {
+  if (S <= 0 || BH <= 0) return 0;
+  if (d != 64 && d != 128) return -1;
+  const int lpr = d / 8;
+  const int64_t threads = int64_t(S) * BH * lpr;
+  const int grid = int((threads + 255) / 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (lpr == 16)
+    attn_merge_kernel<16><<<grid, 256, 0, st>>>((float*)out_acc, (float*)lse_acc, lse_pitch, (const __nv_bfloat16*)out_new,
+                                                (const float*)lse_new, S, BH);
+  else
+    attn_merge_kernel<8><<<grid, 256, 0, st>>>((float*)out_acc, (float*)lse_acc, lse_pitch, (const __nv_bfloat16*)out_new,
+                                               (const float*)lse_new, S, BH);
   return int(cudaGetLastError());
 }
 

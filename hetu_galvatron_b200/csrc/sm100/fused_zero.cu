@@ -9,13 +9,18 @@
 //                                bf16 values are stored straight into every rank's parameter buffer at this
 //                                shard's offset (16-byte peer stores) -- the all-gather happens in the epilogue
 //
-// Neither kernel waits on another GPU: the callers order them against the peers' work with stream-ordered
-// collectives (a one-element all-reduce before the first kernel and after the second), so there is no spin-wait
-// and nothing here can hang.  Buffers that peers touch must come from one symmetric allocation per rank.
+// The fp32-wire reduce-scatter and the AdamW kernel never wait on another GPU: the callers order them against the
+// peers' work with stream-ordered collectives (a one-element all-reduce before the first and after the second).
+// The bf16-wire reduce-scatter carries its own rendezvous: it publishes "my staged gradients are complete" in every
+// peer's signal slots and waits, with a 2-second limit that reports through the status word, for the peers' signals
+// of the same epoch, so a whole unit's reduction is two launches (round, reduce) with no library collective.
+// Buffers that peers touch must come from one symmetric allocation per rank.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
+
+#include "sm100_common.cuh"
 
 namespace {
 
@@ -83,12 +88,53 @@ zero_reduce_scatter_kernel(PeerPtrs grads, int me, long long shard_floats, long 
 // bf16-on-the-wire variant (the reference's default, reduce_in_fp32 = false): every rank first rounds its fp32
 // gradient buffer into a bf16 staging buffer (symmetric memory); this kernel then sums, in fp32 and in rank order,
 // the peers' bf16 slices (16-byte loads of 8 values: half the NVLink bytes of the fp32 kernel) and this rank's own
-// slice taken from the fp32 buffer, unrounded.  n8 = number of 8-element groups of the shard.  With `accumulate` the
-// result is added to `out` (running shard of the per-micro-batch reduction mode).
-template <int T, bool kAcc>
+// slice taken from the fp32 buffer, unrounded.  n8 = number of 8-element groups of the shard.  With kAcc the
+// result is added to `out` (running shard of the per-micro-batch reduction mode).  U groups per thread and
+// iteration keep (T - 1) * U peer loads of 16 bytes in flight per thread.
+struct Rendezvous {
+  int* peer_slots[kMaxPeers];   // peer_slots[r]: rank r's signal array (int[kMaxPeers], symmetric); we write slot `me`
+  const int* my_slots;          // our own array: my_slots[r] >= epoch once rank r's staged data may be read
+  int epoch;                    // 0: no rendezvous (the caller ordered the ranks itself)
+  int* status;
+};
+
+// Publish this rank's epoch to every peer, then wait (bounded) until every peer has published the same epoch.
+// Returns false after a time-out (status word set); the caller then skips its reads.
+template <int T>
+__device__ __forceinline__ bool rendezvous(const Rendezvous& rv, int me) {
+  __shared__ int ok_s;
+  if (rv.epoch == 0) return true;
+  if (threadIdx.x == 0) ok_s = 1;
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x < T && int(threadIdx.x) != me) {
+    // the staged values were written by an earlier kernel of this stream: make them visible system-wide first
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(rv.peer_slots[threadIdx.x] + me), "r"(rv.epoch) : "memory");
+  }
+  if (threadIdx.x < T && int(threadIdx.x) != me) {
+    const int* flag = rv.my_slots + threadIdx.x;
+    const uint64_t t0 = hg::globaltimer_ns();
+    int v;
+    for (;;) {
+      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+      if (v >= rv.epoch) break;
+      if (hg::globaltimer_ns() - t0 > hg::kWaitLimitNs) {
+        hg::set_status(rv.status, hg::kTimeoutPeerFlag);
+        ok_s = 0;
+        break;
+      }
+      __nanosleep(200);
+    }
+  }
+  __syncthreads();
+  return ok_s != 0;
+}
+
+template <int T, bool kAcc, int U>
 __global__ void __launch_bounds__(kThreads)
 zero_reduce_scatter_bf16wire_kernel(PeerPtrs staged, const float* __restrict__ own, int me, long long shard_elems,
-                                    long long n8, float4* __restrict__ out) {
+                                    long long n8, float4* __restrict__ out, Rendezvous rv) {
+  if (!rendezvous<T>(rv, me)) return;
   const uint4* src[T];
 #pragma unroll
   for (int r = 0; r < T; ++r) {
@@ -96,36 +142,48 @@ zero_reduce_scatter_bf16wire_kernel(PeerPtrs staged, const float* __restrict__ o
   }
   const float4* mine = reinterpret_cast<const float4*>(own + me * shard_elems);
   const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += stride) {
-    uint4 a[T];
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < n8; i0 += U * stride) {
+    uint4 a[U][T];
+    float4 m0[U], m1[U];
 #pragma unroll
-    for (int r = 0; r < T; ++r) {
-      if (r != me) a[r] = __ldcs(src[r] + i);
-    }
-    const float4 m0 = __ldcs(mine + 2 * i), m1 = __ldcs(mine + 2 * i + 1);
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i < n8) {
 #pragma unroll
-    for (int r = 0; r < T; ++r) {
-      if (r == me) {
-        acc[0] += m0.x; acc[1] += m0.y; acc[2] += m0.z; acc[3] += m0.w;
-        acc[4] += m1.x; acc[5] += m1.y; acc[6] += m1.z; acc[7] += m1.w;
-      } else {
-        const uint32_t w[4] = {a[r].x, a[r].y, a[r].z, a[r].w};
-#pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          acc[2 * k] += __uint_as_float(w[k] << 16);
-          acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
-        }
+        for (int r = 0; r < T; ++r)
+          if (r != me) a[u][r] = __ldcs(src[r] + i);
+        m0[u] = __ldcs(mine + 2 * i);
+        m1[u] = __ldcs(mine + 2 * i + 1);
       }
     }
-    float4 o0 = make_float4(acc[0], acc[1], acc[2], acc[3]), o1 = make_float4(acc[4], acc[5], acc[6], acc[7]);
-    if (kAcc) {
-      const float4 p0 = out[2 * i], p1 = out[2 * i + 1];
-      o0.x += p0.x; o0.y += p0.y; o0.z += p0.z; o0.w += p0.w;
-      o1.x += p1.x; o1.y += p1.y; o1.z += p1.z; o1.w += p1.w;
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= n8) continue;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < T; ++r) {   // fixed summation order (rank 0, 1, ...): deterministic
+        if (r == me) {
+          acc[0] += m0[u].x; acc[1] += m0[u].y; acc[2] += m0[u].z; acc[3] += m0[u].w;
+          acc[4] += m1[u].x; acc[5] += m1[u].y; acc[6] += m1[u].z; acc[7] += m1[u].w;
+        } else {
+          const uint32_t w[4] = {a[u][r].x, a[u][r].y, a[u][r].z, a[u][r].w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            acc[2 * k] += __uint_as_float(w[k] << 16);
+            acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+          }
+        }
+      }
+      float4 o0 = make_float4(acc[0], acc[1], acc[2], acc[3]), o1 = make_float4(acc[4], acc[5], acc[6], acc[7]);
+      if (kAcc) {
+        const float4 p0 = out[2 * i], p1 = out[2 * i + 1];
+        o0.x += p0.x; o0.y += p0.y; o0.z += p0.z; o0.w += p0.w;
+        o1.x += p1.x; o1.y += p1.y; o1.z += p1.z; o1.w += p1.w;
+      }
+      out[2 * i] = o0;
+      out[2 * i + 1] = o1;
     }
-    out[2 * i] = o0;
-    out[2 * i + 1] = o1;
   }
 }
 
@@ -238,27 +296,39 @@ int hg_zero_reduce_scatter_capped(void* const* grads, int t, int me, long long s
 // bf16 wire: staged[r] = rank r's bf16 staging buffer (t * shard elements, peer-mapped); own = this rank's fp32
 // gradient buffer (local).  shard a multiple of 8.  max_ctas > 0 caps the grid (a reduction that runs beside the
 // backward GEMMs should not take every SM).  accumulate != 0: out += sum.
+// signals[r] = rank r's int[8] signal array (symmetric) and epoch > 0: the kernel does the cross-rank rendezvous
+// itself (epoch must increase by one per call on every rank of the group); signals == null or epoch == 0: the
+// caller has already ordered the ranks (every rank's staging buffer is complete and visible).
 int hg_zero_reduce_scatter_bf16wire(void* const* staged, const void* own, int t, int me, long long shard, void* out,
-                                    int accumulate, int max_ctas, void* stream) {
+                                    int accumulate, int max_ctas, void* const* signals, int epoch, void* stream) {
   if (t < 1 || t > kMaxPeers || me < 0 || me >= t || shard <= 0 || (shard & 7) || own == nullptr) return -1;
   PeerPtrs pp{};
   for (int r = 0; r < t; ++r) pp.p[r] = staged[r];
+  Rendezvous rv{};
+  rv.epoch = (signals != nullptr && t > 1) ? epoch : 0;
+  if (rv.epoch) {
+    for (int r = 0; r < t; ++r) rv.peer_slots[r] = reinterpret_cast<int*>(signals[r]);
+    rv.my_slots = rv.peer_slots[me];
+    rv.status = hg_host::status_ptr();
+  }
   const long long n8 = shard / 8;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int grid = grid_for(n8);
   if (max_ctas > 0 && grid > max_ctas) grid = max_ctas;
-#define HG_RSB(T_)                                                                                                  \
-  if (accumulate) zero_reduce_scatter_bf16wire_kernel<T_, true><<<grid, kThreads, 0, st>>>(pp, (const float*)own, me, shard, n8, (float4*)out); \
-  else zero_reduce_scatter_bf16wire_kernel<T_, false><<<grid, kThreads, 0, st>>>(pp, (const float*)own, me, shard, n8, (float4*)out)
+#define HG_RSB(T_, U_)                                                                                              \
+  if (accumulate)                                                                                                   \
+    zero_reduce_scatter_bf16wire_kernel<T_, true, U_><<<grid, kThreads, 0, st>>>(pp, (const float*)own, me, shard, n8, (float4*)out, rv); \
+  else                                                                                                              \
+    zero_reduce_scatter_bf16wire_kernel<T_, false, U_><<<grid, kThreads, 0, st>>>(pp, (const float*)own, me, shard, n8, (float4*)out, rv)
   switch (t) {
-    case 1: HG_RSB(1); break;
-    case 2: HG_RSB(2); break;
-    case 3: HG_RSB(3); break;
-    case 4: HG_RSB(4); break;
-    case 5: HG_RSB(5); break;
-    case 6: HG_RSB(6); break;
-    case 7: HG_RSB(7); break;
-    default: HG_RSB(8); break;
+    case 1: HG_RSB(1, 4); break;
+    case 2: HG_RSB(2, 4); break;
+    case 3: HG_RSB(3, 2); break;
+    case 4: HG_RSB(4, 2); break;
+    case 5: HG_RSB(5, 2); break;
+    case 6: HG_RSB(6, 1); break;
+    case 7: HG_RSB(7, 1); break;
+    default: HG_RSB(8, 1); break;
   }
 #undef HG_RSB
   return int(cudaGetLastError());

@@ -38,7 +38,8 @@ _SIGNATURES = {
     "hg_router_topk_bwd": [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "hg_zero_reduce_scatter": [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p],
     "hg_zero_reduce_scatter_capped": [c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_void_p],
-    "hg_zero_reduce_scatter_bf16wire": [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_void_p],
+    "hg_zero_reduce_scatter_bf16wire": [c_void_p, c_void_p, c_int, c_int, c_ll, c_void_p, c_int, c_int, c_void_p, c_int,
+                                        c_void_p],
     "hg_add_inplace_f32": [c_void_p, c_void_p, c_ll, c_void_p],
     "hg_zero_adamw_allgather": [c_void_p] * 5 + [c_int, c_ll, c_ll] + [ctypes.c_float] * 5 + [c_int, c_void_p, c_void_p, c_void_p],
     "hg_rope": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
@@ -49,6 +50,7 @@ _SIGNATURES = {
     "hg_embedding_bwd": [c_void_p] * 4 + [c_int] * 6 + [c_void_p],
     "hg_cast_f32_bf16": [c_void_p, c_void_p, c_ll, c_void_p],
     "hg_add_bf16": [c_void_p, c_void_p, c_void_p, c_ll, c_void_p],
+    "hg_attn_merge": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "hg_xent_stats": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "hg_xent_bwd": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "hg_adamw": [c_void_p] * 5 + [c_ll, c_int, c_float, c_float, c_float, c_float, c_float, c_int, c_void_p,
@@ -61,6 +63,8 @@ _SIGNATURES = {
                     [c_int] * 9 + [c_float, c_void_p],
     "hg_ag_gemm_bf16": [c_void_p] * 7 + [c_int] * 10 + [c_void_p],
     "hg_gemm_rs_bf16": [c_void_p] * 5 + [c_int] * 10 + [c_void_p],
+    "hg_ag_gemm2_bf16": [c_void_p] * 7 + [c_int] * 10 + [c_void_p],
+    "hg_gemm_rs2_bf16": [c_void_p] * 5 + [c_int] * 10 + [c_void_p],
     "hg_read_status": [c_int],
     "hg_gemm_gated_selftest": [c_void_p],
     "hg_library_version": [],

@@ -186,3 +186,19 @@ def flash_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, causal: b
 
     out, lse = _Flash.apply(fix(q), fix(k), fix(v), causal, scale, q_pos0, k_pos0)
     return (out, lse) if return_lse else out
+
+
+def attention_merge(out_acc: torch.Tensor, lse_acc: torch.Tensor, out_new: torch.Tensor, lse_new: torch.Tensor):
+    """In-place log-sum-exp merge of a partial attention result over a disjoint key set (CUDA):
+    ``out_acc`` fp32 ``[S, B, h, d]`` contiguous, ``lse_acc`` fp32 ``[B, h, S]`` whose last dimension may be a slice of a
+    longer sequence, ``out_new`` bf16 ``[S, B, h, d]``, ``lse_new`` fp32 ``[B, h, S]``.  Oracle:
+    ``l = logaddexp(lse_acc, lse_new); out = exp(lse_acc - l) * out_acc + exp(lse_new - l) * out_new``."""
+    S, B, h, d = out_acc.shape
+    if not (out_acc.is_contiguous() and lse_acc.stride(2) == 1 and lse_acc.stride(0) == h * lse_acc.stride(1)):
+        raise ValueError("attention_merge: unsupported layout")
+    out_new, lse_new = out_new.contiguous(), lse_new.contiguous()
+    lib = _lib.load()
+    rc = lib.hg_attn_merge(out_acc.data_ptr(), lse_acc.data_ptr(), lse_acc.stride(1), out_new.data_ptr(),
+                           lse_new.data_ptr(), S, B * h, d, _lib.stream())
+    _lib.check(rc, "hg_attn_merge")
+    _lib.count_launch()

@@ -1,4 +1,5 @@
-"""Python face of the fused tensor-parallel kernels (csrc/sm100/fused_tp.cu).
+"""Python face of the fused tensor-parallel kernels (csrc/sm100/fused_tp2.cu on the CTA-pair tile when a rank's slab
+is a multiple of 256 rows, csrc/sm100/fused_tp.cu on the one-CTA tile otherwise).
 
 ``all_gather_linear``      sequence-sharded ``[S/t, B, K]`` x column-parallel weight  -> ``[S, B, N/t]``
 ``linear_reduce_scatter``  ``[S, B, K/t]`` x row-parallel weight -> partial sums reduced to ``[S/t, B, N]``
@@ -17,6 +18,7 @@ with two parities so that call ``n + 1`` never overwrites what a slower peer sti
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Tuple
 
 import torch
@@ -83,6 +85,11 @@ def usable(x2d_rows_per_rank: int, cols: int) -> bool:
     return x2d_rows_per_rank % 128 == 0 and cols % 8 == 0
 
 
+def _pair_tile(slab_rows: int) -> bool:
+    """The CTA-pair kernels tile 256 rows per cluster: a rank's slab must be made of whole pair tiles."""
+    return slab_rows % 256 == 0 and os.environ.get("HG_FUSED_PAIR", "1") == "1"
+
+
 # ---- raw launches ------------------------------------------------------------------------------------------
 def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, bias=None):
     """x_local ``[slab, K]`` (this rank's rows) -> (``[t*slab, N]``, gathered ``[t*slab, K]``)."""
@@ -98,9 +105,10 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, b
     gathered = torch.empty((t * slab, K), dtype=torch.bfloat16, device=x_local.device)
     ready = torch.zeros(t * slab // 128, dtype=torch.int32, device=x_local.device)
     out = torch.empty((t * slab, N), dtype=torch.bfloat16, device=x_local.device)
-    rc = lib.hg_ag_gemm_bf16(ws.ptr_array(ws.off_ag[par]), ws.ptr_array(0), gathered.data_ptr(), ready.data_ptr(),
-                             w.data_ptr(), out.data_ptr(), _lib.ptr(bias), t, ws.me, ws.ag_epoch, slab, N, K,
-                             w.stride(0), out.stride(0), int(b_mn), OUT_BF16, _lib.stream())
+    fn = lib.hg_ag_gemm2_bf16 if _pair_tile(slab) else lib.hg_ag_gemm_bf16
+    rc = fn(ws.ptr_array(ws.off_ag[par]), ws.ptr_array(0), gathered.data_ptr(), ready.data_ptr(),
+            w.data_ptr(), out.data_ptr(), _lib.ptr(bias), t, ws.me, ws.ag_epoch, slab, N, K,
+            w.stride(0), out.stride(0), int(b_mn), OUT_BF16, _lib.stream())
     _lib.check(rc, "hg_ag_gemm_bf16")
     _lib.count_launch()
     return out, gathered
@@ -117,9 +125,10 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False) -> torc
     ws.rs_epoch += 1
     par = ws.rs_epoch & 1
     out = torch.empty((slab, N), dtype=torch.bfloat16, device=x.device)
-    rc = lib.hg_gemm_rs_bf16(x.data_ptr(), w.data_ptr(), out.data_ptr(), ws.ptr_array(ws.off_rs[par]),
-                             ws.ptr_array(ws.off_flags[par]), t, ws.me, ws.rs_epoch, slab, N, K, x.stride(0),
-                             w.stride(0), out.stride(0), int(b_mn), _lib.stream())
+    fn = lib.hg_gemm_rs2_bf16 if _pair_tile(slab) else lib.hg_gemm_rs_bf16
+    rc = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), ws.ptr_array(ws.off_rs[par]),
+            ws.ptr_array(ws.off_flags[par]), t, ws.me, ws.rs_epoch, slab, N, K, x.stride(0),
+            w.stride(0), out.stride(0), int(b_mn), _lib.stream())
     _lib.check(rc, "hg_gemm_rs_bf16")
     _lib.count_launch()
     return out

@@ -78,12 +78,37 @@ def reduce_scatter_peer(grads: SymmetricBuffer, me: int, shard_numel: int, out: 
     return out
 
 
+class SignalSlots:
+    """Per-group signal words in symmetric memory (``int32[8]`` per rank) and the call counter that the ranks of the
+    group advance in lockstep: the bf16-wire reduce-scatter publishes / awaits ``epoch`` through them."""
+
+    _by_group: Dict[tuple, "SignalSlots"] = {}
+
+    def __init__(self, device, pg):
+        self.buf = SymmetricBuffer(8, torch.int32, device, pg)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group=pg)           # every rank's slots are zero before anybody publishes
+
+    @classmethod
+    def get(cls, device, pg) -> "SignalSlots":
+        key = (str(device), id(pg))
+        if key not in cls._by_group:
+            cls._by_group[key] = SignalSlots(device, pg)
+        return cls._by_group[key]
+
+    def next_epoch(self) -> int:
+        self.epoch += 1
+        return self.epoch
+
+
 class StagingPair:
     """Two symmetric buffers of the wire dtype, used alternately by consecutive reductions."""
 
     def __init__(self, numel: int, dtype, device, pg):
         self.bufs = [SymmetricBuffer(numel, dtype, device, pg) for _ in range(2)]
         self.turn = 0
+        self.signals = SignalSlots.get(device, pg)
 
     def next(self) -> SymmetricBuffer:
         b = self.bufs[self.turn]
@@ -117,11 +142,17 @@ def round_into_staging(grad32: torch.Tensor, staging: SymmetricBuffer, me: int, 
 
 
 def reduce_scatter_staged(staging: SymmetricBuffer, own32: torch.Tensor, me: int, shard_numel: int, out: torch.Tensor,
-                          accumulate: bool = False, max_ctas: int = 0):
-    """bf16 on the wire: ``out (+)= own32[slice] + sum_{r != me} staging_r[slice]`` (fp32 sum in rank order)."""
+                          accumulate: bool = False, max_ctas: int = 0, signals: "SignalSlots" = None):
+    """bf16 on the wire: ``out (+)= own32[slice] + sum_{r != me} staging_r[slice]`` (fp32 sum in rank order).
+
+    With ``signals`` the kernel itself waits until every rank of the group has reached the same call (each rank
+    publishes the call's epoch in its peers' signal slots after its rounding kernel, bounded wait); without, the caller
+    must have ordered the ranks (``peer_barrier``)."""
     lib = _lib.load()
+    sig_arr, epoch = (signals.buf.ptr_array(), signals.next_epoch()) if signals is not None else (None, 0)
     rc = lib.hg_zero_reduce_scatter_bf16wire(staging.ptr_array(), own32.data_ptr(), staging.t, me, shard_numel,
-                                             out.data_ptr(), int(bool(accumulate)), int(max_ctas), _lib.stream())
+                                             out.data_ptr(), int(bool(accumulate)), int(max_ctas), sig_arr, epoch,
+                                             _lib.stream())
     _lib.check(rc, "hg_zero_reduce_scatter_bf16wire")
     _lib.count_launch()
     return out

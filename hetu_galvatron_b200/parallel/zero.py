@@ -60,7 +60,7 @@ class _ReduceState:
     def __init__(self):
         self.last_microbatch = True       # set by the pipeline engine before each backward
         self.overlap = os.environ.get("HG_OVERLAP_REDUCE", "1") == "1"
-        self.max_ctas = int(os.environ.get("HG_REDUCE_CTAS", "32"))   # grid cap of a reduction that runs beside GEMMs
+        self.max_ctas = int(os.environ.get("HG_REDUCE_CTAS", "48"))   # grid cap of a reduction that runs beside GEMMs
         self._streams: Dict[int, "torch.cuda.Stream"] = {}
         self.used = False                 # something was queued on a side stream since the last join
 
@@ -389,8 +389,9 @@ class ShardedUnit:
             if lowp:
                 st = self._staging.next()
                 fz.round_into_staging(mg, st, self.rank, self.shard_numel)
-                self.sync_peers()        # every rank's staged gradients are complete
-                fz.reduce_scatter_staged(st, mg, self.rank, self.shard_numel, out, accumulate, max_ctas)
+                # the kernel waits for every rank's staged gradients itself (signal slots, bounded wait)
+                fz.reduce_scatter_staged(st, mg, self.rank, self.shard_numel, out, accumulate, max_ctas,
+                                         signals=self._staging.signals)
                 # no rendezvous afterwards: the staging buffers alternate, and a rank rounds into a buffer again only
                 # after the rendezvous of the unit in between, which every peer enters after its reads of this one
             else:

@@ -1,7 +1,7 @@
 """Device-timed comparison of the fused tensor-parallel kernels with "NCCL collective + the same GEMM".
 
     torchrun --nnodes 1 --nproc-per-node 2 --master-addr 127.0.0.1 -m hetu_galvatron_b200.profiler.fused_tp_bench \
-        --slab 4096 --k 4096 --n 6144
+        --slab 4096 --kdim 4096 --ndim 6144
 
 Per configuration: all-gather -> GEMM (``[t*slab, K] x [N, K]^T`` with the input sharded by rows) and GEMM ->
 reduce-scatter (``[t*slab, K] x [N, K]^T`` summed over ranks, output sharded by rows).  Each variant is timed with
@@ -94,8 +94,8 @@ def fused_vs_nccl(group, slab: int, K: int, N: int, iters: int = 10):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--slab", type=int, default=4096)
-    ap.add_argument("--k", type=int, default=4096)
-    ap.add_argument("--n", type=int, default=6144)
+    ap.add_argument("--kdim", type=int, default=4096)   # not --k / --n: torchrun would read them as its own
+    ap.add_argument("--ndim", type=int, default=6144)
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args()
     rank = int(os.environ.get("LOCAL_RANK", os.environ.get("RANK", "0")))
@@ -105,9 +105,9 @@ def main():
 
     world = dist.get_world_size()
     grp = CommGroup(list(range(world)), dist.group.WORLD, dist.get_rank())
-    res = fused_vs_nccl(grp, a.slab, a.k, a.n, a.iters)
+    res = fused_vs_nccl(grp, a.slab, a.kdim, a.ndim, a.iters)
     if dist.get_rank() == 0:
-        print(json.dumps({"gpus": world, "slab": a.slab, "K": a.k, "N": a.n, **res}))
+        print(json.dumps({"gpus": world, "slab": a.slab, "K": a.kdim, "N": a.ndim, **res}))
     dist.barrier()
     dist.destroy_process_group()
 

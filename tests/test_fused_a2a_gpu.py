@@ -112,10 +112,10 @@ def train_moe(cfg):
                  activation_func="torch.nn.functional.silu", gated_linear_unit=True, num_query_groups=2)
     model.update(cfg.get("model", {}))
     args = GalvatronRuntimeArgs(parallel=dict(mixed_precision="bf16", **cfg.get("parallel", {})), model=model,
-                                train=dict(seq_length=256, global_batch_size=8, chunks=2, lr=1e-3))
+                                train=dict(seq_length=cfg.get("seq", 256), global_batch_size=8, chunks=2, lr=1e-3))
     m = build_model(args, device=dev, full_init=True, fused_comm=cfg["fused"])
     opt = ShardedAdamW(m.sharded_units, lr=1e-3, betas=(0.9, 0.95), weight_decay=0.01, clip_grad=1.0, device=dev)
-    tok = torch.randint(0, 1024, (8, 257), generator=torch.Generator().manual_seed(3))
+    tok = torch.randint(0, 1024, (8, cfg.get("seq", 256) + 1), generator=torch.Generator().manual_seed(3))
     B = m.local_batch_size()
     d = m.vocab_ctx.dp.rank if m.vocab_ctx.dp is not None else 0
     mine = tok[d * B:(d + 1) * B].to(dev)
@@ -180,6 +180,18 @@ def test_model_training_matches_nccl_path(name, cfg):
     for r in range(2):
         for (l0, n0), (l1, n1) in zip(ref[r], got[r]):
             assert abs(l0 - l1) / abs(l0) < 5e-3 and abs(n0 - n1) / n0 < 5e-2, (name, ref, got)
+
+
+def test_ring_context_parallel_matches_the_all_gather_variant():
+    """Zig-zag context parallelism over 2 GPUs: K/V blocks exchanged hop by hop with log-sum-exp merging (flash kernels
+    at chunk offsets, merge kernel, dK/dV accumulators travelling with their block) against the all-gather variant."""
+    _need(2)
+    cfg = {"parallel": {"global_cp_deg": 2, "vocab_cp": 2}, "fused": False, "seq": 512}
+    ref = run_distributed(__file__, "train_moe", 2, cfg, timeout=300, extra_env=dict(ENV, HG_CP_ALLGATHER="1"))
+    got = run_distributed(__file__, "train_moe", 2, cfg, timeout=300, extra_env=ENV)
+    for r in range(2):
+        for (l0, n0), (l1, n1) in zip(ref[r], got[r]):
+            assert abs(l0 - l1) / abs(l0) < 5e-3 and abs(n0 - n1) / n0 < 5e-2, (ref, got)
 
 
 def test_flex_dispatcher_selects_the_pull_kernels():

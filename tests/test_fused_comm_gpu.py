@@ -93,8 +93,10 @@ def _need(n):
         pytest.skip("needs %d GPUs" % n)
 
 
-@pytest.mark.parametrize("slab,K,N", [(256, 512, 768), (1024, 4096, 1536)])
+@pytest.mark.parametrize("slab,K,N", [(256, 512, 768), (1024, 4096, 1536), (384, 1024, 1000), (512, 1024, 1320)])
 def test_fused_tp_kernels_match_reference(slab, K, N):
+    """Slabs of whole 256-row tiles run on the CTA-pair kernels (fused_tp2.cu), the 384-row slab on the one-CTA kernels
+    (fused_tp.cu); N = 1000 / 1320 leave a partial last column tile."""
     _need(2)
     res = run_distributed(__file__, "fused_vs_reference", 2, {"slab": slab, "K": K, "N": N}, timeout=240,
                           extra_env={"HG_BACKEND": "nccl", "NCCL_NVLS_ENABLE": "0"})

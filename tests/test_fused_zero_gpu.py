@@ -57,11 +57,17 @@ def kernels_vs_nccl(cfg):
         fz.reduce_scatter_staged(st, grads.tensor, rank, S, got16, accumulate=False, max_ctas=8 if rep else 0)
         fz.reduce_scatter_staged(st, grads.tensor, rank, S, got16, accumulate=True)
         fz.peer_barrier(dist.group.WORLD, dev)
+        # the same reduction with the kernel's own rendezvous instead of a collective before it
+        st2 = pair.next()
+        fz.round_into_staging(grads.tensor, st2, rank, S)
+        got16b = torch.empty(S, device=dev)
+        fz.reduce_scatter_staged(st2, grads.tensor, rank, S, got16b, signals=pair.signals)
         rounded = [torch.empty(n, device=dev) for _ in range(t)]
         dist.all_gather(rounded, grads.tensor.clone())
         lo, hi = rank * S, (rank + 1) * S
         want = sum((x[lo:hi] if r == rank else x[lo:hi].bfloat16().float()) for r, x in enumerate(rounded))
         out["rs16_%d" % rep] = float((got16 - 2 * want).abs().max() / want.abs().max())
+        out["rs16_flags_%d" % rep] = float((got16b - want).abs().max() / want.abs().max())
         # AdamW + all-gather against the plain kernel + NCCL all-gather
         master = torch.randn(S, device=dev, generator=g)
         m0, v0 = torch.randn(S, device=dev, generator=g) * 0.1, torch.rand(S, device=dev, generator=g) * 0.01
@@ -129,7 +135,7 @@ def test_peer_kernels_match_nccl(shard):
         assert r["status"] == 0, r
         for rep in range(2):
             assert r["rs_%d" % rep] < 1e-6 and r["adam_state_%d" % rep] < 1e-5 and r["gathered_%d" % rep] < 0.04, r
-            assert r["rs16_%d" % rep] < 1e-6, r
+            assert r["rs16_%d" % rep] < 1e-6 and r["rs16_flags_%d" % rep] < 1e-6, r
 
 
 @pytest.mark.parametrize("dp_type,defer,fp32_wire", [("zero2", True, False), ("zero2", True, True), ("zero3", True, False),

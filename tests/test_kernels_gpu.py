@@ -220,6 +220,28 @@ def test_flash_attention(hd, S, B, nh, ng, causal):
     assert rel_err(v.grad, vr.grad) < 3e-2
 
 
+@pytest.mark.parametrize("hd", [128, 64])
+def test_attention_merge_of_two_key_halves(hd):
+    """Attention over keys [0, 256) and over keys [256, 512), merged through their log-sum-exp, equals attention over
+    all 512 keys; the running log-sum-exp is a slice of a longer row, as in the ring."""
+    torch.manual_seed(12)
+    S, B, nh, ng = 256, 2, 4, 2
+    q = torch.randn(S, B, nh, hd, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(2 * S, B, ng, hd, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(2 * S, B, ng, hd, device=DEV, dtype=torch.bfloat16)
+    full, lse_full = ops.attention_reference(q.float(), k.float(), v.float(), causal=True, q_pos0=S, k_pos0=0)
+    acc = torch.zeros(S, B, nh, hd, device=DEV)
+    lse_row = torch.full((B, nh, 3 * S), float("-inf"), device=DEV)
+    lse_acc = lse_row[:, :, S:2 * S]
+    for j in range(2):
+        o, lse = ops.flash_attention(q, k[j * S:(j + 1) * S], v[j * S:(j + 1) * S], causal=True, q_pos0=S, k_pos0=j * S,
+                                     return_lse=True)
+        ops.attention_merge(acc, lse_acc, o, lse)
+    assert rel_err(acc, full) < 2e-2
+    assert torch.allclose(lse_acc, lse_full, rtol=1e-3, atol=2e-3)
+    assert torch.isinf(lse_row[:, :, :S]).all() and torch.isinf(lse_row[:, :, 2 * S:]).all()
+
+
 def test_flash_attention_packed():
     torch.manual_seed(10)
     S, B, nh, ng, hd = 256, 2, 8, 2, 128

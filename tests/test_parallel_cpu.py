@@ -138,6 +138,33 @@ def test_context_parallel_zigzag():
     check(2, {"parallel": {"global_cp_deg": 2, "vocab_cp": 2}})
 
 
+def test_context_parallel_ring_of_four_and_all_gather_variant():
+    """Four ranks: K/V blocks make three hops, the dK/dV accumulators four; the all-gather variant gives the same."""
+    check(4, {"parallel": {"global_cp_deg": 4, "vocab_cp": 4}})
+    res = run_distributed(__file__, "train", 4, {"parallel": {"global_cp_deg": 4, "vocab_cp": 4}},
+                          extra_env={"HG_CP_ALLGATHER": "1"})
+    ref = baseline("dense", {"chunks": 1})
+    assert abs(res[0][0][0] - ref[0][0]) / ref[0][0] < 2e-4 and abs(res[0][2][1] - ref[2][1]) / ref[2][1] < 2e-3
+
+
+def test_ring_step_pairs_cover_the_causal_triangle_once():
+    from hetu_galvatron_b200.parallel.ring_attention import step_pairs
+
+    for c in (2, 3, 4, 8):
+        seen = {}
+        for r in range(c):
+            for t in range(c):
+                src = (r - t) % c
+                qc, kc = (r, 2 * c - 1 - r), (src, 2 * c - 1 - src)
+                for qi, kj in step_pairs(r, src, c):
+                    key = (qc[qi], kc[kj])
+                    assert key not in seen
+                    seen[key] = True
+        assert set(seen) == {(i, j) for i in range(2 * c) for j in range(i + 1)}
+        # balanced: every rank computes the same number of pairs
+        assert len({sum(len(step_pairs(r, (r - t) % c, c)) for t in range(c)) for r in range(c)}) == 1
+
+
 @pytest.mark.parametrize("ptype,chunks", [("gpipe", 2), ("pipedream_flush", 4)])
 def test_pipeline(ptype, chunks):
     check(2, {"chunks": chunks, "parallel": {"pp_deg": 2, "pipeline_type": ptype}})
