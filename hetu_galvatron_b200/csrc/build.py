@@ -57,30 +57,41 @@ def _run(cmd, log: Path | None = None):
     return proc
 
 
-def build_cuda(verbose: bool = False, jobs: int | None = None) -> Path:
+def build_cuda(verbose: bool = False, jobs: int | None = None, debug: bool = False) -> Path:
+    """``debug=True`` builds ``libhg_sm100_debug.so``: the same sources with ``-DHG_DEBUG_BOUNDS`` (index checks that
+    record a status code instead of touching memory; see ``HG_BOUNDS_OK`` in sm100_common.cuh).  ``ops/_lib.py`` loads
+    it when ``HG_DEBUG_KERNELS=1``."""
+    if debug:
+        return _build_cuda_variant(OBJ_DIR / "debug", "libhg_sm100_debug.so", ["-DHG_DEBUG_BOUNDS=1"], verbose, jobs)
+    return _build_cuda_variant(OBJ_DIR, "libhg_sm100.so", [], verbose, jobs)
+
+
+def _build_cuda_variant(obj_dir: Path, lib_name: str, extra_flags, verbose: bool, jobs) -> Path:
     src_dir = CSRC / "sm100"
     sources = sorted(src_dir.glob("*.cu"))
     headers = sorted(src_dir.glob("*.cuh")) + sorted(src_dir.glob("*.h"))
     OBJ_DIR.mkdir(exist_ok=True)
+    obj_dir.mkdir(exist_ok=True)
     LIB_DIR.mkdir(exist_ok=True)
     nvcc = _nvcc()
     todo = []
     objs = []
     for s in sources:
-        o = OBJ_DIR / (s.stem + ".o")
+        o = obj_dir / (s.stem + ".o")
         objs.append(o)
         if _newer([s, *headers], o):
             todo.append((s, o))
 
     def compile_one(pair):
         s, o = pair
-        _run([nvcc, *NVCC_FLAGS, "-I", str(src_dir), "-c", str(s), "-o", str(o)], log=OBJ_DIR / (s.stem + ".log"))
+        _run([nvcc, *NVCC_FLAGS, *extra_flags, "-I", str(src_dir), "-c", str(s), "-o", str(o)],
+             log=obj_dir / (s.stem + ".log"))
         if verbose:
             print("[build] nvcc", s.name)
 
     with ThreadPoolExecutor(max_workers=jobs or os.cpu_count() or 4) as ex:
         list(ex.map(compile_one, todo))
-    lib = LIB_DIR / "libhg_sm100.so"
+    lib = LIB_DIR / lib_name
     if todo or _newer(objs, lib):
         _run([nvcc, "-shared", "-o", str(lib), *map(str, objs), "-lcudart"])
         if verbose:
@@ -108,10 +119,13 @@ def build_host(verbose: bool = False):
     return out
 
 
-def build_all(verbose: bool = False):
+def build_all(verbose: bool = False, debug: bool = True):
     host = build_host(verbose)
     cuda = build_cuda(verbose)
-    return [cuda, *host]
+    out = [cuda, *host]
+    if debug:
+        out.append(build_cuda(verbose, debug=True))
+    return out
 
 
 def ptxas_report() -> str:

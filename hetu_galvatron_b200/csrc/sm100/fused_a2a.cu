@@ -16,6 +16,8 @@
 
 #include <cstdint>
 
+#include "sm100_common.cuh"
+
 namespace {
 
 constexpr int kMaxPeers = 8;
@@ -37,7 +39,9 @@ inline int grid_for(long long items) {
 // All quantities in units of 16 bytes (8 bf16).  vec = chunk / 8.
 __global__ void __launch_bounds__(kThreads)
 peer_gather_kernel(PeerPtrs src, int t, long long rows, int vec, long long src_off, long long src_stride,
-                   uint4* __restrict__ out, long long out_peer_stride, long long out_row_stride) {
+                   uint4* __restrict__ out, long long out_peer_stride, long long out_row_stride, int* status) {
+  if (!HG_BOUNDS_OK(t >= 1 && t <= kMaxPeers && src_off >= 0 && src_stride >= 0 && out_peer_stride >= 0 && out_row_stride >= 0, status))
+    return;
   const long long per_peer = rows * vec;
   const long long total = per_peer * t;
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -65,6 +69,7 @@ peer_gather_kernel(PeerPtrs src, int t, long long rows, int vec, long long src_o
 }
 
 constexpr int kMaxTopK = 8;
+long long g_src_rows_limit = 0;   // rows of the peers' source buffers for the debug build's row check (0 = unknown)
 
 __device__ __forceinline__ void fma8(float (&acc)[8], uint4 v, float s) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
@@ -81,7 +86,8 @@ __device__ __forceinline__ void fma8(float (&acc)[8], uint4 v, float s) {
 template <int K>
 __global__ void __launch_bounds__(kThreads)
 peer_gather_rows_kernel(PeerPtrs src, const int* __restrict__ peer, const int* __restrict__ row, long long n_out,
-                        int vec, long long src_row_stride, uint4* __restrict__ out, const float* __restrict__ scale) {
+                        int vec, long long src_row_stride, uint4* __restrict__ out, const float* __restrict__ scale,
+                        int t, long long src_rows, int* status) {
   const long long total = n_out * vec;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x; j < total; j += stride) {
@@ -94,7 +100,15 @@ peer_gather_rows_kernel(PeerPtrs src, const int* __restrict__ peer, const int* _
       const int pr = peer[o * K + k];
       sc[k] = pr < 0 ? 0.f : (scale ? scale[o * K + k] : 1.f);
       val[k] = make_uint4(0u, 0u, 0u, 0u);
-      if (pr >= 0) val[k] = __ldcs(reinterpret_cast<const uint4*>(src.p[pr]) + (long long)row[o * K + k] * src_row_stride + c);
+      if (pr >= 0) {
+        // the routing table names a peer of the group and a row of its buffer (checked in the debug build)
+        const long long rw = row[o * K + k];
+        if (!HG_BOUNDS_OK(pr < t && rw >= 0 && (src_rows <= 0 || rw < src_rows), status)) {
+          sc[k] = 0.f;
+          continue;
+        }
+        val[k] = __ldcs(reinterpret_cast<const uint4*>(src.p[pr]) + rw * src_row_stride + c);
+      }
     }
     if (K == 1 && scale == nullptr) {
       out[j] = val[0];
@@ -127,7 +141,7 @@ int hg_peer_gather_bf16(const void* const* src, int t, long long rows, long long
   const long long total = rows * (chunk / 8) * t;
   peer_gather_kernel<<<grid_for((total + kUnroll - 1) / kUnroll), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       pp, t, rows, int(chunk / 8), src_off / 8, src_stride / 8, reinterpret_cast<uint4*>(out), out_peer_stride / 8,
-      out_row_stride / 8);
+      out_row_stride / 8, hg_host::status_ptr());
   return int(cudaGetLastError());
 }
 
@@ -146,7 +160,8 @@ int hg_peer_gather_rows_bf16(const void* const* src, int t, const void* peer, co
 #define HG_ROWS(K_)                                                                                               \
   peer_gather_rows_kernel<K_><<<grid_for(total), kThreads, 0, st>>>(                                              \
       pp, reinterpret_cast<const int*>(peer), reinterpret_cast<const int*>(row), n_out, int(width / 8),           \
-      src_row_stride / 8, reinterpret_cast<uint4*>(out), reinterpret_cast<const float*>(scale))
+      src_row_stride / 8, reinterpret_cast<uint4*>(out), reinterpret_cast<const float*>(scale), t, g_src_rows_limit,      \
+      hg_host::status_ptr())
   switch (topk) {
     case 1: HG_ROWS(1); break;
     case 2: HG_ROWS(2); break;
@@ -159,6 +174,14 @@ int hg_peer_gather_rows_bf16(const void* const* src, int t, const void* peer, co
   }
 #undef HG_ROWS
   return int(cudaGetLastError());
+}
+
+// Debug build only: tell the row-list gather how many rows the peers' source buffers hold, so that it can check the
+// routing table's row indices (0 switches the check off).  Returns the previous value.
+long long hg_debug_set_gather_row_limit(long long rows) {
+  const long long old = g_src_rows_limit;
+  g_src_rows_limit = rows;
+  return old;
 }
 
 }  // extern "C"

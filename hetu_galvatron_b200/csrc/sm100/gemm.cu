@@ -85,6 +85,8 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     int counter = 0;
     for (int g = 0; g < gp.G; ++g) {
       const int r0 = gp.row_start[g], r1 = gp.row_start[g + 1];
+      // an expert's row range must lie inside the operand and not run backwards (checked in the debug build)
+      if (!HG_BOUNDS_OK(r0 >= 0 && r1 >= r0 && r1 <= p.M, p.status)) return;
       const int tm_cnt = (r1 - r0 + BM - 1) / BM;
       const int cnt = tm_cnt * tiles_n;
       // tiles of this group owned by this CTA: global index = counter + t

@@ -236,6 +236,7 @@ __device__ __forceinline__ void mma2(const Params& p, const Smem2& s, uint32_t t
 __device__ __forceinline__ void store_block_rows(const Params& p, const float* stg, int row0, int col0) {
   const int lane = int(lane_id());
   const int col = col0 + lane;
+  if (!HG_BOUNDS_OK(row0 >= 0 && row0 < p.M && col0 >= 0 && col0 < p.N, p.status)) return;
   if (col >= p.N) return;
   const float bias = p.bias != nullptr ? __bfloat162float(p.bias[col]) : 0.f;
   const int rows = min(32, p.M - row0);

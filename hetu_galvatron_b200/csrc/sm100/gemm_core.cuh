@@ -268,6 +268,7 @@ __device__ __forceinline__ void mma_loop(const Params& p, const SmemLayout& s, u
 __device__ __forceinline__ void store_row_chunk(const Params& p, int row, int col0, const uint32_t (&r)[32],
                                                 long long c_off = 0) {
   // 32 consecutive output columns of one row
+  if (!HG_BOUNDS_OK(row >= 0 && row < p.M && col0 >= 0 && col0 < p.N && c_off >= 0, p.status)) return;
   const bool full = (col0 + 32 <= p.N);
   float v[32];
 #pragma unroll

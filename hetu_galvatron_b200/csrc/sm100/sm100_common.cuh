@@ -32,6 +32,16 @@ __device__ __forceinline__ void set_status(int* status, int code) {
   if (status != nullptr) atomicCAS(status, 0, code);
 }
 
+// Debug build (-DHG_DEBUG_BOUNDS, libhg_sm100_debug.so): every index a kernel derives from its arguments (tile
+// coordinates, row ranges of expert segments, peer indices, rows of peer buffers) is checked before the access it
+// feeds; a failed check records kBadArgument in the status word and the access is skipped (no trap, no fault).
+// In the regular build the checks compile to nothing.
+#ifdef HG_DEBUG_BOUNDS
+#define HG_BOUNDS_OK(cond, status) ((cond) ? true : (::hg::set_status((status), ::hg::kBadArgument), false))
+#else
+#define HG_BOUNDS_OK(cond, status) (true)
+#endif
+
 // Every spin wait is bounded in wall-clock time (the global nanosecond timer), not in iterations:
 // one mbarrier.try_wait may itself block for a hardware-defined slice of time.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s

@@ -27,6 +27,7 @@ import torch.distributed as dist
 import torch.nn as nn
 
 from .. import ops
+from ..ops.gemm import OUT_F32, OUT_F32_ACC
 from ..parallel import mappings as mp
 from ..parallel.zero import ShardedUnit, UnitWrapper
 from .modules import GalvatronAttention, Norm, _param, init_normal_sharded_, ops_add
@@ -278,6 +279,70 @@ def grouped_linear(x, w, row_start):
     return _GroupedLinear.apply(x, w, row_start)
 
 
+class _ExpertSliceLinear(torch.autograd.Function):
+    """``y = x @ w[j].T`` for one expert ``j`` of a stacked weight ``[E, N, K]`` on the dense tcgen05 GEMM; the weight
+    gradient goes into expert ``j``'s slice of the stacked weight's ``main_grad`` (or of a dense gradient)."""
+
+    @staticmethod
+    def forward(ctx, x, w, j, first_use):
+        ctx.save_for_backward(x, w)
+        ctx.j, ctx.first_use = j, first_use
+        return ops.gemm(x, w[j])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        j = ctx.j
+        dy = dy.contiguous()
+        dx = ops.gemm(dy, w[j], b_mn=True)
+        mg = getattr(w, "main_grad", None)
+        if mg is not None:
+            fresh = getattr(w, "mg_fresh", False)
+            if fresh and ctx.first_use:
+                mg.zero_()               # the experts run one by one: clear the stack once, then every slice accumulates
+                w.mg_fresh = False
+            ops.gemm(dy, x, a_mn=True, b_mn=True, out=mg[j], out_mode=OUT_F32_ACC)
+            return dx, None, None, None
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        ops.gemm(dy, x, a_mn=True, b_mn=True, out=dw[j], out_mode=OUT_F32)
+        return dx, dw.to(w.dtype), None, None
+
+
+def sequential_expert_mlp(x, w1, w2, row_start, activation):
+    """The experts one after the other on the rows ``[row_start[g], row_start[g+1])`` (``moe_grouped_gemm: false``;
+    galvatron/core/runtime/moe/mlp.py:128-211).  The segment bounds are read on the host (one synchronisation per
+    layer), which the grouped form avoids."""
+    rs = row_start.tolist()
+    out = x.new_zeros((x.shape[0], w2.shape[1]))
+    order = [g for g in range(w1.shape[0]) if rs[g + 1] > rs[g]]
+    for n, g in enumerate(order):
+        xs = x[rs[g]:rs[g + 1]]
+        # autograd runs the experts in reverse: the last expert of the forward is the first to touch main_grad
+        first_in_backward = n == len(order) - 1
+        if x.is_cuda:
+            y = _ExpertSliceLinear.apply(xs, w1, g, first_in_backward)
+            o = _ExpertSliceLinear.apply(ops.activation(y, activation), w2, g, first_in_backward)
+        else:
+            o = torch.nn.functional.linear(ops.activation(torch.nn.functional.linear(xs, w1[g]), activation), w2[g])
+        out = _WriteRows.apply(out, o, rs[g])
+    return out
+
+
+class _WriteRows(torch.autograd.Function):
+    """``out[start : start + rows] = part`` as a differentiable in-place write into a buffer built for it."""
+
+    @staticmethod
+    def forward(ctx, out, part, start):
+        ctx.start, ctx.rows = start, part.shape[0]
+        out[start:start + part.shape[0]] = part
+        ctx.mark_dirty(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, g[ctx.start:ctx.start + ctx.rows], None
+
+
 class ExpertMLP(nn.Module):
     def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str):
         super().__init__()
@@ -311,6 +376,9 @@ class ExpertMLP(nn.Module):
                                  seed, base + ".fc2", full_init)
 
     def forward(self, x: torch.Tensor, row_start: torch.Tensor) -> torch.Tensor:
+        if not self.spec.grouped_gemm:
+            return sequential_expert_mlp(x, self.linear_fc1.weight, self.linear_fc2.weight, row_start,
+                                         self.spec.activation)
         y = grouped_linear(x, self.linear_fc1.weight, row_start)
         a = ops.activation(y, self.spec.activation)
         return grouped_linear(a, self.linear_fc2.weight, row_start)

@@ -13,7 +13,9 @@ from pathlib import Path
 import torch
 
 _LIB = None
-_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / "libhg_sm100.so"
+# HG_DEBUG_KERNELS=1 selects the bounds-checking build of the same kernels (csrc/build.py::build_cuda(debug=True))
+DEBUG_KERNELS = os.environ.get("HG_DEBUG_KERNELS", "0") == "1"
+_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / ("libhg_sm100_debug.so" if DEBUG_KERNELS else "libhg_sm100.so")
 
 c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 
@@ -65,6 +67,7 @@ _SIGNATURES = {
     "hg_gemm_rs_bf16": [c_void_p] * 5 + [c_int] * 10 + [c_void_p],
     "hg_ag_gemm2_bf16": [c_void_p] * 7 + [c_int] * 10 + [c_void_p],
     "hg_gemm_rs2_bf16": [c_void_p] * 5 + [c_int] * 10 + [c_void_p],
+    "hg_debug_set_gather_row_limit": [c_ll],
     "hg_read_status": [c_int],
     "hg_gemm_gated_selftest": [c_void_p],
     "hg_library_version": [],
@@ -88,7 +91,7 @@ def load():
         if os.environ.get("HG_AUTOBUILD", "1") == "1":
             from ..csrc import build as _build
 
-            _build.build_cuda()
+            _build.build_cuda(debug=DEBUG_KERNELS)
     if not _LIB_PATH.exists():
         raise RuntimeError(
             "libhg_sm100.so is missing: run `python -m hetu_galvatron_b200.csrc.build` (nvcc, sm_100a) first")

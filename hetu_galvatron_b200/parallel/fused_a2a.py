@@ -140,6 +140,8 @@ def gather_rows(slot: SymmetricBuffer, peer: torch.Tensor, row: torch.Tensor, n_
     """``out[o] = sum_k scale[o, k] * src_{peer[o, k]}[row[o, k]]`` over the peers' staging slots (bf16 rows)."""
     lib = _lib.load()
     out = torch.empty((n_out, width), dtype=torch.bfloat16, device=peer.device)
+    if _lib.DEBUG_KERNELS:     # the debug build checks every routed row against the size of the peers' buffers
+        lib.hg_debug_set_gather_row_limit(slot.tensor.numel() // max(1, src_row_stride))
     rc = lib.hg_peer_gather_rows_bf16(slot.ptr_array(), slot.t, peer.data_ptr(), row.data_ptr(), n_out, topk, width,
                                       src_row_stride, out.data_ptr(), _lib.ptr(scale), _lib.stream())
     _lib.check(rc, "hg_peer_gather_rows_bf16")

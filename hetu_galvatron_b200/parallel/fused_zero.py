@@ -29,20 +29,48 @@ from ..ops import _lib
 MAX_PEERS = 8
 
 
+GUARD_BYTES = 512          # debug build: canary region before and after every symmetric buffer
+GUARD_BYTE = 0xA5
+_GUARDED: List["SymmetricBuffer"] = []
+
+
 class SymmetricBuffer:
-    """A tensor allocated identically on every rank of ``pg`` and mapped into all of them."""
+    """A tensor allocated identically on every rank of ``pg`` and mapped into all of them.
+
+    With ``HG_DEBUG_KERNELS=1`` the allocation carries a canary region on both sides that peers and local kernels must
+    never write; :func:`verify_guards` checks them (a peer store that ran past its slice lands there first)."""
 
     def __init__(self, numel: int, dtype, device, pg):
         import torch.distributed._symmetric_memory as symm
 
-        self.tensor = symm.empty(numel, dtype=dtype, device=device)
-        self.tensor.zero_()
-        self.handle = symm.rendezvous(self.tensor, pg)
-        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        esize = torch.empty(0, dtype=dtype).element_size()
+        guard = GUARD_BYTES // esize if _lib.DEBUG_KERNELS else 0
+        self._raw = symm.empty(numel + 2 * guard, dtype=dtype, device=device)
+        self._raw.zero_()
+        self.tensor = self._raw[guard:guard + numel]
+        self.handle = symm.rendezvous(self._raw, pg)
+        self.ptrs: List[int] = [int(p) + guard * esize for p in self.handle.buffer_ptrs]
         self.t = len(self.ptrs)
+        self._guard = guard
+        if guard:
+            for g in self._guards():
+                g.view(torch.uint8).fill_(GUARD_BYTE)
+            _GUARDED.append(self)
+
+    def _guards(self):
+        g = self._guard
+        return (self._raw[:g], self._raw[self._raw.numel() - g:])
+
+    def guards_intact(self) -> bool:
+        return self._guard == 0 or all(bool((g.view(torch.uint8) == GUARD_BYTE).all()) for g in self._guards())
 
     def ptr_array(self, byte_offset: int = 0):
         return (ctypes.c_void_p * self.t)(*[p + byte_offset for p in self.ptrs])
+
+
+def verify_guards() -> int:
+    """Number of symmetric buffers whose canary regions were overwritten (always 0 outside the debug build)."""
+    return sum(0 if b.guards_intact() else 1 for b in _GUARDED)
 
 
 def available(device, n: int) -> bool:

@@ -392,10 +392,61 @@ def profile_overlap(output_dir: str, multiply: int = 4, n: int = 4096, iters: in
     return coe
 
 
+def profile_fused_tp(tp_degrees: List[int], output_dir: str, nodes: int, gpus_per_node: int, slab_tokens: int = 8192,
+                     hidden: int = 4096, ffn: int = 11008) -> Dict[str, float]:
+    """The fused tensor-parallel kernels (all-gather -> GEMM, GEMM -> reduce-scatter over peer memory) against "NCCL
+    collective + the same GEMM" on consecutive groups of every degree, on the two GEMM shapes of a decoder layer
+    (QKV-like ``hidden -> 3*hidden/t`` and fc2-like ``ffn/t -> hidden``; ``slab_tokens`` rows in total).
+
+    Written to ``fused_tp_time_<nodes>nodes_<gpus>gpus_per_node.json``: the raw times per degree, and
+    ``fused_comm_hidden_fraction_tp<t>`` = the share of the collective's exposed time that the fused kernel hides,
+    ``1 - (fused - gemm_only) / (nccl_path - gemm_only)`` averaged over the two ops (clamped to [0, 1]).  The same
+    fractions are copied into ``b200_refit.json``, where the search's cost model reads them (CUDA only)."""
+    from ..parallel.groups import CommGroup
+    from .fused_tp_bench import fused_vs_nccl
+
+    device, rank = _device(), dist.get_rank()
+    out: Dict[str, float] = {}
+    if device.type != "cuda":
+        return out
+    for tp in tp_degrees:
+        if tp < 2:
+            continue
+        g = gen_profiling_groups(tp, True)
+        ranks = dist.get_process_group_ranks(g)
+        grp = CommGroup(list(ranks), g, ranks.index(rank))
+        slab = max(256, slab_tokens // tp // 256 * 256)
+        ag = fused_vs_nccl(grp, slab, hidden, 3 * hidden // tp // 8 * 8, iters=6)
+        rs = fused_vs_nccl(grp, slab, ffn // tp // 8 * 8, hidden, iters=6)
+        hid = []
+        for res, op in ((ag, "ag"), (rs, "rs")):
+            exposed = res["%s_nccl_ms" % op] - res["gemm_only_ms"]
+            left = res["%s_fused_ms" % op] - res["gemm_only_ms"]
+            hid.append(min(1.0, max(0.0, 1.0 - left / exposed)) if exposed > 1e-6 else 0.0)
+        frac = sum(hid) / len(hid)
+        frac = _group_mean(frac, None, dist.get_world_size(), device)
+        entry = {"fused_tp_size_%d_ag_fused_ms" % tp: ag["ag_fused_ms"], "fused_tp_size_%d_ag_nccl_ms" % tp: ag["ag_nccl_ms"],
+                 "fused_tp_size_%d_rs_fused_ms" % tp: rs["rs_fused_ms"], "fused_tp_size_%d_rs_nccl_ms" % tp: rs["rs_nccl_ms"],
+                 "fused_tp_size_%d_ag_frac_of_roofline" % tp: ag["ag_frac_of_roofline"],
+                 "fused_tp_size_%d_rs_frac_of_roofline" % tp: rs["rs_frac_of_roofline"],
+                 "fused_comm_hidden_fraction_tp%d" % tp: frac}
+        out.update(entry)
+        if rank == 0:
+            for k, v in entry.items():
+                _save(output_dir, "fused_tp_time_%dnodes_%dgpus_per_node.json", nodes, gpus_per_node, k, v)
+                print("%s: %.4f" % (k, v))
+            refit = os.path.join(output_dir, "b200_refit.json")
+            cfg = read_json_config(refit) if os.path.exists(refit) else {}
+            cfg["fused_comm_hidden_fraction_tp%d" % tp] = frac
+            write_json_config(cfg, refit)
+        dist.barrier()
+    return out
+
+
 # ---- command line -----------------------------------------------------------------------------------------------------
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n")[0])
-    ap.add_argument("what", choices=["allreduce", "p2p", "all2all", "overlap", "all"])
+    ap.add_argument("what", choices=["allreduce", "p2p", "all2all", "overlap", "fused", "all"])
     ap.add_argument("--global_tp_deg", type=int, nargs="+", default=None)
     ap.add_argument("--pp_deg", type=int, nargs="+", default=None)
     ap.add_argument("--local_batch_size", type=int, nargs="+", default=[32])
@@ -431,6 +482,8 @@ def main(argv=None):
                                measurements=a.measurements))
     if a.what in ("overlap", "all"):
         res["overlap_coe"] = profile_overlap(a.output_dir, a.overlap_time_multiply)
+    if a.what in ("fused", "all"):
+        res.update(profile_fused_tp(tp, a.output_dir, nodes, gpn))
     dist.barrier()
     return res
 

@@ -69,6 +69,12 @@ def check_device_status(device) -> None:
     so that a step computed from incomplete tiles is rejected everywhere before its parameters are kept or
     checkpointed, and no rank is left waiting in a collective for one that raised."""
     code = _device_status_code(device)
+    if code == 0 and getattr(device, "type", "cpu") == "cuda":
+        from ..ops import _lib
+        from ..parallel import fused_zero
+
+        if _lib.DEBUG_KERNELS and fused_zero.verify_guards():
+            code = 6     # something wrote outside a symmetric buffer: same class as a bad argument
     if dist.is_initialized() and dist.get_world_size() > 1:
         t = torch.tensor([code], dtype=torch.int32, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

@@ -82,7 +82,7 @@ class ProfileHardwareArgs:
     allgather_message_size_to_latency_dict_dict: dict = field(default_factory=dict)
     all2all_message_size_to_latency_dict_dict: dict = field(default_factory=dict)
     # B200 refit: fraction of the TP/SP collective time that the fused compute+collective kernels hide
-    fused_comm_hidden_fraction: float = 0.0
+    fused_comm_hidden_fraction: object = 0.0      # a float, or {tp degree: float}
     # B200 refit: optimizer step of one unsharded layer in ms (memory-bound AdamW + norm; scales with 1/sdp under ZeRO)
     optimizer_ms_per_layer: float = 0.0
 
@@ -168,7 +168,10 @@ class LayerTimeCost:
             if s.checkpoint:
                 n *= 1.5
             msg = self.lbsz * model_args.seq_length * model_args.hidden_size * (2 if train_args.mixed_precision else 4) / 1024 / 1024
-            self.tp_time = _lookup_latency(table, msg) * n * (1.0 - hw.fused_comm_hidden_fraction)
+            hidden = hw.fused_comm_hidden_fraction
+            if isinstance(hidden, dict):      # measured per degree; only the Megatron-TP path has fused GEMM kernels
+                hidden = hidden.get(s.tp_size, 0.0) if s.tp_size > 1 else 0.0
+            self.tp_time = _lookup_latency(table, msg) * n * (1.0 - hidden)
         # pipeline p2p
         self.p2p_coe = None
         if s.pp_size > 1 and hw.p2p_comm_coe_dict is not None:

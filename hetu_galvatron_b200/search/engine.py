@@ -441,7 +441,10 @@ class GalvatronSearchEngine:
         if os.path.exists(refit):
             r = read_json_config(refit)
             self.bwd_fwd_ratio = r.get("backward_forward_ratio")
-            self.fused_hidden = r.get("fused_comm_hidden_fraction", 0.0)
+            # scalar, or one measured value per tensor-parallel degree (profiler/hardware.py::profile_fused_tp)
+            per_tp = {int(k.rsplit("tp", 1)[1]): float(v) for k, v in r.items()
+                      if k.startswith("fused_comm_hidden_fraction_tp")}
+            self.fused_hidden = per_tp if per_tp else r.get("fused_comm_hidden_fraction", 0.0)
             self.optimizer_ms = r.get("optimizer_ms_per_layer", 0.0)
         return self.allreduce_bandwidth, self.p2p_bandwidth, self.overlap_coe, self.sp_allreduce, self.sp_all2all
 

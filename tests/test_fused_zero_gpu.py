@@ -115,6 +115,12 @@ def train(cfg):
         loss = model.forward_backward(mine[:, :-1], it, labels=mine[:, 1:])
         opt.step()
         out.append([float(loss), opt.grad_norm()])
+    if cfg.get("report_guards"):
+        from hetu_galvatron_b200.ops import _lib
+        from hetu_galvatron_b200.parallel import fused_zero as fz
+
+        _lib.assert_healthy()
+        out.append(["guards", fz.verify_guards()])
     return out
 
 

@@ -242,6 +242,13 @@ MOE = {"num_moe_experts": 4, "moe_ffn_hidden_size": 256, "moe_router_topk": 2, "
        "moe_token_dispatcher_type": "alltoall", "moe_aux_loss_coeff": 1e-2}
 
 
+def test_moe_grouped_and_sequential_experts_agree():
+    """``moe_grouped_gemm`` selects one grouped contraction over all experts or a loop over them: same training."""
+    base = {"chunks": 1, "model": MOE}
+    check(2, {"parallel": {"global_ep_deg": 2}, "model": dict(MOE, moe_grouped_gemm=True)}, base, key="moe", rtol=1e-3,
+          norm_rtol=2e-2)
+
+
 def test_moe_allgather_dispatcher():
     base = {"chunks": 1, "model": MOE}
     check(2, {"parallel": {"global_ep_deg": 2}, "model": dict(MOE, moe_token_dispatcher_type="allgather")}, base,
