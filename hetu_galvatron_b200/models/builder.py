@@ -19,7 +19,7 @@ import torch.nn as nn
 
 from ..parallel.groups import GroupFactory, LayerGroups, build_layer_groups, dense_layout, embedding_group_ranks
 from ..parallel.reshard import build_reshard
-from ..parallel.zero import ShardedUnit, UnitWrapper
+from ..parallel.zero import link_prefetch, ShardedUnit, UnitWrapper
 from ..runtime.plan import HybridPlan, LayerPlan
 from .modules import (GalvatronCausalLMHead, GalvatronDecoderLayer, GalvatronEmbedding, GalvatronFinalNorm)
 from .spec import LayerCtx, ModelSpec
@@ -154,4 +154,8 @@ def build_stage(spec: ModelSpec, plan: HybridPlan, groups: ModelGroups, device, 
             stage.reshards.append(re if re is not None else nn.Identity())
             stage.plans.append(lp)
         prev_lp = lp
+    flat = []
+    for u in stage.units:
+        flat.extend(getattr(u, "wrappers", [u]))
+    link_prefetch(flat)
     return stage

@@ -218,8 +218,11 @@ class GalvatronMoERouter(nn.Module):
         if s.jitter_eps and self.training:
             noise = torch.empty_like(xin).uniform_(1.0 - s.jitter_eps, 1.0 + s.jitter_eps)
             xin = xin * noise
-        dt = torch.float64 if s.router_dtype == "fp64" else torch.float32
-        logits = torch.nn.functional.linear(xin.to(dt), self.router.weight.to(dt)).float()
+        if xin.is_cuda and xin.dtype == torch.bfloat16 and s.router_dtype != "fp64" and s.experts % 8 == 0:
+            logits = _GateLinear.apply(xin, self.router.weight)     # tcgen05 GEMM, fp32 accumulation and output
+        else:
+            dt = torch.float64 if s.router_dtype == "fp64" else torch.float32
+            logits = torch.nn.functional.linear(xin.to(dt), self.router.weight.to(dt)).float()
         if s.z_loss_coeff and self.training:
             logits = _AuxLossScaler.apply(logits, z_loss(logits, s.z_loss_coeff))
         bias = getattr(self.router, "expert_bias", None)
@@ -277,6 +280,34 @@ def grouped_linear(x, w, row_start):
         pad = x.new_zeros((x.shape[0] - rs[-1], w.shape[1]))
         return torch.cat(outs + [pad], dim=0)
     return _GroupedLinear.apply(x, w, row_start)
+
+
+class _GateLinear(torch.autograd.Function):
+    """Router logits ``x [T, H] (bf16) @ W[E, H]^T -> [T, E]`` in fp32 on the tcgen05 GEMM (bf16 operands, fp32
+    accumulator written out unrounded), with both gradients on the same kernel; replaces the fp32 library GEMM on a
+    widened copy of the activations (galvatron/core/runtime/moe/router.py gating)."""
+
+    @staticmethod
+    def forward(ctx, x, w):
+        wl = w.detach().to(torch.bfloat16)
+        ctx.save_for_backward(x, wl)
+        ctx.w = w
+        return ops.gemm(x, wl, out_mode=OUT_F32)
+
+    @staticmethod
+    def backward(ctx, dlogits):
+        x, wl = ctx.saved_tensors
+        w = ctx.w
+        dl = dlogits.to(torch.bfloat16).contiguous()
+        dx = ops.gemm(dl, wl, b_mn=True)
+        mg = getattr(w, "main_grad", None)
+        if mg is not None and mg.dtype == torch.float32:
+            fresh = getattr(w, "mg_fresh", False)
+            ops.gemm(dl, x, a_mn=True, b_mn=True, out=mg, out_mode=OUT_F32 if fresh else OUT_F32_ACC)
+            w.mg_fresh = False
+            return dx, None
+        dw = ops.gemm(dl, x, a_mn=True, b_mn=True, out_mode=OUT_F32)
+        return dx, dw.to(w.dtype)
 
 
 class _ExpertSliceLinear(torch.autograd.Function):

@@ -62,6 +62,7 @@ class _ReduceState:
         self.overlap = os.environ.get("HG_OVERLAP_REDUCE", "1") == "1"
         self.max_ctas = int(os.environ.get("HG_REDUCE_CTAS", "48"))   # grid cap of a reduction that runs beside GEMMs
         self._streams: Dict[int, "torch.cuda.Stream"] = {}
+        self._gather_streams: Dict[int, "torch.cuda.Stream"] = {}
         self.used = False                 # something was queued on a side stream since the last join
 
     def stream(self, device):
@@ -71,6 +72,17 @@ class _ReduceState:
         st = self._streams.get(idx)
         if st is None:
             st = self._streams[idx] = torch.cuda.Stream(device=device)
+        return st
+
+    def gather_stream(self, device):
+        """Side stream of the ZeRO-3 parameter prefetch (separate from the reduction stream, so that the parameters
+        of the next unit never queue behind a gradient reduction)."""
+        if device.type != "cuda" or os.environ.get("HG_PREFETCH_PARAMS", "1") != "1":
+            return None
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        st = self._gather_streams.get(idx)
+        if st is None:
+            st = self._gather_streams[idx] = torch.cuda.Stream(device=device)
         return st
 
     def join(self, device):
@@ -181,6 +193,7 @@ class ShardedUnit:
         self._reduced = False
         self._bwd_pending = False
         self._acc_used = False
+        self._gather_event = None
         self.count_in_norm = True  # False for the second copy of a weight tied across pipeline stages
         # a weight tied across pipeline stages is summed over the two stages before the sharding group reduces it:
         # its unit keeps the whole-step gradient and reduces at the optimizer step
@@ -279,13 +292,33 @@ class ShardedUnit:
                 self.sync_peers()        # peers pull from this shard
 
     # ---- ZeRO-3 gather / release --------------------------------------------------------------------
-    def gather(self):
-        if self.dp_type != "zero3" or self.gathered:
+    def gather(self, prefetch: bool = False):
+        """Re-assemble the unit's parameters from the shards of its group.  ``prefetch=True`` queues the gather on a
+        side stream (ordered after what the current stream holds so far) and returns at once; the plain call that
+        follows before the unit runs only makes the current stream wait for it."""
+        if self.dp_type != "zero3":
+            return
+        if self.gathered:
+            if not prefetch and self._gather_event is not None:
+                torch.cuda.current_stream(self.device).wait_event(self._gather_event)
+                self._gather_event = None
             return
         nbytes = self.numel * self.flat.element_size()
         st = self.flat.untyped_storage()
         if st.size() != nbytes:
-            st.resize_(nbytes)
+            st.resize_(nbytes)          # allocated (and later released) on the current stream in both modes
+        side = REDUCE.gather_stream(self.device) if prefetch else None
+        if side is not None:
+            side.wait_stream(torch.cuda.current_stream(self.device))
+            with torch.cuda.stream(side):
+                self._gather_now()
+                self._gather_event = torch.cuda.Event()
+                self._gather_event.record(side)
+        else:
+            self._gather_now()
+        self.gathered = True
+
+    def _gather_now(self):
         if self.flat.device.type == "cpu":
             parts = [torch.empty_like(self.shard_lp) for _ in range(self.n)]
             dist.all_gather(parts, self.shard_lp, group=self.pg)
@@ -296,11 +329,13 @@ class ShardedUnit:
             fz.all_gather_peer(self._sym_shard, self.shard_numel, self.flat)   # pull every rank's shard over NVLink
         else:
             dist.all_gather_into_tensor(self.flat, self.shard_lp, group=self.pg)
-        self.gathered = True
 
     def release(self):
         if self.dp_type != "zero3" or not self.gathered:
             return
+        if self._gather_event is not None:      # prefetched but never used: the copy must land before the storage goes
+            torch.cuda.current_stream(self.device).wait_event(self._gather_event)
+            self._gather_event = None
         # views held by autograd's saved tensors stay attached to the storage object; it is re-filled by
         # the next gather() before anything reads it
         self.flat.untyped_storage().resize_(0)
@@ -565,11 +600,17 @@ class UnitWrapper(nn.Module):
         super().__init__()
         self.inner, self.unit, self.checkpoint = inner, unit, checkpoint
         self.extra_units: List[ShardedUnit] = []  # units owning parameters this module borrows (tied weights)
+        # ZeRO-3: the unit that runs after this one in the forward / in the backward; its parameters are gathered
+        # on a side stream while this unit computes (set by link_prefetch)
+        self.next_unit: Optional[ShardedUnit] = None
+        self.prev_unit: Optional[ShardedUnit] = None
 
     def _pre_backward(self):
         self.unit.gather()
         for e in self.extra_units:
             e.gather()
+        if self.prev_unit is not None and not self.unit._bwd_pending:
+            self.prev_unit.gather(prefetch=True)
         if not self.unit._bwd_pending:
             self.unit.begin_backward()
         self.unit._bwd_pending = True
@@ -593,6 +634,8 @@ class UnitWrapper(nn.Module):
         u.gather()
         for e in self.extra_units:
             e.gather()
+        if self.next_unit is not None:
+            self.next_unit.gather(prefetch=True)
         grad_mode = torch.is_grad_enabled()
         if grad_mode:
             # the unit's backward is over once the gradient has left through *every* differentiable input
@@ -619,3 +662,12 @@ class UnitWrapper(nn.Module):
                 out = tuple(_Boundary.apply(o, self._pre_backward) if torch.is_tensor(o) and o.requires_grad else o
                             for o in out)
         return out
+
+
+def link_prefetch(wrappers: List[UnitWrapper]):
+    """Chain the wrappers of a stage in execution order so that each ZeRO-3 unit is gathered one unit ahead."""
+    for a, b in zip(wrappers, wrappers[1:]):
+        if b.unit.dp_type == "zero3" and b.unit is not a.unit:
+            a.next_unit = b.unit
+        if a.unit.dp_type == "zero3" and b.unit is not a.unit:
+            b.prev_unit = a.unit

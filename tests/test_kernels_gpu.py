@@ -79,6 +79,31 @@ def test_linear_autograd():
     assert w2.grad is None and rel_err(w2.main_grad, 2 * wr.grad) < 1e-3
 
 
+@pytest.mark.parametrize("E", [8, 64, 160])
+def test_router_gate_gemm(E):
+    """Router logits on the tcgen05 GEMM with as few as 8 output columns (fp32 out), and both gradients (contraction
+    over 8 columns for dx, 8 output rows for dW accumulated into an fp32 main_grad)."""
+    from hetu_galvatron_b200.models.moe import _GateLinear
+
+    torch.manual_seed(4)
+    T, H = 1000, 512
+    x = torch.randn(T, H, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    w = torch.nn.Parameter(torch.randn(E, H, device=DEV) * 0.05)
+    w.main_grad = torch.ones(E, H, device=DEV)
+    w.mg_fresh = False
+    logits = _GateLinear.apply(x, w)
+    assert logits.dtype == torch.float32 and logits.shape == (T, E)
+    g = torch.randn(T, E, device=DEV)
+    logits.backward(g)
+    xr = x.detach().float().requires_grad_()
+    wr = w.detach().bfloat16().float().requires_grad_()
+    ref = xr @ wr.t()
+    ref.backward(g.bfloat16().float())
+    assert rel_err(logits, ref) < 1e-3
+    assert rel_err(x.grad, xr.grad) < 1e-2
+    assert rel_err(w.main_grad, 1 + wr.grad) < 1e-2 and w.grad is None
+
+
 def test_grouped_gemm_and_wgrad():
     torch.manual_seed(3)
     G, N, K = 4, 384, 256
