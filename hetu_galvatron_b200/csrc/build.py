@@ -57,12 +57,19 @@ def _run(cmd, log: Path | None = None):
     return proc
 
 
-def build_cuda(verbose: bool = False, jobs: int | None = None, debug: bool = False) -> Path:
-    """``debug=True`` builds ``libhg_sm100_debug.so``: the same sources with ``-DHG_DEBUG_BOUNDS`` (index checks that
-    record a status code instead of touching memory; see ``HG_BOUNDS_OK`` in sm100_common.cuh).  ``ops/_lib.py`` loads
-    it when ``HG_DEBUG_KERNELS=1``."""
+def build_cuda(verbose: bool = False, jobs: int | None = None, debug: bool = False, half: bool = False) -> Path:
+    """The kernel library, or one of its variants built from the same sources:
+
+    * ``debug=True``  ``libhg_sm100_debug.so`` (``-DHG_DEBUG_BOUNDS``: index checks that record a status code instead of
+      touching memory; see ``HG_BOUNDS_OK`` in sm100_common.cuh), loaded when ``HG_DEBUG_KERNELS=1``;
+    * ``half=True``   ``libhg_sm100_fp16.so`` (``-DHG_HALF``: IEEE half as the 16-bit storage type instead of bfloat16;
+      see ``hg_lp_t`` in sm100_common.cuh), loaded for ``mixed_precision: fp16`` models."""
+    if debug and half:
+        raise ValueError("one variant at a time")
     if debug:
         return _build_cuda_variant(OBJ_DIR / "debug", "libhg_sm100_debug.so", ["-DHG_DEBUG_BOUNDS=1"], verbose, jobs)
+    if half:
+        return _build_cuda_variant(OBJ_DIR / "fp16", "libhg_sm100_fp16.so", ["-DHG_HALF=1"], verbose, jobs)
     return _build_cuda_variant(OBJ_DIR, "libhg_sm100.so", [], verbose, jobs)
 
 
@@ -119,12 +126,13 @@ def build_host(verbose: bool = False):
     return out
 
 
-def build_all(verbose: bool = False, debug: bool = True):
+def build_all(verbose: bool = False, variants: bool = True):
     host = build_host(verbose)
     cuda = build_cuda(verbose)
     out = [cuda, *host]
-    if debug:
+    if variants:
         out.append(build_cuda(verbose, debug=True))
+        out.append(build_cuda(verbose, half=True))
     return out
 
 

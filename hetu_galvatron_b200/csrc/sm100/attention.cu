@@ -46,7 +46,7 @@ struct FwdParams {
   int q_pos0, k_pos0;           // global positions of row 0 / key 0 (ring / context-parallel steps)
   float scale;                  // softmax scale (1/sqrt(hd))
   SlotMap qmap, kmap, vmap;
-  __nv_bfloat16* O;             // element (s, b, h, d) at O + s*o_ss + b*o_sb + h*hd + d
+  hg_lp_t* O;             // element (s, b, h, d) at O + s*o_ss + b*o_sb + h*hd + d
   int64_t o_ss, o_sb;
   float* LSE;                   // [B, nheads, Sq]
   int* status;
@@ -165,8 +165,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     if (n_kv > 0) {
       // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
       const bool issuer = elect_one() != 0;
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_o = make_idesc_bf16(128, HD, false, true);
+      constexpr uint32_t idesc_s = make_idesc_lp(128, 128, false, false);
+      constexpr uint32_t idesc_o = make_idesc_lp(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aP = smem_u32(sP);
       bool ok = mbar_wait_warp(q_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       auto issue_s = [&](int j) -> bool {
@@ -300,7 +300,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     const int srow = q0 + row;
     if (n_kv == 0) {
       if (srow < p.Sq) {
-        __nv_bfloat16* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD;
+        hg_lp_t* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD;
 #pragma unroll
         for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(0, 0, 0, 0);
         p.LSE[(size_t(b) * p.nheads + h) * p.Sq + srow] = -INFINITY;
@@ -314,7 +314,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_ld32(tO + lane_off + c * 32, r);
         tmem_ld_wait();
         if (srow < p.Sq) {
-          __nv_bfloat16* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD + c * 32;
+          hg_lp_t* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD + c * 32;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             uint4 u;
@@ -344,7 +344,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 // =================================================================================================
 // Backward, part 0:  D[b,h,s] = sum_d dO * O
 // =================================================================================================
-__global__ void attn_bwd_dot_kernel(const __nv_bfloat16* __restrict__ O, const __nv_bfloat16* __restrict__ dO,
+__global__ void attn_bwd_dot_kernel(const hg_lp_t* __restrict__ O, const hg_lp_t* __restrict__ dO,
                                     int64_t ss, int64_t sb, int64_t dss, int64_t dsb, int S, int B, int nheads, int hd,
                                     float* __restrict__ D) {
   // one warp per (s, b, h)
@@ -355,12 +355,12 @@ __global__ void attn_bwd_dot_kernel(const __nv_bfloat16* __restrict__ O, const _
   const int h = int(gw % nheads);
   const int b = int((gw / nheads) % B);
   const int s = int(gw / (int64_t(nheads) * B));
-  const __nv_bfloat16* o = O + s * ss + b * sb + h * hd;
-  const __nv_bfloat16* d = dO + s * dss + b * dsb + h * hd;
+  const hg_lp_t* o = O + s * ss + b * sb + h * hd;
+  const hg_lp_t* d = dO + s * dss + b * dsb + h * hd;
   float acc = 0.f;
   for (int i = lane * 2; i < hd; i += 64) {
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o + i));
-    const float2 c = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(d + i));
+    const float2 a = hg_lp22ff(*reinterpret_cast<const hg_lp2_t*>(o + i));
+    const float2 c = hg_lp22ff(*reinterpret_cast<const hg_lp2_t*>(d + i));
     acc += a.x * c.x + a.y * c.y;
   }
 #pragma unroll
@@ -380,9 +380,9 @@ struct BwdParams {
   const float* LSE;                 // [B, nheads, Sq]
   const float* D;                   // [B, nheads, Sq]
   // outputs: element (s, b, slot, d) at base + s*ss + b*sb + slot*hd + d
-  __nv_bfloat16* dQ; int64_t dq_ss, dq_sb; SlotMap dqmap;
-  __nv_bfloat16* dK; int64_t dk_ss, dk_sb; SlotMap dkmap;
-  __nv_bfloat16* dV; int64_t dv_ss, dv_sb; SlotMap dvmap;
+  hg_lp_t* dQ; int64_t dq_ss, dq_sb; SlotMap dqmap;
+  hg_lp_t* dK; int64_t dk_ss, dk_sb; SlotMap dkmap;
+  hg_lp_t* dV; int64_t dv_ss, dv_sb; SlotMap dvmap;
   int* status;
 };
 
@@ -507,8 +507,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     if (n_it > 0) {
       // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
       const bool issuer = elect_one() != 0;
-      constexpr uint32_t idesc_st = make_idesc_bf16(128, 64, false, false);
-      constexpr uint32_t idesc_acc = make_idesc_bf16(128, HD, false, true);
+      constexpr uint32_t idesc_st = make_idesc_lp(128, 64, false, false);
+      constexpr uint32_t idesc_acc = make_idesc_lp(128, HD, false, true);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aPT = smem_u32(sPT), aDST = smem_u32(sDST);
       bool ok = mbar_wait_warp(kv_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       int qs_s = 0, qs_d = 0;          // Q / dO ring slot of the next S^T issue and of the next dV / dK issue
@@ -671,8 +671,8 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
     // ---- epilogue ----
     const int krow = k0 + row;
     const int dkslot = p.dkmap.slot(h0, p.qpg), dvslot = p.dvmap.slot(h0, p.qpg);
-    __nv_bfloat16* dk = p.dK + int64_t(krow) * p.dk_ss + int64_t(b) * p.dk_sb + int64_t(dkslot) * HD;
-    __nv_bfloat16* dv = p.dV + int64_t(krow) * p.dv_ss + int64_t(b) * p.dv_sb + int64_t(dvslot) * HD;
+    hg_lp_t* dk = p.dK + int64_t(krow) * p.dk_ss + int64_t(b) * p.dk_sb + int64_t(dkslot) * HD;
+    hg_lp_t* dv = p.dV + int64_t(krow) * p.dv_ss + int64_t(b) * p.dv_sb + int64_t(dvslot) * HD;
     if (n_it == 0) {
       if (krow < p.Skv) {
 #pragma unroll
@@ -816,8 +816,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (n_it > 0) {
       // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
       const bool issuer = elect_one() != 0;
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
+      constexpr uint32_t idesc_s = make_idesc_lp(128, 64, false, false);
+      constexpr uint32_t idesc_dq = make_idesc_lp(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
       bool ok = mbar_wait_warp(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       auto issue_s = [&](int it) -> bool {
@@ -921,7 +921,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_arrive(&ds_full[st]);
     }
     const int dqslot = p.dqmap.slot(h, p.qpg);
-    __nv_bfloat16* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
+    hg_lp_t* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
     if (n_it == 0) {
       if (srow < p.Sq) {
 #pragma unroll
@@ -1074,8 +1074,8 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     if (n_it > 0) {
       // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
       const bool issuer = elect_one() != 0;
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_dq = make_idesc_bf16(128, HD, false, true);
+      constexpr uint32_t idesc_s = make_idesc_lp(128, 128, false, false);
+      constexpr uint32_t idesc_dq = make_idesc_lp(128, HD, false, true);
       const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
       bool ok = mbar_wait_warp(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       int ks_s = 0, ks_d = 0;          // K slot of the next S issue and of the next dQ issue
@@ -1186,7 +1186,7 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       mbar_arrive(ds_full);
     }
     const int dqslot = p.dqmap.slot(h, p.qpg);
-    __nv_bfloat16* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
+    hg_lp_t* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
     if (n_it == 0) {
       if (srow < p.Sq) {
 #pragma unroll
@@ -1244,7 +1244,7 @@ int make_map(CUtensorMap* out, const void* base, int hd, int slots, int S, int B
   cuuint32_t box[4] = {64, 1, cuuint32_t(box_rows), 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   if (B == 1) strides[2] = strides[1] * cuuint64_t(S);  // any legal value; the coordinate is always 0
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+  CUresult r = enc(out, HG_TMAP_LP, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
@@ -1282,7 +1282,7 @@ int hg_flash_fwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
   p.Sq = Sq; p.Skv = Skv; p.B = B; p.nheads = nheads; p.qpg = nheads / nkv; p.causal = causal;
   p.q_pos0 = q_pos0; p.k_pos0 = k_pos0; p.scale = scale;
   p.qmap = {q->gs, q->hs, q->off}; p.kmap = {k->gs, k->hs, k->off}; p.vmap = {v->gs, v->hs, v->off};
-  p.O = reinterpret_cast<__nv_bfloat16*>(o->ptr); p.o_ss = o->ss; p.o_sb = o->sb;
+  p.O = reinterpret_cast<hg_lp_t*>(o->ptr); p.o_ss = o->ss; p.o_sb = o->sb;
   p.LSE = reinterpret_cast<float*>(lse);
   p.status = hg_host::status_ptr();
   dim3 grid((Sq + 127) / 128, nheads, B);
@@ -1311,7 +1311,7 @@ int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
   {
     const int64_t warps = int64_t(Sq) * B * nheads;
     const int blocks = int((warps * 32 + 255) / 256);
-    attn_bwd_dot_kernel<<<blocks, 256, 0, st>>>((const __nv_bfloat16*)o->ptr, (const __nv_bfloat16*)d_o->ptr, o->ss,
+    attn_bwd_dot_kernel<<<blocks, 256, 0, st>>>((const hg_lp_t*)o->ptr, (const hg_lp_t*)d_o->ptr, o->ss,
                                                 o->sb, d_o->ss, d_o->sb, Sq, B, nheads, hd, (float*)dsum);
   }
   BwdParams p{};
@@ -1320,9 +1320,9 @@ int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
   p.qmap = {q->gs, q->hs, q->off}; p.kmap = {k->gs, k->hs, k->off}; p.vmap = {v->gs, v->hs, v->off};
   p.domap = {d_o->gs, d_o->hs, d_o->off};
   p.LSE = (const float*)lse; p.D = (const float*)dsum;
-  p.dQ = (__nv_bfloat16*)dq->ptr; p.dq_ss = dq->ss; p.dq_sb = dq->sb; p.dqmap = {dq->gs, dq->hs, dq->off};
-  p.dK = (__nv_bfloat16*)dk->ptr; p.dk_ss = dk->ss; p.dk_sb = dk->sb; p.dkmap = {dk->gs, dk->hs, dk->off};
-  p.dV = (__nv_bfloat16*)dv->ptr; p.dv_ss = dv->ss; p.dv_sb = dv->sb; p.dvmap = {dv->gs, dv->hs, dv->off};
+  p.dQ = (hg_lp_t*)dq->ptr; p.dq_ss = dq->ss; p.dq_sb = dq->sb; p.dqmap = {dq->gs, dq->hs, dq->off};
+  p.dK = (hg_lp_t*)dk->ptr; p.dk_ss = dk->ss; p.dk_sb = dk->sb; p.dkmap = {dk->gs, dk->hs, dk->off};
+  p.dV = (hg_lp_t*)dv->ptr; p.dv_ss = dv->ss; p.dv_sb = dv->sb; p.dvmap = {dv->gs, dv->hs, dv->off};
   p.status = hg_host::status_ptr();
   {
     CUtensorMap tq, tk, tv, tdo;

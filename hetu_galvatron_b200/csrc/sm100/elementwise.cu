@@ -8,10 +8,10 @@
 namespace {
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const hg_lp2_t* p = reinterpret_cast<const hg_lp2_t*>(&u);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(p[i]);
+    float2 t = hg_lp22ff(p[i]);
     f[2 * i] = t.x;
     f[2 * i + 1] = t.y;
   }
@@ -33,7 +33,7 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 // Token t has position pos[t] when `pos` is given, else (t / batch) + pos_offset ([S,B] order).
 // cos/sin tables are fp32 [max_pos, half].
 // ---------------------------------------------------------------------------------------------
-__global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ head_off, int nheads,
+__global__ void rope_kernel(hg_lp_t* __restrict__ buf, const int* __restrict__ head_off, int nheads,
                             int row_pitch, int tokens, int batch, const int* __restrict__ pos, int pos_offset,
                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, int half, float sign) {
   const int vec_per_head = half >> 3;  // uint4 chunks in one half
@@ -43,7 +43,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const int* __restri
     const int h = int((i / vec_per_head) % nheads);
     const int t = int(i / (int64_t(vec_per_head) * nheads));
     const int p = pos ? pos[t] : (t / batch + pos_offset);
-    __nv_bfloat16* base = buf + size_t(t) * row_pitch + head_off[h] + c * 8;
+    hg_lp_t* base = buf + size_t(t) * row_pitch + head_off[h] + c * 8;
     float a[8], b[8], cs[8], sn[8];
     unpack8(*reinterpret_cast<const uint4*>(base), a);
     unpack8(*reinterpret_cast<const uint4*>(base + half), b);
@@ -69,7 +69,7 @@ __global__ void rope_kernel(__nv_bfloat16* __restrict__ buf, const int* __restri
 //   out[2i]   = x[2i]*cos[i] - x[2i+1]*sin[i]
 //   out[2i+1] = x[2i+1]*cos[i] + x[2i]*sin[i]
 // One thread takes 8 consecutive channels (4 pairs) of one head of one token.
-__global__ void rope_interleaved_kernel(__nv_bfloat16* __restrict__ buf, const int* __restrict__ head_off, int nheads,
+__global__ void rope_interleaved_kernel(hg_lp_t* __restrict__ buf, const int* __restrict__ head_off, int nheads,
                                         int row_pitch, int tokens, int batch, const int* __restrict__ pos,
                                         int pos_offset, const float* __restrict__ cos_t,
                                         const float* __restrict__ sin_t, int half, float sign) {
@@ -80,7 +80,7 @@ __global__ void rope_interleaved_kernel(__nv_bfloat16* __restrict__ buf, const i
     const int h = int((i / vec_per_head) % nheads);
     const int t = int(i / (int64_t(vec_per_head) * nheads));
     const int p = pos ? pos[t] : (t / batch + pos_offset);
-    __nv_bfloat16* base = buf + size_t(t) * row_pitch + head_off[h] + c * 8;
+    hg_lp_t* base = buf + size_t(t) * row_pitch + head_off[h] + c * 8;
     float x[8], o[8];
     unpack8(*reinterpret_cast<const uint4*>(base), x);
     const float4 cs = *reinterpret_cast<const float4*>(cos_t + size_t(p) * half + c * 4);
@@ -109,7 +109,7 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
 }
 
 template <int KIND>
-__global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ out, int64_t rows,
+__global__ void glu_fwd_kernel(const hg_lp_t* __restrict__ y, hg_lp_t* __restrict__ out, int64_t rows,
                                int F) {
   const int vpr = F >> 3;
   const int64_t total = rows * vpr;
@@ -133,8 +133,8 @@ __global__ void glu_fwd_kernel(const __nv_bfloat16* __restrict__ y, __nv_bfloat1
 }
 
 template <int KIND>
-__global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ y,
-                               __nv_bfloat16* __restrict__ dy, int64_t rows, int F) {
+__global__ void glu_bwd_kernel(const hg_lp_t* __restrict__ g, const hg_lp_t* __restrict__ y,
+                               hg_lp_t* __restrict__ dy, int64_t rows, int F) {
   const int vpr = F >> 3;
   const int64_t total = rows * vpr;
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
@@ -173,8 +173,8 @@ __global__ void glu_bwd_kernel(const __nv_bfloat16* __restrict__ g, const __nv_b
 // Embedding: out[t,:] = (v0 <= id < v1) ? W[id - v0,:] : 0   (+ pos_emb[t / batch,:] optional)
 // Gradient: dW[id - v0,:] += dout[t,:] (fp32 atomics)
 // ---------------------------------------------------------------------------------------------
-__global__ void embedding_fwd_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ W,
-                                     const __nv_bfloat16* __restrict__ pos_emb, __nv_bfloat16* __restrict__ out,
+__global__ void embedding_fwd_kernel(const int64_t* __restrict__ ids, const hg_lp_t* __restrict__ W,
+                                     const hg_lp_t* __restrict__ pos_emb, hg_lp_t* __restrict__ out,
                                      int tokens, int H, int v0, int v1, int batch, int pos_offset) {
   const int vpr = H >> 3;
   const int64_t total = int64_t(tokens) * vpr;
@@ -195,7 +195,7 @@ __global__ void embedding_fwd_kernel(const int64_t* __restrict__ ids, const __nv
   }
 }
 
-__global__ void embedding_bwd_kernel(const int64_t* __restrict__ ids, const __nv_bfloat16* __restrict__ dout,
+__global__ void embedding_bwd_kernel(const int64_t* __restrict__ ids, const hg_lp_t* __restrict__ dout,
                                      float* __restrict__ dW, float* __restrict__ dpos, int tokens, int H, int v0,
                                      int v1, int batch, int pos_offset) {
   const int vpr = H >> 3;
@@ -221,18 +221,18 @@ __global__ void embedding_bwd_kernel(const int64_t* __restrict__ ids, const __nv
 // ---------------------------------------------------------------------------------------------
 // Casts and the bf16 residual add
 // ---------------------------------------------------------------------------------------------
-__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ in, __nv_bfloat16* __restrict__ out, int64_t n) {
+__global__ void cast_f32_to_bf16_kernel(const float* __restrict__ in, hg_lp_t* __restrict__ out, int64_t n) {
   const int64_t nv = n >> 3;
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < nv; i += int64_t(gridDim.x) * blockDim.x) {
     const float4 a = reinterpret_cast<const float4*>(in)[2 * i], b = reinterpret_cast<const float4*>(in)[2 * i + 1];
     const float f[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
     reinterpret_cast<uint4*>(out)[i] = pack8(f);
   }
-  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) out[(nv << 3) + threadIdx.x] = __float2bfloat16(in[(nv << 3) + threadIdx.x]);
+  if (blockIdx.x == 0 && threadIdx.x < (n & 7)) out[(nv << 3) + threadIdx.x] = hg_f2lp(in[(nv << 3) + threadIdx.x]);
 }
 
-__global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
-                                __nv_bfloat16* __restrict__ out, int64_t n) {
+__global__ void add_bf16_kernel(const hg_lp_t* __restrict__ a, const hg_lp_t* __restrict__ b,
+                                hg_lp_t* __restrict__ out, int64_t n) {
   const int64_t nv = n >> 3;
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < nv; i += int64_t(gridDim.x) * blockDim.x) {
     float x[8], y[8];
@@ -244,7 +244,7 @@ __global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_
   }
   if (blockIdx.x == 0 && threadIdx.x < (n & 7)) {
     const int64_t k = (nv << 3) + threadIdx.x;
-    out[k] = __float2bfloat16(__bfloat162float(a[k]) + __bfloat162float(b[k]));
+    out[k] = hg_f2lp(hg_lp2f(a[k]) + hg_lp2f(b[k]));
   }
 }
 
@@ -256,7 +256,7 @@ __global__ void add_bf16_kernel(const __nv_bfloat16* __restrict__ a, const __nv_
 // before lane 0 replaces it.
 template <int LPR>
 __global__ void attn_merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse_acc, long long lse_pitch,
-                                  const __nv_bfloat16* __restrict__ out_new, const float* __restrict__ lse_new, int S,
+                                  const hg_lp_t* __restrict__ out_new, const float* __restrict__ lse_new, int S,
                                   int BH) {
   const int64_t rows = int64_t(S) * BH;
   const int64_t t = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
@@ -310,12 +310,12 @@ int hg_rope(void* buf, const void* head_off, int nheads, int row_pitch, int toke
   if (flags & 2) {
     const int64_t work = int64_t(tokens) * nheads * (half >> 2);
     rope_interleaved_kernel<<<grid_for(work, 256), 256, 0, (cudaStream_t)stream>>>(
-        (__nv_bfloat16*)buf, (const int*)head_off, nheads, row_pitch, tokens, batch, (const int*)pos, pos_offset,
+        (hg_lp_t*)buf, (const int*)head_off, nheads, row_pitch, tokens, batch, (const int*)pos, pos_offset,
         (const float*)cos_t, (const float*)sin_t, half, sign);
   } else {
     const int64_t work = int64_t(tokens) * nheads * (half >> 3);
     rope_kernel<<<grid_for(work, 256), 256, 0, (cudaStream_t)stream>>>(
-        (__nv_bfloat16*)buf, (const int*)head_off, nheads, row_pitch, tokens, batch, (const int*)pos, pos_offset,
+        (hg_lp_t*)buf, (const int*)head_off, nheads, row_pitch, tokens, batch, (const int*)pos, pos_offset,
         (const float*)cos_t, (const float*)sin_t, half, sign);
   }
   return int(cudaGetLastError());
@@ -326,9 +326,9 @@ int hg_glu_fwd(const void* y, void* out, long long rows, int F, int kind, void* 
   if (F & 7) return -1;
   const int g = grid_for(rows * (F >> 3), 256);
   cudaStream_t st = (cudaStream_t)stream;
-  if (kind == 0) glu_fwd_kernel<0><<<g, 256, 0, st>>>((const __nv_bfloat16*)y, (__nv_bfloat16*)out, rows, F);
-  else if (kind == 1) glu_fwd_kernel<1><<<g, 256, 0, st>>>((const __nv_bfloat16*)y, (__nv_bfloat16*)out, rows, F);
-  else glu_fwd_kernel<2><<<g, 256, 0, st>>>((const __nv_bfloat16*)y, (__nv_bfloat16*)out, rows, F);
+  if (kind == 0) glu_fwd_kernel<0><<<g, 256, 0, st>>>((const hg_lp_t*)y, (hg_lp_t*)out, rows, F);
+  else if (kind == 1) glu_fwd_kernel<1><<<g, 256, 0, st>>>((const hg_lp_t*)y, (hg_lp_t*)out, rows, F);
+  else glu_fwd_kernel<2><<<g, 256, 0, st>>>((const hg_lp_t*)y, (hg_lp_t*)out, rows, F);
   return int(cudaGetLastError());
 }
 
@@ -337,10 +337,10 @@ int hg_glu_bwd(const void* g_, const void* y, void* dy, long long rows, int F, i
   if (F & 7) return -1;
   const int g = grid_for(rows * (F >> 3), 256);
   cudaStream_t st = (cudaStream_t)stream;
-  auto G = (const __nv_bfloat16*)g_;
-  if (kind == 0) glu_bwd_kernel<0><<<g, 256, 0, st>>>(G, (const __nv_bfloat16*)y, (__nv_bfloat16*)dy, rows, F);
-  else if (kind == 1) glu_bwd_kernel<1><<<g, 256, 0, st>>>(G, (const __nv_bfloat16*)y, (__nv_bfloat16*)dy, rows, F);
-  else glu_bwd_kernel<2><<<g, 256, 0, st>>>(G, (const __nv_bfloat16*)y, (__nv_bfloat16*)dy, rows, F);
+  auto G = (const hg_lp_t*)g_;
+  if (kind == 0) glu_bwd_kernel<0><<<g, 256, 0, st>>>(G, (const hg_lp_t*)y, (hg_lp_t*)dy, rows, F);
+  else if (kind == 1) glu_bwd_kernel<1><<<g, 256, 0, st>>>(G, (const hg_lp_t*)y, (hg_lp_t*)dy, rows, F);
+  else glu_bwd_kernel<2><<<g, 256, 0, st>>>(G, (const hg_lp_t*)y, (hg_lp_t*)dy, rows, F);
   return int(cudaGetLastError());
 }
 
@@ -349,7 +349,7 @@ int hg_embedding_fwd(const void* ids, const void* W, const void* pos_emb, void* 
   if (tokens <= 0) return 0;
   if (H & 7) return -1;
   embedding_fwd_kernel<<<grid_for(int64_t(tokens) * (H >> 3), 256), 256, 0, (cudaStream_t)stream>>>(
-      (const int64_t*)ids, (const __nv_bfloat16*)W, (const __nv_bfloat16*)pos_emb, (__nv_bfloat16*)out, tokens, H, v0,
+      (const int64_t*)ids, (const hg_lp_t*)W, (const hg_lp_t*)pos_emb, (hg_lp_t*)out, tokens, H, v0,
       v1, batch, pos_offset);
   return int(cudaGetLastError());
 }
@@ -359,21 +359,21 @@ int hg_embedding_bwd(const void* ids, const void* dout, void* dW, void* dpos, in
   if (tokens <= 0) return 0;
   if (H & 7) return -1;
   embedding_bwd_kernel<<<grid_for(int64_t(tokens) * (H >> 3), 256), 256, 0, (cudaStream_t)stream>>>(
-      (const int64_t*)ids, (const __nv_bfloat16*)dout, (float*)dW, (float*)dpos, tokens, H, v0, v1, batch, pos_offset);
+      (const int64_t*)ids, (const hg_lp_t*)dout, (float*)dW, (float*)dpos, tokens, H, v0, v1, batch, pos_offset);
   return int(cudaGetLastError());
 }
 
 int hg_cast_f32_bf16(const void* in, void* out, long long n, void* stream) {
   if (n <= 0) return 0;
   cast_f32_to_bf16_kernel<<<grid_for(n >> 3, 256), 256, 0, (cudaStream_t)stream>>>((const float*)in,
-                                                                                    (__nv_bfloat16*)out, n);
+                                                                                    (hg_lp_t*)out, n);
   return int(cudaGetLastError());
 }
 
 int hg_add_bf16(const void* a, const void* b, void* out, long long n, void* stream) {
   if (n <= 0) return 0;
   add_bf16_kernel<<<grid_for(n >> 3, 256), 256, 0, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)a, (const __nv_bfloat16*)b, (__nv_bfloat16*)out, n);
+      (const hg_lp_t*)a, (const hg_lp_t*)b, (hg_lp_t*)out, n);
   return int(cudaGetLastError());
 }
 
@@ -387,10 +387,10 @@ int hg_attn_merge(void* out_acc, void* lse_acc, long long lse_pitch, const void*
   const int grid = int((threads + 255) / 256);
   cudaStream_t st = (cudaStream_t)stream;
   if (lpr == 16)
-    attn_merge_kernel<16><<<grid, 256, 0, st>>>((float*)out_acc, (float*)lse_acc, lse_pitch, (const __nv_bfloat16*)out_new,
+    attn_merge_kernel<16><<<grid, 256, 0, st>>>((float*)out_acc, (float*)lse_acc, lse_pitch, (const hg_lp_t*)out_new,
                                                 (const float*)lse_new, S, BH);
   else
-    attn_merge_kernel<8><<<grid, 256, 0, st>>>((float*)out_acc, (float*)lse_acc, lse_pitch, (const __nv_bfloat16*)out_new,
+    attn_merge_kernel<8><<<grid, 256, 0, st>>>((float*)out_acc, (float*)lse_acc, lse_pitch, (const hg_lp_t*)out_new,
                                                (const float*)lse_new, S, BH);
   return int(cudaGetLastError());
 }

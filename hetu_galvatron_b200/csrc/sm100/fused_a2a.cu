@@ -72,10 +72,10 @@ constexpr int kMaxTopK = 8;
 long long g_src_rows_limit = 0;   // rows of the peers' source buffers for the debug build's row check (0 = unknown)
 
 __device__ __forceinline__ void fma8(float (&acc)[8], uint4 v, float s) {
-  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+  const hg_lp2_t* h = reinterpret_cast<const hg_lp2_t*>(&v);
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    const float2 f = __bfloat1622float2(h[k]);
+    const float2 f = hg_lp22ff(h[k]);
     acc[2 * k] += f.x * s;
     acc[2 * k + 1] += f.y * s;
   }
@@ -117,9 +117,9 @@ peer_gather_rows_kernel(PeerPtrs src, const int* __restrict__ peer, const int* _
 #pragma unroll
       for (int k = 0; k < K; ++k) fma8(acc, val[k], sc[k]);
       uint4 r;
-      __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+      hg_lp2_t* h = reinterpret_cast<hg_lp2_t*>(&r);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) h[k] = __floats2bfloat162_rn(acc[2 * k], acc[2 * k + 1]);
+      for (int k = 0; k < 4; ++k) h[k] = hg_ff2lp2(acc[2 * k], acc[2 * k + 1]);
       out[j] = r;
     }
   }

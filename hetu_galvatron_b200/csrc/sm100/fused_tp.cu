@@ -160,11 +160,11 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // GEMM -> reduce-scatter
 // ------------------------------------------------------------------------------------------------
 struct RsParams {
-  __nv_bfloat16* stage[kMaxRanks];  // stage[d]: rank d's staging area [t][tiles_per_slab][64 KB tile]; we write block `me`
+  hg_lp_t* stage[kMaxRanks];  // stage[d]: rank d's staging area [t][tiles_per_slab][64 KB tile]; we write block `me`
   int* flags[kMaxRanks];            // flags[d]: rank d's tile flags [t][tiles_per_slab]; we write row `me`
-  const __nv_bfloat16* my_stage;
+  const hg_lp_t* my_stage;
   int* my_flags;
-  __nv_bfloat16* out;               // [slab_rows, N] reduced result (local)
+  hg_lp_t* out;               // [slab_rows, N] reduced result (local)
   int ldo;
   int t, me, epoch;
   int slab_rows;
@@ -268,10 +268,10 @@ __device__ __forceinline__ void rs_reduce_phase(const Params& p, const RsParams&
 #pragma unroll
         for (int src = 0; src < kMaxRanks; ++src)
           if (src < rs.t) {
-            const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&part[src][u]);
+            const hg_lp2_t* h = reinterpret_cast<const hg_lp2_t*>(&part[src][u]);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(h[i]);
+              const float2 f = hg_lp22ff(h[i]);
               accv[2 * i] += f.x;
               accv[2 * i + 1] += f.y;
             }
@@ -374,7 +374,7 @@ int hg_ag_gemm_bf16(const void* const* src_ptrs, void* const* signal_ptrs, void*
   rc = b_mn ? hg_host::make_tmap_2d_bf16(&tb, B, K, N, ldb, 64, 64) : hg_host::make_tmap_2d_bf16(&tb, B, N, K, ldb, BN, 64);
   if (rc) return rc;
   Params p{};
-  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C; p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C; p.bias = reinterpret_cast<const hg_lp_t*>(bias);
   p.out_mode = out_mode; p.tiles_m = M / BM; p.tiles_n = (N + BN - 1) / BN; p.group_m = 8;
   p.status = hg_host::status_ptr();
   p.ready = reinterpret_cast<const int*>(block_ready); p.rows_per_flag = BM; p.ready_target = BM / kSubRows;
@@ -422,11 +422,11 @@ int hg_gemm_rs_bf16(const void* A, const void* B, void* out, void* const* stage_
   p.k_ranges = nullptr; p.groups = 1; p.c_group_stride = 0;
   RsParams rs{};
   for (int i = 0; i < t; ++i) {
-    rs.stage[i] = reinterpret_cast<__nv_bfloat16*>(stage_ptrs[i]);
+    rs.stage[i] = reinterpret_cast<hg_lp_t*>(stage_ptrs[i]);
     rs.flags[i] = reinterpret_cast<int*>(flag_ptrs[i]);
   }
   rs.my_stage = rs.stage[me]; rs.my_flags = rs.flags[me];
-  rs.out = reinterpret_cast<__nv_bfloat16*>(out); rs.ldo = ldo;
+  rs.out = reinterpret_cast<hg_lp_t*>(out); rs.ldo = ldo;
   rs.t = t; rs.me = me; rs.epoch = epoch; rs.slab_rows = slab_rows;
   rs.tiles_per_slab = (slab_rows / BM) * p.tiles_n;
   int grid = p.tiles_m * p.tiles_n;

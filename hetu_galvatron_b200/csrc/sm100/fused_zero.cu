@@ -138,7 +138,7 @@ zero_reduce_scatter_bf16wire_kernel(PeerPtrs staged, const float* __restrict__ o
   const uint4* src[T];
 #pragma unroll
   for (int r = 0; r < T; ++r) {
-    src[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(staged.p[r]) + me * shard_elems);
+    src[r] = reinterpret_cast<const uint4*>(reinterpret_cast<const hg_lp_t*>(staged.p[r]) + me * shard_elems);
   }
   const float4* mine = reinterpret_cast<const float4*>(own + me * shard_elems);
   const long long stride = (long long)gridDim.x * blockDim.x;
@@ -170,8 +170,9 @@ zero_reduce_scatter_bf16wire_kernel(PeerPtrs staged, const float* __restrict__ o
           const uint32_t w[4] = {a[u][r].x, a[u][r].y, a[u][r].z, a[u][r].w};
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            acc[2 * k] += __uint_as_float(w[k] << 16);
-            acc[2 * k + 1] += __uint_as_float(w[k] & 0xffff0000u);
+            const float2 f = hg_unpack2(w[k]);
+            acc[2 * k] += f.x;
+            acc[2 * k + 1] += f.y;
           }
         }
       }
@@ -208,7 +209,7 @@ __device__ __forceinline__ float adam_one(float& p, float g, float& m, float& v,
 }
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
-  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  hg_lp2_t h = hg_ff2lp2(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
@@ -248,7 +249,7 @@ zero_adamw_allgather_kernel(float* __restrict__ p, const float* __restrict__ g, 
     }
     packed = make_uint4(w[0], w[1], w[2], w[3]);
     for (int r = 0; r < t_out; ++r) {
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[r]) + dst_off) + i;
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<hg_lp_t*>(params.p[r]) + dst_off) + i;
       *dst = packed;
     }
   }

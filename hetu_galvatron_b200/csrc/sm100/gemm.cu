@@ -129,7 +129,7 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_c
     if (!ok) *s.abort = 1;
   } else if (warp == 1) {
     // the whole warp walks the tile list; one elected lane issues the MMAs (see mma_loop in gemm_core.cuh)
-    constexpr uint32_t idesc = make_idesc_bf16(BM, BN, false, B_MN);
+    constexpr uint32_t idesc = make_idesc_lp(BM, BN, false, B_MN);
     constexpr uint32_t b_lbo = B_MN ? SLAB_BYTES : 16, b_kadv = B_MN ? 2048 : 32;
     uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
     bool ok = true;
@@ -241,7 +241,7 @@ int hg_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M,
   if (rc) return rc;
   Params p{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C;
-  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.bias = reinterpret_cast<const hg_lp_t*>(bias);
   p.out_mode = out_mode;
   p.tiles_m = (M + BM - 1) / BM;
   p.tiles_n = (N + BN - 1) / BN;

@@ -132,7 +132,7 @@ int hg_gemm2_bf16(const void* A, const void* B, void* C, const void* bias, int M
   if (rc) return rc;
   Params p{};
   p.M = M; p.N = N; p.K = K; p.ldc = ldc; p.C = C;
-  p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.bias = reinterpret_cast<const hg_lp_t*>(bias);
   p.out_mode = out_mode;
   p.tiles_m = (M + CM - 1) / CM;
   p.tiles_n = (N + BN - 1) / BN;

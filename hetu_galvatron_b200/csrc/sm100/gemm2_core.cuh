@@ -192,7 +192,7 @@ __device__ __forceinline__ void producer2(const CUtensorMap* tmA, const CUtensor
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ void mma2(const Params& p, const Smem2& s, uint32_t tmem_base, int first, int step,
                                      int num_tiles) {
-  constexpr uint32_t idesc = make_idesc_bf16(CM, BN, A_MN, B_MN);
+  constexpr uint32_t idesc = make_idesc_lp(CM, BN, A_MN, B_MN);
   constexpr uint32_t a_lbo = A_MN ? SLAB_BYTES : 16, a_sbo = 1024, a_kadv = A_MN ? 2048 : 32;
   constexpr uint32_t b_lbo = B_MN ? SLAB_BYTES : 16, b_sbo = 1024, b_kadv = B_MN ? 2048 : 32;
   const int num_kb = (p.K + BK - 1) / BK;
@@ -238,21 +238,21 @@ __device__ __forceinline__ void store_block_rows(const Params& p, const float* s
   const int col = col0 + lane;
   if (!HG_BOUNDS_OK(row0 >= 0 && row0 < p.M && col0 >= 0 && col0 < p.N, p.status)) return;
   if (col >= p.N) return;
-  const float bias = p.bias != nullptr ? __bfloat162float(p.bias[col]) : 0.f;
+  const float bias = p.bias != nullptr ? hg_lp2f(p.bias[col]) : 0.f;
   const int rows = min(32, p.M - row0);
   if (p.out_mode == kOutBf16 || p.out_mode == kOutBf16Acc) {
-    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(row0) * p.ldc + col;
+    hg_lp_t* c = reinterpret_cast<hg_lp_t*>(p.C) + size_t(row0) * p.ldc + col;
     float old[32];
     if (p.out_mode == kOutBf16Acc) {   // all 32 loads in flight before the first use
 #pragma unroll
-      for (int r = 0; r < 32; ++r) old[r] = r < rows ? __bfloat162float(c[size_t(r) * p.ldc]) : 0.f;
+      for (int r = 0; r < 32; ++r) old[r] = r < rows ? hg_lp2f(c[size_t(r) * p.ldc]) : 0.f;
     } else {
 #pragma unroll
       for (int r = 0; r < 32; ++r) old[r] = 0.f;
     }
 #pragma unroll
     for (int r = 0; r < 32; ++r)
-      if (r < rows) c[size_t(r) * p.ldc] = __float2bfloat16(stg[r * 33 + lane] + bias + old[r]);
+      if (r < rows) c[size_t(r) * p.ldc] = hg_f2lp(stg[r * 33 + lane] + bias + old[r]);
   } else {
     float* c = reinterpret_cast<float*>(p.C) + size_t(row0) * p.ldc + col;
     float old[32];

@@ -47,7 +47,7 @@ struct Params {
   int M, N, K;
   int ldc;
   void* C;
-  const __nv_bfloat16* bias;  // optional, per output column
+  const hg_lp_t* bias;  // optional, per output column
   int out_mode;
   int tiles_m, tiles_n;
   int group_m;                // tile-order swizzle: rows of tiles walked together for L2 reuse
@@ -225,7 +225,7 @@ __device__ __forceinline__ void producer_loop(const CUtensorMap* tmA, const CUte
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ void mma_loop(const Params& p, const SmemLayout& s, uint32_t tmem_base, int first_tile,
                                          int tile_step, int num_tiles) {
-  constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+  constexpr uint32_t idesc = make_idesc_lp(BM, BN, A_MN, B_MN);
   // K-major: 8-row groups 1024 B apart, K advance 32 B.  MN-major: 64-wide slabs SLAB_BYTES apart (LBO),
   // 8-row K groups 1024 B apart (SBO), K advance 16 rows * 128 B.
   constexpr uint32_t a_lbo = A_MN ? SLAB_BYTES : 16, a_sbo = 1024, a_kadv = A_MN ? 2048 : 32;
@@ -276,11 +276,11 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, int row, int co
   if (p.bias != nullptr) {
 #pragma unroll
     for (int i = 0; i < 32; ++i)
-      if (full || col0 + i < p.N) v[i] += __bfloat162float(p.bias[col0 + i]);
+      if (full || col0 + i < p.N) v[i] += hg_lp2f(p.bias[col0 + i]);
   }
   const size_t off = size_t(c_off) + size_t(row) * p.ldc + col0;
   if (p.out_mode == kOutBf16 || p.out_mode == kOutBf16Acc) {
-    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + off;
+    hg_lp_t* c = reinterpret_cast<hg_lp_t*>(p.C) + off;
     const bool vec = full && ((reinterpret_cast<uintptr_t>(c) & 15) == 0);
     if (vec) {
       uint4* c4 = reinterpret_cast<uint4*>(c);
@@ -288,10 +288,10 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, int row, int co
       for (int q = 0; q < 4; ++q) {
         if (p.out_mode == kOutBf16Acc) {
           uint4 old = c4[q];
-          const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&old);
+          const hg_lp2_t* o2 = reinterpret_cast<const hg_lp2_t*>(&old);
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
-            float2 f = __bfloat1622float2(o2[j]);
+            float2 f = hg_lp22ff(o2[j]);
             v[q * 8 + 2 * j] += f.x;
             v[q * 8 + 2 * j + 1] += f.y;
           }
@@ -308,8 +308,8 @@ __device__ __forceinline__ void store_row_chunk(const Params& p, int row, int co
       for (int i = 0; i < 32; ++i)
         if (col0 + i < p.N) {
           float x = v[i];
-          if (p.out_mode == kOutBf16Acc) x += __bfloat162float(c[i]);
-          c[i] = __float2bfloat16(x);
+          if (p.out_mode == kOutBf16Acc) x += hg_lp2f(c[i]);
+          c[i] = hg_f2lp(x);
         }
     }
   } else {

@@ -32,10 +32,10 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const hg_lp2_t* p = reinterpret_cast<const hg_lp2_t*>(&u);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(p[i]);
+    float2 t = hg_lp22ff(p[i]);
     f[2 * i] = t.x;
     f[2 * i + 1] = t.y;
   }
@@ -52,9 +52,9 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
 // y = norm(x + residual) * w (+ b);  h_out = x + residual (optional);  stats: rstd (and mean for LN).
 template <bool RMS, int kMaxVec>
 __global__ void __launch_bounds__(kThreads)
-norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ residual,
-                const __nv_bfloat16* __restrict__ w, const __nv_bfloat16* __restrict__ b,
-                __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ h_out, float* __restrict__ rstd_out,
+norm_fwd_kernel(const hg_lp_t* __restrict__ x, const hg_lp_t* __restrict__ residual,
+                const hg_lp_t* __restrict__ w, const hg_lp_t* __restrict__ b,
+                hg_lp_t* __restrict__ y, hg_lp_t* __restrict__ h_out, float* __restrict__ rstd_out,
                 float* __restrict__ mean_out, int rows, int H, float eps) {
   __shared__ float red[kThreads / 32];
   const int nvec = H >> 3;
@@ -129,10 +129,10 @@ norm_fwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __rest
 // dx = rstd * (dy*w - xhat*mean(dy*w*xhat) [- mean(dy*w)]) (+ dres);  partial dw/db per CTA (fp32).
 template <bool RMS, int kMaxVec>
 __global__ void __launch_bounds__(kThreads)
-norm_bwd_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ h,
-                const __nv_bfloat16* __restrict__ w, const float* __restrict__ rstd_in,
-                const float* __restrict__ mean_in, const __nv_bfloat16* __restrict__ dres,
-                __nv_bfloat16* __restrict__ dx, float* __restrict__ dw_partial, float* __restrict__ db_partial,
+norm_bwd_kernel(const hg_lp_t* __restrict__ dy, const hg_lp_t* __restrict__ h,
+                const hg_lp_t* __restrict__ w, const float* __restrict__ rstd_in,
+                const float* __restrict__ mean_in, const hg_lp_t* __restrict__ dres,
+                hg_lp_t* __restrict__ dx, float* __restrict__ dw_partial, float* __restrict__ db_partial,
                 int rows, int H) {
   __shared__ float red[kThreads / 32];
   const int nvec = H >> 3;
@@ -229,12 +229,12 @@ int hg_norm_fwd(const void* x, const void* residual, const void* w, const void* 
   if ((H & 7) || H > kThreads * 8 * 8) return -1;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  auto X = reinterpret_cast<const __nv_bfloat16*>(x);
-  auto R = reinterpret_cast<const __nv_bfloat16*>(residual);
-  auto W = reinterpret_cast<const __nv_bfloat16*>(w);
-  auto B = reinterpret_cast<const __nv_bfloat16*>(b);
-  auto Y = reinterpret_cast<__nv_bfloat16*>(y);
-  auto Ho = reinterpret_cast<__nv_bfloat16*>(h_out);
+  auto X = reinterpret_cast<const hg_lp_t*>(x);
+  auto R = reinterpret_cast<const hg_lp_t*>(residual);
+  auto W = reinterpret_cast<const hg_lp_t*>(w);
+  auto B = reinterpret_cast<const hg_lp_t*>(b);
+  auto Y = reinterpret_cast<hg_lp_t*>(y);
+  auto Ho = reinterpret_cast<hg_lp_t*>(h_out);
 #define HG_FWD(R_, V_) norm_fwd_kernel<R_, V_><<<grid, kThreads, 0, st>>>(X, R, W, B, Y, Ho, (float*)rstd, (float*)mean, rows, H, eps)
   if (rms) { if (H <= 4096) HG_FWD(true, 2); else if (H <= 8192) HG_FWD(true, 4); else HG_FWD(true, 8); }
   else     { if (H <= 4096) HG_FWD(false, 2); else if (H <= 8192) HG_FWD(false, 4); else HG_FWD(false, 8); }
@@ -255,10 +255,10 @@ int hg_norm_bwd(const void* dy, const void* h, const void* w, const void* rstd, 
   float* P = reinterpret_cast<float*>(partial);
   float* PB = P + size_t(parts) * H;
 #define HG_BWD(R_, V_)                                                                                              \
-  norm_bwd_kernel<R_, V_><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,             \
-                                                     (const __nv_bfloat16*)w, (const float*)rstd,                    \
-                                                     (const float*)mean, (const __nv_bfloat16*)dres,                 \
-                                                     (__nv_bfloat16*)dx, P, (R_) ? nullptr : PB, rows, H)
+  norm_bwd_kernel<R_, V_><<<grid, kThreads, 0, st>>>((const hg_lp_t*)dy, (const hg_lp_t*)h,             \
+                                                     (const hg_lp_t*)w, (const float*)rstd,                    \
+                                                     (const float*)mean, (const hg_lp_t*)dres,                 \
+                                                     (hg_lp_t*)dx, P, (R_) ? nullptr : PB, rows, H)
   if (rms) { if (H <= 4096) HG_BWD(true, 2); else if (H <= 8192) HG_BWD(true, 4); else HG_BWD(true, 8); }
   else     { if (H <= 4096) HG_BWD(false, 2); else if (H <= 8192) HG_BWD(false, 4); else HG_BWD(false, 8); }
 #undef HG_BWD
@@ -323,10 +323,10 @@ extern "C" int hg_norm_bwd_noalloc(const void* dy, const void* h, const void* w,
   const int grid = rows < parts ? rows : parts;
   float* PB = P + size_t(parts) * HG_NORM_NOALLOC_MAX_H;
 #define HG_BWD_NA(R_, V_)                                                                                           \
-  norm_bwd_kernel<R_, V_><<<grid, kThreads, 0, st>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)h,             \
-                                                     (const __nv_bfloat16*)w, (const float*)rstd,                    \
-                                                     (const float*)mean, (const __nv_bfloat16*)dres,                 \
-                                                     (__nv_bfloat16*)dx, P, (R_) ? nullptr : PB, rows, H)
+  norm_bwd_kernel<R_, V_><<<grid, kThreads, 0, st>>>((const hg_lp_t*)dy, (const hg_lp_t*)h,             \
+                                                     (const hg_lp_t*)w, (const float*)rstd,                    \
+                                                     (const float*)mean, (const hg_lp_t*)dres,                 \
+                                                     (hg_lp_t*)dx, P, (R_) ? nullptr : PB, rows, H)
   if (rms) { if (H <= 4096) HG_BWD_NA(true, 2); else HG_BWD_NA(true, 4); }
   else     { if (H <= 4096) HG_BWD_NA(false, 2); else HG_BWD_NA(false, 4); }
 #undef HG_BWD_NA

@@ -16,7 +16,7 @@ struct AdamArgs {
 // (overflow / rejected step).
 template <typename GradT>
 __global__ void adamw_kernel(float* __restrict__ p, const GradT* __restrict__ g, float* __restrict__ m,
-                             float* __restrict__ v, __nv_bfloat16* __restrict__ p_lp, int64_t n, AdamArgs a,
+                             float* __restrict__ v, hg_lp_t* __restrict__ p_lp, int64_t n, AdamArgs a,
                              const float* __restrict__ gscale, const int* __restrict__ skip) {
   if (skip != nullptr && *skip != 0) return;
   const float gs = gscale ? *gscale : 1.f;
@@ -24,7 +24,7 @@ __global__ void adamw_kernel(float* __restrict__ p, const GradT* __restrict__ g,
   const float inv_b2 = rsqrtf(a.bias2);
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
     float gi;
-    if constexpr (sizeof(GradT) == 2) gi = __bfloat162float(g[i]) * gs;
+    if constexpr (sizeof(GradT) == 2) gi = hg_lp2f(g[i]) * gs;
     else gi = float(g[i]) * gs;
     float pi = p[i];
     const float mi = a.beta1 * m[i] + (1.f - a.beta1) * gi;
@@ -34,7 +34,7 @@ __global__ void adamw_kernel(float* __restrict__ p, const GradT* __restrict__ g,
     m[i] = mi;
     v[i] = vi;
     p[i] = pi;
-    if (p_lp) p_lp[i] = __float2bfloat16(pi);
+    if (p_lp) p_lp[i] = hg_f2lp(pi);
   }
 }
 
@@ -43,7 +43,7 @@ __global__ void sumsq_partial_kernel(const T* __restrict__ x, int64_t n, float* 
   float s = 0.f;
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
     float f;
-    if constexpr (sizeof(T) == 2) f = __bfloat162float(x[i]);
+    if constexpr (sizeof(T) == 2) f = hg_lp2f(x[i]);
     else f = float(x[i]);
     s += f * f;
   }
@@ -91,7 +91,7 @@ __global__ void scale_kernel(T* __restrict__ x, int64_t n, const float* __restri
   const float c = (coef ? *coef : 1.f) * host_coef;
   if (c == 1.f) return;
   for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < n; i += int64_t(gridDim.x) * blockDim.x) {
-    if constexpr (sizeof(T) == 2) x[i] = __float2bfloat16(__bfloat162float(x[i]) * c);
+    if constexpr (sizeof(T) == 2) x[i] = hg_f2lp(hg_lp2f(x[i]) * c);
     else x[i] = T(float(x[i]) * c);
   }
 }
@@ -115,12 +115,12 @@ int hg_adamw(void* p, const void* g, void* m, void* v, void* p_lp, long long n, 
   a.bias2 = 1.f - powf(beta2, float(step));
   cudaStream_t st = (cudaStream_t)stream;
   if (grad_is_bf16)
-    adamw_kernel<__nv_bfloat16><<<grid_for(n), 256, 0, st>>>((float*)p, (const __nv_bfloat16*)g, (float*)m, (float*)v,
-                                                             (__nv_bfloat16*)p_lp, n, a, (const float*)gscale,
+    adamw_kernel<hg_lp_t><<<grid_for(n), 256, 0, st>>>((float*)p, (const hg_lp_t*)g, (float*)m, (float*)v,
+                                                             (hg_lp_t*)p_lp, n, a, (const float*)gscale,
                                                              (const int*)skip);
   else
     adamw_kernel<float><<<grid_for(n), 256, 0, st>>>((float*)p, (const float*)g, (float*)m, (float*)v,
-                                                     (__nv_bfloat16*)p_lp, n, a, (const float*)gscale,
+                                                     (hg_lp_t*)p_lp, n, a, (const float*)gscale,
                                                      (const int*)skip);
   return int(cudaGetLastError());
 }
@@ -131,7 +131,7 @@ int hg_sumsq(const void* x, long long n, int is_bf16, void* partial, void* out, 
   cudaStream_t st = (cudaStream_t)stream;
   const int g = n > 0 ? grid_for(n) : 0;
   if (g > 0) {
-    if (is_bf16) sumsq_partial_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)x, n, (float*)partial);
+    if (is_bf16) sumsq_partial_kernel<hg_lp_t><<<g, 256, 0, st>>>((const hg_lp_t*)x, n, (float*)partial);
     else sumsq_partial_kernel<float><<<g, 256, 0, st>>>((const float*)x, n, (float*)partial);
   }
   sumsq_final_kernel<<<1, 256, 0, st>>>((const float*)partial, g, (float*)out, accumulate, scale);
@@ -146,7 +146,7 @@ int hg_clip_coef(const void* sumsq, float max_norm, void* coef, void* norm_out, 
 int hg_scale(void* x, long long n, int is_bf16, const void* coef, float host_coef, void* stream) {
   if (n <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
-  if (is_bf16) scale_kernel<__nv_bfloat16><<<grid_for(n), 256, 0, st>>>((__nv_bfloat16*)x, n, (const float*)coef, host_coef);
+  if (is_bf16) scale_kernel<hg_lp_t><<<grid_for(n), 256, 0, st>>>((hg_lp_t*)x, n, (const float*)coef, host_coef);
   else scale_kernel<float><<<grid_for(n), 256, 0, st>>>((float*)x, n, (const float*)coef, host_coef);
   return int(cudaGetLastError());
 }

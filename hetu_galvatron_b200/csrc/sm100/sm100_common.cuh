@@ -7,8 +7,34 @@
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+
+// ---------------------------------------------------------------------------
+// The 16-bit storage type of every kernel.  The regular build works on bfloat16; compiled with -DHG_HALF the same
+// sources work on IEEE half (libhg_sm100_fp16.so, loaded for `mixed_precision: fp16` models).  Accumulation,
+// softmax, normalisation statistics and optimizer state are fp32 in both builds.
+// ---------------------------------------------------------------------------
+#ifdef HG_HALF
+typedef __half hg_lp_t;
+typedef __half2 hg_lp2_t;
+#define HG_TMAP_LP CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+__device__ __forceinline__ float hg_lp2f(hg_lp_t x) { return __half2float(x); }
+__device__ __forceinline__ hg_lp_t hg_f2lp(float x) { return __float2half_rn(x); }
+__device__ __forceinline__ hg_lp2_t hg_ff2lp2(float lo, float hi) { return __floats2half2_rn(lo, hi); }
+__device__ __forceinline__ float2 hg_lp22ff(hg_lp2_t v) { return __half22float2(v); }
+#else
+typedef __nv_bfloat16 hg_lp_t;
+typedef __nv_bfloat162 hg_lp2_t;
+#define HG_TMAP_LP CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+__device__ __forceinline__ float hg_lp2f(hg_lp_t x) { return __bfloat162float(x); }
+__device__ __forceinline__ hg_lp_t hg_f2lp(float x) { return __float2bfloat16(x); }
+__device__ __forceinline__ hg_lp2_t hg_ff2lp2(float lo, float hi) { return __floats2bfloat162_rn(lo, hi); }
+__device__ __forceinline__ float2 hg_lp22ff(hg_lp2_t v) { return __bfloat1622float2(v); }
+#endif
+// two packed 16-bit values of a 32-bit word -> two floats
+__device__ __forceinline__ float2 hg_unpack2(uint32_t w) { return hg_lp22ff(*reinterpret_cast<hg_lp2_t*>(&w)); }
 
 namespace hg {
 
@@ -250,16 +276,17 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_
          (uint64_t((sbo_bytes >> 4) & 0x3FFF) << 32);
 }
 
-// Instruction descriptor of kind::f16 with bf16 inputs and fp32 accumulation.
-__host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, bool a_mn_major, bool b_mn_major) {
-  return (1u << 4)      // D format: f32
-         | (1u << 7)    // A format: bf16
-         | (1u << 10)   // B format: bf16
+// Instruction descriptor of kind::f16 with fp32 accumulation; A / B format 1 = bf16, 0 = f16 (the build's 16-bit type).
+#ifdef HG_HALF
+constexpr uint32_t kIdescLpFormat = 0u;
+#else
+constexpr uint32_t kIdescLpFormat = 1u;
+#endif
+__host__ __device__ constexpr uint32_t make_idesc_lp(int m, int n, bool a_mn_major, bool b_mn_major) {
+  return (1u << 4)                  // D format: f32
+         | (kIdescLpFormat << 7)    // A format
+         | (kIdescLpFormat << 10)   // B format
          | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) |
-         (uint32_t(m >> 4) << 24);
-}
-__host__ __device__ constexpr uint32_t make_idesc_f16(int m, int n, bool a_mn_major, bool b_mn_major) {
-  return (1u << 4) | (uint32_t(a_mn_major) << 15) | (uint32_t(b_mn_major) << 16) | (uint32_t(n >> 3) << 17) |
          (uint32_t(m >> 4) << 24);
 }
 
@@ -307,7 +334,7 @@ __device__ __forceinline__ uint32_t sw128_offset(uint32_t row, uint32_t chunk16)
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
-  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  hg_lp2_t v = hg_ff2lp2(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 

@@ -11,22 +11,22 @@ namespace {
 constexpr int kThreads = 256;
 
 __device__ __forceinline__ void unpack8(const uint4& u, float* f) {
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&u);
+  const hg_lp2_t* p = reinterpret_cast<const hg_lp2_t*>(&u);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float2 t = __bfloat1622float2(p[i]);
+    float2 t = hg_lp22ff(p[i]);
     f[2 * i] = t.x;
     f[2 * i + 1] = t.y;
   }
 }
 
 __global__ void __launch_bounds__(kThreads)
-xent_stats_kernel(const __nv_bfloat16* __restrict__ logits, int64_t pitch, const int64_t* __restrict__ targets,
+xent_stats_kernel(const hg_lp_t* __restrict__ logits, int64_t pitch, const int64_t* __restrict__ targets,
                   int v0, int V, float* __restrict__ out_max, float* __restrict__ out_sum,
                   float* __restrict__ out_pred, int rows) {
   __shared__ float sm[kThreads / 32], ss[kThreads / 32];
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const __nv_bfloat16* x = logits + size_t(row) * pitch;
+    const hg_lp_t* x = logits + size_t(row) * pitch;
     const int nvec = V >> 3;
     float m = -INFINITY, s = 0.f;
     for (int c = threadIdx.x; c < nvec; c += kThreads) {
@@ -40,7 +40,7 @@ xent_stats_kernel(const __nv_bfloat16* __restrict__ logits, int64_t pitch, const
       for (int j = 0; j < 8; ++j) s += __expf(f[j] - m);
     }
     for (int k = (nvec << 3) + threadIdx.x; k < V; k += kThreads) {  // ragged tail
-      const float f = __bfloat162float(x[k]);
+      const float f = hg_lp2f(x[k]);
       if (f > m) { s *= __expf(m - f); m = f; }
       s += __expf(f - m);
     }
@@ -66,18 +66,18 @@ xent_stats_kernel(const __nv_bfloat16* __restrict__ logits, int64_t pitch, const
       out_max[row] = M;
       out_sum[row] = S;
       const int64_t t = targets[row] - v0;
-      out_pred[row] = (t >= 0 && t < V) ? __bfloat162float(x[t]) : 0.f;
+      out_pred[row] = (t >= 0 && t < V) ? hg_lp2f(x[t]) : 0.f;
     }
   }
 }
 
 // logits[row, v] <- (exp(x - gmax[row]) / gsum[row] - [v == target - v0]) * g[row]
 __global__ void __launch_bounds__(kThreads)
-xent_bwd_kernel(__nv_bfloat16* __restrict__ logits, int64_t pitch, const int64_t* __restrict__ targets, int v0, int V,
+xent_bwd_kernel(hg_lp_t* __restrict__ logits, int64_t pitch, const int64_t* __restrict__ targets, int v0, int V,
                 const float* __restrict__ gmax, const float* __restrict__ gsum, const float* __restrict__ g,
                 int rows) {
   for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    __nv_bfloat16* x = logits + size_t(row) * pitch;
+    hg_lp_t* x = logits + size_t(row) * pitch;
     const float m = gmax[row], inv = 1.f / gsum[row], gr = g[row];
     const int64_t t = targets[row] - v0;
     const int nvec = V >> 3;
@@ -98,9 +98,9 @@ xent_bwd_kernel(__nv_bfloat16* __restrict__ logits, int64_t pitch, const int64_t
       reinterpret_cast<uint4*>(x)[c] = u;
     }
     for (int k = (nvec << 3) + threadIdx.x; k < V; k += kThreads) {
-      float p = __expf(__bfloat162float(x[k]) - m) * inv;
+      float p = __expf(hg_lp2f(x[k]) - m) * inv;
       if (k == t) p -= 1.f;
-      x[k] = __float2bfloat16(p * gr);
+      x[k] = hg_f2lp(p * gr);
     }
   }
 }
@@ -114,7 +114,7 @@ int hg_xent_stats(const void* logits, long long pitch, const void* targets, int 
   if (rows <= 0) return 0;
   if (pitch & 7) return -1;
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  xent_stats_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)logits, pitch,
+  xent_stats_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>((const hg_lp_t*)logits, pitch,
                                                                  (const int64_t*)targets, v0, V, (float*)out_max,
                                                                  (float*)out_sum, (float*)out_pred, rows);
   return int(cudaGetLastError());
@@ -125,7 +125,7 @@ int hg_xent_bwd(void* logits, long long pitch, const void* targets, int v0, int 
   if (rows <= 0) return 0;
   if (pitch & 7) return -1;
   const int grid = rows < 148 * 8 ? rows : 148 * 8;
-  xent_bwd_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>((__nv_bfloat16*)logits, pitch, (const int64_t*)targets,
+  xent_bwd_kernel<<<grid, kThreads, 0, (cudaStream_t)stream>>>((hg_lp_t*)logits, pitch, (const int64_t*)targets,
                                                                v0, V, (const float*)gmax, (const float*)gsum,
                                                                (const float*)g, rows);
   return int(cudaGetLastError());

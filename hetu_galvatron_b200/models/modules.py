@@ -387,7 +387,7 @@ class _Add(torch.autograd.Function):
 
 
 def ops_add(a, b):
-    if a.is_cuda and a.dtype == torch.bfloat16 and a.is_contiguous() and b.is_contiguous() and a.shape == b.shape:
+    if a.is_cuda and a.dtype in (torch.bfloat16, torch.float16) and a.is_contiguous() and b.is_contiguous() and a.shape == b.shape:
         return _Add.apply(a, b)
     return a + b
 

@@ -218,7 +218,7 @@ class GalvatronMoERouter(nn.Module):
         if s.jitter_eps and self.training:
             noise = torch.empty_like(xin).uniform_(1.0 - s.jitter_eps, 1.0 + s.jitter_eps)
             xin = xin * noise
-        if xin.is_cuda and xin.dtype == torch.bfloat16 and s.router_dtype != "fp64" and s.experts % 8 == 0:
+        if xin.is_cuda and xin.dtype in (torch.bfloat16, torch.float16) and s.router_dtype != "fp64" and s.experts % 8 == 0:
             logits = _GateLinear.apply(xin, self.router.weight)     # tcgen05 GEMM, fp32 accumulation and output
         else:
             dt = torch.float64 if s.router_dtype == "fp64" else torch.float32
@@ -289,7 +289,7 @@ class _GateLinear(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w):
-        wl = w.detach().to(torch.bfloat16)
+        wl = w.detach().to(x.dtype)
         ctx.save_for_backward(x, wl)
         ctx.w = w
         return ops.gemm(x, wl, out_mode=OUT_F32)
@@ -298,7 +298,7 @@ class _GateLinear(torch.autograd.Function):
     def backward(ctx, dlogits):
         x, wl = ctx.saved_tensors
         w = ctx.w
-        dl = dlogits.to(torch.bfloat16).contiguous()
+        dl = dlogits.to(x.dtype).contiguous()
         dx = ops.gemm(dl, wl, b_mn=True)
         mg = getattr(w, "main_grad", None)
         if mg is not None and mg.dtype == torch.float32:

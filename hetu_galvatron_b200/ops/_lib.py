@@ -15,7 +15,40 @@ import torch
 _LIB = None
 # HG_DEBUG_KERNELS=1 selects the bounds-checking build of the same kernels (csrc/build.py::build_cuda(debug=True))
 DEBUG_KERNELS = os.environ.get("HG_DEBUG_KERNELS", "0") == "1"
-_LIB_PATH = Path(__file__).resolve().parent.parent / "_lib" / ("libhg_sm100_debug.so" if DEBUG_KERNELS else "libhg_sm100.so")
+# 16-bit storage type of the kernels: "bf16" (libhg_sm100.so) or "fp16" (libhg_sm100_fp16.so, the same sources built
+# with IEEE half).  A process binds one build: HG_KERNEL_DTYPE or select_precision() before the first kernel call.
+_PRECISION = os.environ.get("HG_KERNEL_DTYPE", "bf16")
+_LIB_DIR = Path(__file__).resolve().parent.parent / "_lib"
+
+
+def _path_for(precision: str) -> Path:
+    if precision == "fp16":
+        if DEBUG_KERNELS:
+            raise RuntimeError("the bounds-checking debug build exists for the bf16 kernels only")
+        return _LIB_DIR / "libhg_sm100_fp16.so"
+    return _LIB_DIR / ("libhg_sm100_debug.so" if DEBUG_KERNELS else "libhg_sm100.so")
+
+
+_LIB_PATH = _path_for(_PRECISION)
+
+
+def select_precision(precision: str):
+    """Bind this process to the bf16 or the fp16 build of the kernel library (called by ``build_model`` from
+    ``mixed_precision``).  Fails if kernels of the other build have already been loaded."""
+    global _PRECISION, _LIB_PATH
+    if precision not in ("bf16", "fp16"):
+        raise ValueError("kernel precision must be bf16 or fp16, not %r" % (precision,))
+    if precision == _PRECISION:
+        return
+    if _LIB is not None:
+        raise RuntimeError("the %s kernel library is already loaded; a process trains in one 16-bit precision"
+                           % _PRECISION)
+    _PRECISION, _LIB_PATH = precision, _path_for(precision)
+
+
+def lp_dtype() -> torch.dtype:
+    """The 16-bit tensor dtype the loaded (or selected) kernel build works on."""
+    return torch.float16 if _PRECISION == "fp16" else torch.bfloat16
 
 c_void_p, c_int, c_float, c_ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 
@@ -91,7 +124,7 @@ def load():
         if os.environ.get("HG_AUTOBUILD", "1") == "1":
             from ..csrc import build as _build
 
-            _build.build_cuda(debug=DEBUG_KERNELS)
+            _build.build_cuda(debug=DEBUG_KERNELS and _PRECISION != "fp16", half=_PRECISION == "fp16")
     if not _LIB_PATH.exists():
         raise RuntimeError(
             "libhg_sm100.so is missing: run `python -m hetu_galvatron_b200.csrc.build` (nvcc, sm_100a) first")

@@ -66,8 +66,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         else:
             out.copy_(acc.to(out.dtype))
         return out
-    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
-        raise TypeError("the tcgen05 GEMM takes bf16 operands")
+    lp = _lib.lp_dtype()
+    if a.dtype != lp or b.dtype != lp:
+        raise TypeError("the tcgen05 GEMM of this build takes %s operands, got %s and %s" % (lp, a.dtype, b.dtype))
     a, b = _rowmajor(a), _rowmajor(b)
     if a_mn:
         K, M = a.shape
@@ -80,7 +81,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     if K != Kb:
         raise ValueError("contraction mismatch: %s vs %s" % (tuple(a.shape), tuple(b.shape)))
     if out is None:
-        dt = torch.float32 if out_mode in (OUT_F32, OUT_F32_ACC) else torch.bfloat16
+        dt = torch.float32 if out_mode in (OUT_F32, OUT_F32_ACC) else lp
         if out_mode in (OUT_F32_ACC, OUT_BF16_ACC):
             raise ValueError("accumulating output modes need `out`")
         out = torch.empty((M, N), dtype=dt, device=a.device)

@@ -36,7 +36,7 @@ def adamw_step(p32: torch.Tensor, grad: torch.Tensor, m: torch.Tensor, v: torch.
         return
     lib = _lib.load()
     rc = lib.hg_adamw(p32.data_ptr(), grad.data_ptr(), m.data_ptr(), v.data_ptr(), _lib.ptr(p_lp), n,
-                      int(grad.dtype == torch.bfloat16), lr, beta1, beta2, eps, weight_decay, step,
+                      int(grad.dtype == _lib.lp_dtype()), lr, beta1, beta2, eps, weight_decay, step,
                       _lib.ptr(gscale), _lib.ptr(skip), _lib.stream())
     _lib.check(rc, "hg_adamw")
     _lib.count_launch()
@@ -63,7 +63,7 @@ def sumsq(x: torch.Tensor, out: torch.Tensor, accumulate: bool = True, scale: fl
         return out
     lib = _lib.load()
     x = x.contiguous()
-    rc = lib.hg_sumsq(x.data_ptr(), x.numel(), int(x.dtype == torch.bfloat16), _partials(x.device).data_ptr(),
+    rc = lib.hg_sumsq(x.data_ptr(), x.numel(), int(x.dtype == _lib.lp_dtype()), _partials(x.device).data_ptr(),
                       out.data_ptr(), int(accumulate), float(scale), _lib.stream())
     _lib.check(rc, "hg_sumsq")
     _lib.count_launch(2)
@@ -90,7 +90,7 @@ def scale_(x: torch.Tensor, coef: torch.Tensor | None = None, host_coef: float =
         x.mul_(c)
         return x
     lib = _lib.load()
-    _lib.check(lib.hg_scale(x.data_ptr(), x.numel(), int(x.dtype == torch.bfloat16), _lib.ptr(coef), host_coef,
+    _lib.check(lib.hg_scale(x.data_ptr(), x.numel(), int(x.dtype == _lib.lp_dtype()), _lib.ptr(coef), host_coef,
                             _lib.stream()), "hg_scale")
     _lib.count_launch()
     return x

@@ -65,7 +65,7 @@ def staging_for(group, nbytes: int, device) -> A2AStaging:
 
 
 def usable(x: torch.Tensor, group) -> bool:
-    return (x.is_cuda and x.dtype == torch.bfloat16 and group is not None and 1 < group.size <= 8
+    return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and group is not None and 1 < group.size <= 8
             and (x.shape[-1] % 8 == 0))
 
 
@@ -139,7 +139,7 @@ def gather_rows(slot: SymmetricBuffer, peer: torch.Tensor, row: torch.Tensor, n_
                 src_row_stride: int, topk: int = 1, scale: torch.Tensor = None) -> torch.Tensor:
     """``out[o] = sum_k scale[o, k] * src_{peer[o, k]}[row[o, k]]`` over the peers' staging slots (bf16 rows)."""
     lib = _lib.load()
-    out = torch.empty((n_out, width), dtype=torch.bfloat16, device=peer.device)
+    out = torch.empty((n_out, width), dtype=slot.tensor.dtype if slot.tensor.dtype.is_floating_point else _lib.lp_dtype(), device=peer.device)
     if _lib.DEBUG_KERNELS:     # the debug build checks every routed row against the size of the peers' buffers
         lib.hg_debug_set_gather_row_limit(slot.tensor.numel() // max(1, src_row_stride))
     rc = lib.hg_peer_gather_rows_bf16(slot.ptr_array(), slot.t, peer.data_ptr(), row.data_ptr(), n_out, topk, width,

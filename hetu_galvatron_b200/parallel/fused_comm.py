@@ -99,12 +99,12 @@ def ag_gemm(x_local: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False, b
     ws = workspace_for(group, slab, K, x_local.device)
     ws.ag_epoch += 1
     par = ws.ag_epoch & 1
-    stage = ws.local_view(ws.off_ag[par], slab * K * 2).view(torch.bfloat16).view(slab, K)
+    stage = ws.local_view(ws.off_ag[par], slab * K * 2).view(x_local.dtype).view(slab, K)
     stage.copy_(x_local)
     t = ws.t
-    gathered = torch.empty((t * slab, K), dtype=torch.bfloat16, device=x_local.device)
+    gathered = torch.empty((t * slab, K), dtype=x_local.dtype, device=x_local.device)
     ready = torch.zeros(t * slab // 128, dtype=torch.int32, device=x_local.device)
-    out = torch.empty((t * slab, N), dtype=torch.bfloat16, device=x_local.device)
+    out = torch.empty((t * slab, N), dtype=x_local.dtype, device=x_local.device)
     fn = lib.hg_ag_gemm2_bf16 if _pair_tile(slab) else lib.hg_ag_gemm_bf16
     rc = fn(ws.ptr_array(ws.off_ag[par]), ws.ptr_array(0), gathered.data_ptr(), ready.data_ptr(),
             w.data_ptr(), out.data_ptr(), _lib.ptr(bias), t, ws.me, ws.ag_epoch, slab, N, K,
@@ -124,7 +124,7 @@ def gemm_rs(x: torch.Tensor, w: torch.Tensor, group, b_mn: bool = False) -> torc
     ws = workspace_for(group, slab, N, x.device)
     ws.rs_epoch += 1
     par = ws.rs_epoch & 1
-    out = torch.empty((slab, N), dtype=torch.bfloat16, device=x.device)
+    out = torch.empty((slab, N), dtype=x.dtype, device=x.device)
     fn = lib.hg_gemm_rs2_bf16 if _pair_tile(slab) else lib.hg_gemm_rs_bf16
     rc = fn(x.data_ptr(), w.data_ptr(), out.data_ptr(), ws.ptr_array(ws.off_rs[par]),
             ws.ptr_array(ws.off_flags[par]), t, ws.me, ws.rs_epoch, slab, N, K, x.stride(0),

@@ -152,7 +152,7 @@ class Reshard(nn.Module):
         if self.identity:
             return x
         floating = x.is_floating_point()
-        if self.peer and floating and x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 3 and x.shape[-1] % 8 == 0 \
+        if self.peer and floating and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.dim() == 3 and x.shape[-1] % 8 == 0 \
                 and max(self.g_old, self.g_new) <= 8:
             S = x.shape[0] * self.g_old
             return _PeerReshard.apply(x, self, S)

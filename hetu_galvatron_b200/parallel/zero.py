@@ -200,7 +200,7 @@ class ShardedUnit:
         self.reduce_at_step_only = False
         # own reduce-scatter / AdamW+all-gather kernels over peer memory instead of NCCL (parallel/fused_zero.py)
         self.fused = False
-        if fused_zero and params and self.dp_type in ("zero2", "zero3") and self.dtype == torch.bfloat16:
+        if fused_zero and params and self.dp_type in ("zero2", "zero3") and self.dtype in (torch.bfloat16, torch.float16):
             from . import fused_zero as fz
 
             self.fused = fz.available(self.device, self.n)
@@ -525,7 +525,7 @@ class ShardedUnit:
         g = self.grad_shard
         # fold the 1/dp average into the device-side gradient scale
         self._ensure_scale(clip_coef)
-        if self.fused and self.dtype == torch.bfloat16:
+        if self.fused:
             from . import fused_zero as fz
 
             # ZeRO-2: the updated bf16 values go straight into every rank's parameter buffer (no all-gather);

@@ -178,8 +178,12 @@ def build_model(args, device=None, full_init: bool = False, fused_comm: Optional
         fused_zero = getattr(args.parallel, "fused_zero", None)
     if fused_zero is None:
         fused_zero = bool(int(os.environ.get("HG_FUSED_ZERO", "1")))
-    fused_comm = bool(fused_comm) and device.type == "cuda" and spec.dtype == torch.bfloat16
+    fused_comm = bool(fused_comm) and device.type == "cuda" and spec.dtype in (torch.bfloat16, torch.float16)
     fused_zero = bool(fused_zero) and device.type == "cuda"
+    if device.type == "cuda" and spec.dtype in (torch.bfloat16, torch.float16):
+        from ..ops import _lib
+
+        _lib.select_precision("fp16" if spec.dtype == torch.float16 else "bf16")   # one kernel build per process
     stage = build_stage(spec, plan, groups, device, seed=args.train.seed or 1234, full_init=full_init,
                         fused_comm=fused_comm, reduce_in_fp32=bool(args.parallel.reduce_in_fp32),
                         fused_zero=fused_zero)
