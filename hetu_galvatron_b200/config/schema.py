@@ -161,6 +161,10 @@ GalvatronModelArgs = _build("GalvatronModelArgs", {
     "moe_shared_expert_overlap": (bool, False),
     "calculate_per_token_loss": (bool, False),
     "moe_grouped_gemm": (bool, False),
+    # peer-memory dispatcher only: size every rank's expert buffer statically at this multiple of the balanced load
+    # (the routing table is then built on the device with no host read; pairs beyond the buffer are dropped and
+    # reported).  null = exact sizes, one host read per layer call.
+    "moe_expert_buffer_factor": (O[float], None),
     "params_dtype": (Any, torch.float32),
     "gradient_accumulation_fusion": (bool, False),
     "defer_embedding_wgrad_compute": (bool, False),

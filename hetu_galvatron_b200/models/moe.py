@@ -485,12 +485,13 @@ class GalvatronMoEMLP(nn.Module):
             if fa.usable(x2d, c.ep):
                 # peer-memory path: tokens are pulled from their source ranks straight into the aligned expert
                 # segments (all-to-all + permute in one kernel) and the outputs are pulled back home the same way
-                plan = fa.MoERouting(idx.to(torch.int32), c.ep, E, SEG_ALIGN)
+                bound = fa.static_bound(T, k, E_loc, SEG_ALIGN, s.expert_buffer_factor) if s.expert_buffer_factor else 0
+                plan = fa.MoERouting(idx.to(torch.int32), c.ep, E, SEG_ALIGN, bound=bound)
                 buf = fa.moe_dispatch(x2d, plan)
                 out_buf = self.experts(buf, plan.row_start)
-                back = fa.moe_combine(out_buf, plan).view(T, k, H)
                 w = torch.where(idx >= 0, probs, torch.zeros_like(probs)).to(torch.float32)
-                return (back.float() * w[..., None]).sum(1).to(x2d.dtype)
+                # the routing weights are applied inside the pull kernel: no [T, k, H] intermediate
+                return fa.moe_combine_weighted(out_buf, w, plan)
         flat_e = idx.reshape(-1)
         valid = flat_e >= 0
         sort_key = torch.where(valid, flat_e, torch.full_like(flat_e, E))

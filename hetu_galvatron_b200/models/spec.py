@@ -60,6 +60,7 @@ class ModelSpec:
     drop_policy: str = "probs"
     dispatcher: str = "alltoall"
     grouped_gemm: bool = True
+    expert_buffer_factor: Optional[float] = None   # static expert buffers of the peer-memory dispatcher
     jitter_eps: Optional[float] = None
 
     @property
@@ -140,7 +141,7 @@ def spec_from_args(args) -> ModelSpec:
         load_balancing=m.moe_router_load_balancing_type, capacity_factor=m.moe_expert_capacity_factor,
         pad_to_capacity=m.moe_pad_expert_input_to_capacity, drop_policy=m.moe_token_drop_policy,
         shared_ffn=int(getattr(m, "moe_shared_expert_intermediate_size", 0) or 0),
-        dispatcher=m.moe_token_dispatcher_type, grouped_gemm=m.moe_grouped_gemm, jitter_eps=m.moe_input_jitter_eps,
+        dispatcher=m.moe_token_dispatcher_type, grouped_gemm=m.moe_grouped_gemm, expert_buffer_factor=getattr(m, "moe_expert_buffer_factor", None), jitter_eps=m.moe_input_jitter_eps,
     )
 
 

@@ -141,12 +141,41 @@ def gather_rows(slot: SymmetricBuffer, peer: torch.Tensor, row: torch.Tensor, n_
     lib = _lib.load()
     out = torch.empty((n_out, width), dtype=slot.tensor.dtype if slot.tensor.dtype.is_floating_point else _lib.lp_dtype(), device=peer.device)
     if _lib.DEBUG_KERNELS:     # the debug build checks every routed row against the size of the peers' buffers
-        lib.hg_debug_set_gather_row_limit(slot.tensor.numel() // max(1, src_row_stride))
+        lib.hg_debug_set_gather_row_limit(slot.tensor.numel() * slot.tensor.element_size() // (2 * max(1, src_row_stride)))
     rc = lib.hg_peer_gather_rows_bf16(slot.ptr_array(), slot.t, peer.data_ptr(), row.data_ptr(), n_out, topk, width,
                                       src_row_stride, out.data_ptr(), _lib.ptr(scale), _lib.stream())
     _lib.check(rc, "hg_peer_gather_rows_bf16")
     _lib.count_launch()
     return out
+
+
+# Routed (token, expert) pairs dropped because a statically sized expert buffer was full, summed over the layers and
+# iterations since the last read (a device scalar per device; see MoERouting(bound=...)).
+OVERFLOW: Dict[str, torch.Tensor] = {}
+
+
+def note_overflow(count: torch.Tensor):
+    key = str(count.device)
+    if key not in OVERFLOW:
+        OVERFLOW[key] = torch.zeros((), dtype=torch.int64, device=count.device)
+    OVERFLOW[key] += count
+
+
+def read_overflow(device) -> int:
+    """Host read (synchronises) and reset of the dropped-pair counter of ``device``."""
+    t = OVERFLOW.get(str(device))
+    if t is None:
+        return 0
+    v = int(t.item())
+    t.zero_()
+    return v
+
+
+def static_bound(tokens: int, topk: int, experts_local: int, align: int, factor: float) -> int:
+    """Rows of a statically sized expert buffer: ``factor`` times the balanced load of a rank (``tokens * topk``
+    pairs) plus the worst-case alignment padding of its local experts, rounded up to ``align``."""
+    rows = int(factor * tokens * topk) + experts_local * align
+    return (rows + align - 1) // align * align
 
 
 class MoERouting:
@@ -163,7 +192,11 @@ class MoERouting:
     * ``row_start`` ``[E_loc + 1]`` int32 segment starts for the grouped GEMM; ``totals`` rows per rank (host list).
     """
 
-    def __init__(self, idx: torch.Tensor, group, num_experts: int, align: int):
+    def __init__(self, idx: torch.Tensor, group, num_experts: int, align: int, bound: int = 0):
+        """``bound`` > 0: every rank's expert buffer has exactly ``bound`` rows (a static size), the whole table is
+        built on the device and nothing is read back on the host; pairs that would land beyond ``bound`` are dropped
+        and counted in :data:`OVERFLOW` (checked once per iteration by the training loop).  ``bound`` = 0: the
+        buffers are sized exactly, which costs one host read of the per-rank totals per layer call."""
         import torch.distributed as dist
 
         ep, me = group.size, group.rank
@@ -190,10 +223,31 @@ class MoERouting:
         dest_row = torch.empty_like(dest_row_sorted)
         dest_row[order] = dest_row_sorted
         dest_rank = torch.where(valid, flat // E_loc, torch.full_like(flat, -1))
-        self.totals = [int(x) for x in totals_t.tolist()]                      # one host read per layer call
-        self.total, self.max_total = self.totals[me], max(self.totals)
         self.T, self.k, self.ep, self.me = T, k, ep, me
         n = T * k
+        local_astart = astart.view(ep, E_loc)[me]
+        self.group = group
+        if bound > 0:
+            # static buffers, no host reads: rows beyond the bound are dropped (and reported), the rows of this rank's
+            # buffer are filled by a scatter over all (rank, token, slot) entries with a dump slot for foreign ones
+            self.total = self.max_total = int(bound)
+            self.totals = [int(bound)] * ep
+            fits = dest_row < bound
+            note_overflow(((dest_rank >= 0) & ~fits).sum())
+            dest_rank = torch.where(fits, dest_rank, torch.full_like(dest_rank, -1))
+            self.peer_s = dest_rank[me * n:(me + 1) * n].to(torch.int32).contiguous()
+            self.row_s = dest_row[me * n:(me + 1) * n].clamp(min=0, max=bound - 1).to(torch.int32).contiguous()
+            every = torch.arange(flat.numel(), device=dev)
+            tgt = torch.where(dest_rank == me, dest_row, torch.full_like(dest_row, bound))
+            r_of, rem = (every // n).to(torch.int32), every % n
+            self.peer_d = torch.full((bound + 1,), -1, dtype=torch.int32, device=dev).scatter_(0, tgt, r_of)[:bound].contiguous()
+            self.tok_d = torch.zeros((bound + 1,), dtype=torch.int32, device=dev).scatter_(0, tgt, (rem // k).to(torch.int32))[:bound].contiguous()
+            self.slot_d = torch.zeros((bound + 1,), dtype=torch.int32, device=dev).scatter_(0, tgt, rem.to(torch.int32))[:bound].contiguous()
+            ends = torch.cat([local_astart, per_rank[me].sum().reshape(1)]).clamp(max=bound)
+            self.row_start = ends.to(torch.int32)
+            return
+        self.totals = [int(x) for x in totals_t.tolist()]                      # one host read per layer call
+        self.total, self.max_total = self.totals[me], max(self.totals)
         self.peer_s = dest_rank[me * n:(me + 1) * n].to(torch.int32).contiguous()
         self.row_s = dest_row[me * n:(me + 1) * n].clamp(min=0).to(torch.int32).contiguous()
         mine = dest_rank == me
@@ -206,9 +260,7 @@ class MoERouting:
         self.peer_d[rows] = r_of.to(torch.int32)
         self.tok_d[rows] = (rem // k).to(torch.int32)
         self.slot_d[rows] = rem.to(torch.int32)
-        local_astart = astart.view(ep, E_loc)[me]
         self.row_start = torch.cat([local_astart, per_rank[me].sum().reshape(1)]).to(torch.int32)
-        self.group = group
 
 
 def _publish_sized(group, x: torch.Tensor, rows_bound: int) -> SymmetricBuffer:
@@ -249,6 +301,46 @@ class _MoECombine(torch.autograd.Function):
         p = ctx.plan
         slot = _publish_sized(p.group, g, p.T * p.k)
         return gather_rows(slot, p.peer_d, p.slot_d, p.total, g.shape[1], g.shape[1]), None
+
+
+class _MoECombineWeighted(torch.autograd.Function):
+    """``out[t] = sum_k w[t, k] * y_{peer}[row(t, k)]``: the combine with the routing weights applied inside the pull
+    kernel.  Backward: ``dy[row] = w(row) * g[token(row)]`` (one weighted pull of the token gradients, the weights of
+    a row's (token, slot) pair looked up in the gathered weight table) and ``dw[t, k] = <g[t], y_row(t, k)>`` (the
+    rows are pulled once more; nothing of size ``[T, k, H]`` is kept between forward and backward)."""
+
+    @staticmethod
+    def forward(ctx, y, w, plan: MoERouting):
+        ctx.plan = plan
+        ctx.save_for_backward(y, w)
+        slot = _publish_sized(plan.group, y, plan.max_total)
+        p = plan
+        return gather_rows(slot, p.peer_s.view(p.T, p.k), p.row_s.view(p.T, p.k), p.T, y.shape[1], y.shape[1], p.k,
+                           scale=w.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+
+        p = ctx.plan
+        y, w = ctx.saved_tensors
+        g = g.contiguous()
+        H = g.shape[1]
+        # weights of the rows of this rank's expert buffer: w_all[source rank, token * k + slot]
+        w_all = torch.empty((p.ep, p.T * p.k), dtype=w.dtype, device=w.device)
+        dist.all_gather_into_tensor(w_all, w.reshape(-1).contiguous(), group=p.group.group)
+        src = p.peer_d.clamp(min=0).long()
+        w_d = torch.where(p.peer_d >= 0, w_all[src, p.slot_d.long()], torch.zeros((), dtype=w.dtype, device=w.device))
+        slot = _publish_sized(p.group, g, p.T)
+        dy = gather_rows(slot, p.peer_d, p.tok_d, p.total, H, H, 1, scale=w_d.float().contiguous())
+        slot_y = _publish_sized(p.group, y, p.max_total)
+        rows = gather_rows(slot_y, p.peer_s, p.row_s, p.T * p.k, H, H).view(p.T, p.k, H)
+        dw = (rows.float() * g.float().unsqueeze(1)).sum(-1).to(w.dtype)
+        return dy, dw, None
+
+
+def moe_combine_weighted(y, w, plan: MoERouting):
+    return _MoECombineWeighted.apply(y, w, plan)
 
 
 def moe_dispatch(x, plan: MoERouting):

@@ -134,7 +134,8 @@ class DpOnModel:
     def __init__(self, model_args_list, train_args_list, parallel_args_list, profile_model_args_list,
                  profile_hardware_args_list, max_mem: int = 8192, layer_num: List[int] = None,
                  sequence_len: List[int] = None, comm_coe_dict: Dict[str, float] = None, world_size: int = 8,
-                 mem_cache: bool = True, pipeline_type: str = "gpipe", config=None, logger=None, threads: int = 1):
+                 mem_cache: bool = True, pipeline_type: str = "gpipe", config=None, logger=None, threads: int = 1,
+                 mem_cache_fraction: float = 0.2):
         n = len(layer_num)
         for lst in (model_args_list, train_args_list, parallel_args_list, profile_model_args_list,
                     profile_hardware_args_list):
@@ -148,8 +149,9 @@ class DpOnModel:
         self.max_mem = max_mem
         self.mem_cache = 0
         if max_mem // 1024 > 20 and mem_cache:
-            # a fifth of a large budget is left to the caching allocator (fragmentation, transient buffers)
-            self.mem_cache = int(max_mem * 0.2)
+            # part of a large budget is left to the caching allocator (fragmentation, transient buffers): a fifth, as
+            # in the reference, unless the hardware refit measured this framework's own overhead
+            self.mem_cache = int(max_mem * mem_cache_fraction)
             self.max_mem -= self.mem_cache
         self.mem_sub_cache = self.max_mem
 

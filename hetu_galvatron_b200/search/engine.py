@@ -446,6 +446,7 @@ class GalvatronSearchEngine:
                       if k.startswith("fused_comm_hidden_fraction_tp")}
             self.fused_hidden = per_tp if per_tp else r.get("fused_comm_hidden_fraction", 0.0)
             self.optimizer_ms = r.get("optimizer_ms_per_layer", 0.0)
+            self.cache_fraction = r.get("allocator_cache_fraction")
         return self.allreduce_bandwidth, self.p2p_bandwidth, self.overlap_coe, self.sp_allreduce, self.sp_all2all
 
     def set_cost_models(self):
@@ -580,7 +581,8 @@ class GalvatronSearchEngine:
                        self.profile_hardware_args_list, max_mem=self.memory_constraint, layer_num=self.layernum_list,
                        sequence_len=self.seqlen_list, comm_coe_dict=self.allreduce_comm_coe, world_size=self.world_size,
                        pipeline_type=a.parallelism_info.pipeline_type, config=a, logger=logger,
-                       threads=getattr(self, "dp_threads", 1))
+                       threads=getattr(self, "dp_threads", 1),
+                       mem_cache_fraction=getattr(self, "cache_fraction", None) or 0.2)
         best = dp.fit(gbsz, chunks, pp_size, division, global_buffer_tp_size, tp_sp_mode, layers, embeds)
         throughput = gbsz / best["time_cost"]
         logger.info("optimal: %s" % best)

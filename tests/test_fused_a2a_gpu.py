@@ -194,6 +194,62 @@ def test_ring_context_parallel_matches_the_all_gather_variant():
             assert abs(l0 - l1) / abs(l0) < 5e-3 and abs(n0 - n1) / n0 < 5e-2, (ref, got)
 
 
+def moe_layer_without_host_syncs(cfg):
+    """One MoE decoder layer, forward + backward, under ``set_sync_debug_mode("error")`` after a warm-up pass: the
+    statically sized peer-memory dispatcher builds its routing table on the device."""
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+    from hetu_galvatron_b200.ops import _lib
+    from hetu_galvatron_b200.parallel import fused_a2a as fa
+    from hetu_galvatron_b200.runtime.engine import build_model
+
+    rank, t, _ = _init()
+    dev = torch.device("cuda", rank)
+    model = dict(model_size="llama-test", hidden_size=256, num_layers=1, num_attention_heads=4, ffn_hidden_size=768,
+                 vocab_size=1024, make_vocab_size_divisible_by=8, normalization="RMSNorm",
+                 activation_func="torch.nn.functional.silu", gated_linear_unit=True, **MOE)
+    model.update(moe_token_dispatcher_type="flex", moe_grouped_gemm=True, moe_expert_buffer_factor=2.0,
+                 moe_aux_loss_coeff=0.0)
+    args = GalvatronRuntimeArgs(parallel=dict(mixed_precision="bf16", global_ep_deg=2), model=model,
+                                train=dict(seq_length=256, global_batch_size=4, chunks=1, lr=1e-3))
+    m = build_model(args, device=dev, full_init=True, fused_comm=True)
+    layer = [u for lp, u in m.named_units() if lp.startswith("moe_decoder")][0]
+    x = torch.randn(256, 2, 256, device=dev, dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(256, 2, 256, device=dev, dtype=torch.bfloat16)
+    layer(x).backward(g)                   # warm-up: staging buffers, workspaces, kernel modules
+    torch.cuda.synchronize()
+    torch.cuda.set_sync_debug_mode("error")
+    try:
+        y = layer(x)
+        y.backward(g)
+    finally:
+        torch.cuda.set_sync_debug_mode("default")
+    torch.cuda.synchronize()
+    _lib.assert_healthy()
+    return {"dropped": fa.read_overflow(dev), "finite": bool(torch.isfinite(x.grad.float()).all())}
+
+
+REGISTRY["moe_layer_without_host_syncs"] = moe_layer_without_host_syncs
+
+
+def test_moe_layer_has_no_host_synchronisation_with_static_expert_buffers():
+    _need(2)
+    res = run_distributed(__file__, "moe_layer_without_host_syncs", 2, {}, timeout=300, extra_env=ENV)
+    for r in res:
+        assert r["dropped"] == 0 and r["finite"], res
+
+
+def test_static_expert_buffers_train_like_exact_ones():
+    """``moe_expert_buffer_factor`` (device-built routing table, static buffers) against the exactly sized buffers."""
+    _need(2)
+    base = {"parallel": {"global_ep_deg": 2}, "fused": True}
+    ref = run_distributed(__file__, "train_moe", 2, dict(base, model=dict(MOE, moe_grouped_gemm=True)), timeout=300, extra_env=ENV)
+    got = run_distributed(__file__, "train_moe", 2, dict(base, model=dict(MOE, moe_grouped_gemm=True, moe_expert_buffer_factor=2.0)),
+                          timeout=300, extra_env=ENV)
+    for r in range(2):
+        for (l0, n0), (l1, n1) in zip(ref[r], got[r]):
+            assert abs(l0 - l1) / abs(l0) < 2e-3 and abs(n0 - n1) / n0 < 2e-2, (ref, got)
+
+
 def test_flex_dispatcher_selects_the_pull_kernels():
     """``moe_token_dispatcher_type: flex`` runs the fused dispatcher without the global switch and trains like
     the all-to-all dispatcher."""
