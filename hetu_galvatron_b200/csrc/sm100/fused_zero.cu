@@ -100,6 +100,10 @@ struct Rendezvous {
 
 // Publish this rank's epoch to every peer, then wait (bounded) until every peer has published the same epoch.
 // Returns false after a time-out (status word set); the caller then skips its reads.
+// Longer than the 2 s of the in-kernel tile waits: the ranks of a data-parallel group are only loosely in step (first
+// iterations load kernel modules, a rank may log or checkpoint), and giving up here rejects the whole step.
+constexpr uint64_t kRendezvousLimitNs = 10000000000ull;   // 10 s
+
 template <int T>
 __device__ __forceinline__ bool rendezvous(const Rendezvous& rv, int me) {
   __shared__ int ok_s;
@@ -118,7 +122,7 @@ __device__ __forceinline__ bool rendezvous(const Rendezvous& rv, int me) {
     for (;;) {
       asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
       if (v >= rv.epoch) break;
-      if (hg::globaltimer_ns() - t0 > hg::kWaitLimitNs) {
+      if (hg::globaltimer_ns() - t0 > kRendezvousLimitNs) {
         hg::set_status(rv.status, hg::kTimeoutPeerFlag);
         ok_s = 0;
         break;
