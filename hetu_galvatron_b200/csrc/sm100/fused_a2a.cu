@@ -10,13 +10,15 @@
 //                                               src_r[src_off + i*src_stride + c]      r < t, i < rows, c < chunk
 //   peer_gather_rows_kernel variable row lists: out[o, :] = sum_k scale[o,k] * src_{peer[o,k]}[row[o,k], :]
 //
-// Neither kernel waits on another GPU; callers order them with a stream-ordered rendezvous of the group.
+// Both kernels can carry the cross-rank rendezvous themselves (peer_rendezvous.cuh: signal slots, bounded wait), so a
+// whole exchange is a staging copy plus this one launch; without signals the caller orders the ranks with a
+// stream-ordered collective.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <cstdint>
 
-#include "sm100_common.cuh"
+#include "peer_rendezvous.cuh"
 
 namespace {
 
@@ -39,7 +41,9 @@ inline int grid_for(long long items) {
 // All quantities in units of 16 bytes (8 bf16).  vec = chunk / 8.
 __global__ void __launch_bounds__(kThreads)
 peer_gather_kernel(PeerPtrs src, int t, long long rows, int vec, long long src_off, long long src_stride,
-                   uint4* __restrict__ out, long long out_peer_stride, long long out_row_stride, int* status) {
+                   uint4* __restrict__ out, long long out_peer_stride, long long out_row_stride, int* status,
+                   hg::Rendezvous rv) {
+  if (!hg::rendezvous(rv)) return;
   if (!HG_BOUNDS_OK(t >= 1 && t <= kMaxPeers && src_off >= 0 && src_stride >= 0 && out_peer_stride >= 0 && out_row_stride >= 0, status))
     return;
   const long long per_peer = rows * vec;
@@ -87,7 +91,8 @@ template <int K>
 __global__ void __launch_bounds__(kThreads)
 peer_gather_rows_kernel(PeerPtrs src, const int* __restrict__ peer, const int* __restrict__ row, long long n_out,
                         int vec, long long src_row_stride, uint4* __restrict__ out, const float* __restrict__ scale,
-                        int t, long long src_rows, int* status) {
+                        int t, long long src_rows, int* status, hg::Rendezvous rv) {
+  if (!hg::rendezvous(rv)) return;
   const long long total = n_out * vec;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long j = blockIdx.x * (long long)blockDim.x + threadIdx.x; j < total; j += stride) {
@@ -130,29 +135,52 @@ peer_gather_rows_kernel(PeerPtrs src, const int* __restrict__ peer, const int* _
 extern "C" {
 
 // Element counts are in bf16 elements and must be multiples of 8; pointers 16-byte aligned.
+int hg_peer_gather_bf16_rv(const void* const* src, int t, long long rows, long long chunk, long long src_off,
+                           long long src_stride, void* out, long long out_peer_stride, long long out_row_stride,
+                           void* const* signals, int me, int epoch, void* stream);
 int hg_peer_gather_bf16(const void* const* src, int t, long long rows, long long chunk, long long src_off,
                         long long src_stride, void* out, long long out_peer_stride, long long out_row_stride,
                         void* stream) {
+  return hg_peer_gather_bf16_rv(src, t, rows, chunk, src_off, src_stride, out, out_peer_stride, out_row_stride, nullptr,
+                                0, 0, stream);
+}
+// As above with the in-kernel rendezvous: signals[r] = rank r's int[8] signal array, me = this rank's index in the
+// group, epoch = the group's call counter (> 0, +1 per exchange on every rank).
+int hg_peer_gather_bf16_rv(const void* const* src, int t, long long rows, long long chunk, long long src_off,
+                           long long src_stride, void* out, long long out_peer_stride, long long out_row_stride,
+                           void* const* signals, int me, int epoch, void* stream) {
   if (t < 1 || t > kMaxPeers || rows < 0 || chunk <= 0) return -1;
   if ((chunk | src_off | src_stride | out_peer_stride | out_row_stride) & 7) return -1;
-  if (rows == 0) return 0;
+  const hg::Rendezvous rv = hg_host::make_rendezvous(signals, epoch, t, me);
+  if (rows == 0 && rv.epoch == 0) return 0;     // with a rendezvous the peers still wait for this rank's signal
   PeerPtrs pp{};
   for (int r = 0; r < t; ++r) pp.p[r] = src[r];
   const long long total = rows * (chunk / 8) * t;
   peer_gather_kernel<<<grid_for((total + kUnroll - 1) / kUnroll), kThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       pp, t, rows, int(chunk / 8), src_off / 8, src_stride / 8, reinterpret_cast<uint4*>(out), out_peer_stride / 8,
-      out_row_stride / 8, hg_host::status_ptr());
+      out_row_stride / 8, hg_host::status_ptr(), rv);
   return int(cudaGetLastError());
 }
 
 // out[o, 0:width] = sum_{k < topk} scale[o*topk+k] * src_{peer[o*topk+k]}[row[o*topk+k], 0:width]; width multiple of 8;
 // src rows are src_row_stride elements apart; scale may be null (weights 1); entries with peer < 0 are skipped.
+int hg_peer_gather_rows_bf16_rv(const void* const* src, int t, const void* peer, const void* row, long long n_out,
+                                int topk, long long width, long long src_row_stride, void* out, const void* scale,
+                                void* const* signals, int me, int epoch, void* stream);
 int hg_peer_gather_rows_bf16(const void* const* src, int t, const void* peer, const void* row, long long n_out,
                              int topk, long long width, long long src_row_stride, void* out, const void* scale,
                              void* stream) {
+  return hg_peer_gather_rows_bf16_rv(src, t, peer, row, n_out, topk, width, src_row_stride, out, scale, nullptr, 0, 0,
+                                     stream);
+}
+// As above with the in-kernel rendezvous (see hg_peer_gather_bf16_rv).
+int hg_peer_gather_rows_bf16_rv(const void* const* src, int t, const void* peer, const void* row, long long n_out,
+                                int topk, long long width, long long src_row_stride, void* out, const void* scale,
+                                void* const* signals, int me, int epoch, void* stream) {
   if (t < 1 || t > kMaxPeers || n_out < 0 || width <= 0 || ((width | src_row_stride) & 7)) return -1;
   if (topk < 1 || topk > kMaxTopK) return -1;
-  if (n_out == 0) return 0;
+  const hg::Rendezvous rv = hg_host::make_rendezvous(signals, epoch, t, me);
+  if (n_out == 0 && rv.epoch == 0) return 0;    // with a rendezvous the peers still wait for this rank's signal
   PeerPtrs pp{};
   for (int r = 0; r < t; ++r) pp.p[r] = src[r];
   const long long total = n_out * (width / 8);
@@ -161,7 +189,7 @@ int hg_peer_gather_rows_bf16(const void* const* src, int t, const void* peer, co
   peer_gather_rows_kernel<K_><<<grid_for(total), kThreads, 0, st>>>(                                              \
       pp, reinterpret_cast<const int*>(peer), reinterpret_cast<const int*>(row), n_out, int(width / 8),           \
       src_row_stride / 8, reinterpret_cast<uint4*>(out), reinterpret_cast<const float*>(scale), t, g_src_rows_limit,      \
-      hg_host::status_ptr())
+      hg_host::status_ptr(), rv)
   switch (topk) {
     case 1: HG_ROWS(1); break;
     case 2: HG_ROWS(2); break;

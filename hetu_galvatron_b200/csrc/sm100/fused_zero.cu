@@ -20,7 +20,7 @@
 
 #include <cstdint>
 
-#include "sm100_common.cuh"
+#include "peer_rendezvous.cuh"
 
 namespace {
 
@@ -91,54 +91,11 @@ zero_reduce_scatter_kernel(PeerPtrs grads, int me, long long shard_floats, long 
 // slice taken from the fp32 buffer, unrounded.  n8 = number of 8-element groups of the shard.  With kAcc the
 // result is added to `out` (running shard of the per-micro-batch reduction mode).  U groups per thread and
 // iteration keep (T - 1) * U peer loads of 16 bytes in flight per thread.
-struct Rendezvous {
-  int* peer_slots[kMaxPeers];   // peer_slots[r]: rank r's signal array (int[kMaxPeers], symmetric); we write slot `me`
-  const int* my_slots;          // our own array: my_slots[r] >= epoch once rank r's staged data may be read
-  int epoch;                    // 0: no rendezvous (the caller ordered the ranks itself)
-  int* status;
-};
-
-// Publish this rank's epoch to every peer, then wait (bounded) until every peer has published the same epoch.
-// Returns false after a time-out (status word set); the caller then skips its reads.
-// Longer than the 2 s of the in-kernel tile waits: the ranks of a data-parallel group are only loosely in step (first
-// iterations load kernel modules, a rank may log or checkpoint), and giving up here rejects the whole step.
-constexpr uint64_t kRendezvousLimitNs = 10000000000ull;   // 10 s
-
-template <int T>
-__device__ __forceinline__ bool rendezvous(const Rendezvous& rv, int me) {
-  __shared__ int ok_s;
-  if (rv.epoch == 0) return true;
-  if (threadIdx.x == 0) ok_s = 1;
-  __syncthreads();
-  if (blockIdx.x == 0 && threadIdx.x < T && int(threadIdx.x) != me) {
-    // the staged values were written by an earlier kernel of this stream: make them visible system-wide first
-    __threadfence_system();
-    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(rv.peer_slots[threadIdx.x] + me), "r"(rv.epoch) : "memory");
-  }
-  if (threadIdx.x < T && int(threadIdx.x) != me) {
-    const int* flag = rv.my_slots + threadIdx.x;
-    const uint64_t t0 = hg::globaltimer_ns();
-    int v;
-    for (;;) {
-      asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
-      if (v >= rv.epoch) break;
-      if (hg::globaltimer_ns() - t0 > kRendezvousLimitNs) {
-        hg::set_status(rv.status, hg::kTimeoutPeerFlag);
-        ok_s = 0;
-        break;
-      }
-      __nanosleep(200);
-    }
-  }
-  __syncthreads();
-  return ok_s != 0;
-}
-
 template <int T, bool kAcc, int U>
 __global__ void __launch_bounds__(kThreads)
 zero_reduce_scatter_bf16wire_kernel(PeerPtrs staged, const float* __restrict__ own, int me, long long shard_elems,
-                                    long long n8, float4* __restrict__ out, Rendezvous rv) {
-  if (!rendezvous<T>(rv, me)) return;
+                                    long long n8, float4* __restrict__ out, hg::Rendezvous rv) {
+  if (!hg::rendezvous(rv)) return;
   const uint4* src[T];
 #pragma unroll
   for (int r = 0; r < T; ++r) {
@@ -309,13 +266,7 @@ int hg_zero_reduce_scatter_bf16wire(void* const* staged, const void* own, int t,
   if (t < 1 || t > kMaxPeers || me < 0 || me >= t || shard <= 0 || (shard & 7) || own == nullptr) return -1;
   PeerPtrs pp{};
   for (int r = 0; r < t; ++r) pp.p[r] = staged[r];
-  Rendezvous rv{};
-  rv.epoch = (signals != nullptr && t > 1) ? epoch : 0;
-  if (rv.epoch) {
-    for (int r = 0; r < t; ++r) rv.peer_slots[r] = reinterpret_cast<int*>(signals[r]);
-    rv.my_slots = rv.peer_slots[me];
-    rv.status = hg_host::status_ptr();
-  }
+  const hg::Rendezvous rv = hg_host::make_rendezvous(signals, epoch, t, me);
   const long long n8 = shard / 8;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int grid = grid_for(n8);

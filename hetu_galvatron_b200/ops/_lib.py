@@ -69,6 +69,9 @@ _SIGNATURES = {
     "hg_norm_bwd": [c_void_p] * 10 + [c_int] * 5 + [c_void_p],
     "hg_peer_gather_bf16": [c_void_p, c_int, c_ll, c_ll, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p],
     "hg_peer_gather_rows_bf16": [c_void_p, c_int, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_void_p, c_void_p, c_void_p],
+    "hg_peer_gather_bf16_rv": [c_void_p, c_int, c_ll, c_ll, c_ll, c_ll, c_void_p, c_ll, c_ll, c_void_p, c_int, c_int, c_void_p],
+    "hg_peer_gather_rows_bf16_rv": [c_void_p, c_int, c_void_p, c_void_p, c_ll, c_int, c_ll, c_ll, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_int, c_void_p],
     "hg_router_topk_fwd": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float] + [c_void_p] * 5,
     "hg_router_topk_bwd": [c_void_p] * 5 + [c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
     "hg_zero_reduce_scatter": [c_void_p, c_int, c_int, c_ll, c_void_p, c_void_p],

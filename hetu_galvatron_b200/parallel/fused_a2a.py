@@ -10,10 +10,11 @@ symmetric staging buffer and the destination pulls its chunks from all peers str
 a fresh local tensor (one kernel, peer loads over NVLink).  When there are fewer key/value heads than ranks, the
 replication is never materialised: rank ``d`` simply pulls head ``d // (p / ng)``.
 
-Staging has two parities.  Per call: copy into staging[parity] -> ``peer_barrier`` (one-element all-reduce: every
+Staging has two parities.  Per call: copy into staging[parity] -> pull kernel, which carries the cross-rank rendezvous
+itself (signal slots in symmetric memory, bounded wait; ``HG_A2A_RENDEZVOUS=nccl`` restores the older form below).
+Older form: copy into staging[parity] -> ``peer_barrier`` (one-element all-reduce: every
 rank's staging is complete) -> pull.  A parity is rewritten two calls later, after the next call's rendezvous has
 shown that every rank finished pulling from it, so one rendezvous per call is enough.
-The kernels never wait on another GPU.
 
 Capability parity: galvatron/core/runtime/transformer/attention_impl.py:139-198 (layout pre/post), :316-405
 (``DistributedAttention``, GQA replication :339-345), moe/token_dispatcher.py:510-689 for the row-list variant.
@@ -21,12 +22,13 @@ Capability parity: galvatron/core/runtime/transformer/attention_impl.py:139-198 
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, Tuple
 
 import torch
 
 from ..ops import _lib
-from .fused_zero import SymmetricBuffer, peer_barrier
+from .fused_zero import SignalSlots, SymmetricBuffer, peer_barrier
 
 _STAGING: Dict[Tuple[int, ...], "A2AStaging"] = {}
 
@@ -40,15 +42,26 @@ class A2AStaging:
         self.capacity = nbytes
         self.slots = [SymmetricBuffer(nbytes, torch.uint8, device, group.group) for _ in range(2)]
         self.calls = 0
+        # HG_A2A_RENDEZVOUS=nccl: a stream-ordered one-element all-reduce after the copy instead of the pull kernel's
+        # own signal-slot rendezvous
+        self.signals = SignalSlots.get(device, group.group, "a2a") if os.environ.get("HG_A2A_RENDEZVOUS", "kernel") == "kernel" else None
+        for s in self.slots:
+            s.signals, s.epoch, s.me = self.signals, 0, group.rank
 
     def publish(self, x: torch.Tensor) -> SymmetricBuffer:
-        """Copy ``x`` (contiguous) into the next slot and rendezvous; returns the slot."""
+        """Copy ``x`` into the next slot; returns the slot.  The pull kernel that follows waits until every rank of the
+        group has published (``slot.epoch``); each publish must be followed by at least one pull on every rank.  The two
+        slots alternate: a slot is written again only after the pull of the publish in between, whose rendezvous every
+        peer enters after its reads of this one."""
         self.calls += 1
         slot = self.slots[self.calls & 1]
         nbytes = x.numel() * x.element_size()
         # one pass even when ``x`` is a strided view (e.g. q / k / v inside the packed QKV buffer)
         slot.tensor[:nbytes].view(x.dtype).view(x.shape).copy_(x)
-        peer_barrier(self.group.group, self.device)
+        if self.signals is None:
+            peer_barrier(self.group.group, self.device)
+        else:
+            slot.epoch = self.signals.next_epoch()
         return slot
 
 
@@ -69,10 +82,18 @@ def usable(x: torch.Tensor, group) -> bool:
             and (x.shape[-1] % 8 == 0))
 
 
+def _rendezvous_args(slot: SymmetricBuffer):
+    sig = getattr(slot, "signals", None)
+    if sig is None:
+        return None, 0, 0
+    return sig.buf.ptr_array(), slot.me, slot.epoch
+
+
 def _gather(slot: SymmetricBuffer, rows, chunk, src_off, src_stride, out, out_peer_stride, out_row_stride):
     lib = _lib.load()
-    rc = lib.hg_peer_gather_bf16(slot.ptr_array(), slot.t, rows, chunk, src_off, src_stride, out.data_ptr(),
-                                 out_peer_stride, out_row_stride, _lib.stream())
+    sig, me, epoch = _rendezvous_args(slot)
+    rc = lib.hg_peer_gather_bf16_rv(slot.ptr_array(), slot.t, rows, chunk, src_off, src_stride, out.data_ptr(),
+                                    out_peer_stride, out_row_stride, sig, me, epoch, _lib.stream())
     _lib.check(rc, "hg_peer_gather_bf16")
     _lib.count_launch()
 
@@ -142,8 +163,9 @@ def gather_rows(slot: SymmetricBuffer, peer: torch.Tensor, row: torch.Tensor, n_
     out = torch.empty((n_out, width), dtype=slot.tensor.dtype if slot.tensor.dtype.is_floating_point else _lib.lp_dtype(), device=peer.device)
     if _lib.DEBUG_KERNELS:     # the debug build checks every routed row against the size of the peers' buffers
         lib.hg_debug_set_gather_row_limit(slot.tensor.numel() * slot.tensor.element_size() // (2 * max(1, src_row_stride)))
-    rc = lib.hg_peer_gather_rows_bf16(slot.ptr_array(), slot.t, peer.data_ptr(), row.data_ptr(), n_out, topk, width,
-                                      src_row_stride, out.data_ptr(), _lib.ptr(scale), _lib.stream())
+    sig, me, epoch = _rendezvous_args(slot)
+    rc = lib.hg_peer_gather_rows_bf16_rv(slot.ptr_array(), slot.t, peer.data_ptr(), row.data_ptr(), n_out, topk, width,
+                                         src_row_stride, out.data_ptr(), _lib.ptr(scale), sig, me, epoch, _lib.stream())
     _lib.check(rc, "hg_peer_gather_rows_bf16")
     _lib.count_launch()
     return out

@@ -112,17 +112,21 @@ class SignalSlots:
 
     _by_group: Dict[tuple, "SignalSlots"] = {}
 
-    def __init__(self, device, pg):
+    def __init__(self, device, pg, channel: str = "zero"):
         self.buf = SymmetricBuffer(8, torch.int32, device, pg)
+        self.channel = channel
         self.epoch = 0
         torch.cuda.synchronize(device)
         dist.barrier(group=pg)           # every rank's slots are zero before anybody publishes
 
     @classmethod
-    def get(cls, device, pg) -> "SignalSlots":
-        key = (str(device), id(pg))
+    def get(cls, device, pg, channel: str = "zero") -> "SignalSlots":
+        """One set of slots per (group, channel).  A channel is a sequence of kernels that every rank runs in the same
+        order on one stream (the call counter is only meaningful within such a sequence): the gradient reductions on
+        the reduction stream are one channel, the all-to-all exchanges on the compute stream another."""
+        key = (str(device), id(pg), channel)
         if key not in cls._by_group:
-            cls._by_group[key] = SignalSlots(device, pg)
+            cls._by_group[key] = SignalSlots(device, pg, channel)
         return cls._by_group[key]
 
     def next_epoch(self) -> int:

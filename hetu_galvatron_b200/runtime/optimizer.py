@@ -53,6 +53,10 @@ class ShardedAdamW:
         from ..parallel.zero import REDUCE
 
         pending = [u for u in self.units if not u._reduced]
+        if pending and self.units:
+            # what the backward hooks queued on the reduction stream comes first: the in-kernel rendezvous counts calls,
+            # so the reductions of a group must run in one order on every rank
+            REDUCE.join(self.units[0].device)
         if any(getattr(u, "fused", False) and u.defer_sync and u.wire_dtype == torch.float32 for u in pending):
             self._sync_fused_groups()      # every rank's backward has written its gradients
             presynced = True
