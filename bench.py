@@ -189,7 +189,8 @@ def run_ours(a):
         opt.zero_grad()
         loss = model.forward_backward(t[:, :-1], i, labels=t[:, 1:])
         opt.step()
-        return float(loss.item())
+        # the loss lives on the last pipeline stage; the other stages have nothing to read back
+        return float(loss.item()) if loss is not None else None
 
     def barrier():
         if n > 1:
@@ -232,6 +233,11 @@ def run_ours(a):
         t = torch.tensor([ms, e2e_ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
+    if n > 1 and model.plan.pp_deg > 1:
+        # rank 0 prints; with pipeline stages the loss is on the last stage
+        vals = [None] * n
+        dist.all_gather_object(vals, loss_val)
+        loss_val = next((v for v in reversed(vals) if v is not None), None)
     tokens = gbsz * S
     value = tokens / (ms / 1000.0)
     peak_mem = torch.cuda.max_memory_allocated() / 2 ** 30

@@ -50,7 +50,7 @@ def fused_vs_nccl(group, slab: int, K: int, N: int, iters: int = 10):
         ts = []
         for _ in range(iters):
             flush.zero_()
-            dist.barrier()
+            dist.barrier(group=group.group)
             torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -60,18 +60,18 @@ def fused_vs_nccl(group, slab: int, K: int, N: int, iters: int = 10):
             ts.append(a.elapsed_time(b))
         ts.sort()
         v = torch.tensor([ts[len(ts) // 2]], device=dev)
-        dist.all_reduce(v, op=dist.ReduceOp.MAX)
+        dist.all_reduce(v, op=dist.ReduceOp.MAX, group=group.group)
         return float(v)
 
     def nccl_ag():
         xg = torch.empty(t * slab, K, device=dev, dtype=torch.bfloat16)
-        dist.all_gather_into_tensor(xg, x)
+        dist.all_gather_into_tensor(xg, x, group=group.group)
         return ops.gemm(xg, w)
 
     def nccl_rs():
         y = ops.gemm(x2, w)
         o = torch.empty(slab, N, device=dev, dtype=torch.bfloat16)
-        dist.reduce_scatter_tensor(o, y)
+        dist.reduce_scatter_tensor(o, y, group=group.group)
         return o
 
     res = {"ag_fused_ms": timed(lambda: fc.ag_gemm(x, w, group)), "ag_nccl_ms": timed(nccl_ag),
