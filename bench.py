@@ -115,7 +115,8 @@ def plan_knobs(n: int, a):
     else:
         chunks = PER_GPU_BATCH // (a.micro_batch or 2)
         dp_type = a.dp_type
-    if a.layers or a.micro_batch is not None or a.checkpoint or (cfg is not None and cfg.get("global_bsz") != PER_GPU_BATCH * n):
+    if a.layers or a.micro_batch is not None or a.checkpoint or a.pp > 1 or a.tp > 1 or \
+            (cfg is not None and cfg.get("global_bsz") != PER_GPU_BATCH * n):
         cfg = None      # debugging overrides: plain flags with the strategy's micro-batching
     return cfg, path, max(1, chunks), (dp_type if n > 1 else "ddp")
 
@@ -151,7 +152,8 @@ def run_ours(a):
     model_cfg = dict(MODEL)
     if a.layers:
         model_cfg["num_layers"] = a.layers
-    parallel = dict(pp_deg=1, global_tp_deg=1, default_dp_type=dp_type, sdp=1 if dp_type == "zero3" else 0,
+    parallel = dict(pp_deg=a.pp, global_tp_deg=a.tp, vocab_tp=a.tp, pipeline_type="pipedream_flush",
+                    default_dp_type=dp_type if n > a.pp * a.tp else "ddp", sdp=1 if dp_type == "zero3" else 0,
                     mixed_precision="bf16", async_grad_reduce=True, global_checkpoint=int(a.checkpoint))
     if strategy is not None:
         parallel["galvatron_config_path"] = strategy      # JSON mode: the per-layer plan comes from the search
@@ -288,6 +290,8 @@ def main():
     ap.add_argument("--dp-type", default=os.environ.get("HG_BENCH_DP", "zero2"))
     ap.add_argument("--layers", type=int, default=0, help="debug only: fewer layers (result is not a headline number)")
     ap.add_argument("--checkpoint", type=int, default=0)
+    ap.add_argument("--pp", type=int, default=1, help="debug only: pipeline stages of a plain-flags plan")
+    ap.add_argument("--tp", type=int, default=1, help="debug only: tensor-parallel degree of a plain-flags plan")
     a = ap.parse_args()
     a.warmup = max(a.warmup, 3)
     if a.impl == "reference":
