@@ -232,7 +232,8 @@ class MoERouting:
         key = torch.where(valid, flat, torch.full_like(flat, E))
         order = torch.argsort(key, stable=True)
         key_sorted = key[order]
-        counts = torch.bincount(key, minlength=E + 1)[:E]
+        # (not torch.bincount: it reads the largest key back on the host)
+        counts = torch.zeros(E + 1, dtype=torch.int64, device=dev).scatter_add_(0, key, torch.ones_like(key))[:E]
         ustart = torch.cumsum(counts, 0) - counts
         padded = (counts + align - 1) // align * align
         per_rank = padded.view(ep, E_loc)

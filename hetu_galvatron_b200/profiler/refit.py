@@ -12,11 +12,14 @@ in ``configs/computation_profiling_*.json`` and writes
 
     hardware_configs/b200_refit.json   {"backward_forward_ratio": r, ...}
 
-where ``1 + r = (T_full(Lmax) - T_full(Lmin) - o * dL) / (T_fwd(Lmax) - T_fwd(Lmin))`` and ``o`` is the optimizer step
-of one layer, which does not scale with the batch and is therefore kept as its own term
-(``optimizer_ms_per_layer``): AdamW and the gradient norm stream 34 bytes per parameter against the 18 bytes of model
-state the memory profile reports, at the measured copy bandwidth.  The search engine picks the file up from the
-hardware-profile directory.
+where ``1 + r = (T_full(Lmax) - T_full(Lmin) - o * dL) / (T_fwd(Lmax) - T_fwd(Lmin))`` and ``o`` is the part of a layer's
+iteration that does not scale with the number of micro-batches (AdamW, gradient norm, gradient-buffer handling), kept
+as its own term (``optimizer_ms_per_layer``).  ``o`` is measured, not derived: the same two layer counts are run a
+second time with two micro-batches per step (twice the batch, ``chunks=2``); with ``d1`` / ``d2`` the per-layer
+iteration times at one / two micro-batches, ``x = d2 - d1`` is a micro-batch's forward + backward and ``o = 2 d1 - d2``.
+(Streaming 34 bytes per parameter at the copy bandwidth, the analytic estimate used when the second pair of runs is
+missing, gives 0.98 ms for a Llama-2-7B layer; the measurement is about twice that.)  The search engine picks the file
+up from the hardware-profile directory.
 """
 from __future__ import annotations
 
@@ -46,6 +49,20 @@ def ratio_from_times(fwd: Dict[str, float], full: Dict[str, float], lmin: int, l
     if d_fwd <= 0 or d_full <= d_fwd:
         raise ValueError("inconsistent timings: forward %s, full %s" % (d_fwd, d_full))
     return d_full / d_fwd - 1.0
+
+
+def optimizer_ms_from_accumulation(full: Dict[str, float], lmin: int, lmax: int, bsz: int, seq: int) -> Optional[float]:
+    """Per-layer time that does not scale with the micro-batch count, from iteration times at one micro-batch
+    (batch ``bsz``) and two (batch ``2*bsz``): ``o = 2 * d1 - d2`` with ``d`` the per-layer differences.  ``None`` when
+    the two-micro-batch runs are missing or the result is not positive."""
+    k = lambda L, b: "layernum%d_bsz%d_seq%d" % (L, b, seq)  # noqa: E731
+    try:
+        d1 = (full[k(lmax, bsz)] - full[k(lmin, bsz)]) / (lmax - lmin)
+        d2 = (full[k(lmax, 2 * bsz)] - full[k(lmin, 2 * bsz)]) / (lmax - lmin)
+    except KeyError:
+        return None
+    o = 2.0 * d1 - d2
+    return o if 0.0 < o < d1 else None
 
 
 def measured_hbm_gbs(default: float = 6500.0) -> float:
@@ -81,6 +98,10 @@ def main(argv=None, run=os.system, out_dir: Optional[str] = None, no_launch: boo
             ov = dict(base)
             ov["runtime.model.num_layers"] = L
             run(prof._command(ov, log_dir, "full_layernum_%d" % L))
+        for L in (lmin, lmax):     # the same with two micro-batches per step: separates the per-step part
+            ov = dict(base)
+            ov.update({"runtime.model.num_layers": L, "runtime.train.global_batch_size": 2 * bsz, "runtime.train.chunks": 2})
+            run(prof._command(ov, log_dir, "full_layernum_%d_chunks2" % L))
     fwd = read_json_config(prof.time_profiling_path())
     full = read_json_config(prof._config_path("iteration"))
     opt_ms = 0.0
@@ -91,6 +112,9 @@ def main(argv=None, run=os.system, out_dir: Optional[str] = None, no_launch: boo
             if key in mem and str(seq) in mem[key]:
                 opt_ms = optimizer_ms_per_layer(mem[key][str(seq)]["parameter_size"], measured_hbm_gbs())
                 break
+    measured = optimizer_ms_from_accumulation(full, lmin, lmax, bsz, seq)
+    if measured is not None:
+        opt_ms = measured
     r = ratio_from_times(fwd, full, lmin, lmax, bsz, seq, opt_ms)
     out_dir = out_dir or os.path.join(work, "hardware_configs")
     path = os.path.join(out_dir, "b200_refit.json")

@@ -136,6 +136,7 @@ class LayerTimeCost:
         L = model_args.layer_num
         self.L = L
         self.lbsz = global_batch_size // chunks // s.dp_size  # data-parallel (not sdp) split of the batch
+        self.chunks = max(1, int(chunks))
         w = s.tp_sp_size
         # computation
         fwd = pm.forward_computation_time
@@ -208,7 +209,8 @@ class LayerTimeCost:
             res = res + self.zero3_gather_msg * self.dc
         if hw.optimizer_ms_per_layer:
             shard = s.sdp_size if s.dp_type in (DPType.ZERO2, DPType.ZERO3) else 1
-            res = res + hw.optimizer_ms_per_layer * self.L / (s.tp_size * shard)
+            # a per-step cost; this result is one micro-batch's share (the pipeline model multiplies it by `chunks`)
+            res = res + hw.optimizer_ms_per_layer * self.L / (s.tp_size * shard) / self.chunks
         if s.pp_size > 1 and self.p2p_coe is not None:
             res = res + self.p2p_msg * self.p2p_coe
         return res * 0.001 * hw.costmodel_coe / self.L

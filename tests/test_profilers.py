@@ -185,6 +185,11 @@ def test_refit_ratio_and_optimizer_term():
         refit.ratio_from_times(fwd, fwd, 2, 4, 2, 4096)
     # 18 bytes of state per parameter are streamed as 34 bytes per step
     assert refit.optimizer_ms_per_layer(900.0, 6500.0) == pytest.approx(3600.0 * 34 / 18 / 1024 / 6500 * 1e3)
+    # the per-step term from one and two micro-batches per step: d1 = x + o = 13, d2 = 2x + o = 24 -> o = 2
+    full2 = {"layernum2_bsz2_seq4096": 30.0, "layernum4_bsz2_seq4096": 56.0,
+             "layernum2_bsz4_seq4096": 50.0, "layernum4_bsz4_seq4096": 98.0}
+    assert refit.optimizer_ms_from_accumulation(full2, 2, 4, 2, 4096) == pytest.approx(2.0)
+    assert refit.optimizer_ms_from_accumulation(full, 2, 4, 2, 4096) is None
 
     def cost(opt_ms, ratio, dp_type, dp):
         hw = ProfileHardwareArgs(allreduce_latency_per_MB_dict={"%d_1" % dp: 0.0, "%d_0" % dp: 0.0, "1_1": 0.0},
