@@ -78,8 +78,10 @@ def staging_for(group, nbytes: int, device) -> A2AStaging:
 
 
 def usable(x: torch.Tensor, group) -> bool:
+    from .fused_zero import available
+
     return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and group is not None and 1 < group.size <= 8
-            and (x.shape[-1] % 8 == 0))
+            and (x.shape[-1] % 8 == 0) and available(x.device, group.size, group.group))
 
 
 def _rendezvous_args(slot: SymmetricBuffer):

@@ -178,10 +178,16 @@ class _LinearReduceScatter(torch.autograd.Function):
         return dx, dw, None
 
 
+def _peer_ok(x: torch.Tensor, group) -> bool:
+    from .fused_zero import available
+
+    return available(x.device, group.size, group.group)
+
+
 def all_gather_linear(x: torch.Tensor, w: torch.Tensor, bias, group) -> torch.Tensor:
     """``[S_loc, B, K]`` -> ``[S_loc * t, B, N_loc]``"""
     S, B, K = x.shape
-    if not usable(S * B, K):
+    if not usable(S * B, K) or not _peer_ok(x, group):
         from . import mappings as mp
 
         return ops.linear(mp.gather_first_dim(x, group, grad_is_partial=True), w, bias)
@@ -193,7 +199,7 @@ def linear_reduce_scatter(x: torch.Tensor, w: torch.Tensor, group) -> torch.Tens
     """``[S, B, K_loc]`` -> ``[S / t, B, N]``"""
     S, B, K = x.shape
     t = group.size
-    if S % t or not usable(S // t * B, w.shape[0]) or K % 8:
+    if S % t or not usable(S // t * B, w.shape[0]) or K % 8 or not _peer_ok(x, group):
         from . import mappings as mp
 
         return mp.reduce_scatter_first_dim(ops.linear(x, w, None), group)

@@ -73,14 +73,50 @@ def verify_guards() -> int:
     return sum(0 if b.guards_intact() else 1 for b in _GUARDED)
 
 
-def available(device, n: int) -> bool:
+_PROBED: Dict[tuple, bool] = {}
+
+
+def symmetric_memory_works(device, pg) -> bool:
+    """Whether symmetric memory can really be set up over ``pg`` on this machine: a one-time probe that allocates a
+    small buffer, runs the rendezvous and reads the peer pointers, then agrees on the outcome over the group (a rank
+    where the probe failed makes every rank of the group fall back to NCCL together, with one warning).  Collective
+    over ``pg``; the answer is cached."""
+    key = (str(device), id(pg))
+    if key in _PROBED:
+        return _PROBED[key]
+    ok = 1
+    why = ""
+    try:
+        import torch.distributed._symmetric_memory as symm
+
+        t = symm.empty(64, dtype=torch.float32, device=device)
+        h = symm.rendezvous(t, pg)
+        if len(list(h.buffer_ptrs)) != dist.get_world_size(pg):
+            ok, why = 0, "rendezvous returned %d peer pointers" % len(list(h.buffer_ptrs))
+    except Exception as e:     # no peer access, no fabric handle support, an older torch, ...
+        ok, why = 0, "%s: %s" % (type(e).__name__, str(e)[:200])
+    flag = torch.tensor([ok], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=pg)
+    works = bool(int(flag.item()))
+    if not works and dist.get_rank(pg) == 0:
+        import warnings
+
+        warnings.warn("symmetric memory is not usable over this group (%s): the peer-memory kernels are off for it and "
+                      "NCCL carries the traffic" % (why or "a peer rank could not set it up"))
+    _PROBED[key] = works
+    return works
+
+
+def available(device, n: int, pg=None) -> bool:
+    """Peer-memory kernels can serve a group of ``n`` ranks on ``device`` (2..8 ranks of one node, CUDA, and, when the
+    process group is given, a successful :func:`symmetric_memory_works` probe)."""
     if device.type != "cuda" or n < 2 or n > MAX_PEERS:
         return False
     try:
         import torch.distributed._symmetric_memory  # noqa: F401
     except Exception:
         return False
-    return True
+    return True if pg is None else symmetric_memory_works(device, pg)
 
 
 _TICKS: Dict[Tuple[int, int], torch.Tensor] = {}

@@ -131,6 +131,13 @@ class Reshard(nn.Module):
         self.j = rank_in_stage % max(self.g_old, self.g_new)  # index inside the larger block
         self.identity = (old_width == new_width and old_cp == new_cp)
 
+    def _peer_block_ok(self, x: torch.Tensor) -> bool:
+        """Symmetric memory works over the block of ranks this move spans (probed once, agreed over the block)."""
+        from .fused_zero import available
+
+        grp = self.old.tsp_cp if self.g_old >= self.g_new else self.new.tsp_cp
+        return grp is not None and grp.group is not None and available(x.device, grp.size, grp.group)
+
     def _pull(self, x: torch.Tensor, S: int, src, dst) -> torch.Tensor:
         from . import fused_a2a as fa
 
@@ -153,7 +160,7 @@ class Reshard(nn.Module):
             return x
         floating = x.is_floating_point()
         if self.peer and floating and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and x.dim() == 3 and x.shape[-1] % 8 == 0 \
-                and max(self.g_old, self.g_new) <= 8:
+                and max(self.g_old, self.g_new) <= 8 and self._peer_block_ok(x):
             S = x.shape[0] * self.g_old
             return _PeerReshard.apply(x, self, S)
         gather = (lambda t, g: mp.gather_first_dim(t, g, grad_is_partial=True)) if floating else \

@@ -203,7 +203,7 @@ class ShardedUnit:
         if fused_zero and params and self.dp_type in ("zero2", "zero3") and self.dtype in (torch.bfloat16, torch.float16):
             from . import fused_zero as fz
 
-            self.fused = fz.available(self.device, self.n)
+            self.fused = fz.available(self.device, self.n, self.pg)
         # per-micro-batch reduction of a sharded unit: the unsharded gradient buffer is borrowed from a pool
         self.pooled = bool(params) and not defer_sync and self.dp_type in ("zero2", "zero3")
         if params:
