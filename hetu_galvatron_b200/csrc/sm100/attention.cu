@@ -720,6 +720,379 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 }
 
 // =================================================================================================
+// Backward, part 1 with 128-query steps and the probabilities kept in tensor memory (head dim 128).
+// The 64-query version issues its score products with N = 64, which occupy the tensor core as long as N = 128 would,
+// and stages P^T / dS^T through 64 KB of shared memory.  Here a step covers 128 queries:
+//   S^T = K Q^T and dP^T = V dO^T are 128 x 128 products (8 MMAs each);
+//   each softmax thread (one key row, 64 of the 128 query columns) loads its S^T values, and stores
+//   P^T = exp2(S^T c - lse) back as packed 16-bit pairs over the first half of the columns it has just read;
+//   dS^T = P^T (dP^T - D) goes over the dP^T columns the same way;
+//   dV += P^T dO and dK += dS^T Q take their A operand from tensor memory (8 MMAs each, K = 128 queries).
+// Per 128 queries that is 32 MMAs instead of 48, no shared-memory traffic from the softmax threads, and the 64 KB
+// of staging buffers become Q / dO ring slots (three of Q, two of dO: a Q tile lives from its S^T product to its
+// dK product, a dO tile from dP^T to dV).
+//
+// Tensor memory (512 columns): S^T 0..127 (P^T packed in 0..31 and 64..95), dP^T 128..255 (dS^T packed in 128..159
+// and 192..223), dV 256..383, dK 384..511.  There is one S^T / dP^T pair, so the MMA warp and the softmax threads
+// alternate in two half-steps, each overlapping one MMA group with one softmax phase:
+//   MMA  [dV(i), S^T(i+1)]   while the threads turn dP^T(i) into dS^T(i)     (phase B)
+//   MMA  [dK(i), dP^T(i+1)]  while the threads turn S^T(i+1) into P^T(i+1)   (phase A)
+// The tensor core executes its MMAs in issue order, which is what makes the in-place reuse safe: S^T(i+1) is issued
+// after dV(i), the last reader of P^T(i), and dP^T(i+1) after dK(i), the last reader of dS^T(i).
+// =================================================================================================
+template <int HD>
+struct Dkv128Smem {
+  static constexpr int kKV = 128 * HD * 2;       // resident K or V
+  static constexpr int kQD = 128 * HD * 2;       // one Q or dO tile
+  static constexpr int kQStages = 3;
+  static constexpr int kDOStages = 2;
+  static constexpr int kStats = 2 * 2 * 128 * 4;  // -lse*log2e and D of a step, double buffered
+  static constexpr int kBars = 256;
+  static constexpr int kUsed = 2 * kKV + (kQStages + kDOStages) * kQD + kStats + kBars;
+  static constexpr int kTotal = 232448;          // everything a CTA can have; the 1024-byte alignment of the tiles comes out of the rest
+};
+
+template <int HD>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                        const BwdParams p) {
+  static_assert(HD == 128, "the 128-query dK/dV kernel is written for head dim 128");
+  extern __shared__ uint8_t smem_raw[];
+  using L = Dkv128Smem<HD>;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  if (base + L::kUsed > smem_raw + L::kTotal) {   // the same for every thread: nothing has been set up yet
+    if (threadIdx.x == 0) set_status(p.status, kTimeoutOther);
+    return;
+  }
+  uint8_t* sK = base;
+  uint8_t* sV = sK + L::kKV;
+  constexpr int NQ = L::kQStages, ND = L::kDOStages;
+  uint8_t* sQ = sV + L::kKV;                 // NQ tiles
+  uint8_t* sDO = sQ + NQ * L::kQD;           // ND tiles
+  float* sStats = reinterpret_cast<float*>(sDO + ND * L::kQD);   // [2][256]: 128 x -lse2, 128 x D
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStats) + L::kStats);
+  uint64_t* kv_full = bars;          // 1
+  uint64_t* q_full = bars + 1;       // 3
+  uint64_t* q_empty = bars + 4;      // 3
+  uint64_t* do_full = bars + 7;      // 2
+  uint64_t* do_empty = bars + 9;     // 2
+  uint64_t* st_full = bars + 11;     // S^T of a step is in tensor memory
+  uint64_t* dpt_full = bars + 12;    // dP^T of a step is in tensor memory
+  uint64_t* p_full = bars + 13;      // every thread has stored its part of P^T
+  uint64_t* ds_full = bars + 14;     // every thread has stored its part of dS^T
+  uint64_t* acc_full = bars + 15;    // the last dK product has completed
+  uint64_t* stats_full = bars + 16;  // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int kb = blockIdx.x, g = blockIdx.y, b = blockIdx.z;  // g = kv head
+  const int k0 = kb * 128;
+  int q_first = 0;                                            // first query row that can see this key block
+  if (p.causal) q_first = max(0, p.k_pos0 + k0 - p.q_pos0);
+  const int qs0 = q_first / 128;                              // first 128-row query step
+  const int n_qs = (p.Sq + 127) / 128;
+  const int steps_per_head = max(0, n_qs - qs0);
+  const int n_it = steps_per_head * p.qpg;
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ); tma_prefetch_desc(&tmK); tma_prefetch_desc(&tmV); tma_prefetch_desc(&tmDO);
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < NQ; ++i) { mbar_init(&q_full[i], 1); mbar_init(&q_empty[i], 1); }
+    for (int i = 0; i < ND; ++i) { mbar_init(&do_full[i], 1); mbar_init(&do_empty[i], 1); }
+    mbar_init(st_full, 1);
+    mbar_init(dpt_full, 1);
+    mbar_init(p_full, kBwdSoftmaxThreads);
+    mbar_init(ds_full, kBwdSoftmaxThreads);
+    mbar_init(acc_full, 1);
+    mbar_init(&stats_full[0], kBwdSoftmaxThreads);
+    mbar_init(&stats_full[1], kBwdSoftmaxThreads);
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tST = tmem, tDPT = tmem + 128, tDV = tmem + 256, tDK = tmem + 384;
+
+  const int h0 = g * p.qpg;  // first query head of the group
+  const int kslot = p.kmap.slot(h0, p.qpg), vslot = p.vmap.slot(h0, p.qpg);
+
+  if (warp == 0) {
+    if (n_it > 0) {
+      // the whole warp walks the loop, one elected lane issues the copies (see producer_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
+      if (issuer) mbar_expect_tx(kv_full, 2 * L::kKV);
+#pragma unroll
+      for (int c = 0; c < HD / 64; ++c) {
+        if (issuer) tma_load_4d(sK + c * 128 * 128, &tmK, kv_full, c * 64, kslot, k0, b);
+        if (issuer) tma_load_4d(sV + c * 128 * 128, &tmV, kv_full, c * 64, vslot, k0, b);
+      }
+      int qs_slot = 0, ds_slot = 0;
+      uint32_t qph = 0, dph = 0;
+      int h = h0, qs = qs0;
+      for (int it = 0; it < n_it; ++it) {
+        const int qrow = qs * 128;
+        const int qslot = p.qmap.slot(h, p.qpg), doslot = p.domap.slot(h, p.qpg);
+        if (!mbar_wait_warp(&q_empty[qs_slot], qph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&q_full[qs_slot], L::kQD);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          if (issuer) tma_load_4d(sQ + qs_slot * L::kQD + c * 128 * 128, &tmQ, &q_full[qs_slot], c * 64, qslot, qrow, b);
+        if (!mbar_wait_warp(&do_empty[ds_slot], dph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&do_full[ds_slot], L::kQD);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          if (issuer) tma_load_4d(sDO + ds_slot * L::kQD + c * 128 * 128, &tmDO, &do_full[ds_slot], c * 64, doslot, qrow, b);
+        if (++qs_slot == NQ) { qs_slot = 0; qph ^= 1; }
+        if (++ds_slot == ND) { ds_slot = 0; dph ^= 1; }
+        if (++qs == n_qs) { qs = qs0; ++h; }
+      }
+    }
+  } else if (warp == 1) {
+    if (n_it > 0) {
+      // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
+      constexpr uint32_t idesc_st = make_idesc_lp(128, 128, false, false);
+      constexpr uint32_t idesc_acc = make_idesc_lp(128, HD, false, true);
+      const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ0 = smem_u32(sQ), aDO0 = smem_u32(sDO);
+      // ring positions: Q / dO tile of the next S^T / dP^T issue, and of the next dK / dV issue
+      int q_s = 0, q_k = 0, d_p = 0, d_v = 0;
+      uint32_t qph_s = 0, dph_p = 0;
+      auto issue_st = [&]() -> bool {     // S^T of the next step
+        if (!mbar_wait_warp(&q_full[q_s], qph_s, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aQ = aQ0 + q_s * L::kQD;
+        if (issuer) {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tST, kmajor_desc(aK, 128, kk), kmajor_desc(aQ, 128, kk), idesc_st, kk != 0);
+          umma_commit(st_full);
+        }
+        __syncwarp();
+        if (++q_s == NQ) { q_s = 0; qph_s ^= 1; }
+        return true;
+      };
+      auto issue_dpt = [&]() -> bool {    // dP^T of the next step
+        if (!mbar_wait_warp(&do_full[d_p], dph_p, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aDO = aDO0 + d_p * L::kQD;
+        if (issuer) {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tDPT, kmajor_desc(aV, 128, kk), kmajor_desc(aDO, 128, kk), idesc_st, kk != 0);
+          umma_commit(dpt_full);
+        }
+        __syncwarp();
+        if (++d_p == ND) { d_p = 0; dph_p ^= 1; }
+        return true;
+      };
+      bool ok = mbar_wait_warp(kv_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      if (ok) ok = issue_st();
+      if (ok) ok = issue_dpt();
+      for (int it = 0; ok && it < n_it; ++it) {
+        const uint32_t ph = it & 1;
+        // ---- dV(it), then S^T(it+1) over the columns dV has just read
+        if (!mbar_wait_warp(p_full, ph, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (issuer) {
+          const uint32_t aDO = aDO0 + d_v * L::kQD;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)     // k-step kk = queries 16kk..16kk+15 = 8 packed columns of the half kk/4
+            umma_f16_ts(tDV, tST + (kk >> 2) * 64 + (kk & 3) * 8, mnmajor_desc(aDO, 128, kk), idesc_acc, (it | kk) != 0);
+          umma_commit(&do_empty[d_v]);
+        }
+        __syncwarp();
+        if (++d_v == ND) d_v = 0;
+        if (it + 1 < n_it) { ok = issue_st(); if (!ok) break; }
+        // ---- dK(it), then dP^T(it+1) over the columns dK has just read
+        if (!mbar_wait_warp(ds_full, ph, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (issuer) {
+          const uint32_t aQ = aQ0 + q_k * L::kQD;
+#pragma unroll
+          for (int kk = 0; kk < 8; ++kk)
+            umma_f16_ts(tDK, tDPT + (kk >> 2) * 64 + (kk & 3) * 8, mnmajor_desc(aQ, 128, kk), idesc_acc, (it | kk) != 0);
+          umma_commit(&q_empty[q_k]);
+        }
+        __syncwarp();
+        if (++q_k == NQ) q_k = 0;
+        if (it + 1 < n_it) { ok = issue_dpt(); if (!ok) break; }
+      }
+      if (ok && issuer) umma_commit(acc_full);
+      __syncwarp();
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    const int wq = warp & 3;
+    const int half = (warp - 2) >> 2;     // which 64 of the step's 128 query columns this warpgroup owns
+    const int c0 = half * 64;
+    const int row = wq * 32 + lane_id();  // key row inside the block
+    const int tid = threadIdx.x - 64;     // 0..255 among the softmax threads
+    const uint32_t lane_off = uint32_t(wq * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    const int k_pos = p.k_pos0 + k0 + row;
+    const bool k_valid = (k0 + row) < p.Skv;
+    bool ok = true;
+    // Per-query statistics of a step, fetched one step ahead: thread t < 128 carries -lse * log2 e of query t of the
+    // step, thread 128 + t carries D of query t.
+    int ld_h = h0, ld_qs = qs0, ld_it = 0;
+    auto load_stat = [&]() -> float {
+      float v = 0.f;
+      if (ld_it < n_it) {
+        const int q = ld_qs * 128 + (tid & 127);
+        if (q >= p.Sq) {
+          v = (tid < 128) ? INFINITY : 0.f;    // rows past the end: -inf after scaling, 2^-inf = 0
+        } else {
+          const float* src = (tid < 128) ? p.LSE : p.D;
+          v = src[(size_t(b) * p.nheads + ld_h) * p.Sq + q];
+        }
+      }
+      ++ld_it;
+      if (++ld_qs == n_qs) { ld_qs = qs0; ++ld_h; }
+      return v;
+    };
+    const float stat_scale = (tid < 128) ? -kLog2e : 1.f;
+    float stat_next = load_stat();
+    if (n_it > 0) {
+      sStats[tid] = stat_next * stat_scale;
+      mbar_arrive(&stats_full[0]);
+      stat_next = load_stat();
+    }
+    int cur_qs = qs0;
+    for (int it = 0; it < n_it; ++it) {
+      const int sb = it & 1;
+      const uint32_t ph = it & 1;
+      const int qrow = cur_qs * 128;
+      if (++cur_qs == n_qs) cur_qs = qs0;
+      const float* st = sStats + sb * 256;
+      uint32_t pp[32];                    // this thread's 64 probabilities, packed, kept for the second phase
+      // ---------------- phase A: S^T -> P^T
+      if (!mbar_wait_warp(&stats_full[sb], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      if (!mbar_wait_warp(st_full, ph, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      {
+        // only steps that touch the diagonal, or a key block with rows past the end, need the mask
+        const bool need_mask = !k_valid || (p.causal && (p.q_pos0 + qrow < p.k_pos0 + k0 + 127));
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t r[32];
+          tmem_ld32(tST + lane_off + c0 + hh * 32, r);
+          tmem_ld_wait();
+          const float4* nl4 = reinterpret_cast<const float4*>(st + c0 + hh * 32);
+          const int q_base = p.q_pos0 + qrow + c0 + hh * 32;
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 nl = nl4[i >> 2];
+            const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
+            float e[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) e[u] = ex2(fmaf(__uint_as_float(r[i + u]), sl2, nlv[u]));
+            if (need_mask) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u)
+                if (!k_valid || (p.causal && k_pos > q_base + i + u)) e[u] = 0.f;
+            }
+            pp[hh * 16 + (i >> 1)] = pack_bf16(e[0], e[1]);
+            pp[hh * 16 + (i >> 1) + 1] = pack_bf16(e[2], e[3]);
+          }
+        }
+      }
+      tmem_st32(tST + lane_off + c0, pp);   // 32 packed columns over the first half of the 64 just read
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_full);
+      // ---------------- phase B: dP^T -> dS^T
+      if (!mbar_wait_warp(dpt_full, ph, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      {
+        uint32_t dsp[32];
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t r[32];
+          tmem_ld32(tDPT + lane_off + c0 + hh * 32, r);
+          tmem_ld_wait();
+          const float4* dd4 = reinterpret_cast<const float4*>(st + 128 + c0 + hh * 32);
+#pragma unroll
+          for (int i = 0; i < 32; i += 4) {
+            const float4 dd = dd4[i >> 2];
+            const float2 p01 = hg_unpack2(pp[hh * 16 + (i >> 1)]), p23 = hg_unpack2(pp[hh * 16 + (i >> 1) + 1]);
+            dsp[hh * 16 + (i >> 1)] = pack_bf16(p01.x * (__uint_as_float(r[i]) - dd.x),
+                                                 p01.y * (__uint_as_float(r[i + 1]) - dd.y));
+            dsp[hh * 16 + (i >> 1) + 1] = pack_bf16(p23.x * (__uint_as_float(r[i + 2]) - dd.z),
+                                                     p23.y * (__uint_as_float(r[i + 3]) - dd.w));
+          }
+        }
+        tmem_st32(tDPT + lane_off + c0, dsp);
+      }
+      // the next step's statistics go to the other buffer: its last readers were the second phases of step it-1,
+      // and every thread finished that before it arrived on this step's statistics barrier
+      if (it + 1 < n_it) {
+        sStats[(sb ^ 1) * 256 + tid] = stat_next * stat_scale;
+        mbar_arrive(&stats_full[sb ^ 1]);
+        stat_next = load_stat();
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(ds_full);
+    }
+    // ---- epilogue ----
+    const int krow = k0 + row;
+    const int dkslot = p.dkmap.slot(h0, p.qpg), dvslot = p.dvmap.slot(h0, p.qpg);
+    hg_lp_t* dk = p.dK + int64_t(krow) * p.dk_ss + int64_t(b) * p.dk_sb + int64_t(dkslot) * HD;
+    hg_lp_t* dv = p.dV + int64_t(krow) * p.dv_ss + int64_t(b) * p.dv_sb + int64_t(dvslot) * HD;
+    if (n_it == 0) {
+      if (krow < p.Skv) {
+#pragma unroll
+        for (int i = half; i < HD / 8; i += 2) {
+          reinterpret_cast<uint4*>(dk)[i] = make_uint4(0, 0, 0, 0);
+          reinterpret_cast<uint4*>(dv)[i] = make_uint4(0, 0, 0, 0);
+        }
+      }
+    } else if (ok && !*abort_flag && mbar_wait_warp(acc_full, 0, p.status, kTimeoutOther, abort_flag)) {
+      tc_fence_after();
+#pragma unroll
+      for (int c = half; c < HD / 32; c += 2) {   // the two warpgroups take alternate 32-column chunks
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tDV + lane_off + c * 32, r0);
+        tmem_ld32(tDK + lane_off + c * 32, r1);
+        tmem_ld_wait();
+        if (krow < p.Skv) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u, w;
+            u.x = pack_bf16(__uint_as_float(r0[q * 8 + 0]), __uint_as_float(r0[q * 8 + 1]));
+            u.y = pack_bf16(__uint_as_float(r0[q * 8 + 2]), __uint_as_float(r0[q * 8 + 3]));
+            u.z = pack_bf16(__uint_as_float(r0[q * 8 + 4]), __uint_as_float(r0[q * 8 + 5]));
+            u.w = pack_bf16(__uint_as_float(r0[q * 8 + 6]), __uint_as_float(r0[q * 8 + 7]));
+            w.x = pack_bf16(__uint_as_float(r1[q * 8 + 0]) * p.scale, __uint_as_float(r1[q * 8 + 1]) * p.scale);
+            w.y = pack_bf16(__uint_as_float(r1[q * 8 + 2]) * p.scale, __uint_as_float(r1[q * 8 + 3]) * p.scale);
+            w.z = pack_bf16(__uint_as_float(r1[q * 8 + 4]) * p.scale, __uint_as_float(r1[q * 8 + 5]) * p.scale);
+            w.w = pack_bf16(__uint_as_float(r1[q * 8 + 6]) * p.scale, __uint_as_float(r1[q * 8 + 7]) * p.scale);
+            reinterpret_cast<uint4*>(dv + c * 32)[q] = u;
+            reinterpret_cast<uint4*>(dk + c * 32)[q] = w;
+          }
+        }
+      }
+    } else {
+      *abort_flag = 1;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =================================================================================================
 // Backward, part 2: one CTA per (query block of 128, head, batch); loops over 64-row key steps.
 // Thread == query row.   S = Q K^T, dP = dO V^T (N = 64);  dS = P * (dP - D);  dQ += dS K
 // =================================================================================================
@@ -1250,6 +1623,10 @@ int make_map(CUtensorMap* out, const void* base, int hd, int slots, int S, int B
   return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
 }
 
+// dK/dV kernel for head dim 128: 0 = 128-query steps with P^T / dS^T in tensor memory, 1 = 64-query steps staged
+// through shared memory (kept for head dim 64 and for side-by-side timing).
+int g_dkv_variant = 0;
+
 template <typename K>
 int set_smem(K kernel, int bytes) {
   return int(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
@@ -1299,6 +1676,13 @@ int hg_flash_fwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
   return int(cudaGetLastError());
 }
 
+// Selects the dK/dV kernel used for head dim 128 (see g_dkv_variant); returns the previous value.
+int hg_attn_set_dkv_variant(int v) {
+  const int old = g_dkv_variant;
+  g_dkv_variant = v ? 1 : 0;
+  return old;
+}
+
 // dsum: scratch [B, nheads, Sq] fp32 (filled here with rowsum(dO*O)).
 int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTensor* v, const HgAttnTensor* o,
                  const HgAttnTensor* d_o, const void* lse, void* dsum, const HgAttnTensor* dq, const HgAttnTensor* dk,
@@ -1326,12 +1710,18 @@ int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
   p.status = hg_host::status_ptr();
   {
     CUtensorMap tq, tk, tv, tdo;
-    if ((rc = make_map(&tq, q->ptr, hd, q->slots, Sq, B, q->ss, q->sb, 64))) return rc;
+    const bool wide = (hd == 128) && g_dkv_variant == 0;   // 128-query steps, P^T / dS^T in tensor memory
+    const int q_rows = wide ? 128 : 64;
+    if ((rc = make_map(&tq, q->ptr, hd, q->slots, Sq, B, q->ss, q->sb, q_rows))) return rc;
     if ((rc = make_map(&tk, k->ptr, hd, k->slots, Skv, B, k->ss, k->sb, 128))) return rc;
     if ((rc = make_map(&tv, v->ptr, hd, v->slots, Skv, B, v->ss, v->sb, 128))) return rc;
-    if ((rc = make_map(&tdo, d_o->ptr, hd, d_o->slots, Sq, B, d_o->ss, d_o->sb, 64))) return rc;
+    if ((rc = make_map(&tdo, d_o->ptr, hd, d_o->slots, Sq, B, d_o->ss, d_o->sb, q_rows))) return rc;
     dim3 grid((Skv + 127) / 128, nkv, B);
-    if (hd == 128) {
+    if (wide) {
+      static bool cfg = false;
+      if (!cfg) { if ((rc = set_smem(flash_bwd_dkv128_kernel<128>, Dkv128Smem<128>::kTotal))) return rc; cfg = true; }
+      flash_bwd_dkv128_kernel<128><<<grid, kBwdThreads, Dkv128Smem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+    } else if (hd == 128) {
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(flash_bwd_dkv_kernel<128>, DkvSmem<128>::kTotal))) return rc; cfg = true; }
       flash_bwd_dkv_kernel<128><<<grid, kBwdThreads, DkvSmem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);

@@ -25,6 +25,33 @@ __device__ __forceinline__ uint4 pack8(const float* f) {
   return u;
 }
 
+// A grid-stride walk over (row, col) pairs of a [rows, width] index space without a division per step: the
+// stride is split into whole rows and a remainder once per thread, then every step is an add and a carry.
+// (A 64-bit divide per 16-byte access costs more issue slots than the access leaves room for at HBM speed.)
+struct RowColWalk {
+  int64_t row;
+  int col;
+  int64_t d_row;
+  int d_col;
+  int width;
+  __device__ __forceinline__ RowColWalk(int width_) : width(width_) {
+    const int64_t first = blockIdx.x * int64_t(blockDim.x) + threadIdx.x;
+    const int64_t stride = int64_t(gridDim.x) * blockDim.x;
+    row = first / width;
+    col = int(first - row * width);
+    d_row = stride / width;
+    d_col = int(stride - d_row * width);
+  }
+  __device__ __forceinline__ void next() {
+    row += d_row;
+    col += d_col;
+    if (col >= width) {
+      col -= width;
+      ++row;
+    }
+  }
+};
+
 // ---------------------------------------------------------------------------------------------
 // RoPE, rotate-half (non-interleaved) form, applied in place to `nheads` heads that sit at
 // column offsets head_off[h] (elements) of every token row of a [tokens, row_pitch] buffer.
@@ -37,11 +64,10 @@ __global__ void rope_kernel(hg_lp_t* __restrict__ buf, const int* __restrict__ h
                             int row_pitch, int tokens, int batch, const int* __restrict__ pos, int pos_offset,
                             const float* __restrict__ cos_t, const float* __restrict__ sin_t, int half, float sign) {
   const int vec_per_head = half >> 3;  // uint4 chunks in one half
-  const int64_t total = int64_t(tokens) * nheads * vec_per_head;
-  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
-    const int c = int(i % vec_per_head);
-    const int h = int((i / vec_per_head) % nheads);
-    const int t = int(i / (int64_t(vec_per_head) * nheads));
+  const int per_token = nheads * vec_per_head;
+  for (RowColWalk w(per_token); w.row < tokens; w.next()) {
+    const int t = int(w.row);
+    const int h = w.col / vec_per_head, c = w.col - h * vec_per_head;
     const int p = pos ? pos[t] : (t / batch + pos_offset);
     hg_lp_t* base = buf + size_t(t) * row_pitch + head_off[h] + c * 8;
     float a[8], b[8], cs[8], sn[8];
@@ -74,11 +100,10 @@ __global__ void rope_interleaved_kernel(hg_lp_t* __restrict__ buf, const int* __
                                         int pos_offset, const float* __restrict__ cos_t,
                                         const float* __restrict__ sin_t, int half, float sign) {
   const int vec_per_head = half >> 2;  // uint4 chunks over the 2*half rotated channels
-  const int64_t total = int64_t(tokens) * nheads * vec_per_head;
-  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
-    const int c = int(i % vec_per_head);
-    const int h = int((i / vec_per_head) % nheads);
-    const int t = int(i / (int64_t(vec_per_head) * nheads));
+  const int per_token = nheads * vec_per_head;
+  for (RowColWalk w(per_token); w.row < tokens; w.next()) {
+    const int t = int(w.row);
+    const int h = w.col / vec_per_head, c = w.col - h * vec_per_head;
     const int p = pos ? pos[t] : (t / batch + pos_offset);
     hg_lp_t* base = buf + size_t(t) * row_pitch + head_off[h] + c * 8;
     float x[8], o[8];
@@ -99,7 +124,7 @@ __global__ void rope_interleaved_kernel(hg_lp_t* __restrict__ buf, const int* __
 // Gated activations on y = [y1 | y2] (each F wide, row pitch 2F):  out = act(y1) * y2
 //   kind 0: SwiGLU (silu), kind 1: GeGLU (tanh GELU).  Non-gated kind 2: out = gelu_tanh(y) (pitch F).
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float silu(float x) { return __fdividef(x, 1.f + __expf(-x)); }
 __device__ __forceinline__ float gelu_tanh(float x) {
   return 0.5f * x * (1.f + tanhf(0.79788456f * x * (1.f + 0.044715f * x * x)));
 }
@@ -111,11 +136,9 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
 template <int KIND>
 __global__ void glu_fwd_kernel(const hg_lp_t* __restrict__ y, hg_lp_t* __restrict__ out, int64_t rows,
                                int F) {
-  const int vpr = F >> 3;
-  const int64_t total = rows * vpr;
-  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
-    const int64_t r = i / vpr;
-    const int c = int(i % vpr);
+  for (RowColWalk w(F >> 3); w.row < rows; w.next()) {
+    const int64_t r = w.row;
+    const int c = w.col;
     float a[8], o[8];
     if (KIND == 2) {
       unpack8(reinterpret_cast<const uint4*>(y + r * F)[c], a);
@@ -135,11 +158,9 @@ __global__ void glu_fwd_kernel(const hg_lp_t* __restrict__ y, hg_lp_t* __restric
 template <int KIND>
 __global__ void glu_bwd_kernel(const hg_lp_t* __restrict__ g, const hg_lp_t* __restrict__ y,
                                hg_lp_t* __restrict__ dy, int64_t rows, int F) {
-  const int vpr = F >> 3;
-  const int64_t total = rows * vpr;
-  for (int64_t i = blockIdx.x * int64_t(blockDim.x) + threadIdx.x; i < total; i += int64_t(gridDim.x) * blockDim.x) {
-    const int64_t r = i / vpr;
-    const int c = int(i % vpr);
+  for (RowColWalk w(F >> 3); w.row < rows; w.next()) {
+    const int64_t r = w.row;
+    const int c = w.col;
     float gv[8], a[8];
     unpack8(reinterpret_cast<const uint4*>(g + r * F)[c], gv);
     if (KIND == 2) {
@@ -155,7 +176,7 @@ __global__ void glu_bwd_kernel(const hg_lp_t* __restrict__ g, const hg_lp_t* __r
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         if (KIND == 0) {
-          const float s = 1.f / (1.f + __expf(-a[j]));
+          const float s = __fdividef(1.f, 1.f + __expf(-a[j]));
           d1[j] = gv[j] * s * (1.f + a[j] * (1.f - s)) * b[j];
           d2[j] = gv[j] * a[j] * s;
         } else {

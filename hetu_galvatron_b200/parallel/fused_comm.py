@@ -22,6 +22,7 @@ import os
 from typing import Dict, Tuple
 
 import torch
+import torch.distributed as dist
 
 from .. import ops
 from ..ops import _lib
@@ -37,7 +38,7 @@ def _round_up(x, m):
 
 class TPWorkspace:
     def __init__(self, group, slab_rows: int, cols: int, device):
-        import torch.distributed._symmetric_memory as symm
+        from .symm_vmm import allocate
 
         self.group, self.t, self.me = group, group.size, group.rank
         self.slab_rows, self.cols = slab_rows, cols
@@ -52,14 +53,11 @@ class TPWorkspace:
         base += 2 * self.ag_bytes
         self.off_rs = [base + i * self.rs_bytes for i in range(2)]
         total = base + 2 * self.rs_bytes
-        self.buf = symm.empty(total, dtype=torch.uint8, device=device)
-        self.buf.zero_()
-        self.handle = symm.rendezvous(self.buf, group.group)
-        self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.buf, self.ptrs, self.handle = allocate(total, device, group.group)
         self.ag_epoch = 0
         self.rs_epoch = 0
         torch.cuda.synchronize(device)
-        self.handle.barrier()
+        dist.barrier(group=group.group)      # every rank's flags are zero before anybody's kernel polls them
 
     def fits(self, slab_rows, cols):
         return slab_rows <= self.slab_rows and cols <= self.cols

@@ -19,6 +19,7 @@ This replaces FSDP's reduce-scatter / all-gather around the optimizer in the ref
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Dict, List, Tuple
 
 import torch
@@ -41,15 +42,14 @@ class SymmetricBuffer:
     never write; :func:`verify_guards` checks them (a peer store that ran past its slice lands there first)."""
 
     def __init__(self, numel: int, dtype, device, pg):
-        import torch.distributed._symmetric_memory as symm
+        from .symm_vmm import allocate
 
         esize = torch.empty(0, dtype=dtype).element_size()
         guard = GUARD_BYTES // esize if _lib.DEBUG_KERNELS else 0
-        self._raw = symm.empty(numel + 2 * guard, dtype=dtype, device=device)
-        self._raw.zero_()
+        raw, base, self.handle = allocate((numel + 2 * guard) * esize, device, pg)
+        self._raw = raw.view(dtype)
         self.tensor = self._raw[guard:guard + numel]
-        self.handle = symm.rendezvous(self._raw, pg)
-        self.ptrs: List[int] = [int(p) + guard * esize for p in self.handle.buffer_ptrs]
+        self.ptrs: List[int] = [int(p) + guard * esize for p in base]
         self.t = len(self.ptrs)
         self._guard = guard
         if guard:
@@ -87,12 +87,15 @@ def symmetric_memory_works(device, pg) -> bool:
     ok = 1
     why = ""
     try:
-        import torch.distributed._symmetric_memory as symm
+        from .symm_vmm import allocate
 
-        t = symm.empty(64, dtype=torch.float32, device=device)
-        h = symm.rendezvous(t, pg)
-        if len(list(h.buffer_ptrs)) != dist.get_world_size(pg):
-            ok, why = 0, "rendezvous returned %d peer pointers" % len(list(h.buffer_ptrs))
+        _buf, ptrs, _owner = allocate(256, device, pg)
+        if len(ptrs) != dist.get_world_size(pg):
+            ok, why = 0, "the allocator returned %d peer pointers" % len(ptrs)
+        if hasattr(_owner, "close"):
+            torch.cuda.synchronize(device)
+            dist.barrier(group=pg)
+            _owner.close()
     except Exception as e:     # no peer access, no fabric handle support, an older torch, ...
         ok, why = 0, "%s: %s" % (type(e).__name__, str(e)[:200])
     flag = torch.tensor([ok], dtype=torch.int32, device=device)

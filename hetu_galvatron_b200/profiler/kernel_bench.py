@@ -92,11 +92,14 @@ def main(argv=None):
     from hetu_galvatron_b200.ops.gemm import OUT_F32_ACC
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn", "norm", "glu", "xent", "adam"])
+    ap.add_argument("kernel", choices=["gemm", "attn", "norm", "glu", "glu_bwd", "rope", "xent", "adam", "sumsq"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
-    ap.add_argument("--variant", default="fwd", choices=["fwd", "dgrad", "wgrad"])
+    ap.add_argument("--variant", default="fwd", choices=["fwd", "dgrad", "wgrad", "wgrad_bf16", "a_mn", "b_mn"],
+                    help="operand layouts / epilogue: fwd (both K-major), dgrad (B N-major), wgrad (A M-major, B N-major, "
+                         "fp32 C += acc), wgrad_bf16 (the same layouts with the plain bf16 store), a_mn (only A "
+                         "M-major), b_mn (only B N-major; dgrad's layout on the wgrad shape)")
     ap.add_argument("--s", type=int, default=4096)
     ap.add_argument("--b", type=int, default=1)
     ap.add_argument("--heads", type=int, default=32)
@@ -123,14 +126,22 @@ def main(argv=None):
         w = torch.randn(N, K, device=dev, dtype=bf)
         dy = torch.randn(M, N, device=dev, dtype=bf)
         mg = torch.zeros(N, K, device=dev, dtype=torch.float32)
+        # layout probes on the weight-gradient shape: C[N, K] = A[N, M-tokens] B[M-tokens, K] with one or both operands
+        # stored transposed (same arithmetic, the operand values do not matter for the rate)
+        dy_t = torch.randn(N, M, device=dev, dtype=bf) if a.variant == "b_mn" else None
+        x_t = torch.randn(K, M, device=dev, dtype=bf) if a.variant == "a_mn" else None
         fn = {"fwd": lambda: ops.gemm(x, w), "dgrad": lambda: ops.gemm(dy, w, b_mn=True),
-              "wgrad": lambda: ops.gemm(dy, x, a_mn=True, b_mn=True, out=mg, out_mode=OUT_F32_ACC)}[a.variant]
+              "wgrad": lambda: ops.gemm(dy, x, a_mn=True, b_mn=True, out=mg, out_mode=OUT_F32_ACC),
+              "wgrad_bf16": lambda: ops.gemm(dy, x, a_mn=True, b_mn=True),
+              "a_mn": lambda: ops.gemm(dy, x_t, a_mn=True),
+              "b_mn": lambda: ops.gemm(dy_t, x, b_mn=True)}[a.variant]
         ms = timed(fn, a.iters, a.warmup, flush)
         rate = 2.0 * M * N * K / ms / 1e9
         out.update(shape=[M, N, K], variant=a.variant, ms=ms, tflops=rate, frac=rate / tf, frac_of=tag)
         if a.sustain > 0:
             lib_fn = {"fwd": lambda: torch.matmul(x, w.t()), "dgrad": lambda: torch.matmul(dy, w),
-                      "wgrad": lambda: torch.matmul(dy.t(), x)}[a.variant]
+                      "wgrad": lambda: torch.matmul(dy.t(), x), "wgrad_bf16": lambda: torch.matmul(dy.t(), x),
+                      "a_mn": lambda: torch.matmul(dy.t(), x_t.t()), "b_mn": lambda: torch.matmul(dy_t, x)}[a.variant]
             for name, f in (("sustained", fn), ("sustained_cublas", lib_fn)):
                 ms_s, mhz, watts = sustained(f, a.sustain)
                 out[name] = {"tflops": 2.0 * M * N * K / ms_s / 1e9, "sm_mhz": mhz, "watts": watts}
@@ -163,6 +174,25 @@ def main(argv=None):
             y = torch.randn(R, 2 * C, device=dev, dtype=bf)
             fn = lambda: ops.activation(y, "swiglu")
             nbytes = 3 * R * C * 2
+        elif a.kernel == "glu_bwd":
+            y = torch.randn(R, 2 * C, device=dev, dtype=bf, requires_grad=True)
+            o = ops.activation(y, "swiglu")
+            g = torch.randn_like(o)
+            fn = lambda: torch.autograd.grad(o, y, g, retain_graph=True)
+            nbytes = 5 * R * C * 2
+        elif a.kernel == "rope":
+            hd = a.hd
+            slots = C // hd                       # C = width of the packed projection; the first two thirds rotate
+            rot = torch.arange(slots * 2 // 3, device=dev, dtype=torch.int32)
+            qkv = torch.randn(R, C, device=dev, dtype=bf)
+            cos, sin = ops.rope_tables(R, hd, 10000.0, dev)
+            fn = lambda: ops.rope_packed(qkv, rot, hd, cos, sin, 1)
+            nbytes = 2 * R * int(rot.numel()) * hd * 2
+        elif a.kernel == "sumsq":
+            x = torch.randn(R * C, device=dev)
+            acc = torch.zeros(1, device=dev)
+            fn = lambda: ops.sumsq(x, acc)
+            nbytes = R * C * 4
         elif a.kernel == "xent":
             lg = torch.randn(R, C, device=dev, dtype=bf)
             tg = torch.randint(0, C, (R,), device=dev)

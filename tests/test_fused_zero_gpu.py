@@ -86,6 +86,7 @@ def kernels_vs_nccl(cfg):
         out["adam_state_%d" % rep] = max(float((x - y).abs().max()) for x, y in zip(a, b))
         out["gathered_%d" % rep] = float((params.tensor.float() - full.float()).abs().max())
     out["status"] = _lib.read_status()
+    out["allocator"] = "vmm" if type(grads.handle).__name__ == "VmmSymmetricBuffer" else "torch"
     return out
 
 
@@ -142,6 +143,25 @@ def test_peer_kernels_match_nccl(shard):
         for rep in range(2):
             assert r["rs_%d" % rep] < 1e-6 and r["adam_state_%d" % rep] < 1e-5 and r["gathered_%d" % rep] < 0.04, r
             assert r["rs16_%d" % rep] < 1e-6 and r["rs16_flags_%d" % rep] < 1e-6, r
+
+
+def test_own_vmm_allocator_backs_the_peer_kernels():
+    """HG_SYMM_ALLOC=vmm: the buffers come from this framework's own cuMemCreate / export / import / map allocator
+    (descriptors passed between the ranks over Unix sockets); kernels and a training run give the same results."""
+    _need(2)
+    env = dict(ENV, HG_SYMM_ALLOC="vmm")
+    res = run_distributed(__file__, "kernels_vs_nccl", 2, {"shard": 1 << 18}, timeout=240, extra_env=env)
+    for r in res:
+        assert r["status"] == 0 and r["allocator"] == "vmm", r
+        for rep in range(2):
+            assert r["rs_%d" % rep] < 1e-6 and r["adam_state_%d" % rep] < 1e-5 and r["gathered_%d" % rep] < 0.04, r
+            assert r["rs16_%d" % rep] < 1e-6 and r["rs16_flags_%d" % rep] < 1e-6, r
+    cfg = {"dp_type": "zero2", "defer": True, "fp32_wire": False}
+    ref = run_distributed(__file__, "train", 2, dict(cfg, fused=True), timeout=300, extra_env=ENV)
+    got = run_distributed(__file__, "train", 2, dict(cfg, fused=True), timeout=300, extra_env=env)
+    for r in range(2):
+        for (l0, n0), (l1, n1) in zip(ref[r], got[r]):
+            assert abs(l0 - l1) / abs(l0) < 1e-4 and abs(n0 - n1) / n0 < 1e-3, (ref, got)
 
 
 @pytest.mark.parametrize("dp_type,defer,fp32_wire", [("zero2", True, False), ("zero2", True, True), ("zero3", True, False),
