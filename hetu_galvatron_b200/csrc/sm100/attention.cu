@@ -10,6 +10,8 @@
 //
 // Replaces flash_attn_varlen_func / _flash_attn_forward / _flash_attn_backward as called from
 // galvatron/core/runtime/transformer/attention_impl.py:55-111,587-616,696-727.
+#include <type_traits>
+
 #include "sm100_common.cuh"
 
 namespace hg {
@@ -33,6 +35,36 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+
+// 2^x on the FMA pipe, for x <= 0 (probabilities): x is split by the add-a-large-constant rounding trick into an
+// integer n (left in the low mantissa bits of t) and f in [-0.5, 0.5]; 2^f is a degree-3 near-minimax polynomial
+// (maximum relative error 7.5e-5, a fiftieth of the bf16 rounding the result gets next) and n goes straight into
+// the exponent field.  Nine FMA / integer instructions against one on the special-function unit, which delivers
+// far fewer results per clock: giving a share of the elements to this path takes the exp2 unit off the critical path.
+// Inputs below -126 (masked entries, -inf) clamp to 2^-126.
+__device__ __forceinline__ float ex2_poly(float x) {
+  x = fmaxf(x, -126.f);
+  const float t = x + 12582912.f;          // 1.5 * 2^23
+  const float f = x - (t - 12582912.f);
+  float r = fmaf(f, 0.05517165f, 0.24261113f);
+  r = fmaf(r, f, 0.69326097f);
+  r = fmaf(r, f, 0.99992806f);
+  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+}
+// Softmax warpgroups of the 128-query dK/dV kernel (2 or 4).
+#ifndef HG_DKV_WARPGROUPS
+#define HG_DKV_WARPGROUPS 4
+#endif
+constexpr int kDkvWarpgroups = HG_DKV_WARPGROUPS;
+// Softmax warpgroups of the 128-key dQ kernel (2 or 4).
+#ifndef HG_DQ_WARPGROUPS
+#define HG_DQ_WARPGROUPS 4
+#endif
+constexpr int kDqWarpgroups = HG_DQ_WARPGROUPS;
+// How many of every four probabilities of the 128-query dK/dV kernel take ex2_poly instead of the special-function unit.
+#ifndef HG_DKV_POLY_OF_4
+#define HG_DKV_POLY_OF_4 0
+#endif
 
 // Head -> slot mapping inside the (possibly packed) tensor:  slot = (h / qpg) * gs + (h % qpg) * hs + off
 struct SlotMap {
@@ -119,9 +151,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 4);     // one arrival per softmax warp (mbar_arrive_warp)
     }
-    mbar_init(p_full, 128);
+    mbar_init(p_full, 4);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     mbar_fence_init();
@@ -228,7 +260,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[i]);
       }
       tc_fence_before();
-      mbar_arrive(&s_empty[st]);
+      mbar_arrive_warp(&s_empty[st]);
       // masking (only blocks that cross the diagonal or the ragged end need it)
       const int k_base = p.k_pos0 + j * 128;
       const bool need_mask = (p.causal && (k_base + 127 > p.q_pos0 + q0)) || (j * 128 + 128 > p.Skv);
@@ -294,7 +326,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       }
       fence_proxy_async_smem();
       tc_fence_before();
-      mbar_arrive(p_full);
+      mbar_arrive_warp(p_full);
     }
     // ---- epilogue: O / l -> global, LSE ----
     const int srow = q0 + row;
@@ -724,22 +756,62 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // The 64-query version issues its score products with N = 64, which occupy the tensor core as long as N = 128 would,
 // and stages P^T / dS^T through 64 KB of shared memory.  Here a step covers 128 queries:
 //   S^T = K Q^T and dP^T = V dO^T are 128 x 128 products (8 MMAs each);
-//   each softmax thread (one key row, 64 of the 128 query columns) loads its S^T values, and stores
-//   P^T = exp2(S^T c - lse) back as packed 16-bit pairs over the first half of the columns it has just read;
-//   dS^T = P^T (dP^T - D) goes over the dP^T columns the same way;
+//   the softmax threads turn them into P^T = exp2(S^T c - lse) and dS^T = P^T (dP^T - D) and store both back into
+//   tensor memory as packed 16-bit pairs;
 //   dV += P^T dO and dK += dS^T Q take their A operand from tensor memory (8 MMAs each, K = 128 queries).
 // Per 128 queries that is 32 MMAs instead of 48, no shared-memory traffic from the softmax threads, and the 64 KB
 // of staging buffers become Q / dO ring slots (three of Q, two of dO: a Q tile lives from its S^T product to its
 // dK product, a dO tile from dP^T to dV).
 //
-// Tensor memory (512 columns): S^T 0..127 (P^T packed in 0..31 and 64..95), dP^T 128..255 (dS^T packed in 128..159
-// and 192..223), dV 256..383, dK 384..511.  There is one S^T / dP^T pair, so the MMA warp and the softmax threads
-// alternate in two half-steps, each overlapping one MMA group with one softmax phase:
-//   MMA  [dV(i), S^T(i+1)]   while the threads turn dP^T(i) into dS^T(i)     (phase B)
-//   MMA  [dK(i), dP^T(i+1)]  while the threads turn S^T(i+1) into P^T(i+1)   (phase A)
-// The tensor core executes its MMAs in issue order, which is what makes the in-place reuse safe: S^T(i+1) is issued
-// after dV(i), the last reader of P^T(i), and dP^T(i+1) after dK(i), the last reader of dS^T(i).
+// Tensor memory (512 columns): S^T 0..127, dP^T 128..255, dV 256..383, dK 384..511.  A softmax thread (one key row,
+// the 128 / NWG query columns of its warpgroup) loads its S^T values and releases the S^T columns at once, so that
+// S^T of the next step is computed while this step's exponentials run; once dP^T has arrived it loads its dP^T
+// values and then owns those columns: the packed P^T goes over their first half, the packed dS^T over the second.
+// The tensor core executes MMAs in issue order, which makes the reuse safe: dP^T(i+1) is issued after dV(i) and
+// dK(i), the readers of P^T(i) and dS^T(i).  Per step the MMA warp issues S^T(i+1) when the S^T(i) columns are
+// free, dV(i) when P^T(i) is stored, dK(i) and dP^T(i+1) when dS^T(i) is stored.
 // =================================================================================================
+// Per-role cycle counts of CTA (0, 0, 0), for builds with -DHG_ATTN_TIMING: where a step's time goes (waiting for the
+// other role, or working).  Lane 0 of the first softmax warp writes words 16..20 of the device status buffer
+// (steps, wait for S^T, probabilities, wait for dP^T, dS^T and stores), lane 0 of the MMA warp words 24..28 (steps, wait
+// for free S^T columns, wait for P^T, wait for dS^T, time spent issuing).  The counts are clock64() differences; nothing is compiled in without
+// the define.
+#ifdef HG_ATTN_TIMING
+#define HG_DKV_TIMERS(a, b, c, d) long long a = 0, b = 0, c = 0, d = 0
+#define HG_DKV_TICK(t) long long t = clock64()
+#define HG_DKV_TOCK(acc, t)          \
+  do {                               \
+    const long long now_ = clock64(); \
+    acc += now_ - t;                 \
+    t = now_;                        \
+  } while (0)
+#define HG_DKV_REPORT(off, n, a, b, c, d)                                                                   \
+  do {                                                                                                      \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane_id() == 0 && (warp == 1 || warp == 2)) { \
+      p.status[16 + off] = n;                                                                               \
+      p.status[17 + off] = int(a);                                                                          \
+      p.status[18 + off] = int(b);                                                                          \
+      p.status[19 + off] = int(c);                                                                          \
+      p.status[20 + off] = int(d);                                                                          \
+    }                                                                                                       \
+  } while (0)
+#define HG_DKV_REPORT2(off, a, b, c, d)                                                        \
+  do {                                                                                         \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane_id() == 0 && warp == 2) { \
+      p.status[off] = int(a);                                                                  \
+      p.status[off + 1] = int(b);                                                              \
+      p.status[off + 2] = int(c);                                                              \
+      p.status[off + 3] = int(d);                                                              \
+    }                                                                                          \
+  } while (0)
+#else
+#define HG_DKV_REPORT2(off, a, b, c, d)
+#define HG_DKV_TIMERS(a, b, c, d)
+#define HG_DKV_TICK(t)
+#define HG_DKV_TOCK(acc, t)
+#define HG_DKV_REPORT(off, n, a, b, c, d)
+#endif
+
 template <int HD>
 struct Dkv128Smem {
   static constexpr int kKV = 128 * HD * 2;       // resident K or V
@@ -752,12 +824,18 @@ struct Dkv128Smem {
   static constexpr int kTotal = 232448;          // everything a CTA can have; the 1024-byte alignment of the tiles comes out of the rest
 };
 
-template <int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+// NWG softmax warpgroups (2 or 4): thread == key row, warpgroup g owns query columns [g * 128 / NWG, (g + 1) * 128 / NWG)
+// of every step.  Four warpgroups put four warps on every scheduler, which is what keeps the exp2 unit and the FMA
+// pipe busy through the latencies of the loads from tensor memory and of the dependent exp2 / convert chains.
+template <int HD, int NWG>
+__global__ void __launch_bounds__(64 + 128 * NWG, 1)
 flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                         const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                         const BwdParams p) {
   static_assert(HD == 128, "the 128-query dK/dV kernel is written for head dim 128");
+  static_assert(NWG == 2 || NWG == 4, "two or four softmax warpgroups");
+  constexpr int kSoftmaxWarps = 4 * NWG;
+  constexpr int CPT = 128 / NWG;               // query columns per thread and step
   extern __shared__ uint8_t smem_raw[];
   using L = Dkv128Smem<HD>;
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -783,7 +861,8 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   uint64_t* ds_full = bars + 14;     // every thread has stored its part of dS^T
   uint64_t* acc_full = bars + 15;    // the last dK product has completed
   uint64_t* stats_full = bars + 16;  // 2
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 18);
+  uint64_t* x_free = bars + 18;      // every thread has loaded its S^T values: the S^T columns may be overwritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 19);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -803,11 +882,12 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     for (int i = 0; i < ND; ++i) { mbar_init(&do_full[i], 1); mbar_init(&do_empty[i], 1); }
     mbar_init(st_full, 1);
     mbar_init(dpt_full, 1);
-    mbar_init(p_full, kBwdSoftmaxThreads);
-    mbar_init(ds_full, kBwdSoftmaxThreads);
+    mbar_init(p_full, kSoftmaxWarps);       // one arrival per softmax warp (mbar_arrive_warp)
+    mbar_init(ds_full, kSoftmaxWarps);
+    mbar_init(x_free, kSoftmaxWarps);
     mbar_init(acc_full, 1);
-    mbar_init(&stats_full[0], kBwdSoftmaxThreads);
-    mbar_init(&stats_full[1], kBwdSoftmaxThreads);
+    mbar_init(&stats_full[0], kSoftmaxWarps);
+    mbar_init(&stats_full[1], kSoftmaxWarps);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -862,6 +942,9 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       constexpr uint32_t idesc_st = make_idesc_lp(128, 128, false, false);
       constexpr uint32_t idesc_acc = make_idesc_lp(128, HD, false, true);
       const uint32_t aK = smem_u32(sK), aV = smem_u32(sV), aQ0 = smem_u32(sQ), aDO0 = smem_u32(sDO);
+      // queries 16kk.. belong to warpgroup 16kk / CPT; its packed P^T values start at the first of its CPT columns of
+      // the dP^T range, its packed dS^T values CPT / 2 columns further
+      auto packed_col = [](int kk) -> uint32_t { return uint32_t((16 * kk / CPT) * CPT + (16 * kk % CPT) / 2); };
       // ring positions: Q / dO tile of the next S^T / dP^T issue, and of the next dK / dV issue
       int q_s = 0, q_k = 0, d_p = 0, d_v = 0;
       uint32_t qph_s = 0, dph_p = 0;
@@ -896,45 +979,57 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
       bool ok = mbar_wait_warp(kv_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       if (ok) ok = issue_st();
       if (ok) ok = issue_dpt();
+      HG_DKV_TIMERS(tm_wait_x, tm_wait_p, tm_wait_ds, tm_issue);
       for (int it = 0; ok && it < n_it; ++it) {
         const uint32_t ph = it & 1;
-        // ---- dV(it), then S^T(it+1) over the columns dV has just read
+        HG_DKV_TICK(t0);
+        // ---- S^T(it+1), as soon as the S^T(it) values are in the threads' registers
+        if (!mbar_wait_warp(x_free, ph, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        HG_DKV_TOCK(tm_wait_x, t0);
+        if (it + 1 < n_it) { ok = issue_st(); if (!ok) break; }
+        HG_DKV_TOCK(tm_issue, t0);
+        // ---- dV(it)
         if (!mbar_wait_warp(p_full, ph, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        HG_DKV_TOCK(tm_wait_p, t0);
         if (issuer) {
           const uint32_t aDO = aDO0 + d_v * L::kQD;
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)     // k-step kk = queries 16kk..16kk+15 = 8 packed columns of the half kk/4
-            umma_f16_ts(tDV, tST + (kk >> 2) * 64 + (kk & 3) * 8, mnmajor_desc(aDO, 128, kk), idesc_acc, (it | kk) != 0);
+          for (int kk = 0; kk < 8; ++kk)     // k-step kk = queries 16kk..16kk+15 = 8 packed columns of their warpgroup's range
+            umma_f16_ts(tDV, tDPT + packed_col(kk), mnmajor_desc(aDO, 128, kk), idesc_acc, (it | kk) != 0);
           umma_commit(&do_empty[d_v]);
         }
         __syncwarp();
         if (++d_v == ND) d_v = 0;
-        if (it + 1 < n_it) { ok = issue_st(); if (!ok) break; }
-        // ---- dK(it), then dP^T(it+1) over the columns dK has just read
+        HG_DKV_TOCK(tm_issue, t0);
+        // ---- dK(it), then dP^T(it+1) over the columns dV and dK have just read
         if (!mbar_wait_warp(ds_full, ph, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        HG_DKV_TOCK(tm_wait_ds, t0);
         if (issuer) {
           const uint32_t aQ = aQ0 + q_k * L::kQD;
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)
-            umma_f16_ts(tDK, tDPT + (kk >> 2) * 64 + (kk & 3) * 8, mnmajor_desc(aQ, 128, kk), idesc_acc, (it | kk) != 0);
+            umma_f16_ts(tDK, tDPT + CPT / 2 + packed_col(kk), mnmajor_desc(aQ, 128, kk), idesc_acc, (it | kk) != 0);
           umma_commit(&q_empty[q_k]);
         }
         __syncwarp();
         if (++q_k == NQ) q_k = 0;
         if (it + 1 < n_it) { ok = issue_dpt(); if (!ok) break; }
+        HG_DKV_TOCK(tm_issue, t0);
       }
+      HG_DKV_REPORT(8, n_it, tm_wait_x, tm_wait_p, tm_wait_ds, tm_issue);
       if (ok && issuer) umma_commit(acc_full);
       __syncwarp();
       if (!ok) *abort_flag = 1;
     }
   } else {
     const int wq = warp & 3;
-    const int half = (warp - 2) >> 2;     // which 64 of the step's 128 query columns this warpgroup owns
-    const int c0 = half * 64;
+    const int half = (warp - 2) >> 2;     // warpgroup: which CPT of the step's 128 query columns these threads own
+    const int c0 = half * CPT;
     const int row = wq * 32 + lane_id();  // key row inside the block
-    const int tid = threadIdx.x - 64;     // 0..255 among the softmax threads
+    const int tid = threadIdx.x - 64;     // 0..128*NWG-1 among the softmax threads; the first 256 carry the statistics
     const uint32_t lane_off = uint32_t(wq * 32) << 16;
     const float sl2 = p.scale * kLog2e;
     const int k_pos = p.k_pos0 + k0 + row;
@@ -945,7 +1040,7 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     int ld_h = h0, ld_qs = qs0, ld_it = 0;
     auto load_stat = [&]() -> float {
       float v = 0.f;
-      if (ld_it < n_it) {
+      if (tid < 256 && ld_it < n_it) {
         const int q = ld_qs * 128 + (tid & 127);
         if (q >= p.Sq) {
           v = (tid < 128) ? INFINITY : 0.f;    // rows past the end: -inf after scaling, 2^-inf = 0
@@ -961,63 +1056,81 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const float stat_scale = (tid < 128) ? -kLog2e : 1.f;
     float stat_next = load_stat();
     if (n_it > 0) {
-      sStats[tid] = stat_next * stat_scale;
-      mbar_arrive(&stats_full[0]);
+      if (tid < 256) sStats[tid] = stat_next * stat_scale;
+      mbar_arrive_warp(&stats_full[0]);
       stat_next = load_stat();
     }
     int cur_qs = qs0;
+    HG_DKV_TIMERS(tm_wait_a, tm_a, tm_wait_b, tm_b);
     for (int it = 0; it < n_it; ++it) {
       const int sb = it & 1;
       const uint32_t ph = it & 1;
+      HG_DKV_TICK(t0);
       const int qrow = cur_qs * 128;
       if (++cur_qs == n_qs) cur_qs = qs0;
       const float* st = sStats + sb * 256;
-      uint32_t pp[32];                    // this thread's 64 probabilities, packed, kept for the second phase
-      // ---------------- phase A: S^T -> P^T
+      uint32_t pp[CPT / 2];               // this thread's probabilities, packed, kept for the second phase
+      // ---------------- S^T -> probabilities (kept in registers; the S^T columns are released at once)
       if (!mbar_wait_warp(&stats_full[sb], (it >> 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
       if (!mbar_wait_warp(st_full, ph, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
+      HG_DKV_TOCK(tm_wait_a, t0);
       {
         // only steps that touch the diagonal, or a key block with rows past the end, need the mask
         const bool need_mask = !k_valid || (p.causal && (p.q_pos0 + qrow < p.k_pos0 + k0 + 127));
+        uint32_t rr[CPT / 32][32];
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t r[32];
-          tmem_ld32(tST + lane_off + c0 + hh * 32, r);
-          tmem_ld_wait();
-          const float4* nl4 = reinterpret_cast<const float4*>(st + c0 + hh * 32);
-          const int q_base = p.q_pos0 + qrow + c0 + hh * 32;
+        for (int hh = 0; hh < CPT / 32; ++hh) tmem_ld32(tST + lane_off + c0 + hh * 32, rr[hh]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive_warp(x_free);
+        // The masked and the plain form are two straight-line bodies: a branch inside the element loop would cut it
+        // into sixteen basic blocks, and the compiler schedules (overlaps the loads, FMAs and exp2 of different
+        // elements) only inside one.
+        auto probabilities = [&](auto masked) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            const float4 nl = nl4[i >> 2];
-            const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
-            float e[4];
+          for (int hh = 0; hh < CPT / 32; ++hh) {
+            const uint32_t(&r)[32] = rr[hh];
+            const float4* nl4 = reinterpret_cast<const float4*>(st + c0 + hh * 32);
+            const int q_base = p.q_pos0 + qrow + c0 + hh * 32;
 #pragma unroll
-            for (int u = 0; u < 4; ++u) e[u] = ex2(fmaf(__uint_as_float(r[i + u]), sl2, nlv[u]));
-            if (need_mask) {
+            for (int i = 0; i < 32; i += 4) {
+              const float4 nl = nl4[i >> 2];
+              const float nlv[4] = {nl.x, nl.y, nl.z, nl.w};
+              float e[4];
 #pragma unroll
-              for (int u = 0; u < 4; ++u)
-                if (!k_valid || (p.causal && k_pos > q_base + i + u)) e[u] = 0.f;
+              for (int u = 0; u < 4; ++u) {
+                const float x = fmaf(__uint_as_float(r[i + u]), sl2, nlv[u]);
+                e[u] = (u < HG_DKV_POLY_OF_4) ? ex2_poly(x) : ex2(x);
+                if (decltype(masked)::value && (!k_valid || (p.causal && k_pos > q_base + i + u))) e[u] = 0.f;
+              }
+              pp[hh * 16 + (i >> 1)] = pack_bf16(e[0], e[1]);
+              pp[hh * 16 + (i >> 1) + 1] = pack_bf16(e[2], e[3]);
             }
-            pp[hh * 16 + (i >> 1)] = pack_bf16(e[0], e[1]);
-            pp[hh * 16 + (i >> 1) + 1] = pack_bf16(e[2], e[3]);
           }
-        }
+        };
+        if (need_mask) probabilities(std::true_type{});
+        else probabilities(std::false_type{});
       }
-      tmem_st32(tST + lane_off + c0, pp);   // 32 packed columns over the first half of the 64 just read
-      tmem_st_wait();
-      tc_fence_before();
-      mbar_arrive(p_full);
-      // ---------------- phase B: dP^T -> dS^T
+      HG_DKV_TOCK(tm_a, t0);
+      // ---------------- dP^T -> dS^T; P^T and dS^T go, packed, over this thread's own dP^T columns
       if (!mbar_wait_warp(dpt_full, ph, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
+      HG_DKV_TOCK(tm_wait_b, t0);
       {
-        uint32_t dsp[32];
+        uint32_t dsp[CPT / 2];
+        uint32_t rr[CPT / 32][32];
 #pragma unroll
-        for (int hh = 0; hh < 2; ++hh) {
-          uint32_t r[32];
-          tmem_ld32(tDPT + lane_off + c0 + hh * 32, r);
-          tmem_ld_wait();
+        for (int hh = 0; hh < CPT / 32; ++hh) tmem_ld32(tDPT + lane_off + c0 + hh * 32, rr[hh]);
+        tmem_ld_wait();
+        if constexpr (CPT == 64) tmem_st32(tDPT + lane_off + c0, pp);
+        else tmem_st16(tDPT + lane_off + c0, pp);
+        tmem_st_wait();
+        tc_fence_before();
+        mbar_arrive_warp(p_full);
+#pragma unroll
+        for (int hh = 0; hh < CPT / 32; ++hh) {
+          const uint32_t(&r)[32] = rr[hh];
           const float4* dd4 = reinterpret_cast<const float4*>(st + 128 + c0 + hh * 32);
 #pragma unroll
           for (int i = 0; i < 32; i += 4) {
@@ -1029,19 +1142,22 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
                                                      p23.y * (__uint_as_float(r[i + 3]) - dd.w));
           }
         }
-        tmem_st32(tDPT + lane_off + c0, dsp);
+        if constexpr (CPT == 64) tmem_st32(tDPT + lane_off + c0 + CPT / 2, dsp);
+        else tmem_st16(tDPT + lane_off + c0 + CPT / 2, dsp);
       }
       // the next step's statistics go to the other buffer: its last readers were the second phases of step it-1,
       // and every thread finished that before it arrived on this step's statistics barrier
       if (it + 1 < n_it) {
-        sStats[(sb ^ 1) * 256 + tid] = stat_next * stat_scale;
-        mbar_arrive(&stats_full[sb ^ 1]);
+        if (tid < 256) sStats[(sb ^ 1) * 256 + tid] = stat_next * stat_scale;
+        mbar_arrive_warp(&stats_full[sb ^ 1]);
         stat_next = load_stat();
       }
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      mbar_arrive_warp(ds_full);
+      HG_DKV_TOCK(tm_b, t0);
     }
+    HG_DKV_REPORT(0, n_it, tm_wait_a, tm_a, tm_wait_b, tm_b);
     // ---- epilogue ----
     const int krow = k0 + row;
     const int dkslot = p.dkmap.slot(h0, p.qpg), dvslot = p.dvmap.slot(h0, p.qpg);
@@ -1050,7 +1166,7 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     if (n_it == 0) {
       if (krow < p.Skv) {
 #pragma unroll
-        for (int i = half; i < HD / 8; i += 2) {
+        for (int i = half; i < HD / 8; i += NWG) {
           reinterpret_cast<uint4*>(dk)[i] = make_uint4(0, 0, 0, 0);
           reinterpret_cast<uint4*>(dv)[i] = make_uint4(0, 0, 0, 0);
         }
@@ -1058,7 +1174,7 @@ flash_bwd_dkv128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     } else if (ok && !*abort_flag && mbar_wait_warp(acc_full, 0, p.status, kTimeoutOther, abort_flag)) {
       tc_fence_after();
 #pragma unroll
-      for (int c = half; c < HD / 32; c += 2) {   // the two warpgroups take alternate 32-column chunks
+      for (int c = half; c < HD / 32; c += NWG) {   // the warpgroups take alternate 32-column chunks
         uint32_t r0[32], r1[32];
         tmem_ld32(tDV + lane_off + c * 32, r0);
         tmem_ld32(tDK + lane_off + c * 32, r1);
@@ -1336,10 +1452,14 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 // =================================================================================================
 // Backward, part 2 with 128-key steps (head dim 128).  A tcgen05.mma of shape 128 x N x 16 occupies the tensor core
 // for the same time whatever N <= 256 is, so the score products are issued with N = 128 instead of 64: per 128 keys
-// the kernel issues 24 MMAs (8 S, 8 dP, 8 dQ) where the 64-key version issues 40.  Shared memory then holds two
-// 128-row K/V stages (128 KB), Q and dO (64 KB) and one dS buffer (32 KB, two 64-column slabs, one per softmax
-// warpgroup); tensor memory holds one S / dP pair (256 columns) and dQ (128).  The S product of step i+1 is issued
-// as soon as the softmax threads have loaded step i into registers, so it still overlaps their arithmetic.
+// the kernel issues 24 MMAs (8 S, 8 dP, 8 dQ) where the 64-key version issues 40.  Shared memory holds three K
+// stages and one V stage of 128 rows (128 KB) and Q and dO (64 KB); tensor memory holds one S / dP pair (256 columns),
+// dQ (128) and two dS buffers (64 columns each): the softmax threads store dS there as packed 16-bit pairs and the
+// dQ product takes it as its A operand, so nothing of a step goes through shared memory.  The S and dP products of
+// step i+1 are issued as soon as the softmax threads have loaded step i into registers, so they overlap the
+// arithmetic.  NWG softmax warpgroups (2 or 4): thread == query row, warpgroup g owns key columns
+// [g * 128 / NWG, (g + 1) * 128 / NWG) of every step; four warpgroups put four warps on every scheduler, which is
+// what covers the latencies of the tensor-memory loads and of the exp2 / convert chains.
 // =================================================================================================
 template <int HD>
 struct Dq128Smem {
@@ -1349,12 +1469,11 @@ struct Dq128Smem {
   // than a step: three slots let the load of step i+2 start while step i is still being multiplied.  V is read by
   // dP = dO V^T only, early in the step, so one slot suffices: its reload has the rest of the step to land.
   static constexpr int kKStages = 3;
-  static constexpr int kDS = 128 * 128 * 2;    // dS: two K-major slabs of [128 rows x 64 keys]
-  static constexpr int kTotal = 2 * kQ + (kKStages + 1) * kKV + kDS + 1024 + 256;
+  static constexpr int kTotal = 2 * kQ + (kKStages + 1) * kKV + 1024 + 256;
 };
 
-template <int HD>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+template <int HD, int NWG>
+__global__ void __launch_bounds__(64 + 128 * NWG, 1)
 flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                        const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                        const BwdParams p) {
@@ -1366,8 +1485,10 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   constexpr int NK = L::kKStages;
   uint8_t* sK = sDO + L::kQ;            // NK stages
   uint8_t* sV = sK + NK * L::kKV;       // 1 stage
-  uint8_t* sDS = sV + L::kKV;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sDS + L::kDS);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + L::kKV);
+  static_assert(NWG == 2 || NWG == 4, "two or four softmax warpgroups");
+  constexpr int kSoftmaxWarps = 4 * NWG;
+  constexpr int CPT = 128 / NWG;        // key columns per thread and step
   uint64_t* qdo_full = bars;       // 1
   uint64_t* k_full = bars + 1;     // 3
   uint64_t* k_empty = bars + 4;    // 3
@@ -1376,8 +1497,8 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint64_t* s_full = bars + 9;     // 1
   uint64_t* s_empty = bars + 10;   // 1
   uint64_t* ds_full = bars + 11;   // 1
-  uint64_t* ds_empty = bars + 12;  // 1
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+  uint64_t* ds_empty = bars + 12;  // 2
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -1398,9 +1519,10 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     mbar_init(v_full, 1);
     mbar_init(v_empty, 1);
     mbar_init(s_full, 1);
-    mbar_init(s_empty, kBwdSoftmaxThreads);
-    mbar_init(ds_full, kBwdSoftmaxThreads);
-    mbar_init(ds_empty, 1);
+    mbar_init(s_empty, kSoftmaxWarps);   // one arrival per softmax warp (mbar_arrive_warp)
+    mbar_init(ds_full, kSoftmaxWarps);
+    mbar_init(&ds_empty[0], 1);
+    mbar_init(&ds_empty[1], 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
@@ -1413,6 +1535,7 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
   const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+  const uint32_t tDS[2] = {tmem + 384, tmem + 448};   // packed dS, step parity
 
   const int qslot = p.qmap.slot(h, p.qpg), kslot = p.kmap.slot(h, p.qpg), vslot = p.vmap.slot(h, p.qpg),
             doslot = p.domap.slot(h, p.qpg);
@@ -1449,7 +1572,7 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const bool issuer = elect_one() != 0;
       constexpr uint32_t idesc_s = make_idesc_lp(128, 128, false, false);
       constexpr uint32_t idesc_dq = make_idesc_lp(128, HD, false, true);
-      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO), aDS = smem_u32(sDS);
+      const uint32_t aQ = smem_u32(sQ), aDO = smem_u32(sDO);
       bool ok = mbar_wait_warp(qdo_full, 0, p.status, kTimeoutSmemFull, abort_flag);
       int ks_s = 0, ks_d = 0;          // K slot of the next S issue and of the next dQ issue
       uint32_t kph_s = 0;
@@ -1486,10 +1609,10 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const uint32_t aK = smem_u32(sK + ks_d * L::kKV);
         if (issuer) {
 #pragma unroll
-          for (int kk = 0; kk < 8; ++kk)
-            umma_f16_ss(tDQ, kmajor_desc(aDS, 128, kk), mnmajor_desc(aK, 128, kk), idesc_dq, (it | kk) != 0);
+          for (int kk = 0; kk < 8; ++kk)   // k-step kk = keys 16kk..16kk+15 = 8 packed columns
+            umma_f16_ts(tDQ, tDS[it & 1] + kk * 8, mnmajor_desc(aK, 128, kk), idesc_dq, (it | kk) != 0);
           umma_commit(&k_empty[ks_d]);
-          umma_commit(ds_empty);
+          umma_commit(&ds_empty[it & 1]);
         }
         __syncwarp();
         if (++ks_d == NK) ks_d = 0;
@@ -1498,8 +1621,8 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
   } else {
     const int wq = warp & 3;
-    const int half = (warp - 2) >> 2;     // which 64 of the step's 128 key columns this warpgroup owns
-    const int c0 = half * 64;
+    const int half = (warp - 2) >> 2;     // warpgroup: which CPT of the step's 128 key columns these threads own
+    const int c0 = half * CPT;
     const int row = wq * 32 + lane_id();
     const uint32_t lane_off = uint32_t(wq * 32) << 16;
     const float sl2 = p.scale * kLog2e;
@@ -1512,16 +1635,15 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       dsum = p.D[idx];
     }
     const float nlse2 = -lse2;
-    uint8_t* sDSh = sDS + half * (128 * 128);   // this warpgroup's slab
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
       if (!mbar_wait_warp(s_full, it & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      float ds[64];
+      float ds[CPT];
       {
-        float sv[64];
+        float sv[CPT];
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
+        for (int c = 0; c < CPT / 32; ++c) {
           uint32_t r0[32], r1[32];
           tmem_ld32(tS + lane_off + c0 + c * 32, r0);
           tmem_ld32(tDP + lane_off + c0 + c * 32, r1);
@@ -1530,45 +1652,47 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           for (int i = 0; i < 32; ++i) { sv[c * 32 + i] = __uint_as_float(r0[i]); ds[c * 32 + i] = __uint_as_float(r1[i]); }
         }
         tc_fence_before();
-        mbar_arrive(s_empty);
+        mbar_arrive_warp(s_empty);
         const int kbase = it * 128 + c0;
-        const bool need_mask = (p.causal && (p.k_pos0 + kbase + 63 > p.q_pos0 + q0)) || (kbase + 64 > p.Skv);
+        const bool need_mask = (p.causal && (p.k_pos0 + kbase + CPT - 1 > p.q_pos0 + q0)) || (kbase + CPT > p.Skv);
         if (!need_mask) {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) ds[i] = ex2(fmaf(sv[i], sl2, nlse2)) * (ds[i] - dsum);
+          for (int i = 0; i < CPT; ++i) ds[i] = ex2(fmaf(sv[i], sl2, nlse2)) * (ds[i] - dsum);
         } else {
 #pragma unroll
-          for (int i = 0; i < 64; ++i) {
+          for (int i = 0; i < CPT; ++i) {
             const bool dead = (kbase + i >= p.Skv) || (p.causal && (p.k_pos0 + kbase + i > q_pos));
             ds[i] = dead ? 0.f : ex2(fmaf(sv[i], sl2, nlse2)) * (ds[i] - dsum);
           }
         }
       }
-      if (it > 0) {
-        if (!mbar_wait_warp(ds_empty, (it - 1) & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+      if (it >= 2) {   // this dS buffer was last read by the dQ product of step it-2
+        if (!mbar_wait_warp(&ds_empty[it & 1], ((it >> 1) & 1) ^ 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+        tc_fence_after();
       }
+      {
+        uint32_t w[CPT / 2];
 #pragma unroll
-      for (int cc = 0; cc < 8; ++cc) {
-        uint4 w;
-        w.x = pack_bf16(ds[cc * 8 + 0], ds[cc * 8 + 1]); w.y = pack_bf16(ds[cc * 8 + 2], ds[cc * 8 + 3]);
-        w.z = pack_bf16(ds[cc * 8 + 4], ds[cc * 8 + 5]); w.w = pack_bf16(ds[cc * 8 + 6], ds[cc * 8 + 7]);
-        *reinterpret_cast<uint4*>(sDSh + sw128_offset(row, cc)) = w;
+        for (int i = 0; i < CPT / 2; ++i) w[i] = pack_bf16(ds[2 * i], ds[2 * i + 1]);
+        if constexpr (CPT == 64) tmem_st32(tDS[it & 1] + lane_off + half * (CPT / 2), w);
+        else tmem_st16(tDS[it & 1] + lane_off + half * (CPT / 2), w);
       }
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      mbar_arrive_warp(ds_full);
     }
     const int dqslot = p.dqmap.slot(h, p.qpg);
     hg_lp_t* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
     if (n_it == 0) {
       if (srow < p.Sq) {
 #pragma unroll
-        for (int i = half; i < HD / 8; i += 2) reinterpret_cast<uint4*>(dq)[i] = make_uint4(0, 0, 0, 0);
+        for (int i = half; i < HD / 8; i += NWG) reinterpret_cast<uint4*>(dq)[i] = make_uint4(0, 0, 0, 0);
       }
-    } else if (ok && !*abort_flag && mbar_wait_warp(ds_empty, (n_it - 1) & 1, p.status, kTimeoutOther, abort_flag)) {
+    } else if (ok && !*abort_flag &&
+               mbar_wait_warp(&ds_empty[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, p.status, kTimeoutOther, abort_flag)) {
       tc_fence_after();
 #pragma unroll
-      for (int c = half; c < HD / 32; c += 2) {
+      for (int c = half; c < HD / 32; c += NWG) {
         uint32_t r[32];
         tmem_ld32(tDQ + lane_off + c * 32, r);
         tmem_ld_wait();
@@ -1719,8 +1843,8 @@ int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
     dim3 grid((Skv + 127) / 128, nkv, B);
     if (wide) {
       static bool cfg = false;
-      if (!cfg) { if ((rc = set_smem(flash_bwd_dkv128_kernel<128>, Dkv128Smem<128>::kTotal))) return rc; cfg = true; }
-      flash_bwd_dkv128_kernel<128><<<grid, kBwdThreads, Dkv128Smem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+      if (!cfg) { if ((rc = set_smem(flash_bwd_dkv128_kernel<128, kDkvWarpgroups>, Dkv128Smem<128>::kTotal))) return rc; cfg = true; }
+      flash_bwd_dkv128_kernel<128, kDkvWarpgroups><<<grid, 64 + 128 * kDkvWarpgroups, Dkv128Smem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
     } else if (hd == 128) {
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(flash_bwd_dkv_kernel<128>, DkvSmem<128>::kTotal))) return rc; cfg = true; }
@@ -1741,8 +1865,8 @@ int hg_flash_bwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
     dim3 grid((Sq + 127) / 128, nheads, B);
     if (hd == 128) {
       static bool cfg = false;
-      if (!cfg) { if ((rc = set_smem(flash_bwd_dq128_kernel<128>, Dq128Smem<128>::kTotal))) return rc; cfg = true; }
-      flash_bwd_dq128_kernel<128><<<grid, kBwdThreads, Dq128Smem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
+      if (!cfg) { if ((rc = set_smem(flash_bwd_dq128_kernel<128, kDqWarpgroups>, Dq128Smem<128>::kTotal))) return rc; cfg = true; }
+      flash_bwd_dq128_kernel<128, kDqWarpgroups><<<grid, 64 + 128 * kDqWarpgroups, Dq128Smem<128>::kTotal, st>>>(tq, tk, tv, tdo, p);
     } else {
       static bool cfg = false;
       if (!cfg) { if ((rc = set_smem(flash_bwd_dq_kernel<64>, DqSmem<64>::kTotal))) return rc; cfg = true; }

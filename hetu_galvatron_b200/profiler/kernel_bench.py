@@ -106,6 +106,9 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=32)
     ap.add_argument("--hd", type=int, default=128)
     ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--dkv-variant", type=int, default=0,
+                    help="attn --bwd, head dim 128: 0 = dK/dV kernel with 128-query steps and P^T / dS^T in tensor "
+                         "memory, 1 = the 64-query kernel that stages them in shared memory")
     ap.add_argument("--rows", type=int, default=8192)
     ap.add_argument("--cols", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=10)
@@ -152,6 +155,8 @@ def main(argv=None):
         v = torch.randn(S, B, ng, hd, device=dev, dtype=bf, requires_grad=True)
         fl = 4.0 * S * S * B * nh * hd / 2
         if a.bwd:
+            _lib.load().hg_attn_set_dkv_variant(a.dkv_variant)
+            out["dkv_variant"] = a.dkv_variant
             o, lse = ops.flash_attention(q, k, v, return_lse=True)
             g = torch.randn_like(o)
             fn = lambda: ops.flash_backward(q.detach(), k.detach(), v.detach(), o.detach(), g, lse, True,
@@ -211,6 +216,18 @@ def main(argv=None):
         rate = nbytes / ms / 1e6
         out.update(shape=[R, C], ms=ms, gbs=rate, frac=rate / hbm, frac_of=tag)
     out["status"] = _lib.read_status()
+    if os.environ.get("HG_ATTN_TIMING"):
+        # a library built with -DHG_ATTN_TIMING leaves per-role cycle counts of one CTA in words 16..31 of the
+        # device status buffer (see HG_DKV_REPORT in csrc/sm100/attention.cu)
+        import ctypes
+
+        words = (ctypes.c_int * 64)()
+        lib = _lib.load()
+        lib.hg_status_address.restype = ctypes.c_void_p
+        torch.cuda.synchronize()
+        ctypes.CDLL("libcudart.so.12").cudaMemcpy(words, ctypes.c_void_p(lib.hg_status_address()), 256, 2)
+        out["role_cycles"] = {"softmax": list(words[16:21]), "mma": list(words[24:29]),
+                              "softmax_ld_math": list(words[32:36])}
     print(json.dumps(out))
 
 

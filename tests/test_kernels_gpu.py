@@ -245,6 +245,36 @@ def test_flash_attention(hd, S, B, nh, ng, causal):
     assert rel_err(v.grad, vr.grad) < 3e-2
 
 
+@pytest.mark.parametrize("S,B,nh,ng,causal", [(2048, 1, 4, 2, True), (1000, 2, 2, 2, True), (640, 1, 2, 1, False)])
+def test_flash_backward_dkv_kernels_agree(S, B, nh, ng, causal):
+    """Head dim 128 has two dK/dV kernels (128-query steps with P^T / dS^T in tensor memory, and 64-query steps
+    staged through shared memory): same gradients from both, and both close to the fp32 oracle."""
+    from hetu_galvatron_b200.ops import _lib
+
+    torch.manual_seed(13)
+    hd = 128
+    q = torch.randn(S, B, nh, hd, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(S, B, ng, hd, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(S, B, ng, hd, device=DEV, dtype=torch.bfloat16)
+    o, lse = ops.flash_attention(q, k, v, causal=causal, return_lse=True)
+    g = torch.randn_like(o)
+    lib = _lib.load()
+    grads = []
+    try:
+        for variant in (0, 1):
+            lib.hg_attn_set_dkv_variant(variant)
+            grads.append(ops.flash_backward(q, k, v, o, g, lse, causal, 1.0 / hd ** 0.5))
+    finally:
+        lib.hg_attn_set_dkv_variant(0)
+    assert _lib.read_status() == 0
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    ref, _ = ops.attention_reference(qr, kr, vr, causal)
+    ref.backward(g.float())
+    for (dq, dk, dv) in grads:
+        assert rel_err(dk, kr.grad) < 3e-2 and rel_err(dv, vr.grad) < 3e-2 and rel_err(dq, qr.grad) < 3e-2
+    assert rel_err(grads[0][1], grads[1][1]) < 1e-2 and rel_err(grads[0][2], grads[1][2]) < 1e-2
+
+
 @pytest.mark.parametrize("hd", [128, 64])
 def test_attention_merge_of_two_key_halves(hd):
     """Attention over keys [0, 256) and over keys [256, 512), merged through their log-sum-exp, equals attention over
@@ -308,6 +338,15 @@ def test_adamw_and_clip():
     g2 = g.clone()
     ops.scale_(g2, coef)
     assert torch.allclose(g2, g * coef, rtol=1e-6)
+    # slices that start off a 16-byte boundary take the element-wise kernels
+    p2, m2, v2 = p.clone(), torch.zeros_like(p), torch.zeros_like(p)
+    p3, m3, v3 = p.clone(), torch.zeros_like(p), torch.zeros_like(p)
+    ops.adamw_step(p2[1:], g[1:], m2[1:], v2[1:], None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=1)
+    ops.adamw_step(p3, g, m3, v3, None, lr=1e-2, beta1=0.9, beta2=0.95, eps=1e-8, weight_decay=0.1, step=1)
+    assert torch.equal(p2[1:], p3[1:]) and torch.equal(v2[1:], v3[1:])
+    t2 = torch.zeros(1, device=DEV)
+    ops.sumsq(g[1:], t2, accumulate=False)
+    assert abs(t2.item() - g[1:].pow(2).sum().item()) / t2.item() < 1e-4
 
 
 def test_bounded_wait_reports_status():
