@@ -774,7 +774,9 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // Per-role cycle counts of CTA (0, 0, 0), for builds with -DHG_ATTN_TIMING: where a step's time goes (waiting for the
 // other role, or working).  Lane 0 of the first softmax warp writes words 16..20 of the device status buffer
 // (steps, wait for S^T, probabilities, wait for dP^T, dS^T and stores), lane 0 of the MMA warp words 24..28 (steps, wait
-// for free S^T columns, wait for P^T, wait for dS^T, time spent issuing).  The counts are clock64() differences; nothing is compiled in without
+// for free S^T columns, wait for P^T, wait for dS^T, time spent issuing).  The dQ kernel reports in words 40..44 and
+// 48..52: softmax (steps, wait for S, loads, arithmetic, dS store), MMA (steps, S + dP issue including
+// its waits, wait for dS, dQ issue).  The counts are clock64() differences; nothing is compiled in without
 // the define.
 #ifdef HG_ATTN_TIMING
 #define HG_DKV_TIMERS(a, b, c, d) long long a = 0, b = 0, c = 0, d = 0
@@ -795,17 +797,7 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
       p.status[20 + off] = int(d);                                                                          \
     }                                                                                                       \
   } while (0)
-#define HG_DKV_REPORT2(off, a, b, c, d)                                                        \
-  do {                                                                                         \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane_id() == 0 && warp == 2) { \
-      p.status[off] = int(a);                                                                  \
-      p.status[off + 1] = int(b);                                                              \
-      p.status[off + 2] = int(c);                                                              \
-      p.status[off + 3] = int(d);                                                              \
-    }                                                                                          \
-  } while (0)
 #else
-#define HG_DKV_REPORT2(off, a, b, c, d)
 #define HG_DKV_TIMERS(a, b, c, d)
 #define HG_DKV_TICK(t)
 #define HG_DKV_TOCK(acc, t)
@@ -1602,10 +1594,14 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         return true;
       };
       if (ok) ok = issue_s(0);
+      HG_DKV_TIMERS(tm_s, tm_wait_ds, tm_dq, tm_unused);
       for (int it = 0; ok && it < n_it; ++it) {
+        HG_DKV_TICK(t0);
         if (it + 1 < n_it) { ok = issue_s(it + 1); if (!ok) break; }
+        HG_DKV_TOCK(tm_s, t0);
         if (!mbar_wait_warp(ds_full, it & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        HG_DKV_TOCK(tm_wait_ds, t0);
         const uint32_t aK = smem_u32(sK + ks_d * L::kKV);
         if (issuer) {
 #pragma unroll
@@ -1616,7 +1612,9 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         __syncwarp();
         if (++ks_d == NK) ks_d = 0;
+        HG_DKV_TOCK(tm_dq, t0);
       }
+      HG_DKV_REPORT(32, n_it, tm_s, tm_wait_ds, tm_dq, tm_unused);
       if (!ok) *abort_flag = 1;
     }
   } else {
@@ -1636,9 +1634,12 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
     const float nlse2 = -lse2;
     bool ok = true;
+    HG_DKV_TIMERS(tm_wait_s, tm_ld, tm_math, tm_st);
     for (int it = 0; it < n_it; ++it) {
+      HG_DKV_TICK(t0);
       if (!mbar_wait_warp(s_full, it & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
       tc_fence_after();
+      HG_DKV_TOCK(tm_wait_s, t0);
       float ds[CPT];
       {
         float sv[CPT];
@@ -1653,6 +1654,7 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         }
         tc_fence_before();
         mbar_arrive_warp(s_empty);
+        HG_DKV_TOCK(tm_ld, t0);
         const int kbase = it * 128 + c0;
         const bool need_mask = (p.causal && (p.k_pos0 + kbase + CPT - 1 > p.q_pos0 + q0)) || (kbase + CPT > p.Skv);
         if (!need_mask) {
@@ -1666,6 +1668,7 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
           }
         }
       }
+      HG_DKV_TOCK(tm_math, t0);
       if (it >= 2) {   // this dS buffer was last read by the dQ product of step it-2
         if (!mbar_wait_warp(&ds_empty[it & 1], ((it >> 1) & 1) ^ 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -1680,7 +1683,9 @@ flash_bwd_dq128_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive_warp(ds_full);
+      HG_DKV_TOCK(tm_st, t0);
     }
+    HG_DKV_REPORT(24, n_it, tm_wait_s, tm_ld, tm_math, tm_st);
     const int dqslot = p.dqmap.slot(h, p.qpg);
     hg_lp_t* dq = p.dQ + int64_t(srow) * p.dq_ss + int64_t(b) * p.dq_sb + int64_t(dqslot) * HD;
     if (n_it == 0) {

@@ -227,7 +227,7 @@ def main(argv=None):
         torch.cuda.synchronize()
         ctypes.CDLL("libcudart.so.12").cudaMemcpy(words, ctypes.c_void_p(lib.hg_status_address()), 256, 2)
         out["role_cycles"] = {"softmax": list(words[16:21]), "mma": list(words[24:29]),
-                              "softmax_ld_math": list(words[32:36])}
+                              "dq_softmax": list(words[40:45]), "dq_mma": list(words[48:53])}
     print(json.dumps(out))
 
 

@@ -121,8 +121,9 @@ class GalvatronModel:
         if c.cp_size > 1:
             dist.all_reduce(total, group=c.cp.group)
         if c.dp is not None and c.dp.size > 1 and c.dp.group is not None:
-            dist.all_reduce(total, group=c.dp.group)
-            total = total / c.dp.size
+            from ..utils.runtime_utils import average_losses_across_data_parallel_group
+
+            total = average_losses_across_data_parallel_group([total], c.dp)[0]
         return total
 
     # ---- tied embeddings across pipeline stages ---------------------------------------------------------
