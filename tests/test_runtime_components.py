@@ -268,6 +268,43 @@ def test_dataset_index_cache_is_built_once_by_rank_zero(tmp_path):
     assert all(len(r["files"]) == 3 and not any(".tmp." in f for f in r["files"]) for r in res)
 
 
+def _fd_exchange_worker(payload):
+    """One gloo rank: pass an open file to every other rank over the allocator's descriptor exchange."""
+    import torch.distributed as dist
+
+    from hetu_galvatron_b200.parallel.symm_vmm import _exchange_fds
+
+    me = dist.get_rank()
+    path = os.path.join(payload["dir"], "rank%d.txt" % me)
+    with open(path, "w") as f:
+        f.write("written by rank %d" % me)
+    fd = os.open(path, os.O_RDONLY)
+    seen = {}
+    for tag in ("first", "second"):          # two rounds: the socket names of a round are gone before the next
+        got = _exchange_fds(fd, dist.group.WORLD, tag)
+        assert got[me] == -1
+        for r, other in enumerate(got):
+            if r != me:
+                os.lseek(other, 0, os.SEEK_SET)
+                seen["%s_%d" % (tag, r)] = os.read(other, 64).decode()
+                os.close(other)
+    os.close(fd)
+    return seen
+
+
+def test_vmm_allocator_passes_descriptors_between_ranks(tmp_path):
+    """The descriptor exchange behind ``HG_SYMM_ALLOC=vmm`` (abstract Unix sockets, SCM_RIGHTS): every rank ends up with
+    a working descriptor of every other rank's file, in rank order."""
+    from tests.dist_utils import run_distributed
+
+    res = run_distributed(__file__, "fd_exchange", 3, {"dir": str(tmp_path)}, timeout=120)
+    for me, seen in enumerate(res):
+        for tag in ("first", "second"):
+            for r in range(3):
+                if r != me:
+                    assert seen["%s_%d" % (tag, r)] == "written by rank %d" % r
+
+
 def test_nonzero_device_status_rejects_the_step(monkeypatch):
     """A kernel whose bounded wait ran out leaves a code in the device status word; the training loop reads it once
     per iteration and raises instead of keeping the step."""
@@ -501,4 +538,4 @@ def test_expert_bias_update_moves_towards_balance():
 if __name__ == "__main__":
     from tests.dist_utils import worker_main
 
-    worker_main({"cold_cache": _cold_cache_worker})
+    worker_main({"cold_cache": _cold_cache_worker, "fd_exchange": _fd_exchange_worker})
