@@ -41,15 +41,16 @@ __device__ __forceinline__ float ex2(float x) {
 // (maximum relative error 7.5e-5, a fiftieth of the bf16 rounding the result gets next) and n goes straight into
 // the exponent field.  Nine FMA / integer instructions against one on the special-function unit, which delivers
 // far fewer results per clock: giving a share of the elements to this path takes the exp2 unit off the critical path.
-// Inputs below -126 (masked entries, -inf) clamp to 2^-126.
+// Inputs below -126 (masked entries, -inf) give exactly 0, as the flushing hardware instruction does.
 __device__ __forceinline__ float ex2_poly(float x) {
-  x = fmaxf(x, -126.f);
-  const float t = x + 12582912.f;          // 1.5 * 2^23
-  const float f = x - (t - 12582912.f);
+  const float xc = fmaxf(x, -126.f);
+  const float t = xc + 12582912.f;         // 1.5 * 2^23
+  const float f = xc - (t - 12582912.f);
   float r = fmaf(f, 0.05517165f, 0.24261113f);
   r = fmaf(r, f, 0.69326097f);
   r = fmaf(r, f, 0.99992806f);
-  return __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+  r = __int_as_float(__float_as_int(r) + (__float_as_int(t) << 23));
+  return x < -126.f ? 0.f : r;
 }
 // Softmax warpgroups of the 128-query dK/dV kernel (2 or 4).
 #ifndef HG_DKV_WARPGROUPS
@@ -61,9 +62,47 @@ constexpr int kDkvWarpgroups = HG_DKV_WARPGROUPS;
 #define HG_DQ_WARPGROUPS 4
 #endif
 constexpr int kDqWarpgroups = HG_DQ_WARPGROUPS;
+// How many of every four exponentials of the two-tile forward kernel take ex2_poly instead of the special-function unit
+// (its two softmax warpgroups run at the same time and share that unit).
+#ifndef HG_FWD_POLY_OF_4
+#define HG_FWD_POLY_OF_4 0
+#endif
 // How many of every four probabilities of the 128-query dK/dV kernel take ex2_poly instead of the special-function unit.
 #ifndef HG_DKV_POLY_OF_4
 #define HG_DKV_POLY_OF_4 0
+#endif
+
+// Per-role cycle counts of CTA (0, 0, 0), for builds with -DHG_ATTN_TIMING: where a step's time goes (waiting for the
+// other role, or working).  Lane 0 of the first softmax warp writes words 16..20 of the device status buffer
+// (steps, wait for S^T, probabilities, wait for dP^T, dS^T and stores), lane 0 of the MMA warp words 24..28 (steps, wait
+// for free S^T columns, wait for P^T, wait for dS^T, time spent issuing).  The dQ kernel reports in words 40..44 and
+// 48..52: softmax (steps, wait for S, loads, arithmetic, dS store), MMA (steps, S + dP issue including
+// its waits, wait for dS, dQ issue).  The counts are clock64() differences; nothing is compiled in without
+// the define.
+#ifdef HG_ATTN_TIMING
+#define HG_DKV_TIMERS(a, b, c, d) long long a = 0, b = 0, c = 0, d = 0
+#define HG_DKV_TICK(t) long long t = clock64()
+#define HG_DKV_TOCK(acc, t)          \
+  do {                               \
+    const long long now_ = clock64(); \
+    acc += now_ - t;                 \
+    t = now_;                        \
+  } while (0)
+#define HG_DKV_REPORT(off, n, a, b, c, d)                                                                   \
+  do {                                                                                                      \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane_id() == 0 && (warp == 1 || warp == 2)) { \
+      p.status[16 + off] = n;                                                                               \
+      p.status[17 + off] = int(a);                                                                          \
+      p.status[18 + off] = int(b);                                                                          \
+      p.status[19 + off] = int(c);                                                                          \
+      p.status[20 + off] = int(d);                                                                          \
+    }                                                                                                       \
+  } while (0)
+#else
+#define HG_DKV_TIMERS(a, b, c, d)
+#define HG_DKV_TICK(t)
+#define HG_DKV_TOCK(acc, t)
+#define HG_DKV_REPORT(off, n, a, b, c, d)
 #endif
 
 // Head -> slot mapping inside the (possibly packed) tensor:  slot = (h / qpg) * gs + (h % qpg) * hs + off
@@ -344,6 +383,317 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int c = 0; c < HD / 32; ++c) {
         uint32_t r[32];
         tmem_ld32(tO + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (srow < p.Sq) {
+          hg_lp_t* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD + c * 32;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 u;
+            u.x = pack_bf16(__uint_as_float(r[q * 8 + 0]) * inv, __uint_as_float(r[q * 8 + 1]) * inv);
+            u.y = pack_bf16(__uint_as_float(r[q * 8 + 2]) * inv, __uint_as_float(r[q * 8 + 3]) * inv);
+            u.z = pack_bf16(__uint_as_float(r[q * 8 + 4]) * inv, __uint_as_float(r[q * 8 + 5]) * inv);
+            u.w = pack_bf16(__uint_as_float(r[q * 8 + 6]) * inv, __uint_as_float(r[q * 8 + 7]) * inv);
+            reinterpret_cast<uint4*>(o)[q] = u;
+          }
+        }
+      }
+      if (srow < p.Sq)
+        p.LSE[(size_t(b) * p.nheads + h) * p.Sq + srow] = (l > 0.f) ? (m_used + log2f(l)) * kLn2 : -INFINITY;
+    } else {
+      *abort_flag = 1;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =================================================================================================
+// Forward with two query tiles per CTA and P in tensor memory (head dim 128).
+// In the one-tile kernel a scheduler hosts a single softmax warp, so every latency of its step (the loads from tensor
+// memory, the maximum, the exp2 / convert chains) is exposed, and the tensor core idles while the softmax of its only
+// tile runs.  Here a CTA owns 256 queries as two tiles of 128, one softmax warpgroup per tile: while one tile's
+// threads work on their scores, the tensor core runs the other tile's products, and every scheduler has two softmax
+// warps to switch between.  P never goes through shared memory: the threads store it, packed, over the first 64 of
+// the 128 S columns they have just read, and the PV product takes its A operand from tensor memory.
+//
+// Tensor memory (512 columns): S of tile 0 / 1 at 0 / 128, O of tile 0 / 1 at 256 / 384.  Per tile the order is
+// S(j) -> softmax(j) -> P(j) -> PV(j) -> S(j+1): S(j+1) overwrites the columns PV(j) reads, and the tensor core
+// executes in issue order, so the MMA warp issues PV(t, j) and S(t, j+1) back to back when P(t, j) is stored.
+// K and V stages are shared by the two tiles; a stage is released after the last product that reads it.
+// =================================================================================================
+template <int HD>
+struct Fwd2Smem {
+  static constexpr int kQ = 128 * HD * 2;     // one query tile
+  static constexpr int kKV = 128 * HD * 2;    // one stage of K or V
+  static constexpr int kTotal = 2 * kQ + 4 * kKV + 1024 + 256;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(320, 1)
+flash_fwd2_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const FwdParams p) {
+  static_assert(HD == 128, "the two-tile forward is written for head dim 128");
+  extern __shared__ uint8_t smem_raw[];
+  using L = Fwd2Smem<HD>;
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = base;                     // 2 tiles
+  uint8_t* sK = sQ + 2 * L::kQ;           // 2 stages
+  uint8_t* sV = sK + 2 * L::kKV;          // 2 stages
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * L::kKV);
+  uint64_t* q_full = bars;          // 1
+  uint64_t* k_full = bars + 1;      // 2
+  uint64_t* k_empty = bars + 3;     // 2
+  uint64_t* v_full = bars + 5;      // 2
+  uint64_t* v_empty = bars + 7;     // 2
+  uint64_t* s_full = bars + 9;      // 2 (per tile)
+  uint64_t* p_full = bars + 11;     // 2 (per tile)
+  uint64_t* o_done = bars + 13;     // 2 (per tile)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int qb = gridDim.x - 1 - blockIdx.x;  // heavy (late) query blocks first under a causal mask
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int q0 = qb * 256;
+
+  // key blocks each tile attends to (tile 1 never fewer than tile 0)
+  int n_kv_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    int kv_len = p.Skv;
+    if (p.causal) kv_len = min(p.Skv, p.q_pos0 + q0 + t * 128 + 127 - p.k_pos0 + 1);
+    n_kv_t[t] = (kv_len > 0 && q0 + t * 128 < p.Sq) ? (kv_len + 127) / 128 : 0;
+  }
+  const int n_kv = max(n_kv_t[0], n_kv_t[1]);
+
+  if (threadIdx.x == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&k_full[i], 1);
+      mbar_init(&k_empty[i], 1);
+      mbar_init(&v_full[i], 1);
+      mbar_init(&v_empty[i], 1);
+      mbar_init(&s_full[i], 1);
+      mbar_init(&p_full[i], 4);      // one arrival per softmax warp of the tile (mbar_arrive_warp)
+      mbar_init(&o_done[i], 1);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  const uint32_t tS[2] = {tmem, tmem + 128};
+  const uint32_t tO[2] = {tmem + 256, tmem + 384};
+
+  const int qslot = p.qmap.slot(h, p.qpg), kslot = p.kmap.slot(h, p.qpg), vslot = p.vmap.slot(h, p.qpg);
+
+  if (warp == 0) {
+    if (n_kv > 0) {
+      // the whole warp walks the loop, one elected lane issues the copies (see producer_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
+      if (issuer) mbar_expect_tx(q_full, 2 * L::kQ);   // rows past the end of the tensor arrive as zeros
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          if (issuer) tma_load_4d(sQ + t * L::kQ + c * 128 * 128, &tmQ, q_full, c * 64, qslot, q0 + t * 128, b);
+      for (int j = 0; j < n_kv; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait_warp(&k_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&k_full[st], L::kKV);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          if (issuer) tma_load_4d(sK + st * L::kKV + c * 128 * 128, &tmK, &k_full[st], c * 64, kslot, j * 128, b);
+        if (!mbar_wait_warp(&v_empty[st], ph ^ 1, p.status, kTimeoutSmemEmpty, abort_flag)) { *abort_flag = 1; break; }
+        if (issuer) mbar_expect_tx(&v_full[st], L::kKV);
+#pragma unroll
+        for (int c = 0; c < HD / 64; ++c)
+          if (issuer) tma_load_4d(sV + st * L::kKV + c * 128 * 128, &tmV, &v_full[st], c * 64, vslot, j * 128, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (n_kv > 0) {
+      // the whole warp walks the loop, one elected lane issues (see mma_loop in gemm_core.cuh)
+      const bool issuer = elect_one() != 0;
+      constexpr uint32_t idesc_s = make_idesc_lp(128, 128, false, false);
+      constexpr uint32_t idesc_o = make_idesc_lp(128, HD, false, true);
+      bool ok = mbar_wait_warp(q_full, 0, p.status, kTimeoutSmemFull, abort_flag);
+      // the last tile (in issue order) that has a step j: it releases the K / V stage of that step
+      auto last_user = [&](int j) -> int { return j < n_kv_t[1] ? 1 : 0; };
+      auto issue_s = [&](int t, int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait_warp(&k_full[st], (j >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t aQ = smem_u32(sQ + t * L::kQ), aK = smem_u32(sK + st * L::kKV);
+        if (issuer) {
+#pragma unroll
+          for (int kk = 0; kk < HD / 16; ++kk)
+            umma_f16_ss(tS[t], kmajor_desc(aQ, 128, kk), kmajor_desc(aK, 128, kk), idesc_s, kk != 0);
+          umma_commit(&s_full[t]);
+          if (t == last_user(j)) umma_commit(&k_empty[st]);
+        }
+        __syncwarp();
+        return true;
+      };
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        if (ok && n_kv_t[t] > 0) ok = issue_s(t, 0);
+      HG_DKV_TIMERS(tm_wait_p0, tm_wait_p1, tm_issue, tm_unused);
+      HG_DKV_TICK(t0);
+      for (int j = 0; ok && j < n_kv; ++j) {
+        const int st = j & 1;
+#pragma unroll
+        for (int t = 0; t < 2; ++t) {
+          if (!ok || j >= n_kv_t[t]) continue;
+          if (!mbar_wait_warp(&p_full[t], j & 1, p.status, kTimeoutOther, abort_flag)) { ok = false; break; }
+          if (t == 0) { HG_DKV_TOCK(tm_wait_p0, t0); } else { HG_DKV_TOCK(tm_wait_p1, t0); }
+          if (!mbar_wait_warp(&v_full[st], (j >> 1) & 1, p.status, kTimeoutSmemFull, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t aV = smem_u32(sV + st * L::kKV);
+          if (issuer) {
+#pragma unroll
+            for (int kk = 0; kk < 8; ++kk)   // k-step kk = keys 16kk..16kk+15 = 8 packed columns of P
+              umma_f16_ts(tO[t], tS[t] + kk * 8, mnmajor_desc(aV, 128, kk), idesc_o, (j | kk) != 0);
+            if (t == last_user(j)) umma_commit(&v_empty[st]);
+            if (j + 1 >= n_kv_t[t]) umma_commit(&o_done[t]);
+          }
+          __syncwarp();
+          if (j + 1 < n_kv_t[t]) ok = issue_s(t, j + 1);
+          HG_DKV_TOCK(tm_issue, t0);
+        }
+      }
+      HG_DKV_REPORT(8, n_kv, tm_wait_p0, tm_wait_p1, tm_issue, tm_unused);
+      if (!ok) *abort_flag = 1;
+    }
+  } else {
+    // ---- softmax: one warpgroup per tile, thread == query row ----
+    const int t = (warp - 2) >> 2;
+    const int wq = warp & 3;
+    const int row = wq * 32 + lane_id();
+    const uint32_t lane_off = uint32_t(wq * 32) << 16;
+    const float sl2 = p.scale * kLog2e;
+    const int qt0 = q0 + t * 128;
+    const int q_pos = p.q_pos0 + qt0 + row;
+    const int my_kv = n_kv_t[t];
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    HG_DKV_TIMERS(tm_wait_s, tm_ld, tm_math, tm_st);
+    for (int j = 0; j < my_kv; ++j) {
+      HG_DKV_TICK(t0);
+      if (!mbar_wait_warp(&s_full[t], j & 1, p.status, kTimeoutTmemFull, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      HG_DKV_TOCK(tm_wait_s, t0);
+      float s[128];
+      {
+        uint32_t r[4][32];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) tmem_ld32(tS[t] + lane_off + c * 32, r[c]);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[c * 32 + i] = __uint_as_float(r[c][i]);
+      }
+      HG_DKV_TOCK(tm_ld, t0);
+      // masking (only blocks that cross the diagonal or the ragged end need it)
+      const int k_base = p.k_pos0 + j * 128;
+      const bool need_mask = (p.causal && (k_base + 127 > p.q_pos0 + qt0)) || (j * 128 + 128 > p.Skv);
+      if (need_mask) {
+#pragma unroll
+        for (int i = 0; i < 128; ++i) {
+          const bool dead = (j * 128 + i >= p.Skv) || (p.causal && (k_base + i > q_pos));
+          if (dead) s[i] = -INFINITY;
+        }
+      }
+      float mx4[4] = {s[0], s[1], s[2], s[3]};   // four chains: a single one is 127 dependent instructions long
+#pragma unroll
+      for (int i = 4; i < 128; i += 4) {
+        mx4[0] = fmaxf(mx4[0], s[i]); mx4[1] = fmaxf(mx4[1], s[i + 1]);
+        mx4[2] = fmaxf(mx4[2], s[i + 2]); mx4[3] = fmaxf(mx4[3], s[i + 3]);
+      }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      mx *= sl2;
+      // lazy rescale: keep the running reference max unless the new max exceeds it by more than 2^8
+      float alpha = 1.f;
+      bool rescale = false;
+      if (mx > m_used + 8.f) {
+        alpha = (m_used == -INFINITY) ? 0.f : ex2(m_used - mx);
+        m_used = mx;
+        rescale = (j > 0);
+      }
+      const float nmref = (m_used == -INFINITY) ? 0.f : -m_used;
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[64];
+#pragma unroll
+      for (int i = 0; i < 128; i += 4) {
+        float e[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float x = fmaf(s[i + u], sl2, nmref);
+          e[u] = (u < HG_FWD_POLY_OF_4) ? ex2_poly(x) : ex2(x);
+          sum4[u] += e[u];
+        }
+        pk[i >> 1] = pack_bf16(e[0], e[1]);
+        pk[(i >> 1) + 1] = pack_bf16(e[2], e[3]);
+      }
+      l = l * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      HG_DKV_TOCK(tm_math, t0);
+      // S(t, j) was issued after PV(t, j-1), and the tensor core executes in order: O holds steps 0..j-1 by now
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll
+        for (int c = 0; c < HD / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld32(tO[t] + lane_off + c * 32, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+          tmem_st32(tO[t] + lane_off + c * 32, r);
+        }
+      }
+      // P, packed, over the first 64 of this row's S columns
+      {
+        const uint32_t(&lo)[32] = *reinterpret_cast<const uint32_t(*)[32]>(&pk[0]);
+        const uint32_t(&hi)[32] = *reinterpret_cast<const uint32_t(*)[32]>(&pk[32]);
+        tmem_st32(tS[t] + lane_off, lo);
+        tmem_st32(tS[t] + lane_off + 32, hi);
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive_warp(&p_full[t]);
+      HG_DKV_TOCK(tm_st, t0);
+    }
+    if (t == 0) { HG_DKV_REPORT(0, my_kv, tm_wait_s, tm_ld, tm_math, tm_st); }
+    // ---- epilogue: O / l -> global, LSE ----
+    const int srow = qt0 + row;
+    if (my_kv == 0) {
+      if (srow < p.Sq) {
+        hg_lp_t* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD;
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) reinterpret_cast<uint4*>(o)[i] = make_uint4(0, 0, 0, 0);
+        p.LSE[(size_t(b) * p.nheads + h) * p.Sq + srow] = -INFINITY;
+      }
+    } else if (ok && !*abort_flag && mbar_wait_warp(&o_done[t], 0, p.status, kTimeoutOther, abort_flag)) {
+      tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+      for (int c = 0; c < HD / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld32(tO[t] + lane_off + c * 32, r);
         tmem_ld_wait();
         if (srow < p.Sq) {
           hg_lp_t* o = p.O + int64_t(srow) * p.o_ss + int64_t(b) * p.o_sb + h * HD + c * 32;
@@ -771,38 +1121,6 @@ flash_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_const
 // dK(i), the readers of P^T(i) and dS^T(i).  Per step the MMA warp issues S^T(i+1) when the S^T(i) columns are
 // free, dV(i) when P^T(i) is stored, dK(i) and dP^T(i+1) when dS^T(i) is stored.
 // =================================================================================================
-// Per-role cycle counts of CTA (0, 0, 0), for builds with -DHG_ATTN_TIMING: where a step's time goes (waiting for the
-// other role, or working).  Lane 0 of the first softmax warp writes words 16..20 of the device status buffer
-// (steps, wait for S^T, probabilities, wait for dP^T, dS^T and stores), lane 0 of the MMA warp words 24..28 (steps, wait
-// for free S^T columns, wait for P^T, wait for dS^T, time spent issuing).  The dQ kernel reports in words 40..44 and
-// 48..52: softmax (steps, wait for S, loads, arithmetic, dS store), MMA (steps, S + dP issue including
-// its waits, wait for dS, dQ issue).  The counts are clock64() differences; nothing is compiled in without
-// the define.
-#ifdef HG_ATTN_TIMING
-#define HG_DKV_TIMERS(a, b, c, d) long long a = 0, b = 0, c = 0, d = 0
-#define HG_DKV_TICK(t) long long t = clock64()
-#define HG_DKV_TOCK(acc, t)          \
-  do {                               \
-    const long long now_ = clock64(); \
-    acc += now_ - t;                 \
-    t = now_;                        \
-  } while (0)
-#define HG_DKV_REPORT(off, n, a, b, c, d)                                                                   \
-  do {                                                                                                      \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane_id() == 0 && (warp == 1 || warp == 2)) { \
-      p.status[16 + off] = n;                                                                               \
-      p.status[17 + off] = int(a);                                                                          \
-      p.status[18 + off] = int(b);                                                                          \
-      p.status[19 + off] = int(c);                                                                          \
-      p.status[20 + off] = int(d);                                                                          \
-    }                                                                                                       \
-  } while (0)
-#else
-#define HG_DKV_TIMERS(a, b, c, d)
-#define HG_DKV_TICK(t)
-#define HG_DKV_TOCK(acc, t)
-#define HG_DKV_REPORT(off, n, a, b, c, d)
-#endif
 
 template <int HD>
 struct Dkv128Smem {
@@ -1755,6 +2073,9 @@ int make_map(CUtensorMap* out, const void* base, int hd, int slots, int S, int B
 // dK/dV kernel for head dim 128: 0 = 128-query steps with P^T / dS^T in tensor memory, 1 = 64-query steps staged
 // through shared memory (kept for head dim 64 and for side-by-side timing).
 int g_dkv_variant = 0;
+// Forward kernel for head dim 128: 0 = two query tiles per CTA with P in tensor memory (sequences longer than one
+// tile), 1 = one tile per CTA with P staged in shared memory (also what head dim 64 and single-tile calls use).
+int g_fwd_variant = 0;
 
 template <typename K>
 int set_smem(K kernel, int bytes) {
@@ -1793,7 +2114,12 @@ int hg_flash_fwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
   p.status = hg_host::status_ptr();
   dim3 grid((Sq + 127) / 128, nheads, B);
   cudaStream_t st = (cudaStream_t)stream;
-  if (hd == 128) {
+  if (hd == 128 && Sq > 128 && g_fwd_variant == 0) {   // two query tiles per CTA, P in tensor memory
+    static bool cfg = false;
+    if (!cfg) { if ((rc = set_smem(flash_fwd2_kernel<128>, Fwd2Smem<128>::kTotal))) return rc; cfg = true; }
+    dim3 grid2((Sq + 255) / 256, nheads, B);
+    flash_fwd2_kernel<128><<<grid2, 320, Fwd2Smem<128>::kTotal, st>>>(tq, tk, tv, p);
+  } else if (hd == 128) {
     static bool cfg = false;
     if (!cfg) { if ((rc = set_smem(flash_fwd_kernel<128>, FwdSmem<128>::kTotal))) return rc; cfg = true; }
     flash_fwd_kernel<128><<<grid, kThreads, FwdSmem<128>::kTotal, st>>>(tq, tk, tv, p);
@@ -1803,6 +2129,13 @@ int hg_flash_fwd(const HgAttnTensor* q, const HgAttnTensor* k, const HgAttnTenso
     flash_fwd_kernel<64><<<grid, kThreads, FwdSmem<64>::kTotal, st>>>(tq, tk, tv, p);
   }
   return int(cudaGetLastError());
+}
+
+// Selects the forward kernel used for head dim 128 (see g_fwd_variant); returns the previous value.
+int hg_attn_set_fwd_variant(int v) {
+  const int old = g_fwd_variant;
+  g_fwd_variant = v ? 1 : 0;
+  return old;
 }
 
 // Selects the dK/dV kernel used for head dim 128 (see g_dkv_variant); returns the previous value.

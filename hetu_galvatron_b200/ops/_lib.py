@@ -89,6 +89,7 @@ _SIGNATURES = {
     "hg_cast_f32_bf16": [c_void_p, c_void_p, c_ll, c_void_p],
     "hg_add_bf16": [c_void_p, c_void_p, c_void_p, c_ll, c_void_p],
     "hg_attn_set_dkv_variant": [c_int],
+    "hg_attn_set_fwd_variant": [c_int],
     "hg_attn_merge": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     "hg_xent_stats": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "hg_xent_bwd": [c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],

@@ -106,6 +106,9 @@ def main(argv=None):
     ap.add_argument("--kv-heads", type=int, default=32)
     ap.add_argument("--hd", type=int, default=128)
     ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--fwd-variant", type=int, default=0,
+                    help="attn, head dim 128: 0 = forward with two query tiles per CTA and P in tensor memory, 1 = one "
+                         "tile per CTA, P staged in shared memory")
     ap.add_argument("--dkv-variant", type=int, default=0,
                     help="attn --bwd, head dim 128: 0 = dK/dV kernel with 128-query steps and P^T / dS^T in tensor "
                          "memory, 1 = the 64-query kernel that stages them in shared memory")
@@ -154,6 +157,8 @@ def main(argv=None):
         k = torch.randn(S, B, ng, hd, device=dev, dtype=bf, requires_grad=True)
         v = torch.randn(S, B, ng, hd, device=dev, dtype=bf, requires_grad=True)
         fl = 4.0 * S * S * B * nh * hd / 2
+        _lib.load().hg_attn_set_fwd_variant(a.fwd_variant)
+        out["fwd_variant"] = a.fwd_variant
         if a.bwd:
             _lib.load().hg_attn_set_dkv_variant(a.dkv_variant)
             out["dkv_variant"] = a.dkv_variant

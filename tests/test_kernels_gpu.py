@@ -275,6 +275,33 @@ def test_flash_backward_dkv_kernels_agree(S, B, nh, ng, causal):
     assert rel_err(grads[0][1], grads[1][1]) < 1e-2 and rel_err(grads[0][2], grads[1][2]) < 1e-2
 
 
+@pytest.mark.parametrize("S,B,nh,ng,causal", [(2048, 1, 4, 2, True), (1000, 2, 2, 2, True), (640, 1, 2, 1, False),
+                                              (300, 1, 2, 2, True)])
+def test_flash_forward_kernels_agree(S, B, nh, ng, causal):
+    """Head dim 128 has two forward kernels (two query tiles per CTA with P in tensor memory, and one tile per CTA with
+    P staged in shared memory): same output and log-sum-exp from both, and both close to the fp32 oracle."""
+    from hetu_galvatron_b200.ops import _lib
+
+    torch.manual_seed(17)
+    hd = 128
+    q = torch.randn(S, B, nh, hd, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(S, B, ng, hd, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(S, B, ng, hd, device=DEV, dtype=torch.bfloat16)
+    lib = _lib.load()
+    outs = []
+    try:
+        for variant in (0, 1):
+            lib.hg_attn_set_fwd_variant(variant)
+            outs.append(ops.flash_attention(q, k, v, causal=causal, return_lse=True))
+    finally:
+        lib.hg_attn_set_fwd_variant(0)
+    assert _lib.read_status() == 0
+    ref, lse_ref = ops.attention_reference(q.float(), k.float(), v.float(), causal)
+    for o, lse in outs:
+        assert rel_err(o, ref) < 2e-2 and torch.allclose(lse, lse_ref, rtol=1e-3, atol=2e-3)
+    assert rel_err(outs[0][0], outs[1][0]) < 1e-2
+
+
 @pytest.mark.parametrize("hd", [128, 64])
 def test_attention_merge_of_two_key_halves(hd):
     """Attention over keys [0, 256) and over keys [256, 512), merged through their log-sum-exp, equals attention over
