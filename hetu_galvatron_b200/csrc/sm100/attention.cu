@@ -2057,6 +2057,12 @@ namespace {
 // base + s*ss + b*sb + slot*hd + d.  Box = (64, 1, box_rows, 1).
 int make_map(CUtensorMap* out, const void* base, int hd, int slots, int S, int B, int64_t ss, int64_t sb,
              int box_rows) {
+  const uint64_t key[8] = {4, uint64_t(reinterpret_cast<uintptr_t>(base)), (uint64_t(uint32_t(hd)) << 32) | uint32_t(slots),
+                           (uint64_t(uint32_t(S)) << 32) | uint32_t(B), uint64_t(ss), uint64_t(sb), uint64_t(box_rows), 0};
+  if (const CUtensorMap* hit = hg_host::tmap_cache_find(key)) {
+    *out = *hit;
+    return 0;
+  }
   auto enc = hg_host::get_encode_fn();
   if (enc == nullptr) return -2;
   cuuint64_t dims[4] = {cuuint64_t(hd), cuuint64_t(slots), cuuint64_t(S), cuuint64_t(B)};
@@ -2067,6 +2073,7 @@ int make_map(CUtensorMap* out, const void* base, int hd, int slots, int S, int B
   CUresult r = enc(out, HG_TMAP_LP, 4, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) hg_host::tmap_cache_store(key, *out);
   return r == CUDA_SUCCESS ? 0 : -(1000 + int(r));
 }
 

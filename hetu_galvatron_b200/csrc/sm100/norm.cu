@@ -58,19 +58,35 @@ norm_fwd_kernel(const hg_lp_t* __restrict__ x, const hg_lp_t* __restrict__ resid
                 float* __restrict__ mean_out, int rows, int H, float eps) {
   __shared__ float red[kThreads / 32];
   const int nvec = H >> 3;
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+  // The next row's loads are issued before this row's reductions, so that a block always has a row in flight
+  // across its __syncthreads (with one row per trip the memory system idles while the block reduces).
+  uint4 xraw[kMaxVec], rraw[kMaxVec];
+  auto fetch = [&](int row) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + size_t(row) * H);
     const uint4* rr = residual ? reinterpret_cast<const uint4*>(residual + size_t(row) * H) : nullptr;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int c = threadIdx.x + i * kThreads;
+      if (c < nvec) {
+        xraw[i] = xr[c];
+        if (rr) rraw[i] = rr[c];
+      }
+    }
+  };
+  constexpr bool kPrefetch = kMaxVec <= 4;    // the widest rows keep too much in registers to hold a second row
+  if (kPrefetch && int(blockIdx.x) < rows) fetch(blockIdx.x);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    if (!kPrefetch) fetch(row);
     float v[kMaxVec][8];
     float s = 0.f, s2 = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
       const int c = threadIdx.x + i * kThreads;
       if (c < nvec) {
-        unpack8(xr[c], v[i]);
-        if (rr) {
+        unpack8(xraw[i], v[i]);
+        if (residual) {
           float r[8];
-          unpack8(rr[c], r);
+          unpack8(rraw[i], r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[i][j] += r[j];
           if (h_out) {
@@ -84,6 +100,7 @@ norm_fwd_kernel(const hg_lp_t* __restrict__ x, const hg_lp_t* __restrict__ resid
         for (int j = 0; j < 8; ++j) { s += v[i][j]; s2 += v[i][j] * v[i][j]; }
       }
     }
+    if (kPrefetch && row + int(gridDim.x) < rows) fetch(row + gridDim.x);
     float mean = 0.f, var;
     if (RMS) {
       var = block_sum(s2, red) / H;
@@ -147,20 +164,39 @@ norm_bwd_kernel(const hg_lp_t* __restrict__ dy, const hg_lp_t* __restrict__ h,
     const int c = threadIdx.x + i * kThreads;
     if (c < nvec) unpack8(reinterpret_cast<const uint4*>(w)[c], wv[i]);
   }
-  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float rstd = rstd_in[row];
-    const float mean = RMS ? 0.f : mean_in[row];
+  // as in the forward: the next row's dy / h / dres are requested before this row's reductions
+  constexpr bool kPrefetch = kMaxVec <= 4;
+  uint4 dyraw[kMaxVec], hraw[kMaxVec], drraw[kMaxVec];
+  auto fetch = [&](int row) {
     const uint4* dyr = reinterpret_cast<const uint4*>(dy + size_t(row) * H);
     const uint4* hr = reinterpret_cast<const uint4*>(h + size_t(row) * H);
+    const uint4* dr = dres ? reinterpret_cast<const uint4*>(dres + size_t(row) * H) : nullptr;
+#pragma unroll
+    for (int i = 0; i < kMaxVec; ++i) {
+      const int c = threadIdx.x + i * kThreads;
+      if (c < nvec) {
+        dyraw[i] = dyr[c];
+        hraw[i] = hr[c];
+        if (kPrefetch && dr) drraw[i] = dr[c];
+      }
+    }
+  };
+  if (kPrefetch && int(blockIdx.x) < rows) fetch(blockIdx.x);
+  for (int row = blockIdx.x; row < rows; row += gridDim.x) {
+    if (!kPrefetch) fetch(row);
+    const float rstd = rstd_in[row];
+    const float mean = RMS ? 0.f : mean_in[row];
     float g[kMaxVec][8], xh[kMaxVec][8];
+    uint4 drcur[kMaxVec];   // this row's residual gradient, packed (the prefetch below reuses drraw)
     float c1 = 0.f, c2 = 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxVec; ++i) {
       const int c = threadIdx.x + i * kThreads;
       if (c < nvec) {
         float d[8], hv[8];
-        unpack8(dyr[c], d);
-        unpack8(hr[c], hv);
+        unpack8(dyraw[i], d);
+        unpack8(hraw[i], hv);
+        if (kPrefetch && dres) drcur[i] = drraw[i];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (hv[j] - mean) * rstd;
@@ -172,6 +208,7 @@ norm_bwd_kernel(const hg_lp_t* __restrict__ dy, const hg_lp_t* __restrict__ h,
         }
       }
     }
+    if (kPrefetch && row + int(gridDim.x) < rows) fetch(row + gridDim.x);
     c1 = block_sum(c1, red) / H;
     c2 = RMS ? 0.f : block_sum(c2, red) / H;
     uint4* dxr = reinterpret_cast<uint4*>(dx + size_t(row) * H);
@@ -184,7 +221,7 @@ norm_bwd_kernel(const hg_lp_t* __restrict__ dy, const hg_lp_t* __restrict__ h,
         for (int j = 0; j < 8; ++j) o[j] = rstd * (g[i][j] - xh[i][j] * c1 - c2);
         if (dres) {
           float r[8];
-          unpack8(reinterpret_cast<const uint4*>(dres + size_t(row) * H)[c], r);
+          unpack8(kPrefetch ? drcur[i] : reinterpret_cast<const uint4*>(dres + size_t(row) * H)[c], r);
 #pragma unroll
           for (int j = 0; j < 8; ++j) o[j] += r[j];
         }

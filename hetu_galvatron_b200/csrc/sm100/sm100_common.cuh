@@ -372,6 +372,9 @@ int* status_ptr();
 
 // rank-2 bf16 tensor [rows, cols] with row pitch `ld` elements; box = [box_rows, box_cols]; 128B swizzle.
 // Returns 0 on success.
+// Per-thread cache of encoded tensor maps, keyed by eight words that determine the descriptor (runtime.cu).
+const CUtensorMap* tmap_cache_find(const uint64_t (&key)[8]);
+void tmap_cache_store(const uint64_t (&key)[8], const CUtensorMap& map);
 int make_tmap_2d_bf16(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld,
                       uint32_t box_rows, uint32_t box_cols);
 // rank-3 bf16 tensor [d2, d1, d0] (d0 innermost) with strides in elements.

@@ -92,7 +92,7 @@ def main(argv=None):
     from hetu_galvatron_b200.ops.gemm import OUT_F32_ACC
 
     ap = argparse.ArgumentParser()
-    ap.add_argument("kernel", choices=["gemm", "attn", "norm", "glu", "glu_bwd", "rope", "xent", "adam", "sumsq"])
+    ap.add_argument("kernel", choices=["gemm", "attn", "norm", "norm_bwd", "glu", "glu_bwd", "rope", "xent", "adam", "sumsq"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -180,6 +180,14 @@ def main(argv=None):
             w = torch.ones(C, device=dev, dtype=bf)
             fn = lambda: ops.norm(x, w, None, 1e-5, True, residual=r)
             nbytes = 4 * R * C * 2
+        elif a.kernel == "norm_bwd":
+            x = torch.randn(R, C, device=dev, dtype=bf, requires_grad=True)
+            r = torch.randn(R, C, device=dev, dtype=bf)
+            w = torch.ones(C, device=dev, dtype=bf, requires_grad=True)
+            y, hres = ops.norm(x, w, None, 1e-5, True, residual=r)
+            gy, gh = torch.randn_like(y), torch.randn_like(hres)
+            fn = lambda: torch.autograd.grad([y, hres], [x, w], [gy, gh], retain_graph=True)
+            nbytes = 4 * R * C * 2        # dy, h, dres read; dx written
         elif a.kernel == "glu":
             y = torch.randn(R, 2 * C, device=dev, dtype=bf)
             fn = lambda: ops.activation(y, "swiglu")
