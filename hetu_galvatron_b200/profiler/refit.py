@@ -93,12 +93,15 @@ def main(argv=None, run=os.system, out_dir: Optional[str] = None, no_launch: boo
                  "runtime.train.global_batch_size": bsz, "runtime.train.seq_length": seq})
     log_dir = os.path.join(work, "logs/profile_refit")
     os.makedirs(log_dir, exist_ok=True)
+    # The per-step (optimizer) term is a small difference of iteration times, so it is taken over a longer lever than
+    # the ratio: lmin against four times lmax layers (HG_REFIT_ACC_LAYERS overrides), one and two micro-batches.
+    lacc = int(os.environ.get("HG_REFIT_ACC_LAYERS", 4 * lmax))
     if not no_launch:
-        for L in (lmin, lmax):
+        for L in sorted({lmin, lmax, lacc}):
             ov = dict(base)
             ov["runtime.model.num_layers"] = L
             run(prof._command(ov, log_dir, "full_layernum_%d" % L))
-        for L in (lmin, lmax):     # the same with two micro-batches per step: separates the per-step part
+        for L in sorted({lmin, lacc}):     # the same with two micro-batches per step: separates the per-step part
             ov = dict(base)
             ov.update({"runtime.model.num_layers": L, "runtime.train.global_batch_size": 2 * bsz, "runtime.train.chunks": 2})
             run(prof._command(ov, log_dir, "full_layernum_%d_chunks2" % L))
@@ -112,7 +115,9 @@ def main(argv=None, run=os.system, out_dir: Optional[str] = None, no_launch: boo
             if key in mem and str(seq) in mem[key]:
                 opt_ms = optimizer_ms_per_layer(mem[key][str(seq)]["parameter_size"], measured_hbm_gbs())
                 break
-    measured = optimizer_ms_from_accumulation(full, lmin, lmax, bsz, seq)
+    measured = optimizer_ms_from_accumulation(full, lmin, lacc, bsz, seq)
+    if measured is None:
+        measured = optimizer_ms_from_accumulation(full, lmin, lmax, bsz, seq)
     if measured is not None:
         opt_ms = measured
     r = ratio_from_times(fwd, full, lmin, lmax, bsz, seq, opt_ms)
@@ -120,7 +125,8 @@ def main(argv=None, run=os.system, out_dir: Optional[str] = None, no_launch: boo
     path = os.path.join(out_dir, "b200_refit.json")
     cfg = read_json_config(path) if os.path.exists(path) else {}
     cfg.update({"backward_forward_ratio": r, "optimizer_ms_per_layer": opt_ms, "measured_with": {"model": model_name(args), "bsz": bsz, "seq": seq,
-                                                                "layers": [lmin, lmax]}})
+                                                                "layers": [lmin, lmax],
+                                                                "optimizer_term_layers": [lmin, lacc]}})
     write_json_config(cfg, path)
     print("backward / forward ratio %.4f written to %s" % (r, path))
     return r
