@@ -15,6 +15,9 @@
 // Every wait is bounded (2 s); a CTA that gives up raises its abort flag and the status word, its partner runs into
 // its own limit, and both still meet at the final cluster barrier and free their tensor memory.
 // No operand load uses cluster multicast: each CTA loads exactly the bytes it alone needs.
+#include <cstdlib>
+#include <mutex>
+
 #include "gemm2_core.cuh"
 
 namespace hg {
@@ -79,8 +82,59 @@ gemm2_bf16_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 using namespace hg::gemm;
 using namespace hg::gemm2;
 
+namespace {
+
+// Scratch of the tail split: partial tiles and arrival counters, one set per (device, stream) for up to four
+// streams per device (a launch on a fifth stream runs without the split).  Allocated on first use, never freed.
+constexpr int kSplitMaxUnits = 128;                 // >= number of CTA pairs
+struct SplitScratch {
+  cudaStream_t stream;
+  float* ws;
+  int* flags;
+};
+SplitScratch g_split[64][4] = {};
+std::mutex g_split_mu;
+
+bool split_scratch(cudaStream_t st, float** ws, int** flags) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  std::lock_guard<std::mutex> lk(g_split_mu);
+  for (int i = 0; i < 4; ++i) {
+    SplitScratch& e = g_split[dev][i];
+    if (e.ws != nullptr && e.stream != st) continue;
+    if (e.ws == nullptr) {
+      void* p = nullptr;
+      if (cudaMalloc(&p, size_t(kSplitMaxUnits) * kSplitTileFloats * sizeof(float) + kSplitMaxUnits * sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return false;
+      }
+      e.ws = static_cast<float*>(p);
+      e.flags = reinterpret_cast<int*>(e.ws + size_t(kSplitMaxUnits) * kSplitTileFloats);
+      e.stream = st;
+    }
+    *ws = e.ws;
+    *flags = e.flags;
+    return true;
+  }
+  return false;
+}
+
+// HG_GEMM_SPLIT_TAIL=1 switches the tail split on, 0 off.
+constexpr int kSplitDefault = 0;
+bool split_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("HG_GEMM_SPLIT_TAIL");
+    on = (e == nullptr || e[0] == 0) ? kSplitDefault : (e[0] != '0');
+  }
+  return on != 0;
+}
+
+}  // namespace
+
 template <bool A_MN, bool B_MN>
-static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p, int want_pairs, cudaStream_t st) {
+static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p_in, int want_pairs, cudaStream_t st) {
+  Params p = p_in;
   static int max_pairs = -1;
   auto k = gemm2_bf16_kernel<A_MN, B_MN>;
   cudaLaunchConfig_t cfg = {};
@@ -109,6 +163,21 @@ static int launch2(const CUtensorMap& ta, const CUtensorMap& tb, const Params& p
   }
   const int pairs = want_pairs < max_pairs ? want_pairs : max_pairs;
   cfg.gridDim = dim3(unsigned(2 * pairs), 1, 1);
+  // Last wave partly filled: let several pairs share each of its tiles (see Params::split_s).
+  p.split_s = 0;
+  const int tiles = p.tiles_m * p.tiles_n, num_kb = (p.K + BK - 1) / BK;
+  const int full = tiles / pairs, tail = tiles - full * pairs;
+  if (split_enabled() && p.k_ranges == nullptr && p.ready == nullptr && full >= 1 && tail >= 1 && pairs <= kSplitMaxUnits) {
+    int s = pairs / tail;
+    if (s > 4) s = 4;
+    if (s > num_kb / 8) s = num_kb / 8;
+    if (s >= 2 && split_scratch(st, &p.split_ws, &p.split_flags)) {
+      p.split_s = s;
+      p.split_tail_begin = full * pairs;
+      cudaError_t me = cudaMemsetAsync(p.split_flags, 0, size_t(tail) * s * sizeof(int), st);
+      if (me != cudaSuccess) return int(me);
+    }
+  }
   cudaError_t e = cudaLaunchKernelEx(&cfg, k, ta, tb, p);
   return int(e);
 }

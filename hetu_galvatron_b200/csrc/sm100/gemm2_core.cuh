@@ -105,6 +105,33 @@ __device__ __forceinline__ void umma_commit_pair(uint64_t* bar, uint16_t mask) {
       : "memory");
 }
 
+// ---- work units -------------------------------------------------------------------------------------------------
+// Pair `first` of `step` walks tiles first, first + step, ...; with the tail split on, every pair has the same number
+// of whole tiles (split_tail_begin / step) and the first (tail tiles x split_s) pairs one slice of a tail tile after them.
+struct Unit {
+  int tile, kb0, kb1, slice;
+};
+constexpr int kSplitTileFloats = CM * BN;
+__device__ __forceinline__ int unit_count(const Params& p, int first, int step, int num_tiles) {
+  if (p.split_s > 1) return p.split_tail_begin / step + (first < (num_tiles - p.split_tail_begin) * p.split_s ? 1 : 0);
+  return first < num_tiles ? (num_tiles - first + step - 1) / step : 0;
+}
+__device__ __forceinline__ Unit unit_at(const Params& p, int first, int step, int u, int num_kb) {
+  Unit w;
+  if (p.split_s > 1 && u == p.split_tail_begin / step) {
+    w.tile = p.split_tail_begin + first / p.split_s;
+    w.slice = first % p.split_s;
+    w.kb0 = num_kb * w.slice / p.split_s;
+    w.kb1 = num_kb * (w.slice + 1) / p.split_s;
+  } else {
+    w.tile = first + u * step;
+    w.slice = 0;
+    w.kb0 = 0;
+    w.kb1 = num_kb;
+  }
+  return w;
+}
+
 // ---- roles ------------------------------------------------------------------------------------------------------
 template <bool A_MN, bool B_MN>
 __device__ __forceinline__ void producer2(const CUtensorMap* tmA, const CUtensorMap* tmB, const Params& p, const Smem2& s,
@@ -117,9 +144,11 @@ __device__ __forceinline__ void producer2(const CUtensorMap* tmA, const CUtensor
   const int num_kb = (p.K + BK - 1) / BK;
   bool ok = true;
   const bool issuer = elect_one() != 0;   // the warp walks the loop together; only this lane issues the copies
-  for (int tile = first; ok && tile < num_tiles; tile += step) {
+  const int n_units = unit_count(p, first, step, num_tiles);
+  for (int u = 0; ok && u < n_units; ++u) {
+    const Unit w = unit_at(p, first, step, u, num_kb);
     int tm, tn;
-    tile_coords(p, tile, tm, tn);
+    tile_coords(p, w.tile, tm, tn);
     const int m0 = tm * CM + int(rank) * BM;
     const int n0 = tn * BN + int(rank) * HALF_N;
     if (p.ready != nullptr) {
@@ -146,7 +175,7 @@ __device__ __forceinline__ void producer2(const CUtensorMap* tmA, const CUtensor
       if (!landed) { ok = false; break; }
       asm volatile("fence.proxy.async.global;" ::: "memory");
     }
-    for (int kb = 0; kb < num_kb; ++kb) {
+    for (int kb = w.kb0; kb < w.kb1; ++kb) {
       if (!mbar_wait_warp(&s.empty[stage], phase ^ 1, p.status, kTimeoutSmemEmpty, s.abort)) { ok = false; break; }
       const uint32_t bar = map_to_cta(smem_u32(&s.full[stage]), 0);
       uint8_t* sa = s.a + stage * A2_BYTES;
@@ -199,11 +228,13 @@ __device__ __forceinline__ void mma2(const Params& p, const Smem2& s, uint32_t t
   uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
   bool ok = true;
   const bool issuer = elect_one() != 0;   // the warp walks the loop together; only this lane issues (see gemm_core.cuh)
-  for (int tile = first; ok && tile < num_tiles; tile += step) {
+  const int n_units = unit_count(p, first, step, num_tiles);
+  for (int u = 0; ok && u < n_units; ++u) {
+    const Unit w = unit_at(p, first, step, u, num_kb);
     if (!mbar_wait_warp(&s.tmem_empty[acc], acc_phase ^ 1, p.status, kTimeoutTmemEmpty, s.abort)) { ok = false; break; }
     tc_fence_after();
     const uint32_t d = tmem_base + acc * BN;
-    for (int kb = 0; kb < num_kb; ++kb) {
+    for (int kb = w.kb0; kb < w.kb1; ++kb) {
       if (!mbar_wait_warp(&s.full[stage], phase, p.status, kTimeoutSmemFull, s.abort)) { ok = false; break; }
       tc_fence_after();
       const uint32_t sa = smem_u32(s.a + stage * A2_BYTES);
@@ -213,7 +244,7 @@ __device__ __forceinline__ void mma2(const Params& p, const Smem2& s, uint32_t t
         for (int k = 0; k < BK / UMMA_K; ++k) {
           const uint64_t da = make_smem_desc(sa + k * a_kadv, a_lbo, a_sbo);
           const uint64_t db = make_smem_desc(sb + k * b_kadv, b_lbo, b_sbo);
-          umma_f16_ss_pair(d, da, db, idesc, (kb | k) != 0);
+          umma_f16_ss_pair(d, da, db, idesc, ((kb - w.kb0) | k) != 0);
         }
         umma_commit_pair(&s.empty[stage], kPairMask);
       }
@@ -233,8 +264,20 @@ __device__ __forceinline__ void mma2(const Params& p, const Smem2& s, uint32_t t
 // 32-byte sector (138 MB of L2 writes for a 67 MB result, and twice that again for the read-modify-write of the
 // fp32 accumulate mode).  Each warp therefore turns its 32 x 32 block through shared memory and touches global
 // memory one row at a time, 32 lanes on 32 consecutive columns: whole sectors only.
-__device__ __forceinline__ void store_block_rows(const Params& p, const float* stg, int row0, int col0) {
+// `part` (optional): the other slices' partial sums of this 32 x 32 block, slice k at part + k * kSplitTileFloats,
+// rows 256 floats apart, already offset to this lane's column; they are added in slice order before anything else.
+__device__ __forceinline__ void store_block_rows(const Params& p, float* stg, int row0, int col0,
+                                                 const float* part = nullptr, int nparts = 0) {
   const int lane = int(lane_id());
+  if (part != nullptr) {
+    for (int k = 0; k < nparts; ++k) {
+      float add[32];
+#pragma unroll
+      for (int r = 0; r < 32; ++r) add[r] = __ldcg(part + size_t(k) * kSplitTileFloats + r * BN);
+#pragma unroll
+      for (int r = 0; r < 32; ++r) stg[r * 33 + lane] += add[r];
+    }
+  }
   const int col = col0 + lane;
   if (!HG_BOUNDS_OK(row0 >= 0 && row0 < p.M && col0 >= 0 && col0 < p.N, p.status)) return;
   if (col >= p.N) return;
@@ -276,28 +319,79 @@ __device__ __forceinline__ void epilogue2(const Params& p, const Smem2& s, uint3
   const uint32_t lane_off = uint32_t(wq * 32) << 16;
   float* stg = s.epi_stage + wq * EPI_STAGE_FLOATS;
   uint32_t acc = 0, acc_phase = 0;
-  for (int tile = first; tile < num_tiles; tile += step) {
+  const int num_kb = (p.K + BK - 1) / BK;
+  const int n_units = unit_count(p, first, step, num_tiles);
+  for (int u = 0; u < n_units; ++u) {
+    const Unit w = unit_at(p, first, step, u, num_kb);
+    const int tile = w.tile;
     int tm, tn;
     tile_coords(p, tile, tm, tn);
     const int row0 = tm * CM + int(rank) * BM + wq * 32;   // first of this warp's 32 rows
     const int n0 = tn * BN;
+    // a tail tile shared with other pairs: where this pair's partial goes, or where the others' are
+    const bool shared_tile = p.split_s > 1 && tile >= p.split_tail_begin;
+    const int tail_idx = tile - p.split_tail_begin;
+    const int in_row = int(rank) * BM + wq * 32;           // this warp's first row inside the 256 x 256 tile
+    float* ws_mine = nullptr;
+    const float* ws_others = nullptr;
+    if (shared_tile) {
+      float* ws_tile = p.split_ws + size_t(tail_idx) * (p.split_s - 1) * kSplitTileFloats;
+      if (w.slice > 0) ws_mine = ws_tile + size_t(w.slice - 1) * kSplitTileFloats;
+      else ws_others = ws_tile;
+    }
     if (!mbar_wait_warp(&s.tmem_full[acc], acc_phase, p.status, kTimeoutTmemFull, s.abort)) {
       *s.abort = 1;
       break;
     }
     tc_fence_after();
+    if (ws_others != nullptr) {
+      // every epilogue warp of the other slices' pairs (8 each) has stored its part: bounded wait, one lane polls
+      int landed = 1;
+      if (lane == 0) {
+        for (int k = 1; landed && k < p.split_s; ++k) {
+          const int* flag = p.split_flags + tail_idx * p.split_s + k;
+          const uint64_t t0 = globaltimer_ns();
+          while (ld_acquire_gpu(flag) < 2 * EPI_WARPS) {
+            if (*s.abort || globaltimer_ns() - t0 > kWaitLimitNs) {
+              set_status(p.status, kTimeoutPeerFlag);
+              landed = 0;
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
+      }
+      landed = __shfl_sync(0xffffffffu, landed, 0);
+      if (!landed) {
+        *s.abort = 1;
+        break;
+      }
+    }
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
       uint32_t r0[32];
       tmem_ld32(tmem_base + lane_off + acc * BN + c * 32, r0);
       tmem_ld_wait();
-      if (row0 < p.M && n0 + c * 32 < p.N) {   // warp-uniform
+      if (ws_mine != nullptr) {
+        // partial tile: row r of this thread's lane = tile row in_row + lane, 32 consecutive floats
+        float* dst = ws_mine + size_t(in_row + lane) * BN + c * 32;
+#pragma unroll
+        for (int i = 0; i < 32; i += 4)
+          __stcg(reinterpret_cast<float4*>(dst + i), make_float4(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1]),
+                                                                 __uint_as_float(r0[i + 2]), __uint_as_float(r0[i + 3])));
+      } else if (row0 < p.M && n0 + c * 32 < p.N) {   // warp-uniform
 #pragma unroll
         for (int i = 0; i < 32; ++i) stg[lane * 33 + i] = __uint_as_float(r0[i]);   // bank (lane + i) % 32: no conflicts
         __syncwarp();
-        store_block_rows(p, stg, row0, n0 + c * 32);
+        store_block_rows(p, stg, row0, n0 + c * 32,
+                         ws_others ? ws_others + size_t(in_row) * BN + c * 32 + lane : nullptr, p.split_s - 1);
         __syncwarp();
       }
+    }
+    if (ws_mine != nullptr) {
+      __threadfence();
+      __syncwarp();
+      if (lane == 0) atomicAdd(p.split_flags + tail_idx * p.split_s + w.slice, 1);
     }
     tc_fence_before();
     // the accumulator buffer is free again once all 256 epilogue threads of the pair have read it

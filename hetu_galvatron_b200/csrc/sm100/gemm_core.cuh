@@ -65,6 +65,15 @@ struct Params {
   const int* k_ranges;
   int groups;
   long long c_group_stride;
+  // Optional split of the last, partly filled wave (CTA-pair kernel only): tiles from `split_tail_begin` on are each
+  // computed by `split_s` pairs, every pair taking a contiguous share of the k-blocks.  Slices 1.. leave their fp32
+  // partial tile in `split_ws` (256 x 256 floats per (tail tile, slice - 1)) and count their eight epilogue warps into
+  // `split_flags[tail tile * split_s + slice]`; slice 0 waits for them (bounded) and adds the partials in slice order,
+  // so the result does not depend on timing.  split_s < 2: off.
+  int split_s;
+  int split_tail_begin;
+  float* split_ws;
+  int* split_flags;
 };
 
 struct TileInfo {
@@ -109,6 +118,11 @@ __device__ __forceinline__ void tile_coords(const Params& p, int tile, int& tm, 
 __device__ __forceinline__ int ld_acquire_sys(const int* p) {
   int v;
   asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
 

@@ -1,5 +1,6 @@
 """Numerics of every sm_100a kernel against a plain PyTorch fp32 reference of the same op."""
 import math
+import os
 
 import pytest
 import torch
@@ -449,6 +450,49 @@ def _twice(fn):
     a = a if isinstance(a, (list, tuple)) else [a]
     b = b if isinstance(b, (list, tuple)) else [b]
     return all(torch.equal(x, y) for x, y in zip(a, b))
+
+
+@pytest.mark.parametrize("M,N,K,a_mn,b_mn,mode", [(4096, 4096, 8192, True, True, "acc"), (4096, 11008, 4096, True, True, "acc"),
+                                                  (8192, 22016, 2048, False, False, "bf16"), (2304, 2560, 1024, False, True, "f32")])
+def test_gemm_tail_split_matches_unsplit(M, N, K, a_mn, b_mn, mode):
+    """HG_GEMM_SPLIT_TAIL=1: the tiles of a partly filled last wave are shared by several CTA pairs along K and summed
+    in slice order.  Run in a child process (the switch is read once per process): same result as the unsplit kernel up to
+    the order of the fp32 additions, identical bits from two runs, status word clean."""
+    import subprocess
+    import sys as _sys
+
+    code = """
+import torch, json, sys
+from hetu_galvatron_b200 import ops
+from hetu_galvatron_b200.ops import _lib
+from hetu_galvatron_b200.ops.gemm import OUT_BF16, OUT_F32, OUT_F32_ACC
+M, N, K, a_mn, b_mn, mode = %r
+torch.manual_seed(3)
+dev = "cuda"
+a = torch.randn((K, M) if a_mn else (M, K), device=dev, dtype=torch.bfloat16)
+b = torch.randn((K, N) if b_mn else (N, K), device=dev, dtype=torch.bfloat16)
+def run():
+    if mode == "acc":
+        out = torch.full((M, N), 0.5, device=dev, dtype=torch.float32)
+        ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=out, out_mode=OUT_F32_ACC, pair=True)
+        return out
+    return ops.gemm(a, b, a_mn=a_mn, b_mn=b_mn, out_mode=OUT_F32 if mode == "f32" else OUT_BF16, pair=True).float()
+x, y = run(), run()
+A = (a.t() if a_mn else a).float(); B = (b if b_mn else b.t()).float()
+ref = A @ B + (0.5 if mode == "acc" else 0.0)
+print(json.dumps({"same": bool(torch.equal(x, y)), "err": float((x - ref).abs().max() / ref.abs().max()), "status": _lib.read_status()}))
+""" % ((M, N, K, a_mn, b_mn, mode),)
+    import json as _json
+
+    res = {}
+    for flag in ("1", "0"):
+        env = dict(os.environ, HG_GEMM_SPLIT_TAIL=flag)
+        out = subprocess.run([_sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300,
+                             cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+        assert out.returncode == 0, out.stderr[-2000:]
+        res[flag] = _json.loads(out.stdout.strip().splitlines()[-1])
+    for r in res.values():
+        assert r["same"] and r["status"] == 0 and r["err"] < (2e-2 if mode == "bf16" else 2e-3), res
 
 
 @pytest.mark.parametrize("pair", [False, True])
