@@ -86,17 +86,22 @@ class VmmSymmetricBuffer:
             raise RuntimeError("hg_vmm_padded_size failed (%d)" % self.padded)
         h, fd = ctypes.c_ulonglong(0), ctypes.c_int(-1)
         _lib.check(lib.hg_vmm_create(self.padded, dev, ctypes.byref(h), ctypes.byref(fd)), "hg_vmm_create")
-        fds = _exchange_fds(fd.value, pg, "b%d" % _SEQ)
+        fds = [-1] * t
         handles = (ctypes.c_ulonglong * t)()
-        for r in range(t):
-            if r == me:
-                handles[r] = h.value
-            else:
-                hr = ctypes.c_ulonglong(0)
-                _lib.check(lib.hg_vmm_import(fds[r], ctypes.byref(hr)), "hg_vmm_import")
-                os.close(fds[r])
-                handles[r] = hr.value
-        os.close(fd.value)
+        try:
+            fds = _exchange_fds(fd.value, pg, "b%d" % _SEQ)
+            for r in range(t):
+                if r == me:
+                    handles[r] = h.value
+                else:
+                    hr = ctypes.c_ulonglong(0)
+                    _lib.check(lib.hg_vmm_import(fds[r], ctypes.byref(hr)), "hg_vmm_import")
+                    handles[r] = hr.value
+        finally:        # the descriptors are only needed for the import: none outlives this block, error or not
+            for r, other in enumerate(fds):
+                if r != me and other >= 0:
+                    os.close(other)
+            os.close(fd.value)
         ptrs = (ctypes.c_void_p * t)()
         _lib.check(lib.hg_vmm_map(handles, t, self.padded, dev, ptrs), "hg_vmm_map")
         self.ptrs = [int(p) for p in ptrs]
