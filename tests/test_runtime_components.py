@@ -285,8 +285,8 @@ def _fd_exchange_worker(payload):
         assert got[me] == -1
         for r, other in enumerate(got):
             if r != me:
-                os.lseek(other, 0, os.SEEK_SET)
-                seen["%s_%d" % (tag, r)] = os.read(other, 64).decode()
+                # the received descriptor shares its file offset with every other copy: read at an explicit position
+                seen["%s_%d" % (tag, r)] = os.pread(other, 64, 0).decode()
                 os.close(other)
     os.close(fd)
     return seen
