@@ -66,12 +66,13 @@ def hash_name(name: str) -> int:
 
 
 class Norm(nn.Module):
-    def __init__(self, spec: ModelSpec, device):
+    def __init__(self, spec: ModelSpec, device, size: int = 0):
         super().__init__()
         self.rms = spec.norm == "RMSNorm"
         self.eps = spec.eps
-        self.weight = _param((spec.hidden,), spec.dtype, device)
-        self.bias = None if self.rms else _param((spec.hidden,), spec.dtype, device)
+        size = size or spec.hidden
+        self.weight = _param((size,), spec.dtype, device)
+        self.bias = None if self.rms else _param((size,), spec.dtype, device)
         self.weight.tp_replicated = True
         if self.bias is not None:
             self.bias.tp_replicated = True
@@ -131,6 +132,11 @@ class SelfAttention(nn.Module):
         rot = [g * (qpg + 2) + j for g in range(self.ng) for j in range(qpg + 1)]  # q heads and the k head
         self.register_buffer("rope_slots", torch.tensor(rot, dtype=torch.int32, device=device), persistent=False)
         self.rot_dim = int(self.hd * spec.rope_pct)
+        # Optional per-head normalisation of queries and keys (the model's norm type over head_dim, one weight shared by
+        # all heads, hence replicated over the tensor-parallel ranks and its gradient summed over them).
+        # Reference: transformer/attention.py:705-742, 900-913 (q_layernorm / k_layernorm).
+        self.q_layernorm = Norm(spec, device, size=self.hd) if spec.qk_layernorm else None
+        self.k_layernorm = Norm(spec, device, size=self.hd) if spec.qk_layernorm else None
         # set by models.inference.forward_step for the duration of a cached forward; None in training
         self.inference_context = None
         self.layer_number = ctx.layer_index
@@ -147,6 +153,39 @@ class SelfAttention(nn.Module):
                 nn.init.zeros_(lin.bias)
         if self.linear_proj.bias is not None:
             self.linear_proj.bias.tp_replicated = True
+        for n in (self.q_layernorm, self.k_layernorm):
+            if n is not None:
+                n.reset_parameters()
+
+    def _qk_norm(self, qkv2):
+        """Normalise the query heads and the key head of every group inside the packed projection ``[T, P]``."""
+        T = qkv2.shape[0]
+        qpg = self.nh // self.ng
+        g = qkv2.view(T, self.ng, qpg + 2, self.hd)
+        q, _ = self.q_layernorm(g[:, :, :qpg].reshape(-1, self.hd))
+        k, _ = self.k_layernorm(g[:, :, qpg].reshape(-1, self.hd))
+        return torch.cat([q.view(T, self.ng, qpg, self.hd), k.view(T, self.ng, 1, self.hd), g[:, :, qpg + 1:]],
+                         dim=2).reshape(T, -1)
+
+    def run_realtime_tests(self):
+        """``train.test_mode``: the query / key norm parameters must be identical on every data- and tensor-parallel
+        rank (they are replicated, and a silent corruption of one copy would otherwise go unnoticed).
+        Reference: transformer/attention.py:805-874."""
+        if self.q_layernorm is None:
+            return
+        import torch.distributed as dist
+
+        mine = torch.stack([p.detach().float() for n in (self.q_layernorm, self.k_layernorm)
+                            for p in (n.weight, n.bias) if p is not None])
+        for name, grp in (("dp", self.ctx.dp), ("tp", self.ctx.tp)):
+            if grp is None or grp.size < 2 or grp.group is None:
+                continue
+            got = [torch.empty_like(mine) for _ in range(grp.size)]
+            dist.all_gather(got, mine, group=grp.group)
+            for r, other in enumerate(got):
+                if not torch.equal(other, got[0]):
+                    raise AssertionError("%s: query / key norm parameters of %s rank %d differ from rank 0's" %
+                                         (self.name, name, r))
 
     def forward(self, x):
         """x: normalised hidden states ``[S_local, B, H]`` -> attention output ``[S_local, B, H]``."""
@@ -157,6 +196,10 @@ class SelfAttention(nn.Module):
         S_att, B = qkv.shape[0], qkv.shape[1]
         S_full = c.seq_len or S_att * c.cp_size * c.sp_size
         qkv2 = qkv.reshape(S_att * B, -1)
+        if self.q_layernorm is not None:
+            if s.test_mode:
+                self.run_realtime_tests()
+            qkv2 = self._qk_norm(qkv2)
         if self.inference_context is not None:
             ctxv = self._cached_attention(qkv2, S_att, B)
             return row_parallel_linear(ctxv, self.linear_proj.weight, self.linear_proj.bias, c)

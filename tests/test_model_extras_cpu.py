@@ -85,6 +85,41 @@ def test_cross_attention_matches_reference_math():
     assert x.grad is not None and ca.linear_kv.weight.grad is not None
 
 
+def test_qk_layernorm_matches_reference_math():
+    """``qk_layernorm``: every query head and every key head is normalised over head_dim (one weight for all heads)
+    before the rotary embedding; checked against the same attention written out with torch ops (no rotary embedding,
+    LayerNorm, grouped-query heads)."""
+    from hetu_galvatron_b200.models.modules import SelfAttention
+
+    torch.manual_seed(2)
+    H, nh, ng, S, B = 64, 4, 2, 12, 2
+    hd = H // nh
+    spec = ModelSpec(family="gpt", hidden=H, heads=nh, kv_heads=ng, head_dim=hd, layers=1, ffn=96, vocab=128,
+                     padded_vocab=128, seq_len=S, dtype=torch.float32, norm="LayerNorm", pos="learned", qk_layernorm=True)
+    att = SelfAttention(spec, LayerCtx(seq_len=S), torch.device("cpu"), "a")
+    att.reset_parameters(5, True)
+    with torch.no_grad():       # weights away from their initial 1 / 0 so that the test sees them
+        for n in (att.q_layernorm, att.k_layernorm):
+            n.weight.add_(0.3 * torch.randn(hd))
+            n.bias.add_(0.1 * torch.randn(hd))
+    x = torch.randn(S, B, H, requires_grad=True)
+    out = att(x)
+    qpg = nh // ng
+    g = (x @ att.linear_qkv.weight.t()).view(S, B, ng, qpg + 2, hd)
+    ln = torch.nn.functional.layer_norm
+    q = ln(g[..., :qpg, :], (hd,), att.q_layernorm.weight, att.q_layernorm.bias, spec.eps).reshape(S, B, nh, hd)
+    k = ln(g[..., qpg, :], (hd,), att.k_layernorm.weight, att.k_layernorm.bias, spec.eps)
+    v = g[..., qpg + 1, :]
+    k, v = k.repeat_interleave(qpg, dim=2), v.repeat_interleave(qpg, dim=2)
+    sc = torch.einsum("sbnd,tbnd->bnst", q, k) / math.sqrt(hd)
+    sc = sc.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), float("-inf"))
+    ref = torch.einsum("bnst,tbnd->sbnd", sc.softmax(-1), v).reshape(S, B, H) @ att.linear_proj.weight.t()
+    assert torch.allclose(out, ref, atol=1e-5, rtol=1e-4)
+    out.sum().backward()
+    assert att.q_layernorm.weight.grad is not None and att.k_layernorm.bias.grad is not None
+    assert getattr(att.q_layernorm.weight, "tp_replicated", False)
+
+
 def test_cross_attention_rejects_grouped_query_heads():
     spec = ModelSpec(family="llama", hidden=64, heads=4, kv_heads=2, head_dim=16, layers=1, ffn=96, vocab=128,
                      padded_vocab=128, seq_len=16, dtype=torch.float32)

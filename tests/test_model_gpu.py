@@ -12,8 +12,8 @@ from hetu_galvatron_b200.runtime.optimizer import ShardedAdamW
 pytestmark = pytest.mark.gpu
 
 
-def make_args(mp, family="llama", ckpt=0, chunks=2):
-    model = dict(model_size=family + "-test", hidden_size=256, num_layers=3, num_attention_heads=4, ffn_hidden_size=768,
+def make_args(mp, family="llama", ckpt=0, chunks=2, qk_layernorm=False):
+    model = dict(qk_layernorm=qk_layernorm, model_size=family + "-test", hidden_size=256, num_layers=3, num_attention_heads=4, ffn_hidden_size=768,
                  vocab_size=1024, make_vocab_size_divisible_by=8)
     if family == "llama":
         model.update(normalization="RMSNorm", activation_func="torch.nn.functional.silu", gated_linear_unit=True,
@@ -50,6 +50,19 @@ def test_loss_parity_with_cpu_oracle(family, ckpt):
         assert abs(l0 - l1) / l0 < 5e-3, (ref, got)
         assert abs(n0 - n1) / n0 < 5e-2, (ref, got)
     assert got[-1][0] < got[0][0]
+
+
+@pytest.mark.parametrize("family", ["llama", "gpt"])
+def test_qk_layernorm_loss_parity_with_cpu_oracle(family):
+    """Per-head query / key normalisation (RMSNorm or LayerNorm over head_dim) through the norm kernels at H = 64."""
+    torch.manual_seed(0)
+    tok = torch.randint(0, 1024, (4, 257))
+    ref = run(make_args("fp32", family, 0, qk_layernorm=True), "cpu", tok)
+    got = run(make_args("bf16", family, 0, qk_layernorm=True), "cuda", tok)
+    _lib.assert_healthy()
+    for (l0, n0), (l1, n1) in zip(ref, got):
+        assert abs(l0 - l1) / l0 < 5e-3, (ref, got)
+        assert abs(n0 - n1) / n0 < 5e-2, (ref, got)
 
 
 def test_graft_smoke():

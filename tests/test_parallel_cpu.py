@@ -27,6 +27,7 @@ def make_args(cfg):
     parallel = dict(mixed_precision="fp32")
     parallel.update(cfg.get("parallel", {}))
     train = dict(seq_length=SEQ, global_batch_size=GBSZ, chunks=cfg.get("chunks", 1), lr=1e-3, seed=1234)
+    train.update(cfg.get("train", {}))
     return GalvatronRuntimeArgs(parallel=parallel, model=model, train=train)
 
 
@@ -124,6 +125,16 @@ def test_tensor_parallel_with_sequence_parallel_and_vocab_tp():
 
 def test_tp2_dp2_zero3_checkpoint():
     check(4, {"chunks": 2, "parallel": {"global_tp_deg": 2, "vocab_tp": 1, "sdp": 1, "global_checkpoint": 1}})
+
+
+def test_qk_layernorm_under_tensor_and_data_parallelism():
+    """Per-head query / key normalisation: its weights are replicated over the tensor-parallel ranks (each sees its own
+    heads), so their gradients are summed over tp; with ``test_mode`` every forward cross-checks the copies."""
+    model = {"qk_layernorm": True, "num_query_groups": 2}
+    base = {"chunks": 1, "model": model}
+    check(4, {"chunks": 2, "parallel": {"global_tp_deg": 2, "vocab_tp": 2, "default_dp_type": "zero2"}, "model": model,
+              "train": {"test_mode": True}}, base, key="qkln")
+    check(2, {"parallel": {"global_tp_deg": 2, "use_ulysses": True, "vocab_tp": 2}, "model": model}, base, key="qkln")
 
 
 @pytest.mark.parametrize("kv", [None, 1])
