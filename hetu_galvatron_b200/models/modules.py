@@ -118,6 +118,9 @@ def local_positions(ctx: LayerCtx, S_full: int, S_rows: int, row0: int, device):
 # --------------------------------------------------------------------------------------------
 # attention block
 # --------------------------------------------------------------------------------------------
+_WARNED_ATTN_DROPOUT = False
+
+
 class SelfAttention(nn.Module):
     def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str):
         super().__init__()
@@ -211,7 +214,9 @@ class SelfAttention(nn.Module):
             cos, sin = ops.rope_tables(max(S_full, 1), self.rot_dim, s.rope_base, str(qkv.device), s.rope_interp,
                                         s.rope_scaling_factor)
             qkv2 = ops.rope_packed(qkv2, self.rope_slots, self.hd, cos, sin, B, pos, off, s.rope_interleaved)
-        if c.sp_size == 1 and c.cp_size == 1:
+        if s.attention_dropout > 0.0 and self.training:
+            ctxv = self._attention_with_dropout(qkv2, S_att, B)
+        elif c.sp_size == 1 and c.cp_size == 1:
             ctxv = ops.flash_attention_packed(qkv2, S_att, B, self.nh, self.ng, self.hd, causal=True)
             ctxv = ctxv.view(S_att, B, self.nh * self.hd)
         else:
@@ -230,6 +235,37 @@ class SelfAttention(nn.Module):
             ctxv = o.reshape(S_att, B, self.nh * self.hd)
         return row_parallel_linear(ctxv, self.linear_proj.weight, self.linear_proj.bias, c)
 
+
+    def _attention_with_dropout(self, qkv2, S_att: int, B: int):
+        """``attention_dropout`` > 0 while training: the flash kernels have no dropout, so the probabilities are formed
+        explicitly (fp32, O(S^2) memory per head) and dropped from the tensor-parallel random stream (every rank holds
+        different heads).  Reference: attention_impl.py:40-111 passes the rate to flash-attn's ``dropout_p``."""
+        s, c = self.spec, self.ctx
+        if c.sp_size > 1 or c.cp_size > 1:
+            raise NotImplementedError("attention dropout with Ulysses or context parallelism")
+        global _WARNED_ATTN_DROPOUT
+        if not _WARNED_ATTN_DROPOUT:
+            import warnings
+
+            warnings.warn("attention_dropout = %g: attention runs on the unfused path (explicit probabilities) while "
+                          "training" % s.attention_dropout)
+            _WARNED_ATTN_DROPOUT = True
+        q, k, v = ops.attention.split_packed(qkv2, self.nh, self.ng, self.hd)
+        q = q.reshape(S_att, B, self.nh, self.hd)
+        k = k.reshape(S_att, B, self.ng, self.hd)
+        v = v.reshape(S_att, B, self.ng, self.hd)
+
+        def run():
+            return ops.attention.attention_reference(q, k, v, True, dropout_p=s.attention_dropout)[0]
+
+        if c.tp_size > 1:
+            from ..parallel.random import get_rng_tracker, tensor_parallel_rng_name
+
+            tracker, name = get_rng_tracker(), tensor_parallel_rng_name(c.tp_size)
+            if not tracker.check(name):
+                with tracker.fork(name):
+                    return run().reshape(S_att, B, self.nh * self.hd)
+        return run().reshape(S_att, B, self.nh * self.hd)
 
     def _cached_attention(self, qkv2, S_new: int, B: int):
         """Incremental forward with a key / value cache (static batching): the new keys and values are written

@@ -27,8 +27,9 @@ def _desc(t: torch.Tensor, ss: int, sb: int, slots: int, gs: int, hs: int, off: 
     return AttnTensor(t.data_ptr(), ss, sb, slots, gs, hs, off)
 
 
-def attention_reference(q, k, v, causal=True, scale=None, q_pos0=0, k_pos0=0):
-    """q: [S,B,nh,hd], k/v: [Skv,B,ng,hd] -> (out [S,B,nh,hd], lse [B,nh,S]); fp32 math."""
+def attention_reference(q, k, v, causal=True, scale=None, q_pos0=0, k_pos0=0, dropout_p: float = 0.0):
+    """q: [S,B,nh,hd], k/v: [Skv,B,ng,hd] -> (out [S,B,nh,hd], lse [B,nh,S]); fp32 math.  ``dropout_p`` drops
+    attention probabilities (after the softmax, rescaled by 1 / (1 - p)) from the current random stream."""
     S, B, nh, hd = q.shape
     Skv, ng = k.shape[0], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(hd)
@@ -43,6 +44,8 @@ def attention_reference(q, k, v, causal=True, scale=None, q_pos0=0, k_pos0=0):
     lse = torch.logsumexp(s, dim=-1)
     p = torch.exp(s - lse[..., None])
     p = torch.nan_to_num(p, nan=0.0)
+    if dropout_p > 0.0:
+        p = torch.nn.functional.dropout(p, dropout_p, True)
     o = torch.einsum("bhqk,bhkd->bhqd", p, vf)
     return o.permute(2, 0, 1, 3).to(q.dtype), lse
 

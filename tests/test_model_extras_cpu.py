@@ -120,6 +120,30 @@ def test_qk_layernorm_matches_reference_math():
     assert getattr(att.q_layernorm.weight, "tp_replicated", False)
 
 
+def test_attention_dropout_takes_the_unfused_path_in_training_only():
+    from hetu_galvatron_b200.models.modules import SelfAttention
+
+    torch.manual_seed(4)
+    H, nh, S, B = 64, 4, 16, 2
+    kw = dict(family="gpt", hidden=H, heads=nh, kv_heads=nh, head_dim=H // nh, layers=1, ffn=96, vocab=128,
+              padded_vocab=128, seq_len=S, dtype=torch.float32, pos="learned")
+    plain = SelfAttention(ModelSpec(**kw), LayerCtx(seq_len=S), torch.device("cpu"), "a")
+    drop = SelfAttention(ModelSpec(attention_dropout=0.5, **kw), LayerCtx(seq_len=S), torch.device("cpu"), "a")
+    plain.reset_parameters(5, True)
+    drop.reset_parameters(5, True)
+    x = torch.randn(S, B, H)
+    drop.eval()
+    assert torch.allclose(drop(x), plain(x), atol=1e-6)            # no dropout outside training
+    drop.train()
+    with pytest.warns(UserWarning, match="unfused"):
+        y1 = drop(x)
+    y2 = drop(x)
+    assert not torch.allclose(y1, y2) and not torch.allclose(y1, plain(x))      # a fresh mask per call
+    # the first query sees one key only: its probability is 1, so the row is either dropped or doubled
+    ys = torch.stack([drop(x) for _ in range(64)]).mean(0)
+    assert (ys - plain(x)).abs().mean() < 0.25 * plain(x).abs().mean() + 0.05   # unbiased: the mean approaches the plain output
+
+
 def test_cross_attention_rejects_grouped_query_heads():
     spec = ModelSpec(family="llama", hidden=64, heads=4, kv_heads=2, head_dim=16, layers=1, ffn=96, vocab=128,
                      padded_vocab=128, seq_len=16, dtype=torch.float32)
