@@ -223,8 +223,11 @@ class GalvatronMoERouter(nn.Module):
         else:
             dt = torch.float64 if s.router_dtype == "fp64" else torch.float32
             logits = torch.nn.functional.linear(xin.to(dt), self.router.weight.to(dt)).float()
+        # `calculate_per_token_loss`: the trainer then divides every gradient by the token count, so the auxiliary
+        # losses are multiplied by the local token count to keep their weight (reference: moe/router.py:303-312, 334-342)
+        tok_scale = float(x2d.shape[0]) if s.per_token_loss else 1.0
         if s.z_loss_coeff and self.training:
-            logits = _AuxLossScaler.apply(logits, z_loss(logits, s.z_loss_coeff))
+            logits = _AuxLossScaler.apply(logits, z_loss(logits, s.z_loss_coeff) * tok_scale)
         bias = getattr(self.router, "expert_bias", None)
         if s.load_balancing == "sinkhorn":
             probs, idx = sinkhorn_routing(logits, s.topk, self.training)
@@ -235,10 +238,10 @@ class GalvatronMoERouter(nn.Module):
             probs, idx = apply_capacity(probs, idx, s.experts, cap, s.drop_policy)
         if s.aux_loss_coeff and s.load_balancing == "seq_aux_loss" and self.training and getattr(self, "batch_hint", 0):
             probs = _AuxLossScaler.apply(probs, sequence_aux_loss(logits, idx, s.experts, s.topk, s.aux_loss_coeff,
-                                                                  self.batch_hint))
+                                                                  self.batch_hint) * tok_scale)
         elif s.aux_loss_coeff and s.load_balancing in ("aux_loss", "seq_aux_loss") and self.training:
             grp = self.ctx.tp if self.ctx.tp_size > 1 else (self.ctx.sp if self.ctx.sp_size > 1 else None)
-            probs = _AuxLossScaler.apply(probs, switch_aux_loss(logits, idx, s.experts, s.topk, s.aux_loss_coeff, grp))
+            probs = _AuxLossScaler.apply(probs, switch_aux_loss(logits, idx, s.experts, s.topk, s.aux_loss_coeff, grp) * tok_scale)
         if bias is not None:
             with torch.no_grad():
                 v = idx.reshape(-1)

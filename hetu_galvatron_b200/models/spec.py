@@ -34,6 +34,7 @@ class ModelSpec:
     rope_interp: float = 1.0
     rope_scaling_factor: float = 0.0  # > 0: Llama-3.x frequency scaling with this factor
     rope_interleaved: bool = False   # rotate channel pairs (2i, 2i+1) instead of the two halves
+    per_token_loss: bool = False     # `calculate_per_token_loss`: auxiliary losses scaled by the local token count
     attention_dropout: float = 0.0   # dropout on the attention probabilities (training only; unfused path)
     qk_layernorm: bool = False       # normalise every query and key head (over head_dim) before the rotary embedding
     test_mode: bool = False          # cross-check replicated parameters over the ranks while training
@@ -138,6 +139,7 @@ def spec_from_args(args) -> ModelSpec:
         rope_interleaved=bool(getattr(m, "rotary_interleaved", False)),
         qk_layernorm=bool(getattr(m, "qk_layernorm", False)),
         attention_dropout=float(getattr(m, "attention_dropout", 0.0) or 0.0),
+        per_token_loss=bool(getattr(m, "calculate_per_token_loss", False)),
         test_mode=bool(getattr(tr, "test_mode", False)) if tr is not None else False,
         experts=m.num_moe_experts or 0, moe_ffn=m.moe_ffn_hidden_size or m.ffn_hidden_size or 0,
         topk=m.moe_router_topk, router_score=m.moe_router_score_function, router_pre_softmax=m.moe_router_pre_softmax,
