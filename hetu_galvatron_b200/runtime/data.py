@@ -172,7 +172,15 @@ def get_train_valid_test_data_iterators(args, model, collate_fn=None):
                                   coll, t.data_sharding)
         return iter(cyclic_iter(loader)) if t.dataloader_type == "cyclic" else iter(loader)
 
-    return it(train, consumed % max(1, len(train))), it(valid, 0), it(test, 0)
+    out = it(train, consumed % max(1, len(train))), it(valid, 0), it(test, 0)
+    # which phases have data and iterations to run (the reference sets the same flags: runtime/dataloader.py:363-384)
+    if t.skip_train:
+        t.do_train = False
+    else:
+        t.do_train = bool(t.do_train) or (out[0] is not None and (t.train_iters or 0) > 0)
+    t.do_valid = bool(t.do_valid) or (out[1] is not None and (t.eval_iters or 0) > 0)
+    t.do_test = bool(t.do_test) or (out[2] is not None and (t.eval_iters or 0) > 0)
+    return out
 
 
 def get_batch(data_iterator, device) -> Tuple[torch.Tensor, Dict, Optional[object]]:

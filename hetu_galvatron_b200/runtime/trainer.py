@@ -113,6 +113,22 @@ def _profile_window(default):
     return a, b
 
 
+def evaluate(model, data_iterator, iters: int) -> Optional[float]:
+    """Mean loss over ``iters`` forward-only batches of ``data_iterator`` (``None`` on ranks without the last pipeline
+    stage or when there is nothing to evaluate).  Gradients are neither computed nor touched."""
+    if data_iterator is None or iters <= 0:
+        return None
+    total, n = 0.0, 0
+    for _ in range(iters):
+        tokens, kw, loss_fn = get_batch(data_iterator, model.device)
+        loss = model.forward_backward([tokens], 0, None, loss_fn, labels=kw.get("labels"), loss_mask=kw.get("loss_mask"),
+                                      forward_only=True)
+        if loss is not None:
+            total += float(loss)
+            n += 1
+    return total / n if n else None
+
+
 def train(args, max_iters: Optional[int] = None, profile_window=None):
     """Runs ``args.train.train_iters`` iterations (or ``max_iters``); returns the list of per-iteration losses seen
     on this rank (``None`` entries on ranks that do not hold the last pipeline stage)."""
@@ -137,6 +153,8 @@ def train(args, max_iters: Optional[int] = None, profile_window=None):
     profiler = get_runtime_profiler(args, model, start_iter=profile_window[0], end_iter=profile_window[1])
     profiler.profile_memory(0, "After creating model")
     total = max_iters if max_iters is not None else (args.train.train_iters or 0)
+    if args.train.skip_train:
+        total = start      # evaluation / checkpoint conversion only
     gbsz = args.train.global_batch_size
     losses = []
     for it in range(start, total):
@@ -171,6 +189,14 @@ def train(args, max_iters: Optional[int] = None, profile_window=None):
             _state.log_scalars(it + 1, **{"train/loss": loss_val, "train/lr": lr})
         profiler.post_profile_memory(it)
         profiler.profile_time_end(it, loss_val, lr, optimizer.grad_norm() if (optimizer.clip_grad > 0 and not forward_only) else None)
+        if args.train.do_valid and args.train.eval_interval and (it + 1) % args.train.eval_interval == 0:
+            val = evaluate(model, valid_it, args.train.eval_iters or 0)
+            if val is not None:
+                from ..parallel import state as _state
+
+                _state.log_scalars(it + 1, **{"validation/loss": val})
+                if rank == 0 or not dist.is_initialized():
+                    print("| Iteration: %6d | validation loss: %.6e |" % (it + 1, val), flush=True)
         save, leave, code = machine.should_checkpoint_and_exit()
         if c.save is not None and (save or (c.save_interval and (it + 1) % c.save_interval == 0)):
             ckpt.save_distributed_checkpoint(model, optimizer, scheduler, it + 1, c.save,

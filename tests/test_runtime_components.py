@@ -329,6 +329,27 @@ def test_nonzero_device_status_rejects_the_step(monkeypatch):
         trainer.train(args, max_iters=2)
 
 
+def test_training_loop_evaluates_on_the_validation_split(tmp_path, capsys):
+    """With a corpus on disk the loop sets do_train / do_valid, runs ``eval_iters`` forward-only batches of the
+    validation split every ``eval_interval`` iterations and reports their mean loss; evaluation leaves no gradients."""
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+    from hetu_galvatron_b200.runtime import trainer
+
+    prefix = str(tmp_path / "c")
+    _write_corpus(prefix, _docs(400, seed=9))
+    args = GalvatronRuntimeArgs(
+        parallel=dict(mixed_precision="fp32"),
+        model=dict(model_size="llama-test", hidden_size=64, num_layers=1, num_attention_heads=2, ffn_hidden_size=128,
+                   vocab_size=128, make_vocab_size_divisible_by=8, normalization="RMSNorm",
+                   activation_func="torch.nn.functional.silu", gated_linear_unit=True),
+        train=dict(seq_length=16, global_batch_size=2, chunks=1, lr=1e-3, train_iters=4, eval_interval=2, eval_iters=2),
+        data=dict(data_path=[prefix], split="8,1,1", path_to_cache=str(tmp_path / "cache")))
+    losses = trainer.train(args, max_iters=4)
+    out = capsys.readouterr().out
+    assert len(losses) == 4 and args.train.do_train and args.train.do_valid
+    assert out.count("validation loss") == 2
+
+
 def test_blended_dataset_follows_weights():
     from hetu_galvatron_b200.runtime.datasets.blended import BlendedDataset
 
