@@ -149,6 +149,12 @@ def build_model(args, device=None, full_init: bool = False, fused_comm: Optional
     world = dist.get_world_size() if dist.is_initialized() else 1
     rank = dist.get_rank() if dist.is_initialized() else 0
     resolve_model_config(args, vocab_tp=None)
+    if getattr(args.model, "shape_order", "SBH") != "SBH":
+        # same restriction as the reference (hybrid_parallel_model.py:198): activations are [sequence, batch, hidden]
+        raise ValueError("Shape order must be SBH for the hybrid parallel model")
+    if getattr(args.model, "multi_latent_attention", False):
+        raise NotImplementedError("multi_latent_attention: the reference only carries the flag (rope_utils.py); "
+                                  "no latent-attention layer exists there or here")
     plan = build_plan(args, world)
     # pad the vocabulary for the vocab tensor-parallel degree
     from ..config.model_config import finalize_model_args
