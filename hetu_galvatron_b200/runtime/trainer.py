@@ -195,7 +195,8 @@ def train(args, max_iters: Optional[int] = None, profile_window=None):
                 from ..parallel import state as _state
 
                 _state.log_scalars(it + 1, **{"validation/loss": val})
-                if rank == 0 or not dist.is_initialized():
+                # the loss lives on the last pipeline stage; its last rank reports, like the iteration line
+                if not dist.is_initialized() or rank == dist.get_world_size() - 1:
                     print("| Iteration: %6d | validation loss: %.6e |" % (it + 1, val), flush=True)
         save, leave, code = machine.should_checkpoint_and_exit()
         if c.save is not None and (save or (c.save_interval and (it + 1) % c.save_interval == 0)):
