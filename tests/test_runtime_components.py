@@ -350,6 +350,41 @@ def test_training_loop_evaluates_on_the_validation_split(tmp_path, capsys):
     assert out.count("validation loss") == 2
 
 
+def _pp_eval_worker(payload):
+    """One gloo rank of a two-stage pipeline: a few training iterations with periodic evaluation."""
+    import contextlib
+    import io
+
+    import torch.distributed as dist
+
+    from hetu_galvatron_b200.config.schema import GalvatronRuntimeArgs
+    from hetu_galvatron_b200.runtime import trainer
+
+    args = GalvatronRuntimeArgs(
+        parallel=dict(mixed_precision="fp32", pp_deg=2, pipeline_type="pipedream_flush"),
+        model=dict(model_size="llama-test", hidden_size=64, num_layers=2, num_attention_heads=2, ffn_hidden_size=128,
+                   vocab_size=128, make_vocab_size_divisible_by=8, normalization="RMSNorm",
+                   activation_func="torch.nn.functional.silu", gated_linear_unit=True),
+        train=dict(seq_length=16, global_batch_size=4, chunks=2, lr=1e-3, train_iters=4, eval_interval=2, eval_iters=1),
+        data=dict(data_path=[payload["prefix"]], split="8,1,1", path_to_cache=payload["cache"]),
+        rank=dist.get_rank(), world_size=2)
+    buf = io.StringIO()
+    with contextlib.redirect_stdout(buf):
+        losses = trainer.train(args, max_iters=4)
+    return {"losses": losses, "validation_lines": buf.getvalue().count("validation loss")}
+
+
+def test_evaluation_under_pipeline_parallelism(tmp_path):
+    """Forward-only evaluation through a two-stage pipeline: the last stage holds and reports the validation loss."""
+    from tests.dist_utils import run_distributed
+
+    prefix = str(tmp_path / "c")
+    _write_corpus(prefix, _docs(400, seed=9))
+    res = run_distributed(__file__, "pp_eval", 2, {"prefix": prefix, "cache": str(tmp_path / "cache")}, timeout=180)
+    assert res[0]["validation_lines"] == 0 and res[1]["validation_lines"] == 2
+    assert all(l is None for l in res[0]["losses"]) and all(l is not None for l in res[1]["losses"])
+
+
 def test_blended_dataset_follows_weights():
     from hetu_galvatron_b200.runtime.datasets.blended import BlendedDataset
 
@@ -559,4 +594,4 @@ def test_expert_bias_update_moves_towards_balance():
 if __name__ == "__main__":
     from tests.dist_utils import worker_main
 
-    worker_main({"cold_cache": _cold_cache_worker, "fd_exchange": _fd_exchange_worker})
+    worker_main({"cold_cache": _cold_cache_worker, "fd_exchange": _fd_exchange_worker, "pp_eval": _pp_eval_worker})
