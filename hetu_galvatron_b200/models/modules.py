@@ -495,10 +495,11 @@ class GalvatronEmbedding(nn.Module):
     def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str):
         super().__init__()
         self.spec, self.ctx, self.name = spec, ctx, name
-        t = ctx.tp_size
-        if spec.padded_vocab % t:
-            raise ValueError("padded vocab %d not divisible by vocab tp %d" % (spec.padded_vocab, t))
-        self.Vl = spec.padded_vocab // t
+        from ..utils.training_utils import VocabUtility
+
+        # this rank's rows of the (padded) vocabulary; raises when the vocab tp degree does not divide it
+        self.v0, v1 = VocabUtility.vocab_range_from_global_vocab_size(spec.padded_vocab, ctx.tp_rank, ctx.tp_size)
+        self.Vl = v1 - self.v0
         self.embed_tokens = nn.Module()
         self.embed_tokens.weight = _param((self.Vl, spec.hidden), spec.dtype, device)
         self.embed_positions = None
@@ -529,7 +530,7 @@ class GalvatronEmbedding(nn.Module):
         pos_w = self.embed_positions.weight if self.embed_positions is not None else None
         if pos_w is not None and c.cp_size > 1:
             raise NotImplementedError("learned absolute positions with context parallelism")
-        x = ops.embedding(ids.reshape(-1), self.embed_tokens.weight, v0=c.tp_rank * self.Vl, pos_emb=pos_w, batch=B,
+        x = ops.embedding(ids.reshape(-1), self.embed_tokens.weight, v0=self.v0, pos_emb=pos_w, batch=B,
                           pos_offset=row0)
         x = x.view(S_rows, B, s.hidden)
         if c.tp_size > 1:
@@ -558,7 +559,10 @@ class GalvatronCausalLMHead(nn.Module):
     def __init__(self, spec: ModelSpec, ctx: LayerCtx, device, name: str, tied_weight: Optional[nn.Parameter] = None):
         super().__init__()
         self.spec, self.ctx, self.name = spec, ctx, name
-        self.Vl = spec.padded_vocab // ctx.tp_size
+        from ..utils.training_utils import VocabUtility
+
+        self.v0, v1 = VocabUtility.vocab_range_from_global_vocab_size(spec.padded_vocab, ctx.tp_rank, ctx.tp_size)
+        self.Vl = v1 - self.v0
         self.lm_head = nn.Module()
         if tied_weight is not None:
             self.lm_head.weight = tied_weight
@@ -586,7 +590,7 @@ class GalvatronCausalLMHead(nn.Module):
         lab = labels.t().contiguous()  # [S_cp, B]
         if c.sp_size > 1:
             lab = lab[c.sp_rank * S_rows:(c.sp_rank + 1) * S_rows]
-        loss = ops.cross_entropy(logits.reshape(S_rows * B, -1), lab.reshape(-1), v0=c.tp_rank * self.Vl,
+        loss = ops.cross_entropy(logits.reshape(S_rows * B, -1), lab.reshape(-1), v0=self.v0,
                                  group=c.tp if c.tp_size > 1 else None)
         loss = loss.view(S_rows, B)
         if c.sp_size > 1:  # every rank returns the loss of the whole (cp-local) sequence

@@ -183,6 +183,10 @@ def train(args, max_iters: Optional[int] = None, profile_window=None):
         loss_val = float(loss) if loss is not None else None
         check_device_status(model.device)
         losses.append(loss_val)
+        if getattr(args.model, "print_loss", 0) and loss_val is not None:
+            from ..utils.training_utils import print_loss
+
+            print_loss(loss_val, -1, it)          # the model scripts' per-iteration loss line (`model.print_loss`)
         if loss_val is not None:
             from ..parallel import state as _state
 

@@ -42,18 +42,6 @@ def print_loss(loss, ep: int, iter: int):
         print("[Epoch %d] (Iteration %d): Loss = %.3f" % (ep, iter, float(loss)))
 
 
-def distributed_dataloader(dataset, global_bsz: int, shuffle: bool = True, group=None, collate_fn=None):
-    """A ``DataLoader`` with a ``DistributedSampler`` over ``group`` (default: all ranks); batch = global / ranks
-    (galvatron/utils/training_utils.py:13-23)."""
-    from torch.utils.data import DataLoader
-    from torch.utils.data.distributed import DistributedSampler
-
-    rank = dist.get_rank(group) if dist.is_initialized() else 0
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
-    sampler = DistributedSampler(dataset, shuffle=shuffle, num_replicas=world, rank=rank)
-    return DataLoader(dataset, batch_size=max(1, global_bsz // world), sampler=sampler, collate_fn=collate_fn)
-
-
 def divide(numerator: int, denominator: int) -> int:
     if numerator % denominator:
         raise ValueError("%d is not divisible by %d" % (numerator, denominator))
