@@ -115,6 +115,10 @@ def available(device, n: int, pg=None) -> bool:
     process group is given, a successful :func:`symmetric_memory_works` probe)."""
     if device.type != "cuda" or n < 2 or n > MAX_PEERS:
         return False
+    from ..utils.runtime_utils import is_torch_min_version
+
+    if not is_torch_min_version("2.5.0"):      # torch.distributed._symmetric_memory appeared in 2.5
+        return False
     try:
         import torch.distributed._symmetric_memory  # noqa: F401
     except Exception:

@@ -22,20 +22,10 @@ import torch.distributed as dist
 
 from ..config.model_config import resolve_model_config
 from ..models.builder import ModelGroups, StageModel, build_stage
-from ..models.modules import zigzag_positions
 from ..models.spec import ModelSpec, spec_from_args
 from ..parallel.groups import GroupFactory
 from ..parallel.pipeline import PipelineEngine, chunk_batch
 from .plan import HybridPlan, build_plan
-
-
-def slice_for_cp(t: Optional[torch.Tensor], cp: int, cp_rank: int) -> Optional[torch.Tensor]:
-    """Zig-zag context-parallel slice of ``[B, S, ...]`` along the sequence: chunks ``r`` and ``2c-1-r``."""
-    if t is None or cp == 1:
-        return t
-    S = t.shape[1]
-    idx = zigzag_positions(S, cp, cp_rank, t.device)
-    return t.index_select(1, idx)
 
 
 def default_loss_func(loss_mask: Optional[torch.Tensor], cp: int = 1) -> Callable:
@@ -90,9 +80,10 @@ class GalvatronModel:
         if labels is None:
             labels = kwargs.get("labels")
         chunks = max(1, min(self.plan.chunks, tokens.shape[0]))
-        tok = slice_for_cp(tokens, c.cp_size, c.cp_rank)
-        lab = slice_for_cp(labels, c.cp_size, c.cp_rank)
-        msk = slice_for_cp(loss_mask, c.cp_size, c.cp_rank)
+        from ..utils.runtime_utils import get_batch_on_this_cp_rank
+
+        part = get_batch_on_this_cp_rank({"tokens": tokens, "labels": labels, "loss_mask": loss_mask}, c.cp_size, c.cp_rank)
+        tok, lab, msk = part["tokens"], part["labels"], part["loss_mask"]
         toks, labs, msks = chunk_batch(tok, chunks), chunk_batch(lab, chunks), chunk_batch(msk, chunks)
         chunks = len(toks)
         d_vocab = self.plan.dp_size(self.plan.layers[0])
@@ -194,7 +185,9 @@ def build_model(args, device=None, full_init: bool = False, fused_comm: Optional
     stage = build_stage(spec, plan, groups, device, seed=args.train.seed or 1234, full_init=full_init,
                         fused_comm=fused_comm, reduce_in_fp32=bool(args.parallel.reduce_in_fp32),
                         fused_zero=fused_zero)
-    if rank == 0 and os.environ.get("HG_QUIET", "0") != "1":
-        print("================ hybrid-parallel plan (%s) ================" % plan.source)
-        print(plan.describe())
+    if os.environ.get("HG_QUIET", "0") != "1":
+        from ..utils.runtime_utils import print_rank_0
+
+        print_rank_0("================ hybrid-parallel plan (%s) ================" % plan.source)
+        print_rank_0(plan.describe())
     return GalvatronModel(args, spec, plan, groups, stage, device)
